@@ -1,0 +1,115 @@
+/*
+ * rq.h -- C ABI of the B200 (sm_100a) GGUF quantised matrix-vector library.
+ *
+ * This is the boundary a recipe host binds in place of the LLVM-IR GPU lowering of its
+ * quantised contraction nodes. Plain pointers and sizes only; every entry point returns
+ * 0 on success or a negative rq_status, and rq_last_error() gives thread-local text.
+ * The library owns prepared weights and its context; the caller owns every other buffer.
+ * No entry point aborts on bad arguments, none falls back to the CPU.
+ *
+ * Each declaration names the reference interface (nm-z/recipe-dev, file:line) it replaces.
+ */
+#ifndef RQ_H
+#define RQ_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct rq_ctx rq_ctx;       /* one per device; replaces the per-device Gpu + arenas, recipe.rs:28014, :24795-24801 */
+typedef struct rq_weight rq_weight; /* a stored weight resident in HBM; replaces StoredWeight in the device arena, recipe.rs:16032-16045, :2107-2126 */
+
+enum rq_status {
+    RQ_OK = 0,
+    RQ_ERR_INVALID = -1,     /* null pointer, bad shape, K not a multiple of the block, bad enum */
+    RQ_ERR_CUDA = -2,        /* a CUDA runtime call failed; text names it */
+    RQ_ERR_ALLOC = -3,       /* device or host allocation failed */
+    RQ_ERR_UNSUPPORTED = -4, /* valid request this build does not serve */
+    RQ_ERR_LIMIT = -5        /* size beyond a documented fixed maximum */
+};
+
+/* GGML tensor types on this path (recipe.rs:9925-9962). */
+enum { RQ_Q4_0 = 2, RQ_Q8_0 = 8, RQ_Q4_K = 12, RQ_Q6_K = 14 };
+
+/* Activation handling, what `.fp(32)` / `.int(8)` select (recipe.rs:14027-14054, :22326-22369):
+ * FLOAT keeps the activations as they are (run decoders, recipe.rs:7826-7917);
+ * INT8 rounds them to int8 records with one fp32 step per `step` inputs (amd-nv-cpu.ll:1381-1517). */
+enum { RQ_ACT_FLOAT = 0, RQ_ACT_INT8 = 1,
+       /* INT8 over the records the previous RQ_ACT_INT8 call on this context derived: the caller
+        * states that x is that same column (q/k/v, or gate/up, read one activation). The reference
+        * quantises a node's column once per workgroup (amd-nv-cpu.ll:1381-1517); this is that reuse
+        * across the nodes that share the column. Fails if no records of this width are held. */
+       RQ_ACT_INT8_CACHED = 2 };
+
+/* Routing (Scoring, recipe.rs:13955). */
+enum { RQ_SCORE_SOFTMAX = 0, RQ_SCORE_SIGMOID = 1 };
+
+/* ---- context ------------------------------------------------------------------- */
+
+/* Binds a context to CUDA device `device`. Replaces native_prepare / module load for this
+ * path (recipe.rs:28155, :27843). */
+int rq_init(int device, rq_ctx** out);
+void rq_destroy(rq_ctx* ctx);
+/* Thread-local text of the last failure on the calling thread (RecipeError, recipe.rs:13416-13433). */
+const char* rq_last_error(void);
+/* Block geometry of a type: values per block and bytes per block (QUANTIZATIONS, recipe.rs:15811-15822). 0 if unknown. */
+int rq_block_values(int ggml_type);
+int rq_block_bytes(int ggml_type);
+
+/* ---- weights -------------------------------------------------------------------- */
+
+/* Uploads rows [row_first, row_first + row_count) of a host tensor of GGUF blocks
+ * ([rows][cols / block] blocks, rows contiguous) and lays them out for the kernels.
+ * Replaces range_tape's weight upload + recipe_model_load (recipe.rs:22200, :8128-8165);
+ * the row range is a die's share of a row split (lone_split, recipe.rs:21010-21020). */
+int rq_weight_prepare(rq_ctx* ctx, int ggml_type, const void* host_blocks, int64_t rows, int64_t cols,
+                      int64_t row_first, int64_t row_count, rq_weight** out);
+/* Same, from blocks already in device memory (e.g. written by rq_quantize): all `rows`. */
+int rq_weight_prepare_device(rq_ctx* ctx, int ggml_type, const void* dev_blocks, int64_t rows, int64_t cols,
+                             rq_weight** out, void* stream);
+/* Writes the weight back as GGUF blocks into host memory (round-trip check of the layout). */
+int rq_weight_export(rq_ctx* ctx, const rq_weight* w, void* host_blocks);
+void rq_weight_free(rq_ctx* ctx, rq_weight* w);
+int64_t rq_weight_rows(const rq_weight* w);
+int64_t rq_weight_cols(const rq_weight* w);
+int rq_weight_type(const rq_weight* w);
+/* Bytes the weight occupies in HBM (equal to its GGUF size). */
+int64_t rq_weight_bytes(const rq_weight* w);
+
+/* Dequantises every value to fp32, bit-exact with the reference unpacking
+ * (dequant_scalar / dequant_q45k / dequant_q6k, recipe.rs:3687-3833). dev_out: rows*cols floats. */
+int rq_dequant(rq_ctx* ctx, const rq_weight* w, float* dev_out, void* stream);
+
+/* Quantises `count` fp32 device values into GGUF blocks in device memory, byte-exact with
+ * Integer::compress (recipe.rs:16191-16242 Q8_0/Q4_0, :16325-16375 Q4_K, :16376-16414 Q6_K).
+ * count must be a whole number of blocks. */
+int rq_quantize(rq_ctx* ctx, int ggml_type, const float* dev_values, int64_t count, void* dev_blocks, void* stream);
+
+/* ---- matvec ---------------------------------------------------------------------- */
+
+/* y[n*y_n_stride + t*y_t_stride] = sum_k W[n][k] * x[k*x_k_stride + t*x_t_stride], t < tokens.
+ * Device pointers. Replaces contraction_forward_body for blocked weights
+ * (amd-nv-cpu.ll:2242-2300 -> :1231-2241) and packed_rows_body mode 0 (amd-nv-cpu.ll:3136-3508).
+ * The reference's channel-major planes are x_k_stride = tokens, x_t_stride = 1.
+ * act_mode RQ_ACT_INT8 takes step 32 or 256 (recipe.model.int.step); FLOAT ignores step.
+ * Enqueues on `stream` (a cudaStream_t, may be NULL) and returns without synchronising. */
+int rq_matvec(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
+              float* y, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);
+
+/* The same call with HOST buffers: copies x in, runs, copies y out, synchronises. This is the
+ * call a host without device buffers makes (Placed::infer, recipe.rs:21314-21490). */
+int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host_x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
+                   float* host_y, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step);
+
+/* Writes the int8 activation records the INT8 path derives from x (36 bytes per 32 inputs:
+ * fp32 step, 32 codes; build.rs:332-337) for `tokens` columns into dev_records
+ * ([tokens][cols/32][36]). Exposes amd-nv-cpu.ll:1381-1517 for bit-exact checks. */
+int rq_quantize_activations(rq_ctx* ctx, const float* x, int64_t x_k_stride, int64_t x_t_stride, int64_t cols, int tokens,
+                            int step, void* dev_records, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

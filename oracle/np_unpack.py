@@ -1,0 +1,63 @@
+"""Independent NumPy restatement of the reference unpacking -- TEST INFRASTRUCTURE ONLY.
+
+A second, vectorised statement of recipe.rs:3687-3833 (dequant_q45k, dequant_q6k,
+dequant_scalar) evaluated as HostQuantOps does (recipe.rs:3973-4057): every product and the
+final subtract in float64, the result rounded once to float32. It shares no code with
+rq_oracle.c, so agreement between the two pins the layout reading of each. Only tests import it.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+
+
+def _half(raw: np.ndarray) -> np.ndarray:
+    """Two little-endian bytes -> float64 value of the IEEE half."""
+    return np.ascontiguousarray(raw).view("<f2").astype(np.float64)[..., 0]
+
+
+def dequantize(ggml_type: int, blocks: np.ndarray) -> np.ndarray:
+    values, stride = GEOMETRY[ggml_type]
+    b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, stride)
+    n = b.shape[0]
+    if ggml_type == Q8_0:
+        d = _half(b[:, 0:2])
+        q = b[:, 2:34].view(np.int8).astype(np.float64)
+        out = q * d[:, None]
+    elif ggml_type == Q4_0:
+        d = _half(b[:, 0:2])
+        qs = b[:, 2:18]
+        q = np.concatenate([qs & 15, qs >> 4], axis=1).astype(np.float64) - 8.0
+        out = q * d[:, None]
+    elif ggml_type == Q4_K:
+        d, dmin = _half(b[:, 0:2]), _half(b[:, 2:4])
+        s = b[:, 4:16].astype(np.int64)
+        sc = np.empty((n, 8), np.int64)
+        mn = np.empty((n, 8), np.int64)
+        sc[:, :4] = s[:, 0:4] & 63
+        mn[:, :4] = s[:, 4:8] & 63
+        sc[:, 4:] = (s[:, 8:12] & 15) | ((s[:, 0:4] >> 6) << 4)
+        mn[:, 4:] = (s[:, 8:12] >> 4) | ((s[:, 4:8] >> 6) << 4)
+        qs = b[:, 16:144].reshape(n, 4, 32)
+        q = np.stack([qs & 15, qs >> 4], axis=2).reshape(n, 8, 32).astype(np.float64)  # sub-block 2p low, 2p+1 high
+        step = d[:, None] * sc
+        base = dmin[:, None] * mn
+        out = (step[:, :, None] * q - base[:, :, None]).reshape(n, 256)
+    elif ggml_type == Q6_K:
+        ql = b[:, 0:128].reshape(n, 2, 2, 32)          # [chunk][g & 1][w]
+        qh = b[:, 128:192].reshape(n, 2, 32)           # [chunk][w]
+        sc = b[:, 192:208].view(np.int8).astype(np.float64).reshape(n, 2, 4, 2)  # [chunk][g][w // 16]
+        d = _half(b[:, 208:210])
+        out = np.empty((n, 2, 4, 32), np.float64)
+        for g in range(4):
+            lo = (ql[:, :, g & 1, :] >> (4 * (g // 2))) & 15
+            hi = (qh >> (2 * g)) & 3
+            code = (lo | (hi << 4)).astype(np.float64) - 32.0
+            scale = np.repeat(sc[:, :, g, :], 16, axis=2)
+            out[:, :, g, :] = (d[:, None, None] * scale) * code
+        out = out.reshape(n, 256)
+    else:
+        raise ValueError(f"type {ggml_type}")
+    return out.astype(np.float32).reshape(-1)

@@ -1,0 +1,243 @@
+"""ctypes binding of the C ABI in include/rq.h.
+
+Device buffers are torch CUDA tensors (torch is the allocator and the stream provider);
+every call goes straight to the library. If ``librq_b200.so`` is absent the import of the
+library raises: nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+ACT_FLOAT, ACT_INT8 = 0, 1
+SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
+
+_PKG = Path(__file__).resolve().parent
+_LIB = None
+
+
+class RqError(RuntimeError):
+    """A call into librq_b200.so returned a negative status."""
+
+    def __init__(self, status: int, text: str):
+        super().__init__(f"rq status {status}: {text}")
+        self.status = status
+
+
+def library_path() -> Path:
+    return _PKG / "librq_b200.so"
+
+
+def _declare(lib) -> None:
+    p, i32, i64, f32p = C.c_void_p, C.c_int, C.c_int64, C.c_void_p
+    sig = {
+        "rq_init": (i32, [i32, C.POINTER(p)]),
+        "rq_destroy": (None, [p]),
+        "rq_last_error": (C.c_char_p, []),
+        "rq_block_values": (i32, [i32]),
+        "rq_block_bytes": (i32, [i32]),
+        "rq_weight_prepare": (i32, [p, i32, p, i64, i64, i64, i64, C.POINTER(p)]),
+        "rq_weight_prepare_device": (i32, [p, i32, p, i64, i64, C.POINTER(p), p]),
+        "rq_weight_export": (i32, [p, p, p]),
+        "rq_weight_free": (None, [p, p]),
+        "rq_weight_rows": (i64, [p]),
+        "rq_weight_cols": (i64, [p]),
+        "rq_weight_type": (i32, [p]),
+        "rq_weight_bytes": (i64, [p]),
+        "rq_dequant": (i32, [p, p, f32p, p]),
+        "rq_quantize": (i32, [p, i32, f32p, i64, p, p]),
+        "rq_matvec": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
+        "rq_matvec_host": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32]),
+        "rq_quantize_activations": (i32, [p, f32p, i64, i64, i64, i32, i32, p, p]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    # optional groups (declared when the library exports them)
+    optional = {
+        "rq_moe_route": (i32, [p, f32p, i32, i32, i32, i32, f32p, i32, f32p, p]),
+        "rq_moe_prepare": (i32, [p, p, p, p, i32, i32, i32, i32, C.POINTER(p)]),
+        "rq_moe_free": (None, [p, p]),
+        "rq_moe_forward": (i32, [p, p, f32p, f32p, i32, f32p, i32, p]),
+        "rq_matmul": (i32, [p, p, f32p, i32, f32p, i32, i32, p]),
+        "rq_matvec_static": (i32, [p, p, f32p, i32, f32p, i32, p]),
+    }
+    for name, (res, args) in optional.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+
+
+def load_library():
+    """Loads librq_b200.so, or raises: the CUDA extension is the only implementation."""
+    global _LIB
+    if _LIB is None:
+        path = library_path()
+        if not path.exists():
+            raise RqError(-4, f"{path} is missing: build it with `python -m recipe_dev_b200.build` (nvcc, sm_100a); there is no CPU fallback")
+        lib = C.CDLL(str(path))
+        _declare(lib)
+        _LIB = lib
+    return _LIB
+
+
+def block_values(ggml_type: int) -> int:
+    return load_library().rq_block_values(ggml_type)
+
+
+def block_bytes(ggml_type: int) -> int:
+    return load_library().rq_block_bytes(ggml_type)
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise RqError(status, load_library().rq_last_error().decode("utf-8", "replace"))
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        import torch
+
+        return torch.cuda.current_stream().cuda_stream
+    return stream if isinstance(stream, int) else stream.cuda_stream
+
+
+class Weight:
+    """A stored weight resident in HBM (rq_weight)."""
+
+    def __init__(self, ctx: "Context", handle: int):
+        self.ctx, self.handle = ctx, handle
+
+    @property
+    def rows(self) -> int:
+        return self.ctx.lib.rq_weight_rows(self.handle)
+
+    @property
+    def cols(self) -> int:
+        return self.ctx.lib.rq_weight_cols(self.handle)
+
+    @property
+    def type(self) -> int:
+        return self.ctx.lib.rq_weight_type(self.handle)
+
+    @property
+    def nbytes(self) -> int:
+        return self.ctx.lib.rq_weight_bytes(self.handle)
+
+    def free(self) -> None:
+        if self.handle:
+            self.ctx.lib.rq_weight_free(self.ctx.handle, self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Context:
+    """One device context (rq_ctx)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = load_library()
+        handle = C.c_void_p()
+        _check(self.lib.rq_init(device, C.byref(handle)))
+        self.handle = handle.value
+        self.device = device
+
+    def close(self) -> None:
+        if getattr(self, "handle", 0):
+            self.lib.rq_destroy(self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- weights ----
+    def weight_from_host(self, ggml_type: int, blocks: np.ndarray, rows: int, cols: int, row_first: int = 0, row_count: int | None = None) -> Weight:
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        row_count = rows - row_first if row_count is None else row_count
+        out = C.c_void_p()
+        _check(self.lib.rq_weight_prepare(self.handle, ggml_type, blocks.ctypes.data, rows, cols, row_first, row_count, C.byref(out)))
+        return Weight(self, out.value)
+
+    def weight_from_device(self, ggml_type: int, dev_blocks, rows: int, cols: int, stream=None) -> Weight:
+        out = C.c_void_p()
+        _check(self.lib.rq_weight_prepare_device(self.handle, ggml_type, _ptr(dev_blocks), rows, cols, C.byref(out), _stream(stream)))
+        return Weight(self, out.value)
+
+    def export(self, w: Weight) -> np.ndarray:
+        n = w.rows * (w.cols // block_values(w.type)) * block_bytes(w.type)
+        out = np.empty(n, dtype=np.uint8)
+        _check(self.lib.rq_weight_export(self.handle, w.handle, out.ctypes.data))
+        return out
+
+    def dequant(self, w: Weight, out=None, stream=None):
+        import torch
+
+        if out is None:
+            out = torch.empty((w.rows, w.cols), dtype=torch.float32, device=f"cuda:{self.device}")
+        _check(self.lib.rq_dequant(self.handle, w.handle, _ptr(out), _stream(stream)))
+        return out
+
+    def quantize(self, ggml_type: int, values, stream=None):
+        """fp32 CUDA tensor -> uint8 CUDA tensor of GGUF blocks."""
+        import torch
+
+        assert values.is_cuda and values.dtype == torch.float32 and values.is_contiguous()
+        n = values.numel()
+        per, nbytes = block_values(ggml_type), block_bytes(ggml_type)
+        out = torch.empty((n // max(per, 1)) * nbytes if per else 0, dtype=torch.uint8, device=values.device)
+        _check(self.lib.rq_quantize(self.handle, ggml_type, _ptr(values), n, _ptr(out), _stream(stream)))
+        return out
+
+    # ---- matvec ----
+    def matvec(self, w: Weight, x, y=None, act_mode: int = ACT_FLOAT, step: int = 32, stream=None):
+        """x: CUDA fp32, [cols] or [tokens, cols] (token-major) -> y [rows] or [tokens, rows]."""
+        import torch
+
+        single = x.dim() == 1
+        x2 = x.unsqueeze(0) if single else x
+        tokens, cols = x2.shape
+        if y is None:
+            y = torch.empty((tokens, w.rows), dtype=torch.float32, device=x.device)
+        y2 = y.unsqueeze(0) if y.dim() == 1 else y
+        _check(self.lib.rq_matvec(self.handle, w.handle, _ptr(x2), x2.stride(1), x2.stride(0), tokens,
+                                  _ptr(y2), y2.stride(1), y2.stride(0), act_mode, step, _stream(stream)))
+        return y2[0] if single else y2
+
+    def matvec_raw(self, w: Weight, x_ptr: int, sk: int, st: int, tokens: int, y_ptr: int, yn: int, yt: int, act_mode: int, step: int, stream=None) -> int:
+        return self.lib.rq_matvec(self.handle, w.handle, x_ptr, sk, st, tokens, y_ptr, yn, yt, act_mode, step, _stream(stream) if stream is not None else 0)
+
+    def matvec_host(self, w: Weight, x: np.ndarray, act_mode: int = ACT_FLOAT, step: int = 32) -> np.ndarray:
+        """Host buffers in and out: x [cols] or [tokens, cols] float32."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        single = x.ndim == 1
+        x2 = x[None, :] if single else x
+        tokens = x2.shape[0]
+        y = np.empty((tokens, w.rows), dtype=np.float32)
+        _check(self.lib.rq_matvec_host(self.handle, w.handle, x2.ctypes.data, 1, x2.shape[1], tokens, y.ctypes.data, 1, w.rows, act_mode, step))
+        return y[0] if single else y
+
+    def activation_records(self, x, step: int, stream=None):
+        """The 36-byte int8 records of x ([cols] or [tokens, cols]) as a uint8 CUDA tensor."""
+        import torch
+
+        x2 = x.unsqueeze(0) if x.dim() == 1 else x
+        tokens, cols = x2.shape
+        out = torch.empty((tokens, cols // 32, 36), dtype=torch.uint8, device=x.device)
+        _check(self.lib.rq_quantize_activations(self.handle, _ptr(x2), x2.stride(1), x2.stride(0), cols, tokens, step, _ptr(out), _stream(stream)))
+        return out

@@ -1,0 +1,277 @@
+// C ABI of librq_b200.so: context, weights, argument validation, error text.
+// Every entry point validates, returns a status and never aborts; none has a CPU path.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "rq_internal.cuh"
+
+static thread_local char g_error[512] = "";
+
+int rq_fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+extern "C" const char* rq_last_error(void) { return g_error; }
+
+extern "C" int rq_block_values(int t) {
+    switch (t) {
+        case RQ_Q4_0: case RQ_Q8_0: return 32;
+        case RQ_Q4_K: case RQ_Q6_K: return 256;
+        default: return 0;
+    }
+}
+extern "C" int rq_block_bytes(int t) {
+    switch (t) {
+        case RQ_Q4_0: return 18;
+        case RQ_Q8_0: return 34;
+        case RQ_Q4_K: return 144;
+        case RQ_Q6_K: return 210;
+        default: return 0;
+    }
+}
+
+extern "C" int rq_init(int device, rq_ctx** out) {
+    if (!out) return rq_fail(RQ_ERR_INVALID, "rq_init: out is null");
+    *out = nullptr;
+    int count = 0;
+    RQ_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return rq_fail(RQ_ERR_INVALID, "rq_init: device %d out of range (%d visible)", device, count);
+    DeviceGuard guard(device);
+    if (!guard.ok) return rq_fail(RQ_ERR_CUDA, "rq_init: cannot select device %d", device);
+    cudaDeviceProp prop;
+    RQ_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10) return rq_fail(RQ_ERR_UNSUPPORTED, "rq_init: device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    rq_ctx* ctx = new (std::nothrow) rq_ctx();
+    if (!ctx) return rq_fail(RQ_ERR_ALLOC, "rq_init: out of host memory");
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete ctx; return rq_fail(RQ_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
+    *out = ctx;
+    return RQ_OK;
+}
+
+extern "C" void rq_destroy(rq_ctx* ctx) {
+    if (!ctx) return;
+    DeviceGuard guard(ctx->device);
+    if (ctx->act_scratch) cudaFree(ctx->act_scratch);
+    if (ctx->stage_x) cudaFree(ctx->stage_x);
+    if (ctx->stage_y) cudaFree(ctx->stage_y);
+    if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
+    if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->act_scratch_bytes) return RQ_OK;
+    // grow geometrically; the old buffer may still be read by kernels in flight
+    size_t want = bytes + bytes / 2 + 4096;
+    RQ_CUDA(cudaDeviceSynchronize());
+    if (ctx->act_scratch) RQ_CUDA(cudaFree(ctx->act_scratch));
+    ctx->act_scratch = nullptr;
+    ctx->act_scratch_bytes = 0;
+    ctx->act_cols = 0;
+    cudaError_t e = cudaMalloc(&ctx->act_scratch, want);
+    if (e != cudaSuccess) return rq_fail(RQ_ERR_ALLOC, "activation scratch of %zu bytes: %s", want, cudaGetErrorString(e));
+    ctx->act_scratch_bytes = want;
+    return RQ_OK;
+}
+
+// ---- weights ------------------------------------------------------------------------
+
+static int check_shape(const char* who, int type, int64_t rows, int64_t cols) {
+    int per = rq_block_values(type);
+    if (!per) return rq_fail(RQ_ERR_INVALID, "%s: GGML type %d is not one of Q4_0(2) Q8_0(8) Q4_K(12) Q6_K(14)", who, type);
+    if (rows <= 0 || cols <= 0) return rq_fail(RQ_ERR_INVALID, "%s: rows=%lld cols=%lld must be positive", who, (long long)rows, (long long)cols);
+    if (cols % per) return rq_fail(RQ_ERR_INVALID, "%s: cols=%lld is not a multiple of the %d-value block", who, (long long)cols, per);
+    if (cols > (int64_t)1 << 24 || rows > (int64_t)1 << 31) return rq_fail(RQ_ERR_LIMIT, "%s: shape %lld x %lld beyond the supported range", who, (long long)rows, (long long)cols);
+    return RQ_OK;
+}
+
+static int alloc_weight(rq_ctx* ctx, int type, int64_t rows, int64_t cols, rq_weight** out) {
+    rq_weight* w = new (std::nothrow) rq_weight();
+    if (!w) return rq_fail(RQ_ERR_ALLOC, "out of host memory");
+    memset(w, 0, sizeof(*w));
+    w->type = type; w->rows = rows; w->cols = cols; w->device = ctx->device;
+    int per = rq_block_values(type), bytes = rq_block_bytes(type);
+    int64_t blocks = rows * (cols / per);
+    int64_t main_bytes = type == RQ_Q4_K ? blocks * 144 : blocks * (bytes - 2);
+    int64_t scale_bytes = type == RQ_Q4_K ? 0 : blocks * 2;
+    w->bytes = main_bytes + scale_bytes;
+    // one allocation, scale plane after the main plane at a 256-byte boundary
+    int64_t main_padded = (main_bytes + 255) / 256 * 256;
+    uint8_t* base = nullptr;
+    cudaError_t e = cudaMalloc(&base, (size_t)(main_padded + scale_bytes + 256));
+    if (e != cudaSuccess) { delete w; return rq_fail(RQ_ERR_ALLOC, "weight of %lld bytes: %s", (long long)w->bytes, cudaGetErrorString(e)); }
+    w->main = base;
+    w->scale = scale_bytes ? (uint16_t*)(base + main_padded) : nullptr;
+    *out = w;
+    return RQ_OK;
+}
+
+extern "C" void rq_weight_free(rq_ctx* ctx, rq_weight* w) {
+    if (!w) return;
+    DeviceGuard guard(ctx ? ctx->device : w->device);
+    if (w->main) cudaFree(w->main);
+    delete w;
+}
+
+extern "C" int rq_weight_prepare_device(rq_ctx* ctx, int type, const void* dev_blocks, int64_t rows, int64_t cols, rq_weight** out, void* stream) {
+    if (!ctx || !dev_blocks || !out) return rq_fail(RQ_ERR_INVALID, "rq_weight_prepare_device: null argument");
+    *out = nullptr;
+    int rc = check_shape("rq_weight_prepare_device", type, rows, cols);
+    if (rc) return rc;
+    DeviceGuard guard(ctx->device);
+    rq_weight* w = nullptr;
+    rc = alloc_weight(ctx, type, rows, cols, &w);
+    if (rc) return rc;
+    rc = rq_launch_repack(w, (const uint8_t*)dev_blocks, (cudaStream_t)stream);
+    if (rc) { rq_weight_free(ctx, w); return rc; }
+    *out = w;
+    return RQ_OK;
+}
+
+extern "C" int rq_weight_prepare(rq_ctx* ctx, int type, const void* host_blocks, int64_t rows, int64_t cols,
+                                 int64_t row_first, int64_t row_count, rq_weight** out) {
+    if (!ctx || !host_blocks || !out) return rq_fail(RQ_ERR_INVALID, "rq_weight_prepare: null argument");
+    *out = nullptr;
+    int rc = check_shape("rq_weight_prepare", type, rows, cols);
+    if (rc) return rc;
+    if (row_first < 0 || row_count <= 0 || row_first + row_count > rows)
+        return rq_fail(RQ_ERR_INVALID, "rq_weight_prepare: rows [%lld, %lld) outside the tensor's %lld rows", (long long)row_first, (long long)(row_first + row_count), (long long)rows);
+    DeviceGuard guard(ctx->device);
+    int64_t row_bytes = cols / rq_block_values(type) * rq_block_bytes(type);
+    int64_t total = row_count * row_bytes;
+    uint8_t* staging = nullptr;
+    cudaError_t e = cudaMalloc(&staging, (size_t)total + 16);
+    if (e != cudaSuccess) return rq_fail(RQ_ERR_ALLOC, "upload staging of %lld bytes: %s", (long long)total, cudaGetErrorString(e));
+    e = cudaMemcpy(staging, (const uint8_t*)host_blocks + row_first * row_bytes, (size_t)total, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(staging); return rq_fail(RQ_ERR_CUDA, "weight upload: %s", cudaGetErrorString(e)); }
+    rc = rq_weight_prepare_device(ctx, type, staging, row_count, cols, out, nullptr);
+    cudaError_t e2 = cudaDeviceSynchronize();
+    cudaFree(staging);
+    if (rc) return rc;
+    if (e2 != cudaSuccess) { rq_weight_free(ctx, *out); *out = nullptr; return rq_fail(RQ_ERR_CUDA, "weight repack: %s", cudaGetErrorString(e2)); }
+    return RQ_OK;
+}
+
+extern "C" int rq_weight_export(rq_ctx* ctx, const rq_weight* w, void* host_blocks) {
+    if (!ctx || !w || !host_blocks) return rq_fail(RQ_ERR_INVALID, "rq_weight_export: null argument");
+    DeviceGuard guard(ctx->device);
+    int64_t total = w->rows * (w->cols / rq_block_values(w->type)) * rq_block_bytes(w->type);
+    uint8_t* staging = nullptr;
+    cudaError_t e = cudaMalloc(&staging, (size_t)total + 16);
+    if (e != cudaSuccess) return rq_fail(RQ_ERR_ALLOC, "export staging: %s", cudaGetErrorString(e));
+    int rc = rq_launch_export(w, staging, nullptr);
+    if (!rc) {
+        e = cudaMemcpy(host_blocks, staging, (size_t)total, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) rc = rq_fail(RQ_ERR_CUDA, "export copy: %s", cudaGetErrorString(e));
+    }
+    cudaFree(staging);
+    return rc;
+}
+
+extern "C" int64_t rq_weight_rows(const rq_weight* w) { return w ? w->rows : 0; }
+extern "C" int64_t rq_weight_cols(const rq_weight* w) { return w ? w->cols : 0; }
+extern "C" int rq_weight_type(const rq_weight* w) { return w ? w->type : 0; }
+extern "C" int64_t rq_weight_bytes(const rq_weight* w) { return w ? w->bytes : 0; }
+
+extern "C" int rq_dequant(rq_ctx* ctx, const rq_weight* w, float* dev_out, void* stream) {
+    if (!ctx || !w || !dev_out) return rq_fail(RQ_ERR_INVALID, "rq_dequant: null argument");
+    DeviceGuard guard(ctx->device);
+    return rq_launch_dequant(w, dev_out, (cudaStream_t)stream);
+}
+
+extern "C" int rq_quantize(rq_ctx* ctx, int type, const float* dev_values, int64_t count, void* dev_blocks, void* stream) {
+    if (!ctx || !dev_values || !dev_blocks) return rq_fail(RQ_ERR_INVALID, "rq_quantize: null argument");
+    int per = rq_block_values(type);
+    if (!per) return rq_fail(RQ_ERR_INVALID, "rq_quantize: GGML type %d is not on this path", type);
+    if (count <= 0 || count % per) return rq_fail(RQ_ERR_INVALID, "rq_quantize: count=%lld is not a positive multiple of %d", (long long)count, per);
+    DeviceGuard guard(ctx->device);
+    return rq_launch_quantize(type, dev_values, count, (uint8_t*)dev_blocks, (cudaStream_t)stream);
+}
+
+// ---- matvec ---------------------------------------------------------------------------
+
+static int check_matvec(const char* who, const rq_ctx* ctx, const rq_weight* w, const void* x, const void* y, int tokens, int act_mode, int step) {
+    if (!ctx || !w || !x || !y) return rq_fail(RQ_ERR_INVALID, "%s: null argument", who);
+    if (w->device != ctx->device) return rq_fail(RQ_ERR_INVALID, "%s: weight lives on device %d, context on %d", who, w->device, ctx->device);
+    if (tokens <= 0) return rq_fail(RQ_ERR_INVALID, "%s: tokens=%d must be positive", who, tokens);
+    if (act_mode != RQ_ACT_FLOAT && act_mode != RQ_ACT_INT8 && act_mode != RQ_ACT_INT8_CACHED)
+        return rq_fail(RQ_ERR_INVALID, "%s: act_mode=%d is none of FLOAT(0), INT8(1), INT8_CACHED(2)", who, act_mode);
+    if (act_mode != RQ_ACT_FLOAT && step != 32 && step != 256) return rq_fail(RQ_ERR_INVALID, "%s: int8 step=%d must be 32 or 256", who, step);
+    return RQ_OK;
+}
+
+extern "C" int rq_matvec(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
+                         float* y, int64_t yn, int64_t yt, int act_mode, int step, void* stream) {
+    int rc = check_matvec("rq_matvec", ctx, w, x, y, tokens, act_mode, step);
+    if (rc) return rc;
+    if (sk <= 0 || yn <= 0 || (tokens > 1 && (st <= 0 || yt <= 0))) return rq_fail(RQ_ERR_INVALID, "rq_matvec: strides must be positive");
+    DeviceGuard guard(ctx->device);
+    return rq_launch_gemv(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, step, (cudaStream_t)stream);
+}
+
+static int ensure_buffer(float** dev, size_t* dev_bytes, float** pin, size_t* pin_bytes, size_t need) {
+    if (need > *dev_bytes) {
+        if (*dev) cudaFree(*dev);
+        *dev = nullptr; *dev_bytes = 0;
+        RQ_CUDA(cudaMalloc(dev, need));
+        *dev_bytes = need;
+    }
+    if (need > *pin_bytes) {
+        if (*pin) cudaFreeHost(*pin);
+        *pin = nullptr; *pin_bytes = 0;
+        RQ_CUDA(cudaMallocHost(pin, need));
+        *pin_bytes = need;
+    }
+    return RQ_OK;
+}
+
+extern "C" int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host_x, int64_t sk, int64_t st, int tokens,
+                              float* host_y, int64_t yn, int64_t yt, int act_mode, int step) {
+    int rc = check_matvec("rq_matvec_host", ctx, w, host_x, host_y, tokens, act_mode, step);
+    if (rc) return rc;
+    if (sk <= 0 || yn <= 0 || (tokens > 1 && (st <= 0 || yt <= 0))) return rq_fail(RQ_ERR_INVALID, "rq_matvec_host: strides must be positive");
+    DeviceGuard guard(ctx->device);
+    // The host planes are gathered token-major into pinned memory, so one copy moves them.
+    size_t xb = (size_t)tokens * (size_t)w->cols * 4, yb = (size_t)tokens * (size_t)w->rows * 4;
+    rc = ensure_buffer(&ctx->stage_x, &ctx->stage_x_bytes, &ctx->pin_x, &ctx->pin_x_bytes, xb);
+    if (rc) return rc;
+    rc = ensure_buffer(&ctx->stage_y, &ctx->stage_y_bytes, &ctx->pin_y, &ctx->pin_y_bytes, yb);
+    if (rc) return rc;
+    for (int t = 0; t < tokens; ++t)
+        for (int64_t k = 0; k < w->cols; ++k) ctx->pin_x[(size_t)t * w->cols + k] = host_x[k * sk + t * st];
+    RQ_CUDA(cudaMemcpyAsync(ctx->stage_x, ctx->pin_x, xb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = rq_launch_gemv(ctx, w, ctx->stage_x, 1, w->cols, tokens, ctx->stage_y, 1, w->rows, act_mode, step, ctx->stream);
+    if (rc) return rc;
+    RQ_CUDA(cudaMemcpyAsync(ctx->pin_y, ctx->stage_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    RQ_CUDA(cudaStreamSynchronize(ctx->stream));
+    for (int t = 0; t < tokens; ++t)
+        for (int64_t n = 0; n < w->rows; ++n) host_y[n * yn + t * yt] = ctx->pin_y[(size_t)t * w->rows + n];
+    return RQ_OK;
+}
+
+extern "C" int rq_quantize_activations(rq_ctx* ctx, const float* x, int64_t sk, int64_t st, int64_t cols, int tokens,
+                                       int step, void* dev_records, void* stream) {
+    if (!ctx || !x || !dev_records) return rq_fail(RQ_ERR_INVALID, "rq_quantize_activations: null argument");
+    if (cols <= 0 || cols % 32) return rq_fail(RQ_ERR_INVALID, "rq_quantize_activations: cols=%lld is not a positive multiple of 32", (long long)cols);
+    if (step != 32 && step != 256) return rq_fail(RQ_ERR_INVALID, "rq_quantize_activations: step=%d must be 32 or 256", step);
+    if (tokens <= 0 || sk <= 0) return rq_fail(RQ_ERR_INVALID, "rq_quantize_activations: tokens and strides must be positive");
+    DeviceGuard guard(ctx->device);
+    int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols) * (size_t)tokens);
+    if (rc) return rc;
+    rc = rq_launch_act_quant(x, sk, st, cols, tokens, step, ctx->act_scratch, (uint8_t*)dev_records, (cudaStream_t)stream);
+    if (rc) return rc;
+    ctx->act_cols = cols; ctx->act_tokens = tokens; ctx->act_step = step;
+    return RQ_OK;
+}

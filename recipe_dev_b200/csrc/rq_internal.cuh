@@ -1,0 +1,102 @@
+// Internal declarations shared by the translation units of librq_b200.so.
+// Device layouts of the four stored formats, the context, and small device helpers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "rq.h"
+
+// ---------------------------------------------------------------------------------
+// Data layout in HBM.
+//
+// Q4_K keeps its GGUF blocks as they are: 144 bytes = nine 16-byte lines, the first the
+// header (d, dmin, twelve scale bytes), the other eight the nibbles, so every line of a
+// row is a 128-bit load.
+// The other three formats have strides that are only 2-byte aligned (18, 34, 210), so
+// they are split into planes at load, the same bytes in aligned places:
+//   Q6_K : body  [rows][blocks][208] = ql(128) | qh(64) | scales(16)   + d [rows][blocks] fp16
+//   Q8_0 : codes [rows][cols] int8                                      + d [rows][cols/32] fp16
+//   Q4_0 : qs    [rows][cols/32][16]                                    + d [rows][cols/32] fp16
+// No plane is padded: device bytes equal GGUF bytes.
+// ---------------------------------------------------------------------------------
+struct rq_weight {
+    int type;
+    int64_t rows, cols;
+    uint8_t* main;   // Q4_K blocks | Q6_K bodies | Q8_0 codes | Q4_0 nibbles
+    uint16_t* scale; // fp16 d plane (null for Q4_K)
+    int64_t bytes;   // total device bytes
+    int device;
+};
+
+struct rq_ctx {
+    int device;
+    int sm_count;
+    // scratch the INT8 path writes its activation records into (grown on demand)
+    uint8_t* act_scratch;
+    size_t act_scratch_bytes;
+    int64_t act_cols; int act_tokens; int act_step;  // what the scratch holds (0 = nothing)
+    // pinned + device staging for the host-buffer entry points
+    float* stage_x; float* stage_y; size_t stage_x_bytes, stage_y_bytes;
+    float* pin_x; float* pin_y; size_t pin_x_bytes, pin_y_bytes;
+    cudaStream_t stream; // used by the host-buffer entry points
+};
+
+int rq_fail(int status, const char* fmt, ...);
+#define RQ_CUDA(call)                                                                         \
+    do {                                                                                      \
+        cudaError_t e_ = (call);                                                              \
+        if (e_ != cudaSuccess) return rq_fail(RQ_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+struct DeviceGuard {
+    int prev;
+    bool ok;
+    explicit DeviceGuard(int dev) : prev(-1), ok(false) {
+        if (cudaGetDevice(&prev) != cudaSuccess) return;
+        ok = (prev == dev) || cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// Device-side activation scratch, per token (INT8 path): codes then steps then slice sums.
+//   codes [cols] int8 | d [cols/32] fp32 | sum16 [cols/16] int16 (sum of the 16 codes of a slice)
+__host__ __device__ inline size_t rq_act_token_bytes(int64_t cols) {
+    return (size_t)cols + (size_t)(cols / 32) * 4 + (size_t)(cols / 16) * 2;
+}
+
+int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes);
+
+// launchers (defined in the .cu files)
+int rq_launch_repack(const rq_weight* w, const uint8_t* dev_blocks, cudaStream_t s);
+int rq_launch_export(const rq_weight* w, uint8_t* dev_blocks, cudaStream_t s);
+int rq_launch_dequant(const rq_weight* w, float* out, cudaStream_t s);
+int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, int tokens, int step,
+                        uint8_t* scratch, uint8_t* records36, cudaStream_t s);
+int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
+                   float* y, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s);
+int rq_launch_quantize(int type, const float* values, int64_t count, uint8_t* blocks, cudaStream_t s);
+
+// ---------------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float rq_h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// Six-bit scale and minimum of sub-block j from the twelve scale bytes held as three words
+// (little-endian bytes 0..11).
+__device__ __forceinline__ void rq_q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, int& sc, int& mn) {
+    // byte(i) of the 12: i<4 -> s0, i<8 -> s1, else s2
+    if (j < 4) {
+        sc = (s0 >> (8 * j)) & 63;
+        mn = (s1 >> (8 * j)) & 63;
+    } else {
+        int i = j - 4;
+        uint32_t hi = (s2 >> (8 * i)) & 0xff; // byte j+4
+        uint32_t a = (s0 >> (8 * i)) & 0xff;  // byte j-4
+        uint32_t b = (s1 >> (8 * i)) & 0xff;  // byte j
+        sc = (hi & 15) | ((a >> 6) << 4);
+        mn = (hi >> 4) | ((b >> 6) << 4);
+    }
+}
+#endif

@@ -1,0 +1,108 @@
+// Load-time layout kernels (GGUF blocks <-> device planes) and the bit-exact dequantiser.
+#include "rq_internal.cuh"
+
+// GGUF strides 18/34/210 are multiples of two, so blocks move as 16-bit words.
+// mode 0: GGUF -> planes, mode 1: planes -> GGUF.
+template <int TYPE>
+__global__ void rq_plane_kernel(uint16_t* __restrict__ gguf, uint16_t* __restrict__ main_plane, uint16_t* __restrict__ scale_plane,
+                                int64_t blocks, int to_gguf) {
+    constexpr int WORDS = TYPE == RQ_Q6_K ? 105 : (TYPE == RQ_Q8_0 ? 17 : 9);
+    constexpr int BODY = WORDS - 1;                       // 16-bit words of the block that are not d
+    constexpr int D_AT = TYPE == RQ_Q6_K ? 104 : 0;       // where d sits in the GGUF block
+    int64_t total = blocks * WORDS;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t b = i / WORDS;
+        int wd = (int)(i - b * WORDS);
+        uint16_t* g = gguf + i;
+        uint16_t* p;
+        if (wd == D_AT) p = scale_plane + b;
+        else p = main_plane + b * BODY + (TYPE == RQ_Q6_K ? wd : wd - 1);
+        if (to_gguf) *g = *p; else *p = *g;
+    }
+}
+
+static int plane_launch(const rq_weight* w, uint8_t* blocks, int to_gguf, cudaStream_t s) {
+    int64_t nblocks = w->rows * (w->cols / rq_block_values(w->type));
+    if (w->type == RQ_Q4_K) {
+        if (to_gguf) RQ_CUDA(cudaMemcpyAsync(blocks, w->main, (size_t)nblocks * 144, cudaMemcpyDeviceToDevice, s));
+        else RQ_CUDA(cudaMemcpyAsync(w->main, blocks, (size_t)nblocks * 144, cudaMemcpyDeviceToDevice, s));
+        return RQ_OK;
+    }
+    int threads = 256;
+    int64_t words = nblocks * (rq_block_bytes(w->type) / 2);
+    int grid = (int)((words + threads - 1) / threads < 148 * 16 ? (words + threads - 1) / threads : 148 * 16);
+    if (grid < 1) grid = 1;
+    uint16_t* g = (uint16_t*)blocks;
+    uint16_t* m = (uint16_t*)w->main;
+    switch (w->type) {
+        case RQ_Q6_K: rq_plane_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf); break;
+        case RQ_Q8_0: rq_plane_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf); break;
+        case RQ_Q4_0: rq_plane_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf); break;
+        default: return rq_fail(RQ_ERR_INVALID, "layout: type %d", w->type);
+    }
+    RQ_CUDA(cudaGetLastError());
+    return RQ_OK;
+}
+
+int rq_launch_repack(const rq_weight* w, const uint8_t* dev_blocks, cudaStream_t s) { return plane_launch(w, (uint8_t*)dev_blocks, 0, s); }
+int rq_launch_export(const rq_weight* w, uint8_t* dev_blocks, cudaStream_t s) { return plane_launch(w, dev_blocks, 1, s); }
+
+// ---------------------------------------------------------------------------------------
+// Dequantiser: one thread per value. Every fp32 step is a separate rounded operation
+// (__fmul_rn / __fsub_rn never contract), which is what makes the result bit-equal to the
+// reference's f64 unpacking rounded to fp32: d*sc, dmin*m and step*q are exact in fp32, and
+// the one inexact step, the final subtract, rounds the same exact difference.
+// ---------------------------------------------------------------------------------------
+template <int TYPE>
+__global__ void rq_dequant_kernel(const uint8_t* __restrict__ main_plane, const uint16_t* __restrict__ scale_plane, float* __restrict__ out, int64_t count) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+        float value;
+        if (TYPE == RQ_Q4_K) {
+            int64_t b = i >> 8;
+            int v = (int)(i & 255), sub = v >> 5, within = v & 31;
+            const uint8_t* blk = main_plane + b * 144;
+            const uint32_t* hdr = (const uint32_t*)blk;
+            uint32_t dd = hdr[0];
+            int sc, mn;
+            rq_q4k_scale_min(hdr[1], hdr[2], hdr[3], sub, sc, mn);
+            int q = (blk[16 + (sub >> 1) * 32 + within] >> ((sub & 1) * 4)) & 15;
+            float step = __fmul_rn(rq_h2f((uint16_t)(dd & 0xffff)), (float)sc);
+            float base = __fmul_rn(rq_h2f((uint16_t)(dd >> 16)), (float)mn);
+            value = __fsub_rn(__fmul_rn(step, (float)q), base);
+        } else if (TYPE == RQ_Q6_K) {
+            int64_t b = i >> 8;
+            int v = (int)(i & 255), chunk = v >> 7, local = v & 127, group = local >> 5, within = local & 31;
+            const uint8_t* body = main_plane + b * 208;
+            int lo = (body[64 * chunk + 32 * (group & 1) + within] >> (4 * (group >> 1))) & 15;
+            int hi = (body[128 + 32 * chunk + within] >> (2 * group)) & 3;
+            int code = (lo | (hi << 4)) - 32;
+            int scale = (int8_t)body[192 + 8 * chunk + 2 * group + (within >> 4)];
+            float scaled = __fmul_rn(rq_h2f(scale_plane[b]), (float)scale);
+            value = __fmul_rn(scaled, (float)code);
+        } else if (TYPE == RQ_Q8_0) {
+            value = __fmul_rn((float)(int8_t)main_plane[i], rq_h2f(scale_plane[i >> 5]));
+        } else {
+            int64_t b = i >> 5;
+            int v = (int)(i & 31);
+            int code = ((main_plane[b * 16 + (v & 15)] >> ((v >> 4) * 4)) & 15) - 8;
+            value = __fmul_rn((float)code, rq_h2f(scale_plane[b]));
+        }
+        out[i] = value;
+    }
+}
+
+int rq_launch_dequant(const rq_weight* w, float* out, cudaStream_t s) {
+    int64_t count = w->rows * w->cols;
+    int threads = 256;
+    int64_t want = (count + threads - 1) / threads;
+    int grid = (int)(want < 148 * 32 ? want : 148 * 32);
+    switch (w->type) {
+        case RQ_Q4_K: rq_dequant_kernel<RQ_Q4_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count); break;
+        case RQ_Q6_K: rq_dequant_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count); break;
+        case RQ_Q8_0: rq_dequant_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count); break;
+        case RQ_Q4_0: rq_dequant_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count); break;
+        default: return rq_fail(RQ_ERR_INVALID, "dequant: type %d", w->type);
+    }
+    RQ_CUDA(cudaGetLastError());
+    return RQ_OK;
+}

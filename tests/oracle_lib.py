@@ -1,0 +1,137 @@
+"""ctypes access to the CPU oracle for the tests (never imported by the product)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+ORACLE_DIR = ROOT / "oracle"
+LIB_PATH = ORACLE_DIR / "librq_oracle.so"
+
+Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+FLOAT_RUN, FLOAT_EXACT, INT8 = 0, 1, 2
+GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+THREADS = max(1, os.cpu_count() or 1)
+
+
+def build() -> Path:
+    src = [ORACLE_DIR / "rq_oracle.c", ORACLE_DIR / "rq_oracle.h"]
+    if not LIB_PATH.exists() or any(s.stat().st_mtime > LIB_PATH.stat().st_mtime for s in src):
+        subprocess.run(["make", "-C", str(ORACLE_DIR), "-s"], check=True)
+    return LIB_PATH
+
+
+class Oracle:
+    def __init__(self, lib):
+        self.lib = lib
+        p, i32, i64 = C.c_void_p, C.c_int, C.c_int64
+        lib.rqo_fp16.restype = C.c_uint16
+        lib.rqo_fp16.argtypes = [C.c_float]
+        lib.rqo_unfp16.restype = C.c_float
+        lib.rqo_unfp16.argtypes = [C.c_uint16]
+        lib.rqo_qround.restype = C.c_float
+        lib.rqo_qround.argtypes = [C.c_float]
+        lib.rqo_dequantize.argtypes = [i32, p, i64, p, i32]
+        lib.rqo_quantize.argtypes = [i32, p, i64, p, i32]
+        lib.rqo_quantize_activations.argtypes = [p, i64, i64, i32, p]
+        lib.rqo_matvec.argtypes = [i32, p, i64, i64, p, i64, i32, p, i64, i32, i32, i32]
+        for name in ("rqo_exp", "rqo_tanh", "rqo_sigmoid", "rqo_silu"):
+            getattr(lib, name).restype = C.c_float
+            getattr(lib, name).argtypes = [C.c_float]
+        lib.rqo_topk.argtypes = [p, i32, i32, i32, i32, i32, p, p]
+        lib.rqo_moe_forward.argtypes = [i32, p, p, p, i32, i32, i32, i32, p, p, i32, p, p, p, p, p, i32]
+        lib.rqo_normal.argtypes = [C.c_uint64, C.c_uint64, i64, i64, C.c_double, p]
+        lib.rqo_normal.restype = None
+
+    # ---- formats ----
+    def quantize(self, t: int, values: np.ndarray) -> np.ndarray:
+        v = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
+        per, stride = GEOMETRY[t]
+        blocks = (v.size + per - 1) // per
+        out = np.empty(blocks * stride, dtype=np.uint8)
+        assert self.lib.rqo_quantize(t, v.ctypes.data, v.size, out.ctypes.data, THREADS) == 0
+        return out
+
+    def dequantize(self, t: int, blocks: np.ndarray) -> np.ndarray:
+        b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        per, stride = GEOMETRY[t]
+        count = b.size // stride * per
+        out = np.empty(count, dtype=np.float32)
+        assert self.lib.rqo_dequantize(t, b.ctypes.data, count, out.ctypes.data, THREADS) == 0
+        return out
+
+    def activation_records(self, x: np.ndarray, step: int) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty((x.size // 32, 36), dtype=np.uint8)
+        assert self.lib.rqo_quantize_activations(x.ctypes.data, 1, x.size, step, out.ctypes.data) == 0
+        return out
+
+    def matvec(self, t: int, blocks: np.ndarray, rows: int, cols: int, x: np.ndarray, mode: int, step: int = 32, threads: int | None = None) -> np.ndarray:
+        """x: [cols] or [tokens, cols] (token-major) -> y [rows] or [tokens, rows]."""
+        b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        single = x.ndim == 1
+        x2 = x[None, :] if single else x
+        tokens = x2.shape[0]
+        y = np.empty((tokens, rows), dtype=np.float32)
+        # token-major planes: element strides x[k*1 + t*cols] -> the oracle takes x + t and a k stride,
+        # so hand it the channel-major transpose
+        xc = np.ascontiguousarray(x2.T)  # [cols][tokens]
+        yc = np.empty((rows, tokens), dtype=np.float32)
+        rc = self.lib.rqo_matvec(t, b.ctypes.data, rows, cols, xc.ctypes.data, tokens, tokens, yc.ctypes.data, tokens, mode, step, threads or THREADS)
+        assert rc == 0, rc
+        y[:] = yc.T
+        return y[0] if single else y
+
+    def topk(self, scores: np.ndarray, top: int, scoring: int = 0, renormalize: bool = True, bias: np.ndarray | None = None) -> np.ndarray:
+        """scores [experts, tokens] -> weights [experts, tokens]."""
+        s = np.ascontiguousarray(scores, dtype=np.float32)
+        experts, tokens = s.shape
+        w = np.empty_like(s)
+        bp = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32).ctypes.data
+        assert self.lib.rqo_topk(s.ctypes.data, experts, tokens, top, scoring, int(renormalize), bp, w.ctypes.data) == 0
+        return w
+
+    def moe_forward(self, t, gate, up, down, experts, top, hidden, ffn, x, routing, shared=None, threads=None) -> np.ndarray:
+        """x [hidden, tokens], routing [experts, tokens]; shared = (gate, up, down, gate_vector) or None."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        routing = np.ascontiguousarray(routing, dtype=np.float32)
+        tokens = x.shape[1]
+        y = np.zeros((hidden, tokens), dtype=np.float32)
+        g, u, d = (np.ascontiguousarray(a, dtype=np.uint8) for a in (gate, up, down))
+        if shared is None:
+            sg = su = sd = sw = None
+            ptrs = (None, None, None, None)
+        else:
+            sg, su, sd = (np.ascontiguousarray(a, dtype=np.uint8) for a in shared[:3])
+            sw = np.ascontiguousarray(shared[3], dtype=np.float32)
+            ptrs = (sg.ctypes.data, su.ctypes.data, sd.ctypes.data, sw.ctypes.data)
+        rc = self.lib.rqo_moe_forward(t, g.ctypes.data, u.ctypes.data, d.ctypes.data, experts, top, hidden, ffn,
+                                      x.ctypes.data, routing.ctypes.data, tokens, *ptrs, y.ctypes.data, threads or THREADS)
+        assert rc == 0, rc
+        return y
+
+    def normal(self, seed: int, stream: int, count: int, sigma: float = 1.0, first: int = 0) -> np.ndarray:
+        out = np.empty(count, dtype=np.float32)
+        self.lib.rqo_normal(seed, stream, first, count, sigma, out.ctypes.data)
+        return out
+
+    def fp16(self, v: float) -> int:
+        return int(self.lib.rqo_fp16(v))
+
+    def unfp16(self, h: int) -> float:
+        return float(self.lib.rqo_unfp16(h))
+
+
+_ORACLE = None
+
+
+def load() -> Oracle:
+    global _ORACLE
+    if _ORACLE is None:
+        _ORACLE = Oracle(C.CDLL(str(build())))
+    return _ORACLE
