@@ -227,23 +227,38 @@ def run_ours(args):
     gen.manual_seed(100 + rank)
     xs = {4096: torch.randn(4096, generator=gen, device=device), 14336: torch.randn(14336, generator=gen, device=device)}
     ys = {name: torch.empty(rows, device=device) for name, _, rows, _, _ in LAYER}
-    stream = torch.cuda.current_stream()
+    # q/k/v read one activation column, gate/up another: one call (and one launch) per group
+    GROUPS = [[0, 1, 2], [3], [4, 5], [6]]
 
     def layer_pass(li):
         ws = layers[li % n_layers]
-        for (name, t, rows, cols, shares), w in zip(LAYER, ws):
-            ctx.matvec(w, xs[cols], ys[name], act_mode=cached if shares else mode, step=step, stream=stream)
+        for g in GROUPS:
+            cols = LAYER[g[0]][3]
+            ctx.matvec_multi([ws[j] for j in g], xs[cols], [ys[LAYER[j][0]] for j in g], act_mode=mode, step=step)
 
-    launches_per_step = len(LAYER) + (sum(1 for p in LAYER if not p[4]) if mode == rq.ACT_INT8 else 0)
+    launches_per_step = len(GROUPS) * (2 if mode == rq.ACT_INT8 else 1)  # activation quantiser + streaming matvec
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # one CUDA graph per layer of the stack: a step is one graph launch, so the host's launch rate
+    # does not bound the 5-20 us kernels
+    for i in range(3):
+        layer_pass(i)  # grows the library's scratch before capture
+    torch.cuda.synchronize()
+    graphs = []
+    for li in range(n_layers):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            layer_pass(li)
+        graphs.append(g)
+    stream = torch.cuda.current_stream()
+
     # ---- device-resident timing: exactly K steps after W warm-up steps -----------------
     for i in range(args.warmup):
-        layer_pass(i)
+        graphs[i % n_layers].replay()
     sampler = ClockSampler(local)
     barrier()
     if rank == 0:
@@ -253,25 +268,29 @@ def run_ours(args):
     barrier()
     e0.record(stream)
     for i in range(args.steps):
-        layer_pass(args.warmup + i)
+        graphs[(args.warmup + i) % n_layers].replay()
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
+    ctx.check()
 
-    # ---- dominant kernel alone: the Q4_K matvec of gate/up (14336 x 4096), one launch per event pair
-    dom = [(li, j) for li in range(n_layers) for j in (4, 5)]
+    # ---- dominant kernel alone: the streaming Q4_K matvec over gate+up (28672 x 4096), launches back to back
     n_dom = max(args.steps, 20)
+    dom_graphs = []
+    for li in range(n_layers):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            ctx.matvec_multi([layers[li][4], layers[li][5]], xs[4096], [ys["gate"], ys["up"]], act_mode=cached, step=step)
+        dom_graphs.append(g)
     if mode == rq.ACT_INT8:
-        ctx.matvec(layers[0][4], xs[4096], ys["gate"], act_mode=mode, step=step, stream=stream)  # leaves the records
+        ctx.matvec(layers[0][4], xs[4096], ys["gate"], act_mode=mode, step=step)  # leaves the records the cached launches read
     for i in range(4):
-        li, j = dom[i % len(dom)]
-        ctx.matvec(layers[li][j], xs[4096], ys["gate"], act_mode=cached, step=step, stream=stream)
+        dom_graphs[i % n_layers].replay()
     torch.cuda.synchronize()
     d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     d0.record(stream)
     for i in range(n_dom):
-        li, j = dom[i % len(dom)]
-        ctx.matvec(layers[li][j], xs[4096], ys["gate"], act_mode=cached, step=step, stream=stream)
+        dom_graphs[i % n_layers].replay()
     d1.record(stream)
     torch.cuda.synchronize()
     dom_us = 1e3 * d0.elapsed_time(d1) / n_dom
@@ -307,7 +326,7 @@ def run_ours(args):
     total_bytes = LAYER_BYTES * args.steps * world
     value = total_bytes / (ms * 1e-3) / 1e9
     peak, peak_kind = measured_peak_gbs()
-    dom_bytes = algo_bytes(Q4_K, 14336, 4096)
+    dom_bytes = 2 * algo_bytes(Q4_K, 14336, 4096) - 4 * 4096  # two row sets, one activation column
     achieved = dom_bytes / (dom_us * 1e-6) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -316,7 +335,7 @@ def run_ours(args):
         "data": "synthetic", "config": workload_config(args, n_layers),
         "us_per_decode_layer": 1e3 * ms / args.steps,
         "frac_of_hbm_measured": value / world / peak, "frac_of_hbm_nominal_8TBs": value / world / 8000.0,
-        "roofline": {"bound": "hbm", "kernel": "rq_gemv_kernel<Q4_K> 14336x4096 (gate/up), one launch", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "rq_gemv_stream_kernel<Q4_K> over gate+up (2 x 14336 x 4096), one launch", "achieved": achieved, "peak": peak,
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": dom_us, "algorithmic_bytes_per_launch": dom_bytes, "traffic": None},
         "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": UNIT,
@@ -376,17 +395,29 @@ def run_case(args):
         ctx.matvec(ws[i % len(ws)], x, y, act_mode=cached, step=32, stream=stream)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(args.steps):
-        ctx.matvec(ws[(args.warmup + i) % len(ws)], x, y, act_mode=cached, step=32, stream=stream)
-    e1.record(stream)
+    if args.graph:
+        # the launches as one CUDA graph, so that the host's launch rate does not bound short kernels
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(args.steps):
+                ctx.matvec(ws[(args.warmup + i) % len(ws)], x, y, act_mode=cached, step=32)
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record(stream)
+        for i in range(args.steps):
+            ctx.matvec(ws[(args.warmup + i) % len(ws)], x, y, act_mode=cached, step=32, stream=stream)
+        e1.record(stream)
     torch.cuda.synchronize()
     us = 1e3 * e0.elapsed_time(e1) / args.steps
     per, stride = {rq.Q4_K: (256, 144), rq.Q6_K: (256, 210), rq.Q8_0: (32, 34), rq.Q4_0: (32, 18)}[t]
     nbytes = rows * (cols // per) * stride + 4 * cols * tokens + 4 * rows * tokens
     peak, kind = measured_peak_gbs()
     print(json.dumps({"case": args.case, "us_per_launch": us, "GBps": nbytes / us / 1e3, "frac_of_hbm": nbytes / us / 1e3 / peak,
-                      "peak": f"{peak} ({kind})", "algorithmic_bytes": nbytes, "launches": args.steps, "weight_copies": args.layers}), flush=True)
+                      "peak": f"{peak} ({kind})", "algorithmic_bytes": nbytes, "launches": args.steps, "weight_copies": args.layers, "graph": bool(args.graph)}), flush=True)
 
 
 def main():
@@ -399,6 +430,7 @@ def main():
     ap.add_argument("--act", default="int8", choices=["int8", "float"])
     ap.add_argument("--layers", type=int, default=8, help="distinct decode layers in rotation (138 MB each)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--graph", action="store_true", help="--case: replay the launches as one CUDA graph")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -52,6 +52,10 @@ enum { RQ_SCORE_SOFTMAX = 0, RQ_SCORE_SIGMOID = 1 };
  * path (recipe.rs:28155, :27843). */
 int rq_init(int device, rq_ctx** out);
 void rq_destroy(rq_ctx* ctx);
+/* Synchronises the device and reports whether any kernel of this context gave up one of its
+ * bounded waits since the last check (the device code never traps and never spins unbounded;
+ * the reference's hand PTX waits return a status the same way, barrier.ptx:1653-1748). */
+int rq_check(rq_ctx* ctx);
 /* Thread-local text of the last failure on the calling thread (RecipeError, recipe.rs:13416-13433). */
 const char* rq_last_error(void);
 /* Block geometry of a type: values per block and bytes per block (QUANTIZATIONS, recipe.rs:15811-15822). 0 if unknown. */
@@ -97,6 +101,13 @@ int rq_quantize(rq_ctx* ctx, int ggml_type, const float* dev_values, int64_t cou
  * Enqueues on `stream` (a cudaStream_t, may be NULL) and returns without synchronising. */
 int rq_matvec(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
               float* y, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);
+
+/* n matrices of one format and width against the SAME activations (q/k/v, gate/up): the column
+ * is quantised once and, where the shape allows, one launch walks all n row sets. ys[i] receives
+ * matrix i's rows with the strides of rq_matvec. The reference runs such sibling nodes inside
+ * one persistent kernel (recipe_model_forward, recipe.rs:8235-8276); this is that grouping. */
+int rq_matvec_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
+                    float* const* ys, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);
 
 /* The same call with HOST buffers: copies x in, runs, copies y out, synchronises. This is the
  * call a host without device buffers makes (Placed::infer, recipe.rs:21314-21490). */

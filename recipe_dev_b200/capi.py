@@ -37,6 +37,7 @@ def _declare(lib) -> None:
         "rq_init": (i32, [i32, C.POINTER(p)]),
         "rq_destroy": (None, [p]),
         "rq_last_error": (C.c_char_p, []),
+        "rq_check": (i32, [p]),
         "rq_block_values": (i32, [i32]),
         "rq_block_bytes": (i32, [i32]),
         "rq_weight_prepare": (i32, [p, i32, p, i64, i64, i64, i64, C.POINTER(p)]),
@@ -50,6 +51,7 @@ def _declare(lib) -> None:
         "rq_dequant": (i32, [p, p, f32p, p]),
         "rq_quantize": (i32, [p, i32, f32p, i64, p, p]),
         "rq_matvec": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
+        "rq_matvec_multi": (i32, [p, i32, p, f32p, i64, i64, i32, p, i64, i64, i32, i32, p]),
         "rq_matvec_host": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32]),
         "rq_quantize_activations": (i32, [p, f32p, i64, i64, i64, i32, i32, p, p]),
     }
@@ -166,6 +168,10 @@ class Context:
         except Exception:
             pass
 
+    def check(self) -> None:
+        """Synchronises and raises if a kernel gave up a bounded wait since the last check."""
+        _check(self.lib.rq_check(self.handle))
+
     # ---- weights ----
     def weight_from_host(self, ggml_type: int, blocks: np.ndarray, rows: int, cols: int, row_first: int = 0, row_count: int | None = None) -> Weight:
         blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
@@ -218,6 +224,18 @@ class Context:
         _check(self.lib.rq_matvec(self.handle, w.handle, _ptr(x2), x2.stride(1), x2.stride(0), tokens,
                                   _ptr(y2), y2.stride(1), y2.stride(0), act_mode, step, _stream(stream)))
         return y2[0] if single else y2
+
+    def matvec_multi(self, ws, x, ys, act_mode: int = ACT_FLOAT, step: int = 32, stream=None):
+        """Several weights of one format and width against the same x; ys[i] is [rows_i] or [tokens, rows_i]."""
+        x2 = x.unsqueeze(0) if x.dim() == 1 else x
+        tokens = x2.shape[0]
+        y2 = [y.unsqueeze(0) if y.dim() == 1 else y for y in ys]
+        n = len(ws)
+        wa = (C.c_void_p * n)(*[w.handle for w in ws])
+        ya = (C.c_void_p * n)(*[y.data_ptr() for y in y2])
+        _check(self.lib.rq_matvec_multi(self.handle, n, wa, _ptr(x2), x2.stride(1), x2.stride(0), tokens,
+                                        ya, y2[0].stride(1), y2[0].stride(0), act_mode, step, _stream(stream)))
+        return ys
 
     def matvec_raw(self, w: Weight, x_ptr: int, sk: int, st: int, tokens: int, y_ptr: int, yn: int, yt: int, act_mode: int, step: int, stream=None) -> int:
         return self.lib.rq_matvec(self.handle, w.handle, x_ptr, sk, st, tokens, y_ptr, yn, yt, act_mode, step, _stream(stream) if stream is not None else 0)

@@ -55,6 +55,11 @@ extern "C" int rq_init(int device, rq_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete ctx; return rq_fail(RQ_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
+    e = cudaMalloc(&ctx->error_flag, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->error_flag, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMallocHost(&ctx->pin_flag, sizeof(int));
+    if (e == cudaSuccess) *ctx->pin_flag = 0;
+    if (e != cudaSuccess) { cudaStreamDestroy(ctx->stream); delete ctx; return rq_fail(RQ_ERR_CUDA, "error flag: %s", cudaGetErrorString(e)); }
     *out = ctx;
     return RQ_OK;
 }
@@ -63,6 +68,8 @@ extern "C" void rq_destroy(rq_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
     if (ctx->act_scratch) cudaFree(ctx->act_scratch);
+    if (ctx->error_flag) cudaFree(ctx->error_flag);
+    if (ctx->pin_flag) cudaFreeHost(ctx->pin_flag);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_y) cudaFree(ctx->stage_y);
     if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
@@ -83,6 +90,19 @@ int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes) {
     cudaError_t e = cudaMalloc(&ctx->act_scratch, want);
     if (e != cudaSuccess) return rq_fail(RQ_ERR_ALLOC, "activation scratch of %zu bytes: %s", want, cudaGetErrorString(e));
     ctx->act_scratch_bytes = want;
+    return RQ_OK;
+}
+
+extern "C" int rq_check(rq_ctx* ctx) {
+    if (!ctx) return rq_fail(RQ_ERR_INVALID, "rq_check: null context");
+    DeviceGuard guard(ctx->device);
+    RQ_CUDA(cudaDeviceSynchronize());
+    int flag = 0;
+    RQ_CUDA(cudaMemcpy(&flag, ctx->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag) {
+        cudaMemset(ctx->error_flag, 0, sizeof(int));
+        return rq_fail(RQ_ERR_CUDA, "a kernel gave up a bounded wait (code %d: 1 producer/empty, 2 drain, 3 consumer/full); its outputs are not valid", flag);
+    }
     return RQ_OK;
 }
 
@@ -221,6 +241,21 @@ extern "C" int rq_matvec(rq_ctx* ctx, const rq_weight* w, const float* x, int64_
     return rq_launch_gemv(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, step, (cudaStream_t)stream);
 }
 
+extern "C" int rq_matvec_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t sk, int64_t st, int tokens,
+                               float* const* ys, int64_t yn, int64_t yt, int act_mode, int step, void* stream) {
+    if (!ctx || !ws || !ys || n < 1) return rq_fail(RQ_ERR_INVALID, "rq_matvec_multi: null argument or no matrices");
+    if (n > 16) return rq_fail(RQ_ERR_LIMIT, "rq_matvec_multi: %d matrices, at most 16", n);
+    for (int i = 0; i < n; ++i) {
+        int rc = check_matvec("rq_matvec_multi", ctx, ws[i], x, ys[i], tokens, act_mode, step);
+        if (rc) return rc;
+        if (ws[i]->type != ws[0]->type || ws[i]->cols != ws[0]->cols)
+            return rq_fail(RQ_ERR_INVALID, "rq_matvec_multi: matrix %d differs from matrix 0 in format or width (they must read one activation column)", i);
+    }
+    if (sk <= 0 || yn <= 0 || (tokens > 1 && (st <= 0 || yt <= 0))) return rq_fail(RQ_ERR_INVALID, "rq_matvec_multi: strides must be positive");
+    DeviceGuard guard(ctx->device);
+    return rq_launch_gemv_multi(ctx, n, ws, x, sk, st, tokens, ys, yn, yt, act_mode, step, (cudaStream_t)stream);
+}
+
 static int ensure_buffer(float** dev, size_t* dev_bytes, float** pin, size_t* pin_bytes, size_t need) {
     if (need > *dev_bytes) {
         if (*dev) cudaFree(*dev);
@@ -255,7 +290,9 @@ extern "C" int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host
     rc = rq_launch_gemv(ctx, w, ctx->stage_x, 1, w->cols, tokens, ctx->stage_y, 1, w->rows, act_mode, step, ctx->stream);
     if (rc) return rc;
     RQ_CUDA(cudaMemcpyAsync(ctx->pin_y, ctx->stage_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    RQ_CUDA(cudaMemcpyAsync(ctx->pin_flag, ctx->error_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     RQ_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (*ctx->pin_flag) return rq_check(ctx);
     for (int t = 0; t < tokens; ++t)
         for (int64_t n = 0; n < w->rows; ++n) host_y[n * yn + t * yt] = ctx->pin_y[(size_t)t * w->rows + n];
     return RQ_OK;

@@ -10,6 +10,8 @@
 //   Q8_0 : 16 codes            Q4_0 : one block (16 low + 16 high nibbles)
 // LPR lanes share a row group and stride over its items; each group carries R rows at once
 // so the activations a lane reads from shared memory serve R rows; T tokens ride along.
+#include <string.h>
+
 #include "rq_internal.cuh"
 
 namespace {
@@ -316,23 +318,37 @@ __global__ void __launch_bounds__(kThreads) rq_act_quant_kernel(const float* __r
     const float inverse = nonzero ? __fdiv_rn(-127.0f, best) : 0.f;
     const float d = nonzero ? __fdiv_rn(1.0f, inverse) : 0.f;
     uint8_t* tok = scratch + (size_t)t * rq_act_token_bytes(cols);
-    int8_t* codes = (int8_t*)tok;
-    float* dplane = (float*)(tok + cols);
-    int16_t* s16 = (int16_t*)(tok + cols + recs * 4);
+    const bool unit_layout = rq_act_unit_layout(cols);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         if (j < n) {
             int code = __float2int_rn(__fmul_rn(v[j], inverse));
             code = code < -128 ? -128 : (code > 127 ? 127 : code);
             const int64_t rec = rec0 + j;
-            codes[rec * 32 + lane] = (int8_t)code;
+            // where this 32-value group keeps its codes, its step and its two slice sums
+            int8_t* codes; float* dp; int16_t* sp;
+            if (unit_layout) {
+                uint8_t* unit = tok + (size_t)(rec >> 3) * RQ_ACT_RECORD_INT8;
+                codes = (int8_t*)unit + 32 * (rec & 7);
+                dp = (float*)(unit + 256) + (rec & 7);
+                sp = (int16_t*)(unit + 288) + 2 * (rec & 7);
+            } else {
+                codes = (int8_t*)tok + rec * 32;
+                dp = (float*)(tok + cols) + rec;
+                sp = (int16_t*)(tok + cols + recs * 4) + rec * 2;
+            }
+            codes[lane] = (int8_t)code;
             int s = code;
             s += __shfl_xor_sync(0xffffffffu, s, 8);
             s += __shfl_xor_sync(0xffffffffu, s, 4);
             s += __shfl_xor_sync(0xffffffffu, s, 2);
             s += __shfl_xor_sync(0xffffffffu, s, 1);
-            if ((lane & 15) == 0) s16[rec * 2 + (lane >> 4)] = (int16_t)s;
-            if (lane == 0) dplane[rec] = d;
+            if ((lane & 15) == 0) sp[lane >> 4] = (int16_t)s;
+            if (lane == 0) *dp = d;
+            if (unit_layout) {
+                const int g = s + __shfl_xor_sync(0xffffffffu, s, 16);  // the whole group's sum
+                if (lane == 0) ((int16_t*)(tok + (size_t)(rec >> 3) * RQ_ACT_RECORD_INT8 + 320))[rec & 7] = (int16_t)g;
+            }
             if (records36) {
                 uint8_t* r36 = records36 + ((size_t)t * recs + rec) * 36;
                 if (lane == 0) *(float*)r36 = d;
@@ -396,6 +412,45 @@ int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, in
     return RQ_OK;
 }
 
+// Several matrices of one format and width against the same activations, as one launch when the
+// streaming kernel serves the shape (one segment per matrix), else one launch per matrix.
+int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t sk, int64_t st, int tokens,
+                         float* const* ys, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s) {
+    const rq_weight* w0 = ws[0];
+    const uint8_t* act = nullptr;
+    int mode = act_mode;
+    if (act_mode == RQ_ACT_INT8) {
+        int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(w0->cols) * (size_t)tokens);
+        if (rc) return rc;
+        rc = rq_launch_act_quant(x, sk, st, w0->cols, tokens, step, ctx->act_scratch, nullptr, s);
+        if (rc) return rc;
+        ctx->act_cols = w0->cols; ctx->act_tokens = tokens; ctx->act_step = step;
+        act = ctx->act_scratch;
+    } else if (act_mode == RQ_ACT_INT8_CACHED) {
+        if (ctx->act_cols != w0->cols || ctx->act_tokens != tokens || ctx->act_step != step)
+            return rq_fail(RQ_ERR_INVALID, "matvec_multi: no cached int8 records of this width, token count and step");
+        act = ctx->act_scratch;
+        mode = RQ_ACT_INT8;
+    }
+    if (n <= RQ_INLINE_SEGMENTS) {
+        RqSegment seg[RQ_INLINE_SEGMENTS];
+        memset(seg, 0, sizeof(seg));
+        int64_t total = 0;
+        for (int i = 0; i < n; ++i) {
+            seg[i].row_begin = (int)total; seg[i].rows = (int)ws[i]->rows; seg[i].y = ys[i];
+            seg[i].main[0] = ws[i]->main; seg[i].scale[0] = ws[i]->scale; seg[i].act[0] = 0; seg[i].coef[0] = 1.0f;
+            total += ws[i]->rows;
+        }
+        int rc = rq_launch_stream(ctx, w0->type, w0->cols, nullptr, seg, n, 1, RQ_EPI_PLAIN, total, x, sk, st, tokens, 0, yn, yt, mode, act, s);
+        if (rc != RQ_ERR_UNSUPPORTED) return rc;
+    }
+    for (int i = 0; i < n; ++i) {
+        int rc = rq_launch_gemv(ctx, ws[i], x, sk, st, tokens, ys[i], yn, yt, mode == RQ_ACT_INT8 ? RQ_ACT_INT8_CACHED : mode, step, s);
+        if (rc) return rc;
+    }
+    return RQ_OK;
+}
+
 int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
                    float* y, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s) {
     GemvParams p;
@@ -416,6 +471,12 @@ int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, 
         p.act = ctx->act_scratch;
         act_mode = RQ_ACT_INT8;
     }
+    {
+        int rc = rq_launch_gemv_stream(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, p.act, s);
+        if (rc != RQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (rq_act_unit_layout(w->cols) && act_mode == RQ_ACT_INT8)
+        return rq_fail(RQ_ERR_LIMIT, "matvec: %lld inputs per row exceed what one CTA's shared memory holds", (long long)w->cols);
     switch (w->type) {
         case RQ_Q4_K: return launch_t<RQ_Q4_K>(p, act_mode, ctx->sm_count, s);
         case RQ_Q6_K: return launch_t<RQ_Q6_K>(p, act_mode, ctx->sm_count, s);

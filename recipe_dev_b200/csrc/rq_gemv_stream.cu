@@ -1,0 +1,720 @@
+// Streaming matrix-vector kernel for sm_100a: the main path for inputs that are whole
+// 256-value units per row (every K-quant tensor; 32-value formats when cols % 256 == 0).
+//
+// One persistent CTA per SM owns a contiguous range of rows. Rows are contiguous in HBM, so
+// the range is one byte stream; a producer warp moves it into a ring of shared-memory stages
+// with bulk asynchronous copies (cp.async.bulk, completion counted on an mbarrier), far
+// enough ahead that HBM stays busy whatever the consumers do. The consumer warps wait on a
+// stage, and each thread takes one ITEM: half of a 256-value unit of one row (four sub-blocks
+// of a Q4_K block with their six-bit scales, one 128-value chunk of a Q6_K body, four Q8_0 /
+// Q4_0 blocks). Items are dealt flat (thread t takes items t, t + threads, ... of the stage),
+// so any row length fills the lanes; an item's partial sum goes to shared memory and one thread
+// per row adds the row's partials in item order: no floating-point atomics, the same bits on
+// every run.
+// The activation column sits in shared memory as one padded record per 256 inputs (int8 codes
+// with their steps and slice sums, or fp32 with slice sums), padded so that threads on
+// adjacent units read different banks; it is staged while the first weight stages are in flight.
+//
+// Every wait on an mbarrier is bounded in time: when the limit runs out a thread records an
+// error code in the context's flag word and stops waiting (it keeps walking its loop, so the
+// CTA's barriers still balance); the CTA drains the copies it issued before it exits. A set
+// flag makes the next rq_check() fail.
+#include <string.h>
+
+#include "rq_internal.cuh"
+
+#ifdef RQ_TRACE
+unsigned long long* rq_trace_buffer();
+#endif
+
+namespace {
+
+constexpr int kMaxStages = 12;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait on an mbarrier gives up after two seconds
+
+// What a launch computes is described by a table of SEGMENTS of virtual output rows. A virtual
+// row is made of `subs` sub-rows, each a row of some stored matrix dotted with one activation
+// vector, and an epilogue joins the sub-row sums:
+//   plain matvec        : 1 segment, 1 sub-row
+//   q/k/v or gate/up    : one segment per matrix (they read the same activations), 1 sub-row
+//   expert gate and up  : one segment per routed slot, 2 sub-rows (gate row, up row), out = silu(g) * u
+//   expert down         : 1 segment, one sub-row per slot (each with its slot's activations and
+//                         routing weight), out = sum_s coef_s * dot_s in slot order
+struct StreamParams {
+    const RqSegment* table;    // device memory, or null: use `inline_seg`
+    RqSegment inline_seg[RQ_INLINE_SEGMENTS];
+    int n_segments, subs, epilogue;
+    int64_t rows;              // virtual rows of all segments
+    int cols, units;           // units = cols / 256 per row
+    int unit_bytes;            // bytes of one unit in the main plane: 144, 208, 256, 128
+    int scales_per_unit;       // fp16 d values per unit in the scale plane: 0, 1, 8, 8
+    int stage_rows, stages;    // virtual rows per stage, ring depth
+    int units_shift;           // log2(units) when that is a power of two, else -1
+    size_t sub_main_bytes, sub_scale_bytes, stage_bytes, act_bytes, partial_bytes;  // shared-memory sizes
+    int act_vectors;           // activation vectors staged in shared memory
+    const float* x; int64_t sk, st;   // FLOAT: vector v is x + v * st, element stride sk
+    const uint8_t* act;        // INT8 activation scratch, one token's records after another
+    int64_t yn, yt;
+    int tokens;
+    int* error_flag;
+#ifdef RQ_TRACE
+    unsigned long long* trace;  // [grid][64] time stamps of the consumer thread 0 (development builds only)
+#endif
+};
+#ifdef RQ_TRACE
+#define RQ_STAMP(i) do { if (tid == 0 && p.trace && (i) < 64) p.trace[(size_t)blockIdx.x * 64 + (i)] = global_ns(); } while (0)
+#else
+#define RQ_STAMP(i) do { } while (0)
+#endif
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false when the time limit ran out (the caller records the error and stops waiting).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    while (!mbar_try_wait(bar, parity))
+        if (global_ns() - t0 > kWaitLimitNs) return false;
+    return true;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes),
+                 "r"(smem_u32(bar))
+                 : "memory");
+}
+template <int THREADS>
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
+__device__ __forceinline__ int dp4a_us(uint32_t a_unsigned, uint32_t b_signed, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_unsigned), "r"(b_signed), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
+
+// Four unsigned bytes of `w` as floats, exactly: 0x4B0000bb is 2^23 + bb.
+__device__ __forceinline__ void bytes_to_float4(uint32_t w, float* f) {
+    f[0] = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650)) - 8388608.0f;
+    f[1] = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7651)) - 8388608.0f;
+    f[2] = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7652)) - 8388608.0f;
+    f[3] = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7653)) - 8388608.0f;
+}
+// sum over 16 unsigned bytes (four words) times 16 floats
+__device__ __forceinline__ float dot16f(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, const float* x) {
+    float f[4], s0 = 0.f, s1 = 0.f;
+    uint32_t w[4] = {w0, w1, w2, w3};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        bytes_to_float4(w[j], f);
+        s0 = fmaf(f[0], x[4 * j + 0], s0);
+        s1 = fmaf(f[1], x[4 * j + 1], s1);
+        s0 = fmaf(f[2], x[4 * j + 2], s0);
+        s1 = fmaf(f[3], x[4 * j + 3], s1);
+    }
+    return s0 + s1;
+}
+__device__ __forceinline__ void load16f(const float* src, float* dst) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) *(float4*)(dst + 4 * j) = *(const float4*)(src + 4 * j);
+}
+
+// Activations of one token in shared memory: one padded record per 256 inputs.
+//   INT8  (336 bytes): codes[256] int8 | d[8] fp32 @256 | sum16[16] int16 @288 | sum32[8] int16 @320
+//          d = the step of each 32-value group, sum16 / sum32 = the sum of the codes of each
+//          16-value slice / 32-value group
+//   FLOAT (1104 bytes): x[256] fp32 | xsum16[16] fp32 @1024 | pad
+// 336 = 84 words and 1104 = 276 words are both 20 mod 32, so the 128-bit loads of eight threads
+// on adjacent units fall in eight different bank groups.
+
+// ------------------------------------------------------------------------------------------
+// One item = half `h` of a 256-value unit, against the activation record `ar` of the unit.
+// `w` = the unit in shared memory, `sc` = its fp16 d values in shared memory (not Q4_K).
+// ------------------------------------------------------------------------------------------
+template <int TYPE, int MODE>
+__device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const uint16_t* __restrict__ sc, const uint8_t* __restrict__ ar, const int h) {
+    const float* xf = (const float*)ar + 128 * h;      // FLOAT: the half's 128 inputs
+    const float* xsum = (const float*)ar + 256 + 8 * h;  // and its eight slice sums
+    if (TYPE == RQ_Q4_K) {
+        const uint4 hdr = *(const uint4*)w;
+        const float d = rq_h2f((uint16_t)(hdr.x & 0xffff)), dmin = rq_h2f((uint16_t)(hdr.x >> 16));
+        // the four six-bit scales and minimums of sub-blocks 4h .. 4h+3, one per byte
+        const uint32_t scw = h == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u));
+        const uint32_t mnw = h == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u));
+        float acc_s = 0.f, acc_m = 0.f;
+        float d8[4];
+        int g32[4];
+        if (MODE == RQ_ACT_INT8) {
+            const float4 dv = *(const float4*)(ar + 256 + 16 * h);
+            d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
+            const uint2 gv = *(const uint2*)(ar + 320 + 8 * h);
+            g32[0] = (int)(int16_t)(gv.x & 0xffff); g32[1] = (int)(int16_t)(gv.x >> 16);
+            g32[2] = (int)(int16_t)(gv.y & 0xffff); g32[3] = (int)(int16_t)(gv.y >> 16);
+        }
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {  // 32 bytes: sub-block 4h+2pp in the low nibbles, 4h+2pp+1 in the high
+            const uint8_t* qp = w + 16 + 64 * h + 32 * pp;
+            const uint4 q0 = *(const uint4*)qp, q1 = *(const uint4*)(qp + 16);
+            const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            const int sc_lo = (scw >> (16 * pp)) & 0xff, sc_hi = (scw >> (16 * pp + 8)) & 0xff;
+            const int mn_lo = (mnw >> (16 * pp)) & 0xff, mn_hi = (mnw >> (16 * pp + 8)) & 0xff;
+            if (MODE == RQ_ACT_INT8) {
+                const uint4* ac = (const uint4*)(ar + 128 * h + 64 * pp);
+                const uint4 a0 = ac[0], a1 = ac[1], a2 = ac[2], a3 = ac[3];
+                const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+                int dl0 = 0, dl1 = 0, dh0 = 0, dh1 = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    dl0 = dp4a_us(qw[j] & 0x0F0F0F0Fu, al[j], dl0);
+                    dl1 = dp4a_us(qw[j + 1] & 0x0F0F0F0Fu, al[j + 1], dl1);
+                    dh0 = dp4a_us(qw[j] & 0xF0F0F0F0u, ah[j], dh0);  // sixteen times the high-nibble dot
+                    dh1 = dp4a_us(qw[j + 1] & 0xF0F0F0F0u, ah[j + 1], dh1);
+                }
+                const int dl = dl0 + dl1, dh = (dh0 + dh1) >> 4;
+                acc_s = fmaf(d8[2 * pp], (float)(sc_lo * dl), acc_s);
+                acc_s = fmaf(d8[2 * pp + 1], (float)(sc_hi * dh), acc_s);
+                acc_m = fmaf(d8[2 * pp], (float)(mn_lo * g32[2 * pp]), acc_m);
+                acc_m = fmaf(d8[2 * pp + 1], (float)(mn_hi * g32[2 * pp + 1]), acc_m);
+            } else {
+                float xl[16], dl, dh;
+                const float* xs = xf + 64 * pp;
+                load16f(xs, xl);
+                dl = dot16f(qw[0] & 0x0F0F0F0Fu, qw[1] & 0x0F0F0F0Fu, qw[2] & 0x0F0F0F0Fu, qw[3] & 0x0F0F0F0Fu, xl);
+                load16f(xs + 16, xl);
+                dl += dot16f(qw[4] & 0x0F0F0F0Fu, qw[5] & 0x0F0F0F0Fu, qw[6] & 0x0F0F0F0Fu, qw[7] & 0x0F0F0F0Fu, xl);
+                load16f(xs + 32, xl);
+                dh = dot16f((qw[0] >> 4) & 0x0F0F0F0Fu, (qw[1] >> 4) & 0x0F0F0F0Fu, (qw[2] >> 4) & 0x0F0F0F0Fu, (qw[3] >> 4) & 0x0F0F0F0Fu, xl);
+                load16f(xs + 48, xl);
+                dh += dot16f((qw[4] >> 4) & 0x0F0F0F0Fu, (qw[5] >> 4) & 0x0F0F0F0Fu, (qw[6] >> 4) & 0x0F0F0F0Fu, (qw[7] >> 4) & 0x0F0F0F0Fu, xl);
+                const float4 xs4 = *(const float4*)(xsum + 4 * pp);
+                acc_s = fmaf((float)sc_lo, dl, acc_s);
+                acc_s = fmaf((float)sc_hi, dh, acc_s);
+                acc_m = fmaf((float)mn_lo, xs4.x + xs4.y, acc_m);
+                acc_m = fmaf((float)mn_hi, xs4.z + xs4.w, acc_m);
+            }
+        }
+        return d * acc_s - dmin * acc_m;
+    } else if (TYPE == RQ_Q6_K) {
+        // half h = the 128-value chunk h: ql lines 64h.., qh lines 128 + 32h.., scales 8h..8h+7
+        const float d = rq_h2f(sc[0]);
+        const uint2 s2 = *(const uint2*)(w + 192 + 8 * h);
+        const uint32_t scales[2] = {s2.x, s2.y};  // eight int8 scales
+        float d8[4];
+        int s16[8];
+        if (MODE == RQ_ACT_INT8) {
+            const float4 dv = *(const float4*)(ar + 256 + 16 * h);
+            d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
+            const uint4 sv = *(const uint4*)(ar + 288 + 16 * h);
+            const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { s16[2 * i] = (int)(int16_t)(sw[i] & 0xffff); s16[2 * i + 1] = (int)(int16_t)(sw[i] >> 16); }
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int wh = 0; wh < 2; ++wh) {  // sixteen-byte half of the 32-byte lines
+            const uint4 qh4 = *(const uint4*)(w + 128 + 32 * h + 16 * wh);
+            const uint32_t qh[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
+#pragma unroll
+            for (int gl = 0; gl < 2; ++gl) {
+                const uint4 ql4 = *(const uint4*)(w + 64 * h + 32 * gl + 16 * wh);
+                const uint32_t ql[4] = {ql4.x, ql4.y, ql4.z, ql4.w};
+                // slices within the chunk: low nibbles -> group gl, high nibbles -> group gl + 2; slice 2 g + wh
+                const int s_lo = 2 * gl + wh, s_hi = s_lo + 4;
+                const int sc_lo = (int)(int8_t)(scales[s_lo >> 2] >> (8 * (s_lo & 3)));
+                const int sc_hi = (int)(int8_t)(scales[s_hi >> 2] >> (8 * (s_hi & 3)));
+                const int k_lo = 32 * gl + 16 * wh, k_hi = k_lo + 64;  // within the chunk
+                if (MODE == RQ_ACT_INT8) {
+                    // The dot is linear in the code's bit fields, so the fields are dotted where they lie
+                    // (nibbles of ql, bit pairs of qh, as unsigned bytes) and the sums scaled afterwards:
+                    // no six-bit code is ever assembled.
+                    const uint4 al = *(const uint4*)(ar + 128 * h + k_lo), ah = *(const uint4*)(ar + 128 * h + k_hi);
+                    const uint32_t alw[4] = {al.x, al.y, al.z, al.w}, ahw[4] = {ah.x, ah.y, ah.z, ah.w};
+                    constexpr uint32_t kPairLo = 0x03030303u, kPairHi = 0x30303030u;
+                    int nl = 0, nh = 0, pl = 0, ph = 0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        nl = dp4a_us(ql[j] & 0x0F0F0F0Fu, alw[j], nl);            // low nibbles
+                        nh = dp4a_us(ql[j] & 0xF0F0F0F0u, ahw[j], nh);            // 16 x high nibbles
+                        pl = dp4a_us(qh[j] & (kPairLo << (2 * gl)), alw[j], pl);  // 4^gl x the pair of group gl
+                        ph = dp4a_us(qh[j] & (kPairHi << (2 * gl)), ahw[j], ph);  // 16 * 4^gl x the pair of group gl + 2
+                    }
+                    // code = nibble + 16 * pair, less the offset of 32 through the slice's sum of activations
+                    const int dl = nl + ((pl >> (2 * gl)) << 4) - 32 * s16[k_lo >> 4];
+                    const int dh = (nh >> 4) + (ph >> (2 * gl)) - 32 * s16[k_hi >> 4];
+                    acc = fmaf(d8[k_lo >> 5], (float)(sc_lo * dl), acc);
+                    acc = fmaf(d8[k_hi >> 5], (float)(sc_hi * dh), acc);
+                } else {
+                    uint32_t lo[4], hi[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        lo[j] = (ql[j] & 0x0F0F0F0Fu) | (((qh[j] >> (2 * gl)) & 0x03030303u) << 4);
+                        hi[j] = ((ql[j] >> 4) & 0x0F0F0F0Fu) | (((qh[j] >> (2 * gl + 4)) & 0x03030303u) << 4);
+                    }
+                    float xv[16];
+                    load16f(xf + k_lo, xv);
+                    float dl = dot16f(lo[0], lo[1], lo[2], lo[3], xv) - 32.0f * xsum[k_lo >> 4];
+                    load16f(xf + k_hi, xv);
+                    float dh = dot16f(hi[0], hi[1], hi[2], hi[3], xv) - 32.0f * xsum[k_hi >> 4];
+                    acc = fmaf((float)sc_lo, dl, acc);
+                    acc = fmaf((float)sc_hi, dh, acc);
+                }
+            }
+        }
+        return d * acc;
+    } else if (TYPE == RQ_Q8_0) {
+        const uint2 dd = *(const uint2*)(sc + 4 * h);  // four fp16 d values
+        const uint32_t dw[2] = {dd.x, dd.y};
+        float d8[4];
+        if (MODE == RQ_ACT_INT8) {
+            const float4 dv = *(const float4*)(ar + 256 + 16 * h);
+            d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
+            const uint8_t* qp = w + 128 * h + 32 * b;
+            const uint4 q0 = *(const uint4*)qp, q1 = *(const uint4*)(qp + 16);
+            if (MODE == RQ_ACT_INT8) {
+                const uint8_t* ap = ar + 128 * h + 32 * b;
+                const uint4 a0 = *(const uint4*)ap, a1 = *(const uint4*)(ap + 16);
+                int dot = dp4a_ss(q0.x, a0.x, 0), dot1 = dp4a_ss(q1.x, a1.x, 0);
+                dot = dp4a_ss(q0.y, a0.y, dot); dot1 = dp4a_ss(q1.y, a1.y, dot1);
+                dot = dp4a_ss(q0.z, a0.z, dot); dot1 = dp4a_ss(q1.z, a1.z, dot1);
+                dot = dp4a_ss(q0.w, a0.w, dot); dot1 = dp4a_ss(q1.w, a1.w, dot1);
+                acc = fmaf(d8[b] * d, (float)(dot + dot1), acc);
+            } else {
+                float xv[16];
+                load16f(xf + 32 * b, xv);
+                // codes biased by 128 to unsigned bytes; the bias leaves through the slice sums of x
+                float dot = dot16f(q0.x ^ 0x80808080u, q0.y ^ 0x80808080u, q0.z ^ 0x80808080u, q0.w ^ 0x80808080u, xv);
+                load16f(xf + 32 * b + 16, xv);
+                dot += dot16f(q1.x ^ 0x80808080u, q1.y ^ 0x80808080u, q1.z ^ 0x80808080u, q1.w ^ 0x80808080u, xv);
+                acc = fmaf(d, dot - 128.0f * (xsum[2 * b] + xsum[2 * b + 1]), acc);
+            }
+        }
+        return acc;
+    } else {  // Q4_0: four blocks of sixteen bytes
+        const uint2 dd = *(const uint2*)(sc + 4 * h);
+        const uint32_t dw[2] = {dd.x, dd.y};
+        float d8[4];
+        int g32[4];
+        if (MODE == RQ_ACT_INT8) {
+            const float4 dv = *(const float4*)(ar + 256 + 16 * h);
+            d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
+            const uint2 gv = *(const uint2*)(ar + 320 + 8 * h);
+            g32[0] = (int)(int16_t)(gv.x & 0xffff); g32[1] = (int)(int16_t)(gv.x >> 16);
+            g32[2] = (int)(int16_t)(gv.y & 0xffff); g32[3] = (int)(int16_t)(gv.y >> 16);
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
+            const uint4 q = *(const uint4*)(w + 64 * h + 16 * b);
+            const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+            if (MODE == RQ_ACT_INT8) {
+                const uint8_t* ap = ar + 128 * h + 32 * b;
+                const uint4 al = *(const uint4*)ap, ah = *(const uint4*)(ap + 16);
+                const uint32_t alw[4] = {al.x, al.y, al.z, al.w}, ahw[4] = {ah.x, ah.y, ah.z, ah.w};
+                int dl = 0, dh = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    dl = dp4a_us(qw[j] & 0x0F0F0F0Fu, alw[j], dl);
+                    dh = dp4a_us(qw[j] & 0xF0F0F0F0u, ahw[j], dh);
+                }
+                const int dot = dl + (dh >> 4) - 8 * g32[b];
+                acc = fmaf(d8[b] * d, (float)dot, acc);
+            } else {
+                float xv[16];
+                load16f(xf + 32 * b, xv);
+                float dot = dot16f(qw[0] & 0x0F0F0F0Fu, qw[1] & 0x0F0F0F0Fu, qw[2] & 0x0F0F0F0Fu, qw[3] & 0x0F0F0F0Fu, xv);
+                load16f(xf + 32 * b + 16, xv);
+                dot += dot16f((qw[0] >> 4) & 0x0F0F0F0Fu, (qw[1] >> 4) & 0x0F0F0F0Fu, (qw[2] >> 4) & 0x0F0F0F0Fu, (qw[3] >> 4) & 0x0F0F0F0Fu, xv);
+                acc = fmaf(d, dot - 8.0f * (xsum[2 * b] + xsum[2 * b + 1]), acc);
+            }
+        }
+        return acc;
+    }
+}
+
+// recipe's portable transcendentals for the expert epilogue (build.rs:1079-1176, math = "portable"):
+// tanh(x) = u / (u + 2), u = expm1(2x), evaluated in double and rounded once; sigmoid and silu as
+// the activation programs spell them (recipe.rs:22662-22668).
+__device__ double rq_exp_wide(double x) {
+    if (x != x) return x;
+    if (x > 709.782712893383973096) return __longlong_as_double(0x7ff0000000000000LL);
+    if (x < -745.133219101941108420) return 0.0;
+    const double kf = floor(x * 1.4426950408889634074 + 0.5);
+    const int k = (int)kf;
+    const double r = (x - kf * __longlong_as_double(0x3FE62E42FEE00000LL)) - kf * 1.90821492927058770002e-10;
+    double factorial = 1.0, coeff[13];
+#pragma unroll
+    for (int t = 1; t <= 13; ++t) { factorial *= (double)t; coeff[t - 1] = 1.0 / factorial; }
+    double cur = coeff[12];
+#pragma unroll
+    for (int t = 11; t >= 0; --t) cur = fma(cur, r, coeff[t]);
+    const double expanded = 1.0 + r * cur;
+    const int half = k >> 1, rest = k - half;
+    auto pow2 = [](int e) { int b = e + 1023; b = b < 0 ? 0 : (b > 2046 ? 2046 : b); return __longlong_as_double((long long)b << 52); };
+    return expanded * pow2(half) * pow2(rest);
+}
+__device__ float rq_tanh_portable(float xf) {
+    const double x = (double)xf;
+    if (x != x) return xf;
+    if (fabs(x) >= 20.0) return x < 0.0 ? -1.0f : 1.0f;
+    const double z = 2.0 * x;
+    double u;
+    if (fabs(z) < 0.35) {
+        double factorial = 1.0, coeff[16];
+#pragma unroll
+        for (int t = 1; t <= 16; ++t) { factorial *= (double)t; coeff[t - 1] = 1.0 / factorial; }
+        double cur = coeff[15];
+#pragma unroll
+        for (int t = 14; t >= 0; --t) cur = fma(cur, z, coeff[t]);
+        u = z * cur;
+    } else {
+        u = rq_exp_wide(z) - 1.0;
+    }
+    return (float)(u / (u + 2.0));
+}
+__device__ __forceinline__ float rq_sigmoid_portable(float x) { return __fmul_rn(0.5f, __fadd_rn(rq_tanh_portable(__fmul_rn(0.5f, x)), 1.0f)); }
+__device__ __forceinline__ float rq_silu_portable(float x) { return __fmul_rn(x, rq_sigmoid_portable(x)); }
+
+template <int TYPE, int MODE, int T, int NW>
+__global__ void __launch_bounds__(NW * 32 + 32, 1) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+    constexpr int kConsumers = NW * 32;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
+    uint8_t* act_smem = smem;                                              // activation vectors x units records
+    float* partial = (float*)(smem + p.act_bytes * p.act_vectors);         // [2][T][stage items]
+    uint8_t* ring = smem + p.act_bytes * p.act_vectors + p.partial_bytes;  // stages
+
+    const int tid = threadIdx.x;
+    // this CTA's virtual rows: an even split, sizes differ by at most one
+    const int64_t row_begin = (p.rows * (int64_t)blockIdx.x) / gridDim.x;
+    const int64_t row_end = (p.rows * (int64_t)(blockIdx.x + 1)) / gridDim.x;
+    const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
+    const int row_scales = p.units * p.scales_per_unit;
+    const int stage_items = 2 * p.subs * p.stage_rows * p.units;
+    // The segment table sits in shared memory for the whole kernel: the producer and the consumers
+    // both index it with run-time values.
+    __shared__ RqSegment table[RQ_MAX_SEGMENTS];
+
+    RQ_STAMP(0);
+    if (tid == 0) {
+        for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NW); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Programmatic dependent launch: the next kernel in the stream may start its own prologue now.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    {
+        // A table in device memory may have been written by the kernel before this one: wait for it.
+        // An inline table came with the launch, and the weights are constants of the model, so the
+        // producer of a plain matvec streams weights while the previous kernel is still running.
+        if (p.table) asm volatile("griddepcontrol.wait;" ::: "memory");
+        const uint32_t* src = (const uint32_t*)(p.table ? p.table : p.inline_seg);
+        uint32_t* dst = (uint32_t*)table;
+        const int words = p.n_segments * (int)(sizeof(RqSegment) / 4);
+        for (int i = tid; i < words; i += blockDim.x) dst[i] = src[i];
+    }
+    __syncthreads();
+
+    const int tok0 = blockIdx.y * T;
+
+    if (tid >= kConsumers) {
+        // ---------------------------------------------------------------- producer warp
+        if (tid == kConsumers) {
+            int issued = 0, seg = 0;
+            int64_t r = row_begin;
+            for (int st = 0; r < row_end; ++st) {
+                while (seg + 1 < p.n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
+                const RqSegment& sg = table[seg];
+                const int slot = st % p.stages;
+                if (st >= p.stages && !mbar_wait(&empty_bar[slot], ((st / p.stages) - 1) & 1)) { atomicExch(p.error_flag, 1); break; }
+                const int64_t seg_end = sg.row_begin + sg.rows;
+                int64_t stop = r + p.stage_rows;
+                if (stop > seg_end) stop = seg_end;
+                if (stop > row_end) stop = row_end;
+                const int nr = (int)(stop - r);
+                const int64_t lr0 = r - sg.row_begin;  // first row, local to the segment
+                uint8_t* dst = ring + (size_t)slot * p.stage_bytes;
+                const uint32_t main_bytes = (uint32_t)(nr * row_bytes);
+                // bytes first, then the copies: the barrier must expect them before any can complete
+                uint32_t total = main_bytes * p.subs;
+                if (TYPE != RQ_Q4_K) {
+                    for (int s = 0; s < p.subs; ++s) {
+                        // the rows' d values, widened to whole 16-byte lines (the plane has slack past its end)
+                        const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
+                        const uintptr_t last = first + (uintptr_t)nr * row_scales * 2;
+                        total += (uint32_t)(((last + 15) & ~(uintptr_t)15) - (first & ~(uintptr_t)15));
+                    }
+                }
+                mbar_expect_tx(&full_bar[slot], total);
+#ifdef RQ_TRACE
+                if (p.trace && st < 16) p.trace[(size_t)blockIdx.x * 64 + 48 + st] = global_ns();
+#endif
+                for (int s = 0; s < p.subs; ++s) {
+                    bulk_g2s(dst + (size_t)s * p.sub_main_bytes, sg.main[s] + lr0 * row_bytes, main_bytes, &full_bar[slot]);
+                    if (TYPE != RQ_Q4_K) {
+                        const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
+                        const uintptr_t last = first + (uintptr_t)nr * row_scales * 2;
+                        const uintptr_t a0 = first & ~(uintptr_t)15, a1 = (last + 15) & ~(uintptr_t)15;
+                        bulk_g2s(dst + (size_t)p.subs * p.sub_main_bytes + (size_t)s * p.sub_scale_bytes, (const void*)a0, (uint32_t)(a1 - a0), &full_bar[slot]);
+                    }
+                }
+                issued = st + 1;
+                r = stop;
+            }
+            // leave only after every copy this CTA issued has landed (bounded)
+            for (int st = (issued > p.stages ? issued - p.stages : 0); st < issued; ++st)
+                if (!mbar_wait(&full_bar[st % p.stages], (st / p.stages) & 1)) { atomicExch(p.error_flag, 2); break; }
+        }
+    } else {
+        // ---------------------------------------------------------------- consumers
+        // Everything below reads what earlier kernels wrote (activations, tables) or writes what
+        // they may still read (y): wait for them. The producer's weight copies are already running.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        // stage the activations while the first weight stages are in flight
+        if (MODE == RQ_ACT_FLOAT) {
+            for (int v = 0; v < p.act_vectors; ++v) {
+                uint8_t* base = act_smem + v * p.act_bytes;
+                const int vec = tok0 + v;  // plain: token; expert banks: slot vector (one token per launch)
+                const bool live = p.act_vectors > T || vec < p.tokens;
+                const float* src = p.x + (int64_t)(live ? vec : tok0) * p.st;
+                for (int k = tid; k < p.cols; k += kConsumers)
+                    ((float*)(base + (size_t)(k >> 8) * kRecord))[k & 255] = live ? __ldg(src + (int64_t)k * p.sk) : 0.0f;
+            }
+            consumer_sync<kConsumers>();
+            for (int v = 0; v < p.act_vectors; ++v) {
+                uint8_t* base = act_smem + v * p.act_bytes;
+                for (int s = tid; s < (p.cols >> 4); s += kConsumers) {
+                    float* rec = (float*)(base + (size_t)(s >> 4) * kRecord);
+                    float acc = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc += rec[16 * (s & 15) + i];
+                    rec[256 + (s & 15)] = acc;
+                }
+            }
+        } else {
+            const size_t src_bytes = (size_t)p.units * kRecord;
+            for (int v = 0; v < p.act_vectors; ++v) {
+                const int vec = tok0 + v;
+                const bool live = p.act_vectors > T || vec < p.tokens;
+                const uint4* src = (const uint4*)(p.act + (size_t)(live ? vec : tok0) * src_bytes);
+                uint4* dst = (uint4*)(act_smem + v * p.act_bytes);
+                for (int i = tid; i < (int)(src_bytes / 16); i += kConsumers) dst[i] = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+            }
+        }
+        consumer_sync<kConsumers>();
+        RQ_STAMP(1);
+
+        const int lane = tid & 31;
+        bool dead = false;  // a wait ran out: no more waiting, the results are flagged invalid
+        int seg = 0;
+        int64_t r = row_begin;
+        for (int st = 0; r < row_end; ++st) {
+            while (seg + 1 < p.n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
+            const RqSegment& sg = table[seg];
+            const int64_t seg_end = sg.row_begin + sg.rows;
+            int64_t stop = r + p.stage_rows;
+            if (stop > seg_end) stop = seg_end;
+            if (stop > row_end) stop = row_end;
+            const int nr = (int)(stop - r);
+            const int64_t lr0 = r - sg.row_begin;
+            const int slot = st % p.stages;
+            if (!dead && !mbar_wait(&full_bar[slot], (st / p.stages) & 1)) { atomicExch(p.error_flag, 3); dead = true; }
+            RQ_STAMP(2 + 3 * st);
+            const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+            float* part = partial + (size_t)(st & 1) * T * stage_items;
+            // items of the stage: first every unit's half 0, then every unit's half 1, so that a warp
+            // works on one half (no divergence) of adjacent units (no bank conflicts)
+            const int sub_units = nr * p.units, n_units = p.subs * sub_units, n_items = 2 * n_units;
+            for (int f = tid; f < n_items; f += kConsumers) {
+                const int h = f >= n_units ? 1 : 0, fu = f - h * n_units;  // half, flat unit of the stage
+                const int s = p.subs == 1 ? 0 : fu / sub_units;           // sub-row
+                const int su = fu - s * sub_units;                        // flat unit within the sub-row chunk
+                const int u = p.units_shift >= 0 ? (su & (p.units - 1)) : su % p.units;  // unit within its row
+                const uint8_t* w = stage + (size_t)s * p.sub_main_bytes + (size_t)su * p.unit_bytes;
+                const uint16_t* sc = nullptr;
+                if (TYPE != RQ_Q4_K) {
+                    // where this sub-row's first d value sits inside its 16-byte-aligned copy
+                    const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
+                    sc = (const uint16_t*)(stage + (size_t)p.subs * p.sub_main_bytes + (size_t)s * p.sub_scale_bytes + (first & 15)) + (size_t)su * p.scales_per_unit;
+                }
+                const uint8_t* a0 = act_smem + (size_t)sg.act[s] * p.act_bytes + (size_t)u * kRecord;
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    const uint8_t* ar = a0 + t * p.act_bytes;
+                    part[t * stage_items + f] = item_dot<TYPE, MODE>(w, sc, ar, h);
+                }
+            }
+            // this warp is done with the stage's weights: the producer may refill the slot
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[slot]);
+            RQ_STAMP(3 + 3 * st);
+            consumer_sync<kConsumers>();
+            RQ_STAMP(4 + 3 * st);
+            // one thread per (row, token) adds the row's partials in sub-row, then item order
+            for (int i = tid; i < nr * T; i += kConsumers) {
+                const int lr = i / T, t = i - lr * T;
+                if (tok0 + t < p.tokens) {
+                    float out = 0.f, gate = 0.f;
+                    for (int s = 0; s < p.subs; ++s) {
+                        const float* lo = part + t * stage_items + s * sub_units + lr * p.units;  // half-0 partials, then half-1
+                        const float* hi = lo + n_units;
+                        float sum = 0.f;
+                        for (int j = 0; j < p.units; ++j) sum += lo[j] + hi[j];
+                        if (p.epilogue == RQ_EPI_GLU) { if (s == 0) gate = sum; else out = rq_silu_portable(gate) * sum; }
+                        else if (p.epilogue == RQ_EPI_WSUM) out += sum * sg.coef[s];
+                        else out = sum;
+                    }
+                    sg.y[(lr0 + lr) * p.yn + (int64_t)(tok0 + t) * p.yt] = out;
+                }
+            }
+            r = stop;
+        }
+    }
+}
+
+template <int TYPE, int MODE, int T, int NW>
+int launch_stream(const StreamParams& p, int grid_x, size_t smem, cudaStream_t s) {
+    auto kernel = rq_gemv_stream_kernel<TYPE, MODE, T, NW>;
+    static bool configured[64] = {};  // per instantiation and device: the opt-in to large dynamic shared memory
+    int dev = 0;
+    RQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        // everything a block may take (227 KB on sm_100), less this kernel's static shared memory
+        cudaFuncAttributes fa;
+        int optin = 0;
+        RQ_CUDA(cudaFuncGetAttributes(&fa, kernel));
+        RQ_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        RQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - (int)fa.sharedSizeBytes));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid_x, (unsigned)((p.tokens + T - 1) / T));
+    cfg.blockDim = dim3(NW * 32 + 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    return RQ_OK;
+}
+
+template <int TYPE, int MODE>
+int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s) {
+    constexpr size_t kSmemBudget = 212 * 1024;  // dynamic; the segment table and barriers are static
+    constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
+    constexpr int NW = MODE == RQ_ACT_INT8 ? 16 : 8;  // consumer warps
+    constexpr int kConsumers = NW * 32;
+    p.act_bytes = ((size_t)p.units * kRecord + 127) & ~(size_t)127;
+    int t = 1;
+    if (vectors_per_launch > 0) {
+        p.act_vectors = vectors_per_launch;  // expert banks: one token, a vector per slot
+    } else {
+        t = (p.tokens >= 2 && 4 * p.act_bytes <= 72 * 1024) ? 4 : 1;
+        p.act_vectors = t;
+    }
+    if (p.act_bytes * p.act_vectors > 110 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
+    const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
+    const int64_t rows_per_cta = (p.rows + sm_count - 1) / sm_count;
+    const int ipr = 2 * p.units * p.subs;  // items per virtual row
+    p.units_shift = (p.units & (p.units - 1)) == 0 ? __builtin_ctz(p.units) : -1;
+    // Stage: whole virtual rows that (nearly) fill one pass of the consumer threads, 48 KB at most.
+    int stage_rows = ipr < kConsumers ? kConsumers / ipr : 1;
+    while (stage_rows > 1 && (int64_t)stage_rows * row_bytes * p.subs > 48 * 1024) --stage_rows;
+    if (stage_rows > rows_per_cta) stage_rows = (int)rows_per_cta;
+    p.stage_rows = stage_rows;
+    p.sub_main_bytes = ((size_t)stage_rows * row_bytes + 127) & ~(size_t)127;
+    p.sub_scale_bytes = p.scales_per_unit ? (((size_t)stage_rows * p.units * p.scales_per_unit * 2 + 32 + 127) & ~(size_t)127) : 0;
+    p.stage_bytes = (p.sub_main_bytes + p.sub_scale_bytes) * p.subs;
+    p.partial_bytes = ((size_t)2 * t * stage_rows * ipr * 4 + 127) & ~(size_t)127;
+    const size_t fixed = p.act_bytes * p.act_vectors + p.partial_bytes;
+    if (fixed + 2 * p.stage_bytes > kSmemBudget) return RQ_ERR_UNSUPPORTED;
+    int stages = (int)((kSmemBudget - fixed) / p.stage_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    p.stages = stages;
+    const size_t smem = fixed + (size_t)stages * p.stage_bytes;
+    const int grid_x = (int)(p.rows < sm_count ? p.rows : sm_count);
+    return t == 4 ? launch_stream<TYPE, MODE, 4, NW>(p, grid_x, smem, s) : launch_stream<TYPE, MODE, 1, NW>(p, grid_x, smem, s);
+}
+
+}  // namespace
+
+#ifdef RQ_TRACE
+// development builds: a device buffer of time stamps, read back with rq_trace_read()
+static unsigned long long* g_trace = nullptr;
+unsigned long long* rq_trace_buffer() {
+    if (!g_trace) { cudaMalloc(&g_trace, 1024 * 64 * 8); cudaMemset(g_trace, 0, 1024 * 64 * 8); }
+    return g_trace;
+}
+extern "C" int rq_trace_read(unsigned long long* host, int ctas) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpy(host, rq_trace_buffer(), (size_t)ctas * 64 * 8, cudaMemcpyDeviceToHost);
+}
+#endif
+
+// Launches the streaming kernel over a segment table. `table` is device memory, or null with the
+// segments in `inline_seg` (at most RQ_INLINE_SEGMENTS, one sub-row each).
+// vectors_per_launch = 0: the activation vectors are the tokens (x + t * st); > 0: one token, that
+// many slot vectors. Returns RQ_ERR_UNSUPPORTED (without error text) when the shape is not served.
+int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table, const RqSegment* inline_seg, int n_segments, int subs,
+                     int epilogue, int64_t total_rows, const float* x, int64_t sk, int64_t st, int tokens, int vectors_per_launch,
+                     int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s) {
+    if (cols % 256 || subs < 1 || subs > RQ_MAX_SUB) return RQ_ERR_UNSUPPORTED;
+    if ((!table && n_segments > RQ_INLINE_SEGMENTS) || n_segments < 1 || n_segments > RQ_MAX_SEGMENTS) return RQ_ERR_UNSUPPORTED;
+    StreamParams p;
+    memset(&p, 0, sizeof(p));
+    p.table = table;
+    if (!table) for (int i = 0; i < n_segments; ++i) p.inline_seg[i] = inline_seg[i];
+    p.n_segments = n_segments; p.subs = subs; p.epilogue = epilogue;
+    p.rows = total_rows; p.cols = (int)cols; p.units = (int)(cols / 256);
+    p.x = x; p.sk = sk; p.st = st; p.act = act; p.yn = yn; p.yt = yt; p.tokens = tokens;
+    p.error_flag = ctx->error_flag;
+#ifdef RQ_TRACE
+    p.trace = rq_trace_buffer();
+#endif
+    switch (type) {
+        case RQ_Q4_K: p.unit_bytes = 144; p.scales_per_unit = 0; break;
+        case RQ_Q6_K: p.unit_bytes = 208; p.scales_per_unit = 1; break;
+        case RQ_Q8_0: p.unit_bytes = 256; p.scales_per_unit = 8; break;
+        case RQ_Q4_0: p.unit_bytes = 128; p.scales_per_unit = 8; break;
+        default: return RQ_ERR_UNSUPPORTED;
+    }
+    const bool f = act_mode == RQ_ACT_FLOAT;
+    const int v = vectors_per_launch, sm = ctx->sm_count;
+    switch (type) {
+        case RQ_Q4_K: return f ? dispatch_stream<RQ_Q4_K, RQ_ACT_FLOAT>(p, sm, v, s) : dispatch_stream<RQ_Q4_K, RQ_ACT_INT8>(p, sm, v, s);
+        case RQ_Q6_K: return f ? dispatch_stream<RQ_Q6_K, RQ_ACT_FLOAT>(p, sm, v, s) : dispatch_stream<RQ_Q6_K, RQ_ACT_INT8>(p, sm, v, s);
+        case RQ_Q8_0: return f ? dispatch_stream<RQ_Q8_0, RQ_ACT_FLOAT>(p, sm, v, s) : dispatch_stream<RQ_Q8_0, RQ_ACT_INT8>(p, sm, v, s);
+        default: return f ? dispatch_stream<RQ_Q4_0, RQ_ACT_FLOAT>(p, sm, v, s) : dispatch_stream<RQ_Q4_0, RQ_ACT_INT8>(p, sm, v, s);
+    }
+}
+
+int rq_launch_gemv_stream(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
+                          float* y, int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s) {
+    RqSegment seg;
+    memset(&seg, 0, sizeof(seg));
+    seg.row_begin = 0; seg.rows = (int)w->rows; seg.y = y;
+    seg.main[0] = w->main; seg.scale[0] = w->scale; seg.act[0] = 0; seg.coef[0] = 1.0f;
+    return rq_launch_stream(ctx, w->type, w->cols, nullptr, &seg, 1, 1, RQ_EPI_PLAIN, w->rows, x, sk, st, tokens, 0, yn, yt, act_mode, act, s);
+}

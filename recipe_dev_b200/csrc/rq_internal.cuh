@@ -36,6 +36,8 @@ struct rq_ctx {
     uint8_t* act_scratch;
     size_t act_scratch_bytes;
     int64_t act_cols; int act_tokens; int act_step;  // what the scratch holds (0 = nothing)
+    int* error_flag;  // device word a kernel sets when a bounded wait ran out
+    int* pin_flag;    // pinned host copy, refreshed by the host-buffer entry points
     // pinned + device staging for the host-buffer entry points
     float* stage_x; float* stage_y; size_t stage_x_bytes, stage_y_bytes;
     float* pin_x; float* pin_y; size_t pin_x_bytes, pin_y_bytes;
@@ -59,10 +61,18 @@ struct DeviceGuard {
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
 };
 
-// Device-side activation scratch, per token (INT8 path): codes then steps then slice sums.
-//   codes [cols] int8 | d [cols/32] fp32 | sum16 [cols/16] int16 (sum of the 16 codes of a slice)
+// Device-side activation scratch, per token (INT8 path).
+// Inputs that are whole 256-value units use one padded record per unit, the layout the streaming
+// kernel keeps in shared memory:
+//   codes[256] int8 | d[8] fp32 @256 | sum16[16] int16 @288 | sum32[8] int16 @320   (336 bytes)
+// Other widths use three planes: codes [cols] int8 | d [cols/32] fp32 | sum16 [cols/16] int16.
+// d = the step of a 32-value group, sum16 = the sum of the 16 codes of a slice.
+#define RQ_ACT_RECORD_INT8 336
+#define RQ_ACT_RECORD_FLOAT 1104
+__host__ __device__ inline bool rq_act_unit_layout(int64_t cols) { return cols % 256 == 0; }
 __host__ __device__ inline size_t rq_act_token_bytes(int64_t cols) {
-    return (size_t)cols + (size_t)(cols / 32) * 4 + (size_t)(cols / 16) * 2;
+    return rq_act_unit_layout(cols) ? (size_t)(cols / 256) * RQ_ACT_RECORD_INT8
+                                    : (size_t)cols + (size_t)(cols / 32) * 4 + (size_t)(cols / 16) * 2;
 }
 
 int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes);
@@ -75,7 +85,28 @@ int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, in
                         uint8_t* scratch, uint8_t* records36, cudaStream_t s);
 int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
                    float* y, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s);
+int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t sk, int64_t st, int tokens,
+                         float* const* ys, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s);
 int rq_launch_quantize(int type, const float* values, int64_t count, uint8_t* blocks, cudaStream_t s);
+// A run of virtual output rows of the streaming kernel (see rq_gemv_stream.cu).
+#define RQ_MAX_SUB 16
+#define RQ_INLINE_SEGMENTS 4
+#define RQ_MAX_SEGMENTS 16
+enum { RQ_EPI_PLAIN = 0, RQ_EPI_WSUM = 1, RQ_EPI_GLU = 2 };
+struct RqSegment {
+    int row_begin, rows;                 // virtual rows [row_begin, row_begin + rows)
+    float* y;                            // y[local_row * yn + token * yt]
+    const uint8_t* main[RQ_MAX_SUB];     // main plane of each sub-row's matrix, at this segment's first row
+    const uint16_t* scale[RQ_MAX_SUB];   // its fp16 d plane there (null for Q4_K)
+    int act[RQ_MAX_SUB];                 // the staged activation vector each sub-row dots
+    float coef[RQ_MAX_SUB];              // RQ_EPI_WSUM: the coefficient of each sub-row
+};
+int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table, const RqSegment* inline_seg, int n_segments, int subs,
+                     int epilogue, int64_t total_rows, const float* x, int64_t sk, int64_t st, int tokens, int vectors_per_launch,
+                     int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s);
+// RQ_ERR_UNSUPPORTED (no error text) = shape not served by the streaming kernel
+int rq_launch_gemv_stream(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
+                          float* y, int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s);
 
 // ---------------------------------------------------------------------------------
 // device helpers

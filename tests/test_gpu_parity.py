@@ -201,3 +201,27 @@ def test_argument_validation(rq_ctx, oracle):
         rq_ctx.quantize(ol.Q4_K, torch_cuda(np.zeros(100, np.float32)))
     # the context still works afterwards
     assert np.all(np.isfinite(rq_ctx.matvec(w, x).cpu().numpy()))
+
+
+@pytest.mark.parametrize("mode,step", [(0, 32), (1, 32), (1, 256)])
+@pytest.mark.parametrize("t,cols", [(ol.Q4_K, 1024), (ol.Q6_K, 768), (ol.Q8_0, 512), (ol.Q4_0, 96)])
+def test_matvec_multi_equals_single(rq_ctx, oracle, t, cols, mode, step):
+    """q/k/v-style siblings in one call give, bit for bit, what one call per matrix gives."""
+    import torch
+
+    row_counts = [70, 19, 33]
+    x = oracle.normal(12, t, 2 * cols, 1.0).reshape(2, cols)
+    xd = torch_cuda(x)
+    ws, singles = [], []
+    for i, rows in enumerate(row_counts):
+        blocks = oracle.quantize(t, oracle.normal(12, 10 * t + i, rows * cols, 0.02))
+        w = rq_ctx.weight_from_host(t, blocks, rows, cols)
+        ws.append(w)
+        singles.append(rq_ctx.matvec(w, xd, act_mode=mode, step=step).cpu().numpy())
+        omode = ol.FLOAT_RUN if mode == 0 else ol.INT8
+        assert rel_err(singles[-1], oracle.matvec(t, blocks, rows, cols, x, omode, step)) <= TOL
+    ys = [torch.zeros((2, rows), dtype=torch.float32, device="cuda") for rows in row_counts]
+    rq_ctx.matvec_multi(ws, xd, ys, act_mode=mode, step=step)
+    for y, ref in zip(ys, singles):
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    rq_ctx.check()
