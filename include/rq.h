@@ -37,10 +37,10 @@ enum { RQ_Q4_0 = 2, RQ_Q8_0 = 8, RQ_Q4_K = 12, RQ_Q6_K = 14 };
  * FLOAT keeps the activations as they are (run decoders, recipe.rs:7826-7917);
  * INT8 rounds them to int8 records with one fp32 step per `step` inputs (amd-nv-cpu.ll:1381-1517). */
 enum { RQ_ACT_FLOAT = 0, RQ_ACT_INT8 = 1,
-       /* INT8 over the records the previous RQ_ACT_INT8 call on this context derived: the caller
-        * states that x is that same column (q/k/v, or gate/up, read one activation). The reference
-        * quantises a node's column once per workgroup (amd-nv-cpu.ll:1381-1517); this is that reuse
-        * across the nodes that share the column. Fails if no records of this width are held. */
+       /* INT8 where the caller states that x is the same column, token count and step as the previous
+        * RQ_ACT_INT8 call on this context (q/k/v, or gate/up, read one activation): the library may
+        * reuse the records it derived then instead of deriving them again. The results are the same
+        * bits either way. Fails if the previous INT8 call was of another width, token count or step. */
        RQ_ACT_INT8_CACHED = 2 };
 
 /* Routing (Scoring, recipe.rs:13955). */

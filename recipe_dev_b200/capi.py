@@ -231,6 +231,8 @@ class Context:
         tokens = x2.shape[0]
         y2 = [y.unsqueeze(0) if y.dim() == 1 else y for y in ys]
         n = len(ws)
+        if any(y.stride(1) != y2[0].stride(1) or (tokens > 1 and y.stride(0) != y2[0].stride(0)) for y in y2):
+            raise ValueError("matvec_multi: every output must have the same strides (e.g. column slices of one [tokens, all rows] plane)")
         wa = (C.c_void_p * n)(*[w.handle for w in ws])
         ya = (C.c_void_p * n)(*[y.data_ptr() for y in y2])
         _check(self.lib.rq_matvec_multi(self.handle, n, wa, _ptr(x2), x2.stride(1), x2.stride(0), tokens,

@@ -12,6 +12,7 @@
 // so the activations a lane reads from shared memory serve R rows; T tokens ride along.
 #include <string.h>
 
+#include "rq_actquant.cuh"
 #include "rq_internal.cuh"
 
 namespace {
@@ -215,7 +216,8 @@ template <int TYPE, int MODE, int LPR, int R, int T>
 __global__ void __launch_bounds__(kThreads) rq_gemv_kernel(GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int64_t cols = p.cols;
-    const size_t tok_bytes = MODE == RQ_ACT_FLOAT ? (size_t)(cols + (cols >> 4)) * 4 : ((rq_act_token_bytes(cols) + 15) & ~(size_t)15);
+    // every token's activations start on a 16-byte boundary: the rows read them with 128-bit loads
+    const size_t tok_bytes = MODE == RQ_ACT_FLOAT ? (((size_t)(cols + (cols >> 4)) * 4 + 15) & ~(size_t)15) : ((rq_act_token_bytes(cols) + 15) & ~(size_t)15);
     const int tok0 = blockIdx.y * T;
 
     // ---- stage the activations of this CTA's tokens -------------------------------------
@@ -287,75 +289,18 @@ __global__ void __launch_bounds__(kThreads) rq_gemv_kernel(GemvParams p) {
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads) rq_act_quant_kernel(const float* __restrict__ x, int64_t sk, int64_t st, int64_t cols, int tokens,
                                                                int step, uint8_t* __restrict__ scratch, uint8_t* __restrict__ records36) {
+    // Programmatic dependent launch: the matvec behind this kernel may start streaming its weights
+    // now; x may come from the kernel before this one, so wait for that one before reading it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int span = step >> 5;                                  // 32-value records per group
+    const int span = step >> 5;
     const int64_t recs = cols >> 5, groups = (recs + span - 1) / span;
     const int64_t g = (int64_t)blockIdx.x * (kThreads / 32) + warp;
     const int t = blockIdx.y;
     if (g >= groups || t >= tokens) return;
-    const float* xt = x + (int64_t)t * st;
-    const int64_t rec0 = g * span;
-    const int n = (int)((rec0 + span <= recs ? span : recs - rec0));
-    float v[8];
-    float best = 0.f;
-    int best_at = 0x7fffffff;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        v[j] = 0.f;
-        if (j < n) {
-            v[j] = __ldg(xt + ((rec0 + j) * 32 + lane) * sk);
-            if (fabsf(v[j]) > fabsf(best)) { best = v[j]; best_at = j * 32 + lane; }
-        }
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        float ob = __shfl_xor_sync(0xffffffffu, best, off);
-        int oa = __shfl_xor_sync(0xffffffffu, best_at, off);
-        bool take = fabsf(ob) > fabsf(best) || (fabsf(ob) == fabsf(best) && oa < best_at);
-        if (take) { best = ob; best_at = oa; }
-    }
-    const bool nonzero = fabsf(best) > 0.f;
-    const float inverse = nonzero ? __fdiv_rn(-127.0f, best) : 0.f;
-    const float d = nonzero ? __fdiv_rn(1.0f, inverse) : 0.f;
-    uint8_t* tok = scratch + (size_t)t * rq_act_token_bytes(cols);
-    const bool unit_layout = rq_act_unit_layout(cols);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        if (j < n) {
-            int code = __float2int_rn(__fmul_rn(v[j], inverse));
-            code = code < -128 ? -128 : (code > 127 ? 127 : code);
-            const int64_t rec = rec0 + j;
-            // where this 32-value group keeps its codes, its step and its two slice sums
-            int8_t* codes; float* dp; int16_t* sp;
-            if (unit_layout) {
-                uint8_t* unit = tok + (size_t)(rec >> 3) * RQ_ACT_RECORD_INT8;
-                codes = (int8_t*)unit + 32 * (rec & 7);
-                dp = (float*)(unit + 256) + (rec & 7);
-                sp = (int16_t*)(unit + 288) + 2 * (rec & 7);
-            } else {
-                codes = (int8_t*)tok + rec * 32;
-                dp = (float*)(tok + cols) + rec;
-                sp = (int16_t*)(tok + cols + recs * 4) + rec * 2;
-            }
-            codes[lane] = (int8_t)code;
-            int s = code;
-            s += __shfl_xor_sync(0xffffffffu, s, 8);
-            s += __shfl_xor_sync(0xffffffffu, s, 4);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            if ((lane & 15) == 0) sp[lane >> 4] = (int16_t)s;
-            if (lane == 0) *dp = d;
-            if (unit_layout) {
-                const int g = s + __shfl_xor_sync(0xffffffffu, s, 16);  // the whole group's sum
-                if (lane == 0) ((int16_t*)(tok + (size_t)(rec >> 3) * RQ_ACT_RECORD_INT8 + 320))[rec & 7] = (int16_t)g;
-            }
-            if (records36) {
-                uint8_t* r36 = records36 + ((size_t)t * recs + rec) * 36;
-                if (lane == 0) *(float*)r36 = d;
-                r36[4 + lane] = (uint8_t)(int8_t)code;
-            }
-        }
-    }
+    rq_quantise_group(x + (int64_t)t * st, sk, cols, step, g, lane, scratch + (size_t)t * rq_act_token_bytes(cols), rq_act_unit_layout(cols),
+                      records36 ? records36 + (size_t)t * recs * 36 : nullptr);
 }
 
 template <int TYPE, int MODE, int LPR, int R, int T>
@@ -382,7 +327,7 @@ template <int TYPE, int MODE>
 int launch_tm(const GemvParams& p, int sm_count, cudaStream_t s) {
     const int items = (int)(p.cols / item_values<TYPE>());
     const int lpr = items % 32 == 0 ? 32 : 8;
-    const size_t tok = MODE == RQ_ACT_FLOAT ? (size_t)(p.cols + (p.cols >> 4)) * 4 : ((rq_act_token_bytes(p.cols) + 15) & ~(size_t)15);
+    const size_t tok = MODE == RQ_ACT_FLOAT ? (((size_t)(p.cols + (p.cols >> 4)) * 4 + 15) & ~(size_t)15) : ((rq_act_token_bytes(p.cols) + 15) & ~(size_t)15);
     const size_t limit = 200 * 1024;
     if (tok > limit) return rq_fail(RQ_ERR_LIMIT, "matvec: %lld inputs per row exceed the %zu bytes of shared memory one token may take", (long long)p.cols, limit);
     const int t = (p.tokens >= 2 && 4 * tok <= limit) ? 4 : 1;
@@ -406,9 +351,36 @@ int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, in
                         uint8_t* scratch, uint8_t* records36, cudaStream_t s) {
     const int span = step / 32;
     const int64_t recs = cols / 32, groups = (recs + span - 1) / span;
-    dim3 grid((unsigned)((groups + kThreads / 32 - 1) / (kThreads / 32)), (unsigned)tokens);
-    rq_act_quant_kernel<<<grid, kThreads, 0, s>>>(x, sk, st, cols, tokens, step, scratch, records36);
-    RQ_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((groups + kThreads / 32 - 1) / (kThreads / 32)), (unsigned)tokens);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_act_quant_kernel, x, sk, st, cols, tokens, step, scratch, records36));
+    return RQ_OK;
+}
+
+// INT8 activations reach a matvec through the context's scratch: RQ_ACT_INT8 runs the quantiser
+// kernel, RQ_ACT_INT8_CACHED reuses what the previous INT8 call left there. The quantiser and the
+// matvec are both launched with programmatic stream serialization: the matvec's producer warp
+// streams weights while the quantiser is still running, and only its consumers wait for it.
+static int int8_records(rq_ctx* ctx, const char* who, const float* x, int64_t sk, int64_t st, int64_t cols, int tokens, int step, int act_mode,
+                        cudaStream_t s) {
+    if (act_mode == RQ_ACT_INT8) {
+        int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols) * (size_t)tokens);
+        if (rc) return rc;
+        rc = rq_launch_act_quant(x, sk, st, cols, tokens, step, ctx->act_scratch, nullptr, s);
+        if (rc) return rc;
+        ctx->act_cols = cols; ctx->act_tokens = tokens; ctx->act_step = step;
+    } else if (act_mode == RQ_ACT_INT8_CACHED) {
+        if (ctx->act_cols != cols || ctx->act_tokens != tokens || ctx->act_step != step)
+            return rq_fail(RQ_ERR_INVALID, "%s: no cached int8 records for %lld inputs x %d tokens at step %d (held: %lld x %d at %d)", who,
+                           (long long)cols, tokens, step, (long long)ctx->act_cols, ctx->act_tokens, ctx->act_step);
+    }
     return RQ_OK;
 }
 
@@ -417,21 +389,9 @@ int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, in
 int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t sk, int64_t st, int tokens,
                          float* const* ys, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s) {
     const rq_weight* w0 = ws[0];
-    const uint8_t* act = nullptr;
-    int mode = act_mode;
-    if (act_mode == RQ_ACT_INT8) {
-        int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(w0->cols) * (size_t)tokens);
-        if (rc) return rc;
-        rc = rq_launch_act_quant(x, sk, st, w0->cols, tokens, step, ctx->act_scratch, nullptr, s);
-        if (rc) return rc;
-        ctx->act_cols = w0->cols; ctx->act_tokens = tokens; ctx->act_step = step;
-        act = ctx->act_scratch;
-    } else if (act_mode == RQ_ACT_INT8_CACHED) {
-        if (ctx->act_cols != w0->cols || ctx->act_tokens != tokens || ctx->act_step != step)
-            return rq_fail(RQ_ERR_INVALID, "matvec_multi: no cached int8 records of this width, token count and step");
-        act = ctx->act_scratch;
-        mode = RQ_ACT_INT8;
-    }
+    const int mode = act_mode == RQ_ACT_FLOAT ? RQ_ACT_FLOAT : RQ_ACT_INT8;
+    int rc = int8_records(ctx, "matvec_multi", x, sk, st, w0->cols, tokens, step, act_mode, s);
+    if (rc) return rc;
     if (n <= RQ_INLINE_SEGMENTS) {
         RqSegment seg[RQ_INLINE_SEGMENTS];
         memset(seg, 0, sizeof(seg));
@@ -441,11 +401,11 @@ int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const f
             seg[i].main[0] = ws[i]->main; seg[i].scale[0] = ws[i]->scale; seg[i].act[0] = 0; seg[i].coef[0] = 1.0f;
             total += ws[i]->rows;
         }
-        int rc = rq_launch_stream(ctx, w0->type, w0->cols, nullptr, seg, n, 1, RQ_EPI_PLAIN, total, x, sk, st, tokens, 0, yn, yt, mode, act, s);
+        rc = rq_launch_stream(ctx, w0->type, w0->cols, nullptr, seg, n, 1, RQ_EPI_PLAIN, total, x, sk, st, tokens, 0, yn, yt, mode, ctx->act_scratch, s);
         if (rc != RQ_ERR_UNSUPPORTED) return rc;
     }
     for (int i = 0; i < n; ++i) {
-        int rc = rq_launch_gemv(ctx, ws[i], x, sk, st, tokens, ys[i], yn, yt, mode == RQ_ACT_INT8 ? RQ_ACT_INT8_CACHED : mode, step, s);
+        rc = rq_launch_gemv(ctx, ws[i], x, sk, st, tokens, ys[i], yn, yt, mode == RQ_ACT_INT8 ? RQ_ACT_INT8_CACHED : mode, step, s);
         if (rc) return rc;
     }
     return RQ_OK;
@@ -453,35 +413,22 @@ int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const f
 
 int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
                    float* y, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s) {
+    const int mode = act_mode == RQ_ACT_FLOAT ? RQ_ACT_FLOAT : RQ_ACT_INT8;
+    int rc = int8_records(ctx, "matvec", x, sk, st, w->cols, tokens, step, act_mode, s);
+    if (rc) return rc;
+    rc = rq_launch_gemv_stream(ctx, w, x, sk, st, tokens, y, yn, yt, mode, ctx->act_scratch, s);
+    if (rc != RQ_ERR_UNSUPPORTED) return rc;
+    if (rq_act_unit_layout(w->cols) && mode == RQ_ACT_INT8)
+        return rq_fail(RQ_ERR_LIMIT, "matvec: %lld inputs per row exceed what one CTA's shared memory holds", (long long)w->cols);
     GemvParams p;
     p.main = w->main; p.scale = w->scale; p.rows = w->rows; p.cols = w->cols;
-    p.x = x; p.sk = sk; p.st = st; p.act = nullptr;
+    p.x = x; p.sk = sk; p.st = st; p.act = mode == RQ_ACT_INT8 ? ctx->act_scratch : nullptr;
     p.y = y; p.yn = yn; p.yt = yt; p.tokens = tokens;
-    if (act_mode == RQ_ACT_INT8) {
-        int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(w->cols) * (size_t)tokens);
-        if (rc) return rc;
-        rc = rq_launch_act_quant(x, sk, st, w->cols, tokens, step, ctx->act_scratch, nullptr, s);
-        if (rc) return rc;
-        ctx->act_cols = w->cols; ctx->act_tokens = tokens; ctx->act_step = step;
-        p.act = ctx->act_scratch;
-    } else if (act_mode == RQ_ACT_INT8_CACHED) {
-        if (ctx->act_cols != w->cols || ctx->act_tokens != tokens || ctx->act_step != step)
-            return rq_fail(RQ_ERR_INVALID, "matvec: no cached int8 records for %lld inputs x %d tokens at step %d (held: %lld x %d at %d)",
-                           (long long)w->cols, tokens, step, (long long)ctx->act_cols, ctx->act_tokens, ctx->act_step);
-        p.act = ctx->act_scratch;
-        act_mode = RQ_ACT_INT8;
-    }
-    {
-        int rc = rq_launch_gemv_stream(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, p.act, s);
-        if (rc != RQ_ERR_UNSUPPORTED) return rc;
-    }
-    if (rq_act_unit_layout(w->cols) && act_mode == RQ_ACT_INT8)
-        return rq_fail(RQ_ERR_LIMIT, "matvec: %lld inputs per row exceed what one CTA's shared memory holds", (long long)w->cols);
     switch (w->type) {
-        case RQ_Q4_K: return launch_t<RQ_Q4_K>(p, act_mode, ctx->sm_count, s);
-        case RQ_Q6_K: return launch_t<RQ_Q6_K>(p, act_mode, ctx->sm_count, s);
-        case RQ_Q8_0: return launch_t<RQ_Q8_0>(p, act_mode, ctx->sm_count, s);
-        case RQ_Q4_0: return launch_t<RQ_Q4_0>(p, act_mode, ctx->sm_count, s);
+        case RQ_Q4_K: return launch_t<RQ_Q4_K>(p, mode, ctx->sm_count, s);
+        case RQ_Q6_K: return launch_t<RQ_Q6_K>(p, mode, ctx->sm_count, s);
+        case RQ_Q8_0: return launch_t<RQ_Q8_0>(p, mode, ctx->sm_count, s);
+        case RQ_Q4_0: return launch_t<RQ_Q4_0>(p, mode, ctx->sm_count, s);
         default: return rq_fail(RQ_ERR_INVALID, "matvec: type %d", w->type);
     }
 }

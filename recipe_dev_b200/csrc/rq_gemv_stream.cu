@@ -52,6 +52,7 @@ struct StreamParams {
     int units_shift;           // log2(units) when that is a power of two, else -1
     size_t sub_main_bytes, sub_scale_bytes, stage_bytes, act_bytes, partial_bytes;  // shared-memory sizes
     int act_vectors;           // activation vectors staged in shared memory
+    int act_regs;              // INT8, one token, every sub-row on vector 0: each thread keeps its activations in registers
     const float* x; int64_t sk, st;   // FLOAT: vector v is x + v * st, element stride sk
     const uint8_t* act;        // INT8 activation scratch, one token's records after another
     int64_t yn, yt;
@@ -139,12 +140,37 @@ __device__ __forceinline__ void load16f(const float* src, float* dst) {
 // 336 = 84 words and 1104 = 276 words are both 20 mod 32, so the 128-bit loads of eight threads
 // on adjacent units fall in eight different bank groups.
 
+// The int8 activations one item needs: the 128 codes of its half record, their four steps, and
+// the sums of its eight slices / four groups. A thread's item always covers the same inputs
+// (its unit and half never change from stage to stage), so a single-token launch loads this
+// once, from global memory, and keeps it in registers for the whole kernel.
+struct ActHalf {
+    uint32_t c[32];
+    float d8[4];
+    uint32_t s16w[4];  // eight int16 slice sums
+    uint32_t g32w[2];  // four int16 group sums
+    __device__ __forceinline__ void load(const uint8_t* rec, int h) {
+        const uint4* cp = (const uint4*)(rec + 128 * h);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const uint4 v = cp[i]; c[4 * i] = v.x; c[4 * i + 1] = v.y; c[4 * i + 2] = v.z; c[4 * i + 3] = v.w; }
+        const float4 dv = *(const float4*)(rec + 256 + 16 * h);
+        d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
+        const uint4 sv = *(const uint4*)(rec + 288 + 16 * h);
+        s16w[0] = sv.x; s16w[1] = sv.y; s16w[2] = sv.z; s16w[3] = sv.w;
+        const uint2 gv = *(const uint2*)(rec + 320 + 8 * h);
+        g32w[0] = gv.x; g32w[1] = gv.y;
+    }
+    __device__ __forceinline__ int s16(int i) const { return (int)(int16_t)(s16w[i >> 1] >> (16 * (i & 1))); }
+    __device__ __forceinline__ int g32(int i) const { return (int)(int16_t)(g32w[i >> 1] >> (16 * (i & 1))); }
+};
+
 // ------------------------------------------------------------------------------------------
-// One item = half `h` of a 256-value unit, against the activation record `ar` of the unit.
+// One item = half `h` of a 256-value unit, against the activation record `ar` of the unit
+// (FLOAT) or the item's int8 activations `ah` (INT8).
 // `w` = the unit in shared memory, `sc` = its fp16 d values in shared memory (not Q4_K).
 // ------------------------------------------------------------------------------------------
 template <int TYPE, int MODE>
-__device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const uint16_t* __restrict__ sc, const uint8_t* __restrict__ ar, const int h) {
+__device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const uint16_t* __restrict__ sc, const uint8_t* __restrict__ ar, const ActHalf& ah8, const int h) {
     const float* xf = (const float*)ar + 128 * h;      // FLOAT: the half's 128 inputs
     const float* xsum = (const float*)ar + 256 + 8 * h;  // and its eight slice sums
     if (TYPE == RQ_Q4_K) {
@@ -154,15 +180,6 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
         const uint32_t scw = h == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u));
         const uint32_t mnw = h == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u));
         float acc_s = 0.f, acc_m = 0.f;
-        float d8[4];
-        int g32[4];
-        if (MODE == RQ_ACT_INT8) {
-            const float4 dv = *(const float4*)(ar + 256 + 16 * h);
-            d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
-            const uint2 gv = *(const uint2*)(ar + 320 + 8 * h);
-            g32[0] = (int)(int16_t)(gv.x & 0xffff); g32[1] = (int)(int16_t)(gv.x >> 16);
-            g32[2] = (int)(int16_t)(gv.y & 0xffff); g32[3] = (int)(int16_t)(gv.y >> 16);
-        }
 #pragma unroll
         for (int pp = 0; pp < 2; ++pp) {  // 32 bytes: sub-block 4h+2pp in the low nibbles, 4h+2pp+1 in the high
             const uint8_t* qp = w + 16 + 64 * h + 32 * pp;
@@ -171,10 +188,8 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
             const int sc_lo = (scw >> (16 * pp)) & 0xff, sc_hi = (scw >> (16 * pp + 8)) & 0xff;
             const int mn_lo = (mnw >> (16 * pp)) & 0xff, mn_hi = (mnw >> (16 * pp + 8)) & 0xff;
             if (MODE == RQ_ACT_INT8) {
-                const uint4* ac = (const uint4*)(ar + 128 * h + 64 * pp);
-                const uint4 a0 = ac[0], a1 = ac[1], a2 = ac[2], a3 = ac[3];
-                const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+                const uint32_t* al = ah8.c + 16 * pp;      // the 32 codes of sub-block 4h+2pp
+                const uint32_t* ah = ah8.c + 16 * pp + 8;  // and of sub-block 4h+2pp+1
                 int dl0 = 0, dl1 = 0, dh0 = 0, dh1 = 0;
 #pragma unroll
                 for (int j = 0; j < 8; j += 2) {
@@ -184,10 +199,10 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
                     dh1 = dp4a_us(qw[j + 1] & 0xF0F0F0F0u, ah[j + 1], dh1);
                 }
                 const int dl = dl0 + dl1, dh = (dh0 + dh1) >> 4;
-                acc_s = fmaf(d8[2 * pp], (float)(sc_lo * dl), acc_s);
-                acc_s = fmaf(d8[2 * pp + 1], (float)(sc_hi * dh), acc_s);
-                acc_m = fmaf(d8[2 * pp], (float)(mn_lo * g32[2 * pp]), acc_m);
-                acc_m = fmaf(d8[2 * pp + 1], (float)(mn_hi * g32[2 * pp + 1]), acc_m);
+                acc_s = fmaf(ah8.d8[2 * pp], (float)(sc_lo * dl), acc_s);
+                acc_s = fmaf(ah8.d8[2 * pp + 1], (float)(sc_hi * dh), acc_s);
+                acc_m = fmaf(ah8.d8[2 * pp], (float)(mn_lo * ah8.g32(2 * pp)), acc_m);
+                acc_m = fmaf(ah8.d8[2 * pp + 1], (float)(mn_hi * ah8.g32(2 * pp + 1)), acc_m);
             } else {
                 float xl[16], dl, dh;
                 const float* xs = xf + 64 * pp;
@@ -212,16 +227,6 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
         const float d = rq_h2f(sc[0]);
         const uint2 s2 = *(const uint2*)(w + 192 + 8 * h);
         const uint32_t scales[2] = {s2.x, s2.y};  // eight int8 scales
-        float d8[4];
-        int s16[8];
-        if (MODE == RQ_ACT_INT8) {
-            const float4 dv = *(const float4*)(ar + 256 + 16 * h);
-            d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
-            const uint4 sv = *(const uint4*)(ar + 288 + 16 * h);
-            const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { s16[2 * i] = (int)(int16_t)(sw[i] & 0xffff); s16[2 * i + 1] = (int)(int16_t)(sw[i] >> 16); }
-        }
         float acc = 0.f;
 #pragma unroll
         for (int wh = 0; wh < 2; ++wh) {  // sixteen-byte half of the 32-byte lines
@@ -240,8 +245,8 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
                     // The dot is linear in the code's bit fields, so the fields are dotted where they lie
                     // (nibbles of ql, bit pairs of qh, as unsigned bytes) and the sums scaled afterwards:
                     // no six-bit code is ever assembled.
-                    const uint4 al = *(const uint4*)(ar + 128 * h + k_lo), ah = *(const uint4*)(ar + 128 * h + k_hi);
-                    const uint32_t alw[4] = {al.x, al.y, al.z, al.w}, ahw[4] = {ah.x, ah.y, ah.z, ah.w};
+                    const uint32_t* alw = ah8.c + (k_lo >> 2);
+                    const uint32_t* ahw = ah8.c + (k_hi >> 2);
                     constexpr uint32_t kPairLo = 0x03030303u, kPairHi = 0x30303030u;
                     int nl = 0, nh = 0, pl = 0, ph = 0;
 #pragma unroll
@@ -252,10 +257,10 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
                         ph = dp4a_us(qh[j] & (kPairHi << (2 * gl)), ahw[j], ph);  // 16 * 4^gl x the pair of group gl + 2
                     }
                     // code = nibble + 16 * pair, less the offset of 32 through the slice's sum of activations
-                    const int dl = nl + ((pl >> (2 * gl)) << 4) - 32 * s16[k_lo >> 4];
-                    const int dh = (nh >> 4) + (ph >> (2 * gl)) - 32 * s16[k_hi >> 4];
-                    acc = fmaf(d8[k_lo >> 5], (float)(sc_lo * dl), acc);
-                    acc = fmaf(d8[k_hi >> 5], (float)(sc_hi * dh), acc);
+                    const int dl = nl + ((pl >> (2 * gl)) << 4) - 32 * ah8.s16(k_lo >> 4);
+                    const int dh = (nh >> 4) + (ph >> (2 * gl)) - 32 * ah8.s16(k_hi >> 4);
+                    acc = fmaf(ah8.d8[k_lo >> 5], (float)(sc_lo * dl), acc);
+                    acc = fmaf(ah8.d8[k_hi >> 5], (float)(sc_hi * dh), acc);
                 } else {
                     uint32_t lo[4], hi[4];
 #pragma unroll
@@ -277,11 +282,6 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
     } else if (TYPE == RQ_Q8_0) {
         const uint2 dd = *(const uint2*)(sc + 4 * h);  // four fp16 d values
         const uint32_t dw[2] = {dd.x, dd.y};
-        float d8[4];
-        if (MODE == RQ_ACT_INT8) {
-            const float4 dv = *(const float4*)(ar + 256 + 16 * h);
-            d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
-        }
         float acc = 0.f;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
@@ -289,13 +289,13 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
             const uint8_t* qp = w + 128 * h + 32 * b;
             const uint4 q0 = *(const uint4*)qp, q1 = *(const uint4*)(qp + 16);
             if (MODE == RQ_ACT_INT8) {
-                const uint8_t* ap = ar + 128 * h + 32 * b;
-                const uint4 a0 = *(const uint4*)ap, a1 = *(const uint4*)(ap + 16);
-                int dot = dp4a_ss(q0.x, a0.x, 0), dot1 = dp4a_ss(q1.x, a1.x, 0);
-                dot = dp4a_ss(q0.y, a0.y, dot); dot1 = dp4a_ss(q1.y, a1.y, dot1);
-                dot = dp4a_ss(q0.z, a0.z, dot); dot1 = dp4a_ss(q1.z, a1.z, dot1);
-                dot = dp4a_ss(q0.w, a0.w, dot); dot1 = dp4a_ss(q1.w, a1.w, dot1);
-                acc = fmaf(d8[b] * d, (float)(dot + dot1), acc);
+                const uint32_t* a0 = ah8.c + 8 * b;
+                const uint32_t* a1 = a0 + 4;
+                int dot = dp4a_ss(q0.x, a0[0], 0), dot1 = dp4a_ss(q1.x, a1[0], 0);
+                dot = dp4a_ss(q0.y, a0[1], dot); dot1 = dp4a_ss(q1.y, a1[1], dot1);
+                dot = dp4a_ss(q0.z, a0[2], dot); dot1 = dp4a_ss(q1.z, a1[2], dot1);
+                dot = dp4a_ss(q0.w, a0[3], dot); dot1 = dp4a_ss(q1.w, a1[3], dot1);
+                acc = fmaf(ah8.d8[b] * d, (float)(dot + dot1), acc);
             } else {
                 float xv[16];
                 load16f(xf + 32 * b, xv);
@@ -310,15 +310,6 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
     } else {  // Q4_0: four blocks of sixteen bytes
         const uint2 dd = *(const uint2*)(sc + 4 * h);
         const uint32_t dw[2] = {dd.x, dd.y};
-        float d8[4];
-        int g32[4];
-        if (MODE == RQ_ACT_INT8) {
-            const float4 dv = *(const float4*)(ar + 256 + 16 * h);
-            d8[0] = dv.x; d8[1] = dv.y; d8[2] = dv.z; d8[3] = dv.w;
-            const uint2 gv = *(const uint2*)(ar + 320 + 8 * h);
-            g32[0] = (int)(int16_t)(gv.x & 0xffff); g32[1] = (int)(int16_t)(gv.x >> 16);
-            g32[2] = (int)(int16_t)(gv.y & 0xffff); g32[3] = (int)(int16_t)(gv.y >> 16);
-        }
         float acc = 0.f;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
@@ -326,17 +317,16 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
             const uint4 q = *(const uint4*)(w + 64 * h + 16 * b);
             const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
             if (MODE == RQ_ACT_INT8) {
-                const uint8_t* ap = ar + 128 * h + 32 * b;
-                const uint4 al = *(const uint4*)ap, ah = *(const uint4*)(ap + 16);
-                const uint32_t alw[4] = {al.x, al.y, al.z, al.w}, ahw[4] = {ah.x, ah.y, ah.z, ah.w};
+                const uint32_t* alw = ah8.c + 8 * b;
+                const uint32_t* ahw = alw + 4;
                 int dl = 0, dh = 0;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     dl = dp4a_us(qw[j] & 0x0F0F0F0Fu, alw[j], dl);
                     dh = dp4a_us(qw[j] & 0xF0F0F0F0u, ahw[j], dh);
                 }
-                const int dot = dl + (dh >> 4) - 8 * g32[b];
-                acc = fmaf(d8[b] * d, (float)dot, acc);
+                const int dot = dl + (dh >> 4) - 8 * ah8.g32(b);
+                acc = fmaf(ah8.d8[b] * d, (float)dot, acc);
             } else {
                 float xv[16];
                 load16f(xf + 32 * b, xv);
@@ -489,8 +479,22 @@ __global__ void __launch_bounds__(NW * 32 + 32, 1) rq_gemv_stream_kernel(const _
         // Everything below reads what earlier kernels wrote (activations, tables) or writes what
         // they may still read (y): wait for them. The producer's weight copies are already running.
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        // stage the activations while the first weight stages are in flight
-        if (MODE == RQ_ACT_FLOAT) {
+        // A thread's item is the same (half, sub-row, row slot, unit) in every stage: thread t takes
+        // item t of the stage's grid [half][sub-row][row][unit]. Halves are outermost so that a warp
+        // works on one half of adjacent units: no divergence, no bank conflicts.
+        const int su_cap = p.stage_rows * p.units;          // units of one sub-row in a full stage
+        const int items_cap = 2 * p.subs * su_cap;
+        const int my_h = tid / (p.subs * su_cap);
+        const int my_rem = tid - my_h * (p.subs * su_cap);
+        const int my_s = my_rem / su_cap, my_su = my_rem - my_s * su_cap;
+        const int my_lr = my_su / p.units, my_u = my_su - my_lr * p.units;
+        ActHalf areg;
+        if (MODE == RQ_ACT_INT8 && p.act_regs) {
+            // single token: this thread's 128 codes, steps and sums, straight from the scratch the
+            // quantiser wrote, kept in registers for the whole kernel
+            if (tid < items_cap) areg.load(p.act + ((size_t)tok0 * p.units + my_u) * kRecord, my_h);
+        } else if (MODE == RQ_ACT_FLOAT) {
+            // stage the activations while the first weight stages are in flight
             for (int v = 0; v < p.act_vectors; ++v) {
                 uint8_t* base = act_smem + v * p.act_bytes;
                 const int vec = tok0 + v;  // plain: token; expert banks: slot vector (one token per launch)
@@ -510,6 +514,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, 1) rq_gemv_stream_kernel(const _
                     rec[256 + (s & 15)] = acc;
                 }
             }
+            consumer_sync<kConsumers>();
         } else {
             const size_t src_bytes = (size_t)p.units * kRecord;
             for (int v = 0; v < p.act_vectors; ++v) {
@@ -519,8 +524,8 @@ __global__ void __launch_bounds__(NW * 32 + 32, 1) rq_gemv_stream_kernel(const _
                 uint4* dst = (uint4*)(act_smem + v * p.act_bytes);
                 for (int i = tid; i < (int)(src_bytes / 16); i += kConsumers) dst[i] = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
             }
+            consumer_sync<kConsumers>();
         }
-        consumer_sync<kConsumers>();
         RQ_STAMP(1);
 
         const int lane = tid & 31;
@@ -541,26 +546,24 @@ __global__ void __launch_bounds__(NW * 32 + 32, 1) rq_gemv_stream_kernel(const _
             RQ_STAMP(2 + 3 * st);
             const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
             float* part = partial + (size_t)(st & 1) * T * stage_items;
-            // items of the stage: first every unit's half 0, then every unit's half 1, so that a warp
-            // works on one half (no divergence) of adjacent units (no bank conflicts)
-            const int sub_units = nr * p.units, n_units = p.subs * sub_units, n_items = 2 * n_units;
-            for (int f = tid; f < n_items; f += kConsumers) {
-                const int h = f >= n_units ? 1 : 0, fu = f - h * n_units;  // half, flat unit of the stage
-                const int s = p.subs == 1 ? 0 : fu / sub_units;           // sub-row
-                const int su = fu - s * sub_units;                        // flat unit within the sub-row chunk
-                const int u = p.units_shift >= 0 ? (su & (p.units - 1)) : su % p.units;  // unit within its row
-                const uint8_t* w = stage + (size_t)s * p.sub_main_bytes + (size_t)su * p.unit_bytes;
+            if (tid < items_cap && my_lr < nr) {
+                const uint8_t* w = stage + (size_t)my_s * p.sub_main_bytes + (size_t)my_su * p.unit_bytes;
                 const uint16_t* sc = nullptr;
                 if (TYPE != RQ_Q4_K) {
                     // where this sub-row's first d value sits inside its 16-byte-aligned copy
-                    const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
-                    sc = (const uint16_t*)(stage + (size_t)p.subs * p.sub_main_bytes + (size_t)s * p.sub_scale_bytes + (first & 15)) + (size_t)su * p.scales_per_unit;
+                    const uintptr_t first = (uintptr_t)sg.scale[my_s] + (uintptr_t)(lr0 * row_scales * 2);
+                    sc = (const uint16_t*)(stage + (size_t)p.subs * p.sub_main_bytes + (size_t)my_s * p.sub_scale_bytes + (first & 15)) + (size_t)my_su * p.scales_per_unit;
                 }
-                const uint8_t* a0 = act_smem + (size_t)sg.act[s] * p.act_bytes + (size_t)u * kRecord;
+                if (MODE == RQ_ACT_INT8 && T == 1 && p.act_regs) {
+                    part[tid] = item_dot<TYPE, MODE>(w, sc, nullptr, areg, my_h);
+                } else {
+                    const uint8_t* a0 = act_smem + (size_t)sg.act[my_s] * p.act_bytes + (size_t)my_u * kRecord;
 #pragma unroll
-                for (int t = 0; t < T; ++t) {
-                    const uint8_t* ar = a0 + t * p.act_bytes;
-                    part[t * stage_items + f] = item_dot<TYPE, MODE>(w, sc, ar, h);
+                    for (int t = 0; t < T; ++t) {
+                        const uint8_t* ar = a0 + t * p.act_bytes;
+                        if (MODE == RQ_ACT_INT8) areg.load(ar, my_h);
+                        part[t * stage_items + tid] = item_dot<TYPE, MODE>(w, sc, ar, areg, my_h);
+                    }
                 }
             }
             // this warp is done with the stage's weights: the producer may refill the slot
@@ -575,8 +578,8 @@ __global__ void __launch_bounds__(NW * 32 + 32, 1) rq_gemv_stream_kernel(const _
                 if (tok0 + t < p.tokens) {
                     float out = 0.f, gate = 0.f;
                     for (int s = 0; s < p.subs; ++s) {
-                        const float* lo = part + t * stage_items + s * sub_units + lr * p.units;  // half-0 partials, then half-1
-                        const float* hi = lo + n_units;
+                        const float* lo = part + t * stage_items + s * su_cap + lr * p.units;  // the row's half-0 partials
+                        const float* hi = lo + p.subs * su_cap;                                // and its half-1 partials
                         float sum = 0.f;
                         for (int j = 0; j < p.units; ++j) sum += lo[j] + hi[j];
                         if (p.epilogue == RQ_EPI_GLU) { if (s == 0) gate = sum; else out = rq_silu_portable(gate) * sum; }
@@ -634,13 +637,17 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
         t = (p.tokens >= 2 && 4 * p.act_bytes <= 72 * 1024) ? 4 : 1;
         p.act_vectors = t;
     }
+    // single-token INT8 launches whose sub-rows all read vector 0 keep the activations in registers
+    p.act_regs = (MODE == RQ_ACT_INT8 && t == 1 && vectors_per_launch == 0 && p.table == nullptr) ? 1 : 0;
+    if (p.act_regs) p.act_vectors = 0;  // nothing staged: the threads read the scratch directly
     if (p.act_bytes * p.act_vectors > 110 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
     const int64_t rows_per_cta = (p.rows + sm_count - 1) / sm_count;
     const int ipr = 2 * p.units * p.subs;  // items per virtual row
     p.units_shift = (p.units & (p.units - 1)) == 0 ? __builtin_ctz(p.units) : -1;
     // Stage: whole virtual rows that (nearly) fill one pass of the consumer threads, 48 KB at most.
-    int stage_rows = ipr < kConsumers ? kConsumers / ipr : 1;
+    if (ipr > kConsumers) return RQ_ERR_UNSUPPORTED;  // a row must fit one pass of the consumer threads
+    int stage_rows = kConsumers / ipr;
     while (stage_rows > 1 && (int64_t)stage_rows * row_bytes * p.subs > 48 * 1024) --stage_rows;
     if (stage_rows > rows_per_cta) stage_rows = (int)rows_per_cta;
     p.stage_rows = stage_rows;

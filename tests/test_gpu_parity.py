@@ -220,7 +220,12 @@ def test_matvec_multi_equals_single(rq_ctx, oracle, t, cols, mode, step):
         singles.append(rq_ctx.matvec(w, xd, act_mode=mode, step=step).cpu().numpy())
         omode = ol.FLOAT_RUN if mode == 0 else ol.INT8
         assert rel_err(singles[-1], oracle.matvec(t, blocks, rows, cols, x, omode, step)) <= TOL
-    ys = [torch.zeros((2, rows), dtype=torch.float32, device="cuda") for rows in row_counts]
+    # the siblings' outputs side by side in one [tokens, all rows] plane: one token stride for all
+    plane = torch.zeros((2, sum(row_counts)), dtype=torch.float32, device="cuda")
+    ys, at = [], 0
+    for rows in row_counts:
+        ys.append(plane[:, at:at + rows])
+        at += rows
     rq_ctx.matvec_multi(ws, xd, ys, act_mode=mode, step=step)
     for y, ref in zip(ys, singles):
         assert np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
