@@ -384,7 +384,7 @@ __device__ __forceinline__ float rq_sigmoid_portable(float x) { return __fmul_rn
 __device__ __forceinline__ float rq_silu_portable(float x) { return __fmul_rn(x, rq_sigmoid_portable(x)); }
 
 template <int TYPE, int MODE, int T, int NW>
-__global__ void __launch_bounds__(NW * 32 + 32, 1) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+__global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int kConsumers = NW * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
@@ -625,30 +625,35 @@ int launch_stream(const StreamParams& p, int grid_x, size_t smem, cudaStream_t s
 
 template <int TYPE, int MODE>
 int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s) {
-    constexpr size_t kSmemBudget = 212 * 1024;  // dynamic; the segment table and barriers are static
+    // Two CTAs share an SM (eight consumer warps and about 100 KB each): their barriers and waits
+    // interleave, and when a CTA of one launch exits, a CTA of the next launch (programmatic
+    // dependent launch) takes its place and prefetches weights while the other is still working.
+    constexpr int kCtasPerSm = 2;
+    constexpr size_t kSmemBudget = 104 * 1024;  // dynamic; the segment table and barriers are static
     constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
-    constexpr int NW = MODE == RQ_ACT_INT8 ? 16 : 8;  // consumer warps
+    constexpr int NW = 8;  // consumer warps
     constexpr int kConsumers = NW * 32;
     p.act_bytes = ((size_t)p.units * kRecord + 127) & ~(size_t)127;
     int t = 1;
     if (vectors_per_launch > 0) {
         p.act_vectors = vectors_per_launch;  // expert banks: one token, a vector per slot
     } else {
-        t = (p.tokens >= 2 && 4 * p.act_bytes <= 72 * 1024) ? 4 : 1;
+        t = (p.tokens >= 2 && 4 * p.act_bytes <= 40 * 1024) ? 4 : 1;
         p.act_vectors = t;
     }
     // single-token INT8 launches whose sub-rows all read vector 0 keep the activations in registers
     p.act_regs = (MODE == RQ_ACT_INT8 && t == 1 && vectors_per_launch == 0 && p.table == nullptr) ? 1 : 0;
     if (p.act_regs) p.act_vectors = 0;  // nothing staged: the threads read the scratch directly
-    if (p.act_bytes * p.act_vectors > 110 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
+    if (p.act_bytes * p.act_vectors > 64 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
-    const int64_t rows_per_cta = (p.rows + sm_count - 1) / sm_count;
+    const int ctas = sm_count * kCtasPerSm;
+    const int64_t rows_per_cta = (p.rows + ctas - 1) / ctas;
     const int ipr = 2 * p.units * p.subs;  // items per virtual row
     p.units_shift = (p.units & (p.units - 1)) == 0 ? __builtin_ctz(p.units) : -1;
     // Stage: whole virtual rows that (nearly) fill one pass of the consumer threads, 48 KB at most.
     if (ipr > kConsumers) return RQ_ERR_UNSUPPORTED;  // a row must fit one pass of the consumer threads
     int stage_rows = kConsumers / ipr;
-    while (stage_rows > 1 && (int64_t)stage_rows * row_bytes * p.subs > 48 * 1024) --stage_rows;
+    while (stage_rows > 1 && (int64_t)stage_rows * row_bytes * p.subs > 32 * 1024) --stage_rows;
     if (stage_rows > rows_per_cta) stage_rows = (int)rows_per_cta;
     p.stage_rows = stage_rows;
     p.sub_main_bytes = ((size_t)stage_rows * row_bytes + 127) & ~(size_t)127;
@@ -661,7 +666,7 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
     if (stages > kMaxStages) stages = kMaxStages;
     p.stages = stages;
     const size_t smem = fixed + (size_t)stages * p.stage_bytes;
-    const int grid_x = (int)(p.rows < sm_count ? p.rows : sm_count);
+    const int grid_x = (int)(p.rows < ctas ? p.rows : ctas);
     return t == 4 ? launch_stream<TYPE, MODE, 4, NW>(p, grid_x, smem, s) : launch_stream<TYPE, MODE, 1, NW>(p, grid_x, smem, s);
 }
 
