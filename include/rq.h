@@ -114,6 +114,22 @@ int rq_matvec_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float*
 int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host_x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
                    float* host_y, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step);
 
+/* The INT8 product of one contiguous column (x[cols] -> y[rows]) for callers that cannot allocate.
+ * No counterpart in the reference: there the host owns every arena and kernels never allocate, so
+ * the question does not arise; here rq_matvec grows a scratch buffer with cudaMalloc on demand.
+ * This entry point calls no allocating routine at all. Its activation scratch is a fixed array in
+ * the library's device image, held by every GPU that loads the library until the process exits.
+ * Who needs it: a host that has given all device memory to its own pre-planned arenas, and a decode
+ * loop that must never stall on the device-wide synchronisation an allocation or free brings.
+ *  - at most RQ_STATIC_MAX_COLS inputs per row; wider weights are refused with RQ_ERR_LIMIT;
+ *  - the first call on a device looks up the array's device address; make that first call before
+ *    any stream capture begins;
+ *  - all calls on a device share the array: calls that overlap on the GPU race (one stream is safe);
+ *    nothing in it needs clearing between calls, every byte that is read is written first.
+ * Same results as rq_matvec(..., RQ_ACT_INT8, step, ...) with tokens = 1 and unit strides. */
+#define RQ_STATIC_MAX_COLS 32768
+int rq_matvec_int8_static(rq_ctx* ctx, const rq_weight* w, const float* x, float* y, int step, void* stream);
+
 /* Writes the int8 activation records the INT8 path derives from x (36 bytes per 32 inputs:
  * fp32 step, 32 codes; build.rs:332-337) for `tokens` columns into dev_records
  * ([tokens][cols/32][36]). Exposes amd-nv-cpu.ll:1381-1517 for bit-exact checks. */

@@ -54,6 +54,7 @@ def _declare(lib) -> None:
         "rq_matvec_multi": (i32, [p, i32, p, f32p, i64, i64, i32, p, i64, i64, i32, i32, p]),
         "rq_matvec_host": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32]),
         "rq_quantize_activations": (i32, [p, f32p, i64, i64, i64, i32, i32, p, p]),
+        "rq_matvec_int8_static": (i32, [p, p, f32p, f32p, i32, p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -66,7 +67,6 @@ def _declare(lib) -> None:
         "rq_moe_free": (None, [p, p]),
         "rq_moe_forward": (i32, [p, p, f32p, f32p, i32, f32p, i32, p]),
         "rq_matmul": (i32, [p, p, f32p, i32, f32p, i32, i32, p]),
-        "rq_matvec_static": (i32, [p, p, f32p, i32, f32p, i32, p]),
     }
     for name, (res, args) in optional.items():
         if hasattr(lib, name):
@@ -251,6 +251,17 @@ class Context:
         y = np.empty((tokens, w.rows), dtype=np.float32)
         _check(self.lib.rq_matvec_host(self.handle, w.handle, x2.ctypes.data, 1, x2.shape[1], tokens, y.ctypes.data, 1, w.rows, act_mode, step))
         return y[0] if single else y
+
+    def matvec_int8_static(self, w: Weight, x, y=None, step: int = 32, stream=None):
+        """The INT8 product of one contiguous column through the entry point that allocates nothing
+        (its scratch is a fixed array in the library; at most 32768 inputs per row)."""
+        import torch
+
+        assert x.dim() == 1 and x.is_contiguous()
+        if y is None:
+            y = torch.empty(w.rows, dtype=torch.float32, device=x.device)
+        _check(self.lib.rq_matvec_int8_static(self.handle, w.handle, _ptr(x), _ptr(y), step, _stream(stream)))
+        return y
 
     def activation_records(self, x, step: int, stream=None):
         """The 36-byte int8 records of x ([cols] or [tokens, cols]) as a uint8 CUDA tensor."""

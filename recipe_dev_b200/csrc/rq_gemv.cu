@@ -432,3 +432,20 @@ int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, 
         default: return rq_fail(RQ_ERR_INVALID, "matvec: type %d", w->type);
     }
 }
+
+// The tiled kernel over int8 records the caller already holds at `act` (plane layout).
+int rq_launch_gemv_tiled_int8(rq_ctx* ctx, const rq_weight* w, int tokens, float* y, int64_t yn, int64_t yt, const uint8_t* act, cudaStream_t s) {
+    if (rq_act_unit_layout(w->cols))
+        return rq_fail(RQ_ERR_LIMIT, "matvec: %lld inputs per row exceed what one CTA's shared memory holds", (long long)w->cols);
+    GemvParams p;
+    p.main = w->main; p.scale = w->scale; p.rows = w->rows; p.cols = w->cols;
+    p.x = nullptr; p.sk = 1; p.st = w->cols; p.act = act;
+    p.y = y; p.yn = yn; p.yt = yt; p.tokens = tokens;
+    switch (w->type) {
+        case RQ_Q4_K: return launch_t<RQ_Q4_K>(p, RQ_ACT_INT8, ctx->sm_count, s);
+        case RQ_Q6_K: return launch_t<RQ_Q6_K>(p, RQ_ACT_INT8, ctx->sm_count, s);
+        case RQ_Q8_0: return launch_t<RQ_Q8_0>(p, RQ_ACT_INT8, ctx->sm_count, s);
+        case RQ_Q4_0: return launch_t<RQ_Q4_0>(p, RQ_ACT_INT8, ctx->sm_count, s);
+        default: return rq_fail(RQ_ERR_INVALID, "matvec: type %d", w->type);
+    }
+}
