@@ -136,6 +136,41 @@ int rq_matvec_int8_static(rq_ctx* ctx, const rq_weight* w, const float* x, float
 int rq_quantize_activations(rq_ctx* ctx, const float* x, int64_t x_k_stride, int64_t x_t_stride, int64_t cols, int tokens,
                             int step, void* dev_records, void* stream);
 
+/* ---- gguf_moe: routing and expert banks ------------------------------------------------ */
+
+typedef struct rq_moe rq_moe; /* the expert tables of one gguf_moe block resident in HBM (MoeTensors / SharedTensors, recipe.rs:14382-14420) */
+
+/* Routing weights of `tokens` positions from their router scores: softmax or sigmoid scoring, the
+ * top_k experts by score (ties to the lower index; with a selection bias, by probability + bias),
+ * renormalised over the kept experts or not. Writes the dense plane the expert bodies read:
+ * weights[e * weight_e_stride + t * weight_t_stride], zero for experts not taken.
+ * Replaces topk_forward_body (amd-nv-cpu.ll:4666-4716), same bits (its exp is build.rs:1079-1120). */
+int rq_moe_route(rq_ctx* ctx, const float* scores, int64_t score_e_stride, int64_t score_t_stride, int experts, int top_k, int scoring,
+                 int renormalize, const float* selection_bias, int tokens, float* weights, int64_t weight_e_stride, int64_t weight_t_stride,
+                 void* stream);
+
+/* Uploads experts [expert_first, expert_first + expert_count) of the three expert tables (host GGUF
+ * blocks: gate and up are [experts][ffn][hidden], down is [experts][hidden][ffn]) and, optionally, a
+ * gated shared expert (one expert of the same shape and its [hidden] fp32 gate vector; all four
+ * null for none). The expert range is this GPU's share of an expert-parallel split; the reference
+ * instead slices every expert's rows across dies (recipe.rs:4764-4766, :21015-21016). */
+int rq_moe_prepare(rq_ctx* ctx, int ggml_type, const void* gate, const void* up, const void* down, int experts, int expert_first,
+                   int expert_count, int hidden, int ffn, const void* shared_gate, const void* shared_up, const void* shared_down,
+                   const float* shared_gate_vector, rq_moe** out);
+void rq_moe_free(rq_ctx* ctx, rq_moe* moe);
+int64_t rq_moe_bytes(const rq_moe* moe);
+
+/* y[n * y_n_stride + t * y_t_stride] = sum over the experts of this bank that token t routes to of
+ * w_e * down_e( silu(gate_e x) * up_e x ), plus (include_shared != 0) the shared expert at weight
+ * sigmoid(gate_vector . x). Activations stay fp32 (expert tables are never int sums in the
+ * reference, recipe.rs:24284-24294). Tokens nothing here is routed to get zeros, so the outputs of
+ * the ranks of an expert-parallel split add up to the block's output.
+ * Replaces lower_experts over the packed bodies, modes 1 and 2 (recipe.rs:23386-23459,
+ * amd-nv-cpu.ll:2304-2365, :3136-3508). At most 64 tokens per call, top_k <= 15. */
+int rq_moe_forward(rq_ctx* ctx, rq_moe* moe, const float* x, int64_t x_k_stride, int64_t x_t_stride, const float* routing,
+                   int64_t routing_e_stride, int64_t routing_t_stride, int top_k, int tokens, int include_shared, float* y,
+                   int64_t y_n_stride, int64_t y_t_stride, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

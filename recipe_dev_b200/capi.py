@@ -62,10 +62,11 @@ def _declare(lib) -> None:
         fn.argtypes = args
     # optional groups (declared when the library exports them)
     optional = {
-        "rq_moe_route": (i32, [p, f32p, i32, i32, i32, i32, f32p, i32, f32p, p]),
-        "rq_moe_prepare": (i32, [p, p, p, p, i32, i32, i32, i32, C.POINTER(p)]),
+        "rq_moe_route": (i32, [p, f32p, i64, i64, i32, i32, i32, i32, f32p, i32, f32p, i64, i64, p]),
+        "rq_moe_prepare": (i32, [p, i32, p, p, p, i32, i32, i32, i32, i32, p, p, p, f32p, C.POINTER(p)]),
         "rq_moe_free": (None, [p, p]),
-        "rq_moe_forward": (i32, [p, p, f32p, f32p, i32, f32p, i32, p]),
+        "rq_moe_bytes": (i64, [p]),
+        "rq_moe_forward": (i32, [p, p, f32p, i64, i64, f32p, i64, i64, i32, i32, i32, f32p, i64, i64, p]),
         "rq_matmul": (i32, [p, p, f32p, i32, f32p, i32, i32, p]),
     }
     for name, (res, args) in optional.items():
@@ -138,6 +139,28 @@ class Weight:
     def free(self) -> None:
         if self.handle:
             self.ctx.lib.rq_weight_free(self.ctx.handle, self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class MoeBank:
+    """The expert tables of one gguf_moe block resident in HBM (rq_moe)."""
+
+    def __init__(self, ctx: "Context", handle: int, hidden: int, ffn: int):
+        self.ctx, self.handle, self.hidden, self.ffn = ctx, handle, hidden, ffn
+
+    @property
+    def nbytes(self) -> int:
+        return self.ctx.lib.rq_moe_bytes(self.handle)
+
+    def free(self) -> None:
+        if self.handle:
+            self.ctx.lib.rq_moe_free(self.ctx.handle, self.handle)
             self.handle = 0
 
     def __del__(self):
@@ -261,6 +284,45 @@ class Context:
         if y is None:
             y = torch.empty(w.rows, dtype=torch.float32, device=x.device)
         _check(self.lib.rq_matvec_int8_static(self.handle, w.handle, _ptr(x), _ptr(y), step, _stream(stream)))
+        return y
+
+    # ---- gguf_moe ----
+    def moe_route(self, scores, top_k: int, scoring: int = SCORE_SOFTMAX, renormalize: bool = True, bias=None, stream=None):
+        """scores: CUDA fp32 [experts, tokens] (the reference's channel-major plane) -> weights of the same shape."""
+        import torch
+
+        experts, tokens = scores.shape
+        weights = torch.empty_like(scores)
+        _check(self.lib.rq_moe_route(self.handle, _ptr(scores), scores.stride(0), scores.stride(1), experts, top_k, scoring, int(renormalize),
+                                     _ptr(bias), tokens, _ptr(weights), weights.stride(0), weights.stride(1), _stream(stream)))
+        return weights
+
+    def moe_prepare(self, ggml_type: int, gate, up, down, experts: int, hidden: int, ffn: int, expert_first: int = 0, expert_count: int | None = None,
+                    shared=None) -> "MoeBank":
+        """gate/up/down: host uint8 GGUF blocks of the whole bank; shared = (gate, up, down, gate_vector) or None."""
+        expert_count = experts - expert_first if expert_count is None else expert_count
+        g, u, d = (np.ascontiguousarray(a, dtype=np.uint8) for a in (gate, up, down))
+        keep = [g, u, d]
+        sp = [None, None, None, None]
+        if shared is not None:
+            sg, su, sd = (np.ascontiguousarray(a, dtype=np.uint8) for a in shared[:3])
+            sv = np.ascontiguousarray(shared[3], dtype=np.float32)
+            keep += [sg, su, sd, sv]
+            sp = [sg.ctypes.data, su.ctypes.data, sd.ctypes.data, sv.ctypes.data]
+        out = C.c_void_p()
+        _check(self.lib.rq_moe_prepare(self.handle, ggml_type, g.ctypes.data, u.ctypes.data, d.ctypes.data, experts, expert_first, expert_count,
+                                       hidden, ffn, sp[0], sp[1], sp[2], sp[3], C.byref(out)))
+        return MoeBank(self, out.value, hidden, ffn)
+
+    def moe_forward(self, bank: "MoeBank", x, routing, top_k: int, include_shared: bool = True, y=None, stream=None):
+        """x: CUDA fp32 [hidden, tokens]; routing: [experts, tokens] -> y [hidden, tokens] (channel-major planes)."""
+        import torch
+
+        hidden, tokens = x.shape
+        if y is None:
+            y = torch.empty((hidden, tokens), dtype=torch.float32, device=x.device)
+        _check(self.lib.rq_moe_forward(self.handle, bank.handle, _ptr(x), x.stride(0), x.stride(1), _ptr(routing), routing.stride(0), routing.stride(1),
+                                       top_k, tokens, int(include_shared), _ptr(y), y.stride(0), y.stride(1), _stream(stream)))
         return y
 
     def activation_records(self, x, step: int, stream=None):

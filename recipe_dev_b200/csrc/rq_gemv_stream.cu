@@ -42,6 +42,7 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait on an mbar
 //                         routing weight), out = sum_s coef_s * dot_s in slot order
 struct StreamParams {
     const RqSegment* table;    // device memory, or null: use `inline_seg`
+    const RqPlan* plan;        // device memory written by an earlier kernel: table and counts come from it
     RqSegment inline_seg[RQ_INLINE_SEGMENTS];
     int n_segments, subs, epilogue;
     int64_t rows;              // virtual rows of all segments
@@ -395,15 +396,13 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
     uint8_t* ring = smem + p.act_bytes * p.act_vectors + p.partial_bytes;  // stages
 
     const int tid = threadIdx.x;
-    // this CTA's virtual rows: an even split, sizes differ by at most one
-    const int64_t row_begin = (p.rows * (int64_t)blockIdx.x) / gridDim.x;
-    const int64_t row_end = (p.rows * (int64_t)(blockIdx.x + 1)) / gridDim.x;
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
     const int row_scales = p.units * p.scales_per_unit;
     const int stage_items = 2 * p.subs * p.stage_rows * p.units;
     // The segment table sits in shared memory for the whole kernel: the producer and the consumers
     // both index it with run-time values.
     __shared__ RqSegment table[RQ_MAX_SEGMENTS];
+    __shared__ int plan_counts[4];
 
     RQ_STAMP(0);
     if (tid == 0) {
@@ -416,13 +415,22 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
         // A table in device memory may have been written by the kernel before this one: wait for it.
         // An inline table came with the launch, and the weights are constants of the model, so the
         // producer of a plain matvec streams weights while the previous kernel is still running.
-        if (p.table) asm volatile("griddepcontrol.wait;" ::: "memory");
-        const uint32_t* src = (const uint32_t*)(p.table ? p.table : p.inline_seg);
+        if (p.table || p.plan) asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (p.plan && tid == 0) { plan_counts[0] = p.plan->n_segments; plan_counts[1] = p.plan->subs; plan_counts[2] = p.plan->total_rows; }
+        const int n_copy = p.plan ? p.plan->n_segments : p.n_segments;
+        const uint32_t* src = (const uint32_t*)(p.plan ? p.plan->seg : (p.table ? p.table : p.inline_seg));
         uint32_t* dst = (uint32_t*)table;
-        const int words = p.n_segments * (int)(sizeof(RqSegment) / 4);
+        const int words = (n_copy < RQ_MAX_SEGMENTS ? n_copy : RQ_MAX_SEGMENTS) * (int)(sizeof(RqSegment) / 4);
         for (int i = tid; i < words; i += blockDim.x) dst[i] = src[i];
     }
     __syncthreads();
+    // counts: from the launch, or (planned launches) from the device-side plan, never above the launch's
+    const int n_segments = p.plan ? min(plan_counts[0], p.n_segments) : p.n_segments;
+    const int subs = p.plan ? min(plan_counts[1], p.subs) : p.subs;
+    const int64_t rows = p.plan ? min((int64_t)plan_counts[2], p.rows) : p.rows;
+    // this CTA's virtual rows: an even split, sizes differ by at most one
+    const int64_t row_begin = (rows * (int64_t)blockIdx.x) / gridDim.x;
+    const int64_t row_end = (rows * (int64_t)(blockIdx.x + 1)) / gridDim.x;
 
     const int tok0 = blockIdx.y * T;
 
@@ -432,7 +440,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
             int issued = 0, seg = 0;
             int64_t r = row_begin;
             for (int st = 0; r < row_end; ++st) {
-                while (seg + 1 < p.n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
+                while (seg + 1 < n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
                 const RqSegment& sg = table[seg];
                 const int slot = st % p.stages;
                 if (st >= p.stages && !mbar_wait(&empty_bar[slot], ((st / p.stages) - 1) & 1)) { atomicExch(p.error_flag, 1); break; }
@@ -445,9 +453,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
                 uint8_t* dst = ring + (size_t)slot * p.stage_bytes;
                 const uint32_t main_bytes = (uint32_t)(nr * row_bytes);
                 // bytes first, then the copies: the barrier must expect them before any can complete
-                uint32_t total = main_bytes * p.subs;
+                uint32_t total = main_bytes * subs;
                 if (TYPE != RQ_Q4_K) {
-                    for (int s = 0; s < p.subs; ++s) {
+                    for (int s = 0; s < subs; ++s) {
                         // the rows' d values, widened to whole 16-byte lines (the plane has slack past its end)
                         const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
                         const uintptr_t last = first + (uintptr_t)nr * row_scales * 2;
@@ -458,7 +466,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
 #ifdef RQ_TRACE
                 if (p.trace && st < 16) p.trace[(size_t)blockIdx.x * 64 + 48 + st] = global_ns();
 #endif
-                for (int s = 0; s < p.subs; ++s) {
+                for (int s = 0; s < subs; ++s) {
                     bulk_g2s(dst + (size_t)s * p.sub_main_bytes, sg.main[s] + lr0 * row_bytes, main_bytes, &full_bar[slot]);
                     if (TYPE != RQ_Q4_K) {
                         const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
@@ -533,7 +541,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
         int seg = 0;
         int64_t r = row_begin;
         for (int st = 0; r < row_end; ++st) {
-            while (seg + 1 < p.n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
+            while (seg + 1 < n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
             const RqSegment& sg = table[seg];
             const int64_t seg_end = sg.row_begin + sg.rows;
             int64_t stop = r + p.stage_rows;
@@ -546,7 +554,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
             RQ_STAMP(2 + 3 * st);
             const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
             float* part = partial + (size_t)(st & 1) * T * stage_items;
-            if (tid < items_cap && my_lr < nr) {
+            if (tid < items_cap && my_lr < nr && my_s < subs) {
                 const uint8_t* w = stage + (size_t)my_s * p.sub_main_bytes + (size_t)my_su * p.unit_bytes;
                 const uint16_t* sc = nullptr;
                 if (TYPE != RQ_Q4_K) {
@@ -577,7 +585,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
                 const int lr = i / T, t = i - lr * T;
                 if (tok0 + t < p.tokens) {
                     float out = 0.f, gate = 0.f;
-                    for (int s = 0; s < p.subs; ++s) {
+                    for (int s = 0; s < subs; ++s) {
                         const float* lo = part + t * stage_items + s * su_cap + lr * p.units;  // the row's half-0 partials
                         const float* hi = lo + p.subs * su_cap;                                // and its half-1 partials
                         float sum = 0.f;
@@ -642,7 +650,7 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
         p.act_vectors = t;
     }
     // single-token INT8 launches whose sub-rows all read vector 0 keep the activations in registers
-    p.act_regs = (MODE == RQ_ACT_INT8 && t == 1 && vectors_per_launch == 0 && p.table == nullptr) ? 1 : 0;
+    p.act_regs = (MODE == RQ_ACT_INT8 && t == 1 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr) ? 1 : 0;
     if (p.act_regs) p.act_vectors = 0;  // nothing staged: the threads read the scratch directly
     if (p.act_bytes * p.act_vectors > 64 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
@@ -719,6 +727,37 @@ int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table
         case RQ_Q6_K: return f ? dispatch_stream<RQ_Q6_K, RQ_ACT_FLOAT>(p, sm, v, s) : dispatch_stream<RQ_Q6_K, RQ_ACT_INT8>(p, sm, v, s);
         case RQ_Q8_0: return f ? dispatch_stream<RQ_Q8_0, RQ_ACT_FLOAT>(p, sm, v, s) : dispatch_stream<RQ_Q8_0, RQ_ACT_INT8>(p, sm, v, s);
         default: return f ? dispatch_stream<RQ_Q4_0, RQ_ACT_FLOAT>(p, sm, v, s) : dispatch_stream<RQ_Q4_0, RQ_ACT_INT8>(p, sm, v, s);
+    }
+}
+
+// A launch whose segment table and counts a kernel wrote into `plan` (device memory): the host
+// sizes the launch for the maxima. FLOAT activations only: vector v is x + v * st.
+int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* plan, int max_segments, int max_subs, int epilogue, int64_t max_rows,
+                          const float* x, int64_t sk, int64_t st, int vectors, int64_t yn, int64_t yt, cudaStream_t s) {
+    if (cols % 256 || max_subs < 1 || max_subs > RQ_MAX_SUB || max_segments < 1 || max_segments > RQ_MAX_SEGMENTS || vectors < 1) return RQ_ERR_UNSUPPORTED;
+    StreamParams p;
+    memset(&p, 0, sizeof(p));
+    p.plan = plan;
+    p.n_segments = max_segments; p.subs = max_subs; p.epilogue = epilogue;
+    p.rows = max_rows; p.cols = (int)cols; p.units = (int)(cols / 256);
+    p.x = x; p.sk = sk; p.st = st; p.yn = yn; p.yt = yt; p.tokens = 1;
+    p.error_flag = ctx->error_flag;
+#ifdef RQ_TRACE
+    p.trace = rq_trace_buffer();
+#endif
+    switch (type) {
+        case RQ_Q4_K: p.unit_bytes = 144; p.scales_per_unit = 0; break;
+        case RQ_Q6_K: p.unit_bytes = 208; p.scales_per_unit = 1; break;
+        case RQ_Q8_0: p.unit_bytes = 256; p.scales_per_unit = 8; break;
+        case RQ_Q4_0: p.unit_bytes = 128; p.scales_per_unit = 8; break;
+        default: return RQ_ERR_UNSUPPORTED;
+    }
+    const int sm = ctx->sm_count;
+    switch (type) {
+        case RQ_Q4_K: return dispatch_stream<RQ_Q4_K, RQ_ACT_FLOAT>(p, sm, vectors, s);
+        case RQ_Q6_K: return dispatch_stream<RQ_Q6_K, RQ_ACT_FLOAT>(p, sm, vectors, s);
+        case RQ_Q8_0: return dispatch_stream<RQ_Q8_0, RQ_ACT_FLOAT>(p, sm, vectors, s);
+        default: return dispatch_stream<RQ_Q4_0, RQ_ACT_FLOAT>(p, sm, vectors, s);
     }
 }
 

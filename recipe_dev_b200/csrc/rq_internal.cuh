@@ -102,6 +102,17 @@ struct RqSegment {
     int act[RQ_MAX_SUB];                 // the staged activation vector each sub-row dots
     float coef[RQ_MAX_SUB];              // RQ_EPI_WSUM: the coefficient of each sub-row
 };
+// A segment table in device memory, written by a kernel (the expert planner): the counts are read
+// on the device, so the host launches without knowing how many experts a token routed here.
+struct RqPlan {
+    int n_segments;   // <= RQ_MAX_SEGMENTS
+    int subs;         // sub-rows per virtual row in use, <= the launch's `subs`
+    int total_rows;   // virtual rows of all segments
+    int pad;
+    RqSegment seg[RQ_MAX_SEGMENTS];
+};
+int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* plan, int max_segments, int max_subs, int epilogue, int64_t max_rows,
+                          const float* x, int64_t sk, int64_t st, int vectors, int64_t yn, int64_t yt, cudaStream_t s);
 int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table, const RqSegment* inline_seg, int n_segments, int subs,
                      int epilogue, int64_t total_rows, const float* x, int64_t sk, int64_t st, int tokens, int vectors_per_launch,
                      int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s);
