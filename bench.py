@@ -313,6 +313,10 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
+    for ws in layers:
+        for w in ws:
+            w.free()
+    sharded_out = run_sharded_configs(ctx, rq, torch, dist, rank, world, device, args.steps) if args.sharded else None
 
     # max over ranks
     if dist is not None:
@@ -345,6 +349,8 @@ def run_ours(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
+    if sharded_out is not None:
+        line["sharded"] = sharded_out
     if args.cpu_baseline:
         from tests import oracle_lib as ol
 
@@ -421,6 +427,104 @@ def run_case(args):
                       "peak": f"{peak} ({kind})", "algorithmic_bytes": nbytes, "launches": args.steps, "weight_copies": args.layers, "graph": bool(args.graph)}), flush=True)
 
 
+def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
+    """The two configs that shard across GPUs, timed on the device (max over ranks):
+    the row-split Q6_K LM head (262144 x 2560, logits all-gathered) at batch 1 and 4, and the
+    expert-parallel Q4_K MoE bank (256 experts, top-8, hidden 2048, ffn 512, gated shared expert on
+    rank 0, outputs all-reduced) at batch 1 and 16. Returns a dict for the JSON line."""
+    from recipe_dev_b200 import sharded
+
+    out = {}
+    stream = torch.cuda.current_stream()
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        us = torch.tensor([1e3 * e0.elapsed_time(e1) / reps], device=device, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(us, op=dist.ReduceOp.MAX)
+        return float(us[0])
+
+    # ---- LM head: rows [first, first + count) of 262144 x 2560 Q6_K on this rank
+    rows, cols = 262144, 2560
+    first, count = sharded.shard_range(rows, world, rank)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(2000 + rank)
+    copies = []
+    for _ in range(2 if count * cols // 256 * 210 < 200_000_000 else 1):  # small shares rotate two copies so L2 cannot hold them
+        w32 = torch.randn(count * cols, generator=gen, device=device) * 0.02
+        copies.append(ctx.weight_from_device(Q6_K, ctx.quantize(Q6_K, w32), count, cols))
+        del w32
+    mode = rq.ACT_INT8
+    for tokens in (1, 4):
+        x = torch.randn(tokens, cols, generator=gen, device=device)
+        local = torch.empty(tokens, count, device=device)
+        it = [0]
+
+        def head_step():
+            ctx.matvec(copies[it[0] % len(copies)], x, local, act_mode=mode, step=32)
+            it[0] += 1
+            return sharded.gather_rows(local, rows, dist, world, rank)
+
+        us = timed(head_step, max(10, steps // 10))
+        nbytes = rows * (cols // 256) * 210 + 4 * cols * tokens + 4 * rows * tokens
+        out[f"lm_head_q6k_262144x2560_batch{tokens}"] = {"us": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes": nbytes,
+                                                         "rows_per_gpu": count, "collective": "all_gather fp32 logits" if world > 1 else "none"}
+    for w in copies:
+        w.free()
+    del copies
+    # ---- MoE bank: experts [first, first + count) of 256 on this rank
+    experts, top, hidden, ffn = 256, 8, 2048, 512
+    ef, ec = sharded.shard_range(experts, world, rank)
+    gen.manual_seed(3000 + rank)
+
+    def host_blocks(n_rows, n_cols):
+        w32 = torch.randn(n_rows * n_cols, generator=gen, device=device) * 0.02
+        b = ctx.quantize(Q4_K, w32).cpu().numpy()
+        del w32
+        return b
+
+    gate, up, down = host_blocks(ec * ffn, hidden), host_blocks(ec * ffn, hidden), host_blocks(ec * hidden, ffn)
+    shared = None
+    if rank == 0:
+        shared = (host_blocks(ffn, hidden), host_blocks(ffn, hidden), host_blocks(hidden, ffn), (torch.randn(hidden, generator=gen, device=device) * 0.02).cpu().numpy())
+    bank = ctx.moe_prepare(Q4_K, gate, up, down, ec, hidden, ffn, shared=shared)
+    del gate, up, down
+    rgen = torch.Generator(device=device)
+    rgen.manual_seed(3999)  # the router scores are the same on every rank (the router is replicated)
+    expert_bytes = 3 * ffn * (hidden // 256) * 144
+    for tokens in (1, 16):
+        scores = torch.randn(experts, tokens, generator=rgen, device=device)
+        xm = torch.randn(hidden, tokens, generator=rgen, device=device)
+        y = torch.empty(hidden, tokens, device=device)
+
+        def moe_step():
+            routing = ctx.moe_route(scores, top)
+            ctx.moe_forward(bank, xm, routing[ef:ef + ec], top, include_shared=(rank == 0), y=y)
+            if dist is not None:
+                dist.all_reduce(y)
+            return y
+
+        us = timed(moe_step, max(10, steps // 10))
+        nbytes = tokens * ((top + 1) * expert_bytes + (top + 1) * 3 * 4 * (hidden + ffn))
+        loads = sharded.routed_bytes_per_rank(ctx.moe_route(scores, top), experts, world, expert_bytes)
+        out[f"moe_q4k_256e_top8_batch{tokens}"] = {"us": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes": nbytes, "experts_per_gpu": ec,
+                                                  "routed_bytes_per_rank_min_max": [min(loads), max(loads)],
+                                                  "collective": "all_reduce fp32 [hidden, tokens]" if world > 1 else "none"}
+    ctx.check()
+    bank.free()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default=None, help="profile one matvec shape, e.g. q4k:14336x4096:int8")
@@ -431,6 +535,7 @@ def main():
     ap.add_argument("--act", default="int8", choices=["int8", "float"])
     ap.add_argument("--layers", type=int, default=8, help="distinct decode layers in rotation (138 MB each)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--no-sharded", dest="sharded", action="store_false", help="skip the row-split LM head and expert-parallel MoE configs")
     ap.add_argument("--graph", action="store_true", help="--case: replay the launches as one CUDA graph")
     args = ap.parse_args()
     if args.warmup < 3:

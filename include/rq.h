@@ -109,6 +109,15 @@ int rq_matvec(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t x_k_strid
 int rq_matvec_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
                     float* const* ys, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);
 
+/* The batched product (prefill, multi-sequence decode): the same contraction as rq_matvec for many
+ * tokens. With RQ_ACT_FLOAT the weights are dequantised a tile at a time into shared memory and
+ * multiplied on the tensor cores (tcgen05.mma, fp16 hi + lo operand pairs, fp32 accumulation in
+ * tensor memory); with RQ_ACT_INT8 the exact integer dots of the matvec kernels run, four tokens a
+ * pass. Replaces contraction_forward_body's position loop and contraction_forward_gemm_body
+ * (amd-nv-cpu.ll:1231-2241, :3509-3649). Same arguments as rq_matvec. */
+int rq_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
+              float* y, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);
+
 /* The same call with HOST buffers: copies x in, runs, copies y out, synchronises. This is the
  * call a host without device buffers makes (Placed::infer, recipe.rs:21314-21490). */
 int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host_x, int64_t x_k_stride, int64_t x_t_stride, int tokens,

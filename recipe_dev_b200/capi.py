@@ -51,6 +51,7 @@ def _declare(lib) -> None:
         "rq_dequant": (i32, [p, p, f32p, p]),
         "rq_quantize": (i32, [p, i32, f32p, i64, p, p]),
         "rq_matvec": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
+        "rq_matmul": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
         "rq_matvec_multi": (i32, [p, i32, p, f32p, i64, i64, i32, p, i64, i64, i32, i32, p]),
         "rq_matvec_host": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32]),
         "rq_quantize_activations": (i32, [p, f32p, i64, i64, i64, i32, i32, p, p]),
@@ -67,7 +68,6 @@ def _declare(lib) -> None:
         "rq_moe_free": (None, [p, p]),
         "rq_moe_bytes": (i64, [p]),
         "rq_moe_forward": (i32, [p, p, f32p, i64, i64, f32p, i64, i64, i32, i32, i32, f32p, i64, i64, p]),
-        "rq_matmul": (i32, [p, p, f32p, i32, f32p, i32, i32, p]),
     }
     for name, (res, args) in optional.items():
         if hasattr(lib, name):
@@ -247,6 +247,17 @@ class Context:
         _check(self.lib.rq_matvec(self.handle, w.handle, _ptr(x2), x2.stride(1), x2.stride(0), tokens,
                                   _ptr(y2), y2.stride(1), y2.stride(0), act_mode, step, _stream(stream)))
         return y2[0] if single else y2
+
+    def matmul(self, w: Weight, x, y=None, act_mode: int = ACT_FLOAT, step: int = 32, stream=None):
+        """x: CUDA fp32 [tokens, cols] -> y [tokens, rows]; the tensor-core path for RQ_ACT_FLOAT."""
+        import torch
+
+        tokens, cols = x.shape
+        if y is None:
+            y = torch.empty((tokens, w.rows), dtype=torch.float32, device=x.device)
+        _check(self.lib.rq_matmul(self.handle, w.handle, _ptr(x), x.stride(1), x.stride(0), tokens, _ptr(y), y.stride(1), y.stride(0), act_mode, step,
+                                  _stream(stream)))
+        return y
 
     def matvec_multi(self, ws, x, ys, act_mode: int = ACT_FLOAT, step: int = 32, stream=None):
         """Several weights of one format and width against the same x; ys[i] is [rows_i] or [tokens, rows_i]."""

@@ -256,6 +256,20 @@ extern "C" int rq_matvec_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, c
     return rq_launch_gemv_multi(ctx, n, ws, x, sk, st, tokens, ys, yn, yt, act_mode, step, (cudaStream_t)stream);
 }
 
+extern "C" int rq_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
+                         float* y, int64_t yn, int64_t yt, int act_mode, int step, void* stream) {
+    int rc = check_matvec("rq_matmul", ctx, w, x, y, tokens, act_mode, step);
+    if (rc) return rc;
+    if (sk <= 0 || yn <= 0 || (tokens > 1 && (st <= 0 || yt <= 0))) return rq_fail(RQ_ERR_INVALID, "rq_matmul: strides must be positive");
+    DeviceGuard guard(ctx->device);
+    if (act_mode == RQ_ACT_FLOAT) {
+        rc = rq_launch_matmul(ctx, w, x, sk, st, tokens, y, yn, yt, (cudaStream_t)stream);
+        if (rc != RQ_ERR_UNSUPPORTED) return rc;
+    }
+    // int8 activations (exact integer dots) and odd widths go through the matvec kernels, four tokens a pass
+    return rq_launch_gemv(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, step, (cudaStream_t)stream);
+}
+
 static int ensure_buffer(float** dev, size_t* dev_bytes, float** pin, size_t* pin_bytes, size_t need) {
     if (need > *dev_bytes) {
         if (*dev) cudaFree(*dev);

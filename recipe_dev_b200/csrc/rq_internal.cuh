@@ -88,6 +88,8 @@ int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, 
 int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t sk, int64_t st, int tokens,
                          float* const* ys, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s);
 int rq_launch_gemv_tiled_int8(rq_ctx* ctx, const rq_weight* w, int tokens, float* y, int64_t yn, int64_t yt, const uint8_t* act, cudaStream_t s);
+// RQ_ERR_UNSUPPORTED (no error text) = width not served by the tensor-core kernel
+int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s);
 int rq_launch_quantize(int type, const float* values, int64_t count, uint8_t* blocks, cudaStream_t s);
 // A run of virtual output rows of the streaming kernel (see rq_gemv_stream.cu).
 #define RQ_MAX_SUB 16
