@@ -155,14 +155,20 @@ __device__ __forceinline__ void row_values(const MatmulParams& p, int64_t row, i
     }
 }
 
-// Splits 64 fp32 values into fp16 hi and lo and writes the row into the two swizzled tiles.
-__device__ __forceinline__ void store_row_split(const float* v, uint8_t* tile_hi, uint8_t* tile_lo, int row) {
+// Weights are scaled by 2^8 before the split and the accumulator by 2^-8 after: a weight of 0.02
+// leaves a residual near 1e-5, which fp16 could only hold as a subnormal with a few bits; scaled, the
+// residual keeps its eleven. (Weights of magnitude 255 and more would overflow fp16; GGUF model
+// weights are orders of magnitude below that.)
+constexpr float kWeightScale = 256.0f, kWeightUnscale = 1.0f / 256.0f;
+
+// Splits 64 fp32 values (times `scale`) into fp16 hi and lo and writes the row into the two swizzled tiles.
+__device__ __forceinline__ void store_row_split(const float* v, float scale, uint8_t* tile_hi, uint8_t* tile_lo, int row) {
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         uint32_t hw[4], lw[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float a = v[8 * c + 2 * j], b = v[8 * c + 2 * j + 1];
+            const float a = v[8 * c + 2 * j] * scale, b = v[8 * c + 2 * j + 1] * scale;
             const __half ha = __float2half_rn(a), hb = __float2half_rn(b);
             const __half la = __float2half_rn(a - __half2float(ha)), lb = __float2half_rn(b - __half2float(hb));
             hw[j] = (uint32_t)__half_as_ushort(ha) | ((uint32_t)__half_as_ushort(hb) << 16);
@@ -213,7 +219,7 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
             uint8_t* stage = smem + (size_t)slot * kStageBytes;
             float v[64];
             row_values<TYPE>(p, row, ks * BK, v);
-            store_row_split(v, stage, stage + kTileBytes, tid);
+            store_row_split(v, kWeightScale, stage, stage + kTileBytes, tid);
             if (live_token) {
                 if (p.x_vec) {
 #pragma unroll
@@ -226,7 +232,7 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
 #pragma unroll
                 for (int j = 0; j < 64; ++j) v[j] = 0.0f;
             }
-            store_row_split(v, stage + 2 * kTileBytes, stage + 3 * kTileBytes, tid);
+            store_row_split(v, 1.0f, stage + 2 * kTileBytes, stage + 3 * kTileBytes, tid);
             // the tensor core reads shared memory through the async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(&full_bar[slot]);
@@ -252,7 +258,7 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int t = n0 + c0 + j;
-                    if (t < p.tokens) p.y[out_row * p.yn + (int64_t)t * p.yt] = __uint_as_float(r[j]);
+                    if (t < p.tokens) p.y[out_row * p.yn + (int64_t)t * p.yt] = __uint_as_float(r[j]) * kWeightUnscale;
                 }
             }
         }

@@ -31,10 +31,12 @@ def test_matmul_float_parity(rq_ctx, oracle, t, rows, cols, tokens):
     ref = oracle.matvec(t, blocks, rows, cols, x, ol.FLOAT_RUN)
     assert rel_err(y, ref) <= TOL
     exact = x.astype(np.float64) @ oracle.dequantize(t, blocks).astype(np.float64).reshape(rows, cols).T
-    assert rel_err(y, exact) <= 1e-4
-    # the same rows the matvec kernel gives, to summation order
+    # the dropped lo x lo term is 2^-22 of a product: a few 1e-7 of the largest output
+    assert rel_err(y, exact) <= 5e-4
+    assert np.max(np.abs(y - exact)) <= 3e-6 * np.max(np.abs(exact))
+    # the same rows the matvec kernel gives, to that noise
     one = rq_ctx.matvec(w, cuda(x[0])).cpu().numpy()
-    assert rel_err(y[0], one) <= 1e-4
+    assert rel_err(y[0], one) <= 5e-4
 
 
 def test_matmul_channel_major_planes_and_int8(rq_ctx, oracle):
