@@ -342,7 +342,10 @@ def run_ours(args):
         "frac_of_hbm_measured": value / world / peak, "frac_of_hbm_nominal_8TBs": value / world / 8000.0,
         "roofline": {"bound": "hbm", "kernel": "rq_gemv_stream_kernel<Q4_K> over gate+up (2 x 14336 x 4096), one launch", "achieved": achieved, "peak": peak,
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": achieved / peak,
-                     "us_per_launch": dom_us, "algorithmic_bytes_per_launch": dom_bytes, "traffic": None},
+                     "us_per_launch": dom_us, "algorithmic_bytes_per_launch": dom_bytes,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the same kernel over one of the two
+                     # row sets (14336 x 4096: 33,079,808 bytes), scaled to the launch's two row sets
+                     "traffic": 2 * 33_079_808, "traffic_source": "profiles/rq_gemv_stream_q4k_14336x4096_int8.md, x2 row sets"},
         "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": sum(4 * c for _, _, _, c, _ in LAYER), "d2h_bytes_per_step": sum(4 * r for _, _, r, _, _ in LAYER),
                 "ms_per_step": 1e3 * e2e_s / args.steps, "call": "rq_matvec_host x 7 per step (host x in, host y out)"},
