@@ -384,24 +384,46 @@ static int int8_records(rq_ctx* ctx, const char* who, const float* x, int64_t sk
     return RQ_OK;
 }
 
+// A single-token INT8 call over whole 256-value units can quantise inside the matvec launch. True when
+// that is to be tried (the scratch is then large enough for the records the launch leaves behind);
+// *rc carries an allocation failure.
+static bool fused_int8(rq_ctx* ctx, int act_mode, int tokens, int64_t cols, int* rc) {
+    *rc = RQ_OK;
+    if (act_mode != RQ_ACT_INT8 || tokens != 1 || cols % 256) return false;
+    *rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols));
+    return *rc == RQ_OK;
+}
+
 // Several matrices of one format and width against the same activations, as one launch when the
 // streaming kernel serves the shape (one segment per matrix), else one launch per matrix.
 int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t sk, int64_t st, int tokens,
                          float* const* ys, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s) {
     const rq_weight* w0 = ws[0];
     const int mode = act_mode == RQ_ACT_FLOAT ? RQ_ACT_FLOAT : RQ_ACT_INT8;
-    int rc = int8_records(ctx, "matvec_multi", x, sk, st, w0->cols, tokens, step, act_mode, s);
-    if (rc) return rc;
+    int rc;
+    RqSegment seg[RQ_INLINE_SEGMENTS];
+    int64_t total = 0;
     if (n <= RQ_INLINE_SEGMENTS) {
-        RqSegment seg[RQ_INLINE_SEGMENTS];
         memset(seg, 0, sizeof(seg));
-        int64_t total = 0;
         for (int i = 0; i < n; ++i) {
             seg[i].row_begin = (int)total; seg[i].rows = (int)ws[i]->rows; seg[i].y = ys[i];
             seg[i].main[0] = ws[i]->main; seg[i].scale[0] = ws[i]->scale; seg[i].act[0] = 0; seg[i].coef[0] = 1.0f;
             total += ws[i]->rows;
         }
-        rc = rq_launch_stream(ctx, w0->type, w0->cols, nullptr, seg, n, 1, RQ_EPI_PLAIN, total, x, sk, st, tokens, 0, yn, yt, mode, ctx->act_scratch, s);
+        if (fused_int8(ctx, act_mode, tokens, w0->cols, &rc)) {
+            // one launch: the matvec quantises x in its prologue
+            rc = rq_launch_stream(ctx, w0->type, w0->cols, nullptr, seg, n, 1, RQ_EPI_PLAIN, total, x, sk, st, tokens, 0, yn, yt, mode, ctx->act_scratch, step,
+                                  ctx->act_scratch, s);
+            if (rc == RQ_OK) { ctx->act_cols = w0->cols; ctx->act_tokens = tokens; ctx->act_step = step; }
+            if (rc != RQ_ERR_UNSUPPORTED) return rc;
+        } else if (rc) {
+            return rc;
+        }
+    }
+    rc = int8_records(ctx, "matvec_multi", x, sk, st, w0->cols, tokens, step, act_mode, s);
+    if (rc) return rc;
+    if (n <= RQ_INLINE_SEGMENTS) {
+        rc = rq_launch_stream(ctx, w0->type, w0->cols, nullptr, seg, n, 1, RQ_EPI_PLAIN, total, x, sk, st, tokens, 0, yn, yt, mode, ctx->act_scratch, 0, nullptr, s);
         if (rc != RQ_ERR_UNSUPPORTED) return rc;
     }
     for (int i = 0; i < n; ++i) {
@@ -414,9 +436,18 @@ int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const f
 int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
                    float* y, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s) {
     const int mode = act_mode == RQ_ACT_FLOAT ? RQ_ACT_FLOAT : RQ_ACT_INT8;
-    int rc = int8_records(ctx, "matvec", x, sk, st, w->cols, tokens, step, act_mode, s);
+    int rc;
+    if (fused_int8(ctx, act_mode, tokens, w->cols, &rc)) {
+        // one launch: the matvec quantises x in its prologue
+        rc = rq_launch_gemv_stream(ctx, w, x, sk, st, tokens, y, yn, yt, mode, ctx->act_scratch, step, ctx->act_scratch, s);
+        if (rc == RQ_OK) { ctx->act_cols = w->cols; ctx->act_tokens = tokens; ctx->act_step = step; }
+        if (rc != RQ_ERR_UNSUPPORTED) return rc;
+    } else if (rc) {
+        return rc;
+    }
+    rc = int8_records(ctx, "matvec", x, sk, st, w->cols, tokens, step, act_mode, s);
     if (rc) return rc;
-    rc = rq_launch_gemv_stream(ctx, w, x, sk, st, tokens, y, yn, yt, mode, ctx->act_scratch, s);
+    rc = rq_launch_gemv_stream(ctx, w, x, sk, st, tokens, y, yn, yt, mode, ctx->act_scratch, 0, nullptr, s);
     if (rc != RQ_ERR_UNSUPPORTED) return rc;
     if (rq_act_unit_layout(w->cols) && mode == RQ_ACT_INT8)
         return rq_fail(RQ_ERR_LIMIT, "matvec: %lld inputs per row exceed what one CTA's shared memory holds", (long long)w->cols);

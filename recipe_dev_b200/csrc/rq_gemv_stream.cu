@@ -54,6 +54,11 @@ struct StreamParams {
     size_t sub_main_bytes, sub_scale_bytes, stage_bytes, act_bytes, partial_bytes;  // shared-memory sizes
     int act_vectors;           // activation vectors staged in shared memory
     int act_regs;              // INT8, one token, every sub-row on vector 0: each thread keeps its activations in registers
+    int warp_rows;             // > 0: the warp scheme -- a row's 2 * units items are that many adjacent lanes (a power of two), a warp
+                               // pass covers warp_rows = 32 / (2 * units) rows, and the lanes of a row join their sums by shuffles
+    int rows_per_thread;       // warp scheme: passes per stage (1 or 2)
+    int fuse_step;             // act_regs launches: 32 or 256 = quantise x in the prologue (no quantiser launch before), 0 = read `act`
+    uint8_t* act_out;          // fused launches: CTA 0 leaves the records here for later INT8_CACHED calls
     const float* x; int64_t sk, st;   // FLOAT: vector v is x + v * st, element stride sk
     const uint8_t* act;        // INT8 activation scratch, one token's records after another
     int64_t yn, yt;
@@ -150,6 +155,7 @@ struct ActHalf {
     float d8[4];
     uint32_t s16w[4];  // eight int16 slice sums
     uint32_t g32w[2];  // four int16 group sums
+    float dg[4];       // step x group sum, per group (the Q4_K minimum term)
     __device__ __forceinline__ void load(const uint8_t* rec, int h) {
         const uint4* cp = (const uint4*)(rec + 128 * h);
 #pragma unroll
@@ -160,6 +166,8 @@ struct ActHalf {
         s16w[0] = sv.x; s16w[1] = sv.y; s16w[2] = sv.z; s16w[3] = sv.w;
         const uint2 gv = *(const uint2*)(rec + 320 + 8 * h);
         g32w[0] = gv.x; g32w[1] = gv.y;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dg[i] = d8[i] * (float)g32(i);
     }
     __device__ __forceinline__ int s16(int i) const { return (int)(int16_t)(s16w[i >> 1] >> (16 * (i & 1))); }
     __device__ __forceinline__ int g32(int i) const { return (int)(int16_t)(g32w[i >> 1] >> (16 * (i & 1))); }
@@ -202,8 +210,8 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
                 const int dl = dl0 + dl1, dh = (dh0 + dh1) >> 4;
                 acc_s = fmaf(ah8.d8[2 * pp], (float)(sc_lo * dl), acc_s);
                 acc_s = fmaf(ah8.d8[2 * pp + 1], (float)(sc_hi * dh), acc_s);
-                acc_m = fmaf(ah8.d8[2 * pp], (float)(mn_lo * ah8.g32(2 * pp)), acc_m);
-                acc_m = fmaf(ah8.d8[2 * pp + 1], (float)(mn_hi * ah8.g32(2 * pp + 1)), acc_m);
+                acc_m = fmaf(ah8.dg[2 * pp], (float)mn_lo, acc_m);  // the same roundings as dot_regs
+                acc_m = fmaf(ah8.dg[2 * pp + 1], (float)mn_hi, acc_m);
             } else {
                 float xl[16], dl, dh;
                 const float* xs = xf + 64 * pp;
@@ -341,6 +349,241 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Register-resident items (single-token INT8 launches): a thread copies its item's weights out
+// of the stage into registers and releases the stage at once, so the ring slot is busy only while
+// the bytes are in flight, and works on two items at a time for instruction-level parallelism.
+// ------------------------------------------------------------------------------------------
+template <int TYPE> struct ItemRegs;
+template <> struct ItemRegs<RQ_Q4_K> {
+    uint4 hdr, q[4];
+    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t*, int h) {
+        hdr = *(const uint4*)w;
+        const uint4* qp = (const uint4*)(w + 16 + 64 * h);
+        q[0] = qp[0]; q[1] = qp[1]; q[2] = qp[2]; q[3] = qp[3];
+    }
+};
+template <> struct ItemRegs<RQ_Q6_K> {
+    uint4 ql[4], qh[2];  // ql[2 * gl + wh], qh[wh]
+    uint2 sc;
+    uint32_t d16;
+    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h) {
+        const uint4* lp = (const uint4*)(w + 64 * h);
+        ql[0] = lp[0]; ql[1] = lp[1]; ql[2] = lp[2]; ql[3] = lp[3];
+        const uint4* hp = (const uint4*)(w + 128 + 32 * h);
+        qh[0] = hp[0]; qh[1] = hp[1];
+        sc = *(const uint2*)(w + 192 + 8 * h);
+        d16 = scp[0];
+    }
+};
+template <> struct ItemRegs<RQ_Q8_0> {
+    uint4 q[8];
+    uint2 dd;
+    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h) {
+        const uint4* qp = (const uint4*)(w + 128 * h);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = qp[i];
+        dd = *(const uint2*)(scp + 4 * h);
+    }
+};
+template <> struct ItemRegs<RQ_Q4_0> {
+    uint4 q[4];
+    uint2 dd;
+    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h) {
+        const uint4* qp = (const uint4*)(w + 64 * h);
+        q[0] = qp[0]; q[1] = qp[1]; q[2] = qp[2]; q[3] = qp[3];
+        dd = *(const uint2*)(scp + 4 * h);
+    }
+};
+
+// An integer of magnitude below 2^22 as a float, exactly, without the conversion unit:
+// 0x4B400000 is 1.5 * 2^23, whose mantissa takes the integer as it is.
+__device__ __forceinline__ float small_int_to_float(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }
+
+__device__ __forceinline__ float dot_regs(const ItemRegs<RQ_Q4_K>& r, const ActHalf& a, const int h) {
+    const uint4 hdr = r.hdr;
+    const float d = rq_h2f((uint16_t)(hdr.x & 0xffff)), dmin = rq_h2f((uint16_t)(hdr.x >> 16));
+    const uint32_t scw = h == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u));
+    const uint32_t mnw = h == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u));
+    float mn[4];
+    bytes_to_float4(mnw, mn);
+    float acc_s = 0.f, acc_m = 0.f;
+#pragma unroll
+    for (int pp = 0; pp < 2; ++pp) {
+        const uint4 q0 = r.q[2 * pp], q1 = r.q[2 * pp + 1];
+        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const int sc_lo = (int)__byte_perm(scw, 0, 0x4440 + 2 * pp), sc_hi = (int)__byte_perm(scw, 0, 0x4441 + 2 * pp);
+        const uint32_t* al = a.c + 16 * pp;
+        const uint32_t* ah = a.c + 16 * pp + 8;
+        int dl0 = 0, dl1 = 0, dh0 = 0, dh1 = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            dl0 = dp4a_us(qw[j] & 0x0F0F0F0Fu, al[j], dl0);
+            dl1 = dp4a_us(qw[j + 1] & 0x0F0F0F0Fu, al[j + 1], dl1);
+            dh0 = dp4a_us(qw[j] & 0xF0F0F0F0u, ah[j], dh0);  // sixteen times the high-nibble dot
+            dh1 = dp4a_us(qw[j + 1] & 0xF0F0F0F0u, ah[j + 1], dh1);
+        }
+        // |scale * dot| <= 63 * 32 * 15 * 128 < 2^22
+        acc_s = fmaf(a.d8[2 * pp], small_int_to_float(sc_lo * (dl0 + dl1)), acc_s);
+        acc_s = fmaf(a.d8[2 * pp + 1], small_int_to_float(sc_hi * ((dh0 + dh1) >> 4)), acc_s);
+        acc_m = fmaf(a.dg[2 * pp], mn[2 * pp], acc_m);
+        acc_m = fmaf(a.dg[2 * pp + 1], mn[2 * pp + 1], acc_m);
+    }
+    return d * acc_s - dmin * acc_m;
+}
+
+__device__ __forceinline__ float dot_regs(const ItemRegs<RQ_Q6_K>& r, const ActHalf& a, const int) {
+    const float d = rq_h2f((uint16_t)r.d16);
+    const uint32_t scales[2] = {r.sc.x, r.sc.y};
+    float acc = 0.f;
+#pragma unroll
+    for (int wh = 0; wh < 2; ++wh) {
+        const uint32_t qh[4] = {r.qh[wh].x, r.qh[wh].y, r.qh[wh].z, r.qh[wh].w};
+#pragma unroll
+        for (int gl = 0; gl < 2; ++gl) {
+            const uint4 ql4 = r.ql[2 * gl + wh];
+            const uint32_t ql[4] = {ql4.x, ql4.y, ql4.z, ql4.w};
+            const int s_lo = 2 * gl + wh, s_hi = s_lo + 4;
+            const int sc_lo = (int)(int8_t)(scales[s_lo >> 2] >> (8 * (s_lo & 3)));
+            const int sc_hi = (int)(int8_t)(scales[s_hi >> 2] >> (8 * (s_hi & 3)));
+            const int k_lo = 32 * gl + 16 * wh, k_hi = k_lo + 64;
+            const uint32_t* alw = a.c + (k_lo >> 2);
+            const uint32_t* ahw = a.c + (k_hi >> 2);
+            constexpr uint32_t kPairLo = 0x03030303u, kPairHi = 0x30303030u;
+            int nl = 0, nh = 0, pl = 0, ph = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                nl = dp4a_us(ql[j] & 0x0F0F0F0Fu, alw[j], nl);
+                nh = dp4a_us(ql[j] & 0xF0F0F0F0u, ahw[j], nh);
+                pl = dp4a_us(qh[j] & (kPairLo << (2 * gl)), alw[j], pl);
+                ph = dp4a_us(qh[j] & (kPairHi << (2 * gl)), ahw[j], ph);
+            }
+            const int dl = nl + ((pl >> (2 * gl)) << 4) - 32 * a.s16(k_lo >> 4);
+            const int dh = (nh >> 4) + (ph >> (2 * gl)) - 32 * a.s16(k_hi >> 4);
+            acc = fmaf(a.d8[k_lo >> 5], (float)(sc_lo * dl), acc);
+            acc = fmaf(a.d8[k_hi >> 5], (float)(sc_hi * dh), acc);
+        }
+    }
+    return d * acc;
+}
+
+__device__ __forceinline__ float dot_regs(const ItemRegs<RQ_Q8_0>& r, const ActHalf& a, const int) {
+    const uint32_t dw[2] = {r.dd.x, r.dd.y};
+    float acc = 0.f;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
+        const uint4 q0 = r.q[2 * b], q1 = r.q[2 * b + 1];
+        const uint32_t* a0 = a.c + 8 * b;
+        const uint32_t* a1 = a0 + 4;
+        int dot = dp4a_ss(q0.x, a0[0], 0), dot1 = dp4a_ss(q1.x, a1[0], 0);
+        dot = dp4a_ss(q0.y, a0[1], dot); dot1 = dp4a_ss(q1.y, a1[1], dot1);
+        dot = dp4a_ss(q0.z, a0[2], dot); dot1 = dp4a_ss(q1.z, a1[2], dot1);
+        dot = dp4a_ss(q0.w, a0[3], dot); dot1 = dp4a_ss(q1.w, a1[3], dot1);
+        acc = fmaf(a.d8[b] * d, (float)(dot + dot1), acc);
+    }
+    return acc;
+}
+
+__device__ __forceinline__ float dot_regs(const ItemRegs<RQ_Q4_0>& r, const ActHalf& a, const int) {
+    const uint32_t dw[2] = {r.dd.x, r.dd.y};
+    float acc = 0.f;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
+        const uint32_t qw[4] = {r.q[b].x, r.q[b].y, r.q[b].z, r.q[b].w};
+        const uint32_t* alw = a.c + 8 * b;
+        const uint32_t* ahw = alw + 4;
+        int dl = 0, dh = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            dl = dp4a_us(qw[j] & 0x0F0F0F0Fu, alw[j], dl);
+            dh = dp4a_us(qw[j] & 0xF0F0F0F0u, ahw[j], dh);
+        }
+        const int dot = dl + (dh >> 4) - 8 * a.g32(b);
+        acc = fmaf(a.d8[b] * d, (float)dot, acc);
+    }
+    return acc;
+}
+
+// The int8 activation quantiser inside the matvec's prologue: the CTA's consumer threads turn the
+// `cols` inputs of one token into unit records in shared memory. A thread owns slices of sixteen
+// inputs (all its loads are issued before any arithmetic, so the prologue costs one trip to L2);
+// the two threads of a 32-value group, or the sixteen of a 256-value group, agree on the extreme
+// by shuffles. Same arithmetic as the standalone quantiser: the extreme is the FIRST input of
+// strictly largest magnitude, inverse = -127 / extreme, d = 1 / inverse (IEEE divides),
+// code = clamp(rint(x * inverse)).
+template <int THREADS>
+__device__ __forceinline__ void quantise_to_smem(const float* __restrict__ x, int64_t sk, int cols, int step, uint8_t* __restrict__ rec_base, int tid) {
+    constexpr int kRecord = RQ_ACT_RECORD_INT8;
+    const int slices = cols >> 4;
+    const bool vec = sk == 1 && ((uintptr_t)x & 15) == 0;
+    for (int base = 0; base < slices; base += 4 * THREADS) {
+        float v[4][16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int sl = base + i * THREADS + tid;
+            if (sl < slices) {
+                if (vec) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) *(float4*)&v[i][4 * j] = __ldg((const float4*)(x + 16 * (int64_t)sl) + j);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[i][j] = __ldg(x + (16 * (int64_t)sl + j) * sk);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (base + i * THREADS >= slices) break;  // uniform over the CTA
+            const int sl = base + i * THREADS + tid;
+            const int slot = sl & 15;                 // slice within its unit
+            float best = 0.f;
+            int best_at = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (fabsf(v[i][j]) > fabsf(best)) { best = v[i][j]; best_at = 16 * slot + j; }
+            const int reach = step == 32 ? 1 : 8;     // partners: lane ^ 1, or the sixteen lanes of the unit
+            for (int off = 1; off <= reach; off <<= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+                const int oa = __shfl_xor_sync(0xffffffffu, best_at, off);
+                const bool take = fabsf(ob) > fabsf(best) || (fabsf(ob) == fabsf(best) && oa < best_at);
+                if (take) { best = ob; best_at = oa; }
+            }
+            const bool nonzero = fabsf(best) > 0.f;
+            const float inverse = nonzero ? __fdiv_rn(-127.0f, best) : 0.f;
+            const float d = nonzero ? __fdiv_rn(1.0f, inverse) : 0.f;
+            uint32_t cw[4];
+            int sum = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    int code = __float2int_rn(__fmul_rn(v[i][4 * j + b], inverse));
+                    code = code < -128 ? -128 : (code > 127 ? 127 : code);
+                    sum += code;
+                    word |= (uint32_t)(code & 0xff) << (8 * b);
+                }
+                cw[j] = word;
+            }
+            const int pair_sum = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
+            if (sl < slices) {
+                uint8_t* rec = rec_base + (size_t)(sl >> 4) * kRecord;
+                *(uint4*)(rec + 16 * slot) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+                ((int16_t*)(rec + 288))[slot] = (int16_t)sum;
+                if ((slot & 1) == 0) {
+                    ((float*)(rec + 256))[slot >> 1] = d;
+                    ((int16_t*)(rec + 320))[slot >> 1] = (int16_t)pair_sum;
+                }
+            }
+        }
+    }
+}
+
 // recipe's portable transcendentals for the expert epilogue (build.rs:1079-1176, math = "portable"):
 // tanh(x) = u / (u + 2), u = expm1(2x), evaluated in double and rounded once; sigmoid and silu as
 // the activation programs spell them (recipe.rs:22662-22668).
@@ -385,7 +628,7 @@ __device__ __forceinline__ float rq_sigmoid_portable(float x) { return __fmul_rn
 __device__ __forceinline__ float rq_silu_portable(float x) { return __fmul_rn(x, rq_sigmoid_portable(x)); }
 
 template <int TYPE, int MODE, int T, int NW>
-__global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+__global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int kConsumers = NW * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
@@ -403,6 +646,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
     // both index it with run-time values.
     __shared__ RqSegment table[RQ_MAX_SEGMENTS];
     __shared__ int plan_counts[4];
+    // what the producer put into each ring slot: rows, segment, first row (local to the segment), and where the
+    // first d value sits inside its 16-byte-aligned copy. Written before the copies are issued, read after they land.
+    __shared__ int4 stage_info[kMaxStages];
 
     RQ_STAMP(0);
     if (tid == 0) {
@@ -439,11 +685,12 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
         if (tid == kConsumers) {
             int issued = 0, seg = 0;
             int64_t r = row_begin;
+            int slot = 0;
+            uint32_t phase = 1;  // parity of the slot's previous round: the first round of the ring waits for nothing
             for (int st = 0; r < row_end; ++st) {
                 while (seg + 1 < n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
                 const RqSegment& sg = table[seg];
-                const int slot = st % p.stages;
-                if (st >= p.stages && !mbar_wait(&empty_bar[slot], ((st / p.stages) - 1) & 1)) { atomicExch(p.error_flag, 1); break; }
+                if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase)) { atomicExch(p.error_flag, 1); break; }
                 const int64_t seg_end = sg.row_begin + sg.rows;
                 int64_t stop = r + p.stage_rows;
                 if (stop > seg_end) stop = seg_end;
@@ -462,6 +709,8 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
                         total += (uint32_t)(((last + 15) & ~(uintptr_t)15) - (first & ~(uintptr_t)15));
                     }
                 }
+                stage_info[slot] = make_int4(nr, seg, (int)lr0,
+                                             TYPE != RQ_Q4_K ? (int)(((uintptr_t)sg.scale[0] + (uintptr_t)(lr0 * row_scales * 2)) & 15) : 0);
                 mbar_expect_tx(&full_bar[slot], total);
 #ifdef RQ_TRACE
                 if (p.trace && st < 16) p.trace[(size_t)blockIdx.x * 64 + 48 + st] = global_ns();
@@ -477,6 +726,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
                 }
                 issued = st + 1;
                 r = stop;
+                if (++slot == p.stages) { slot = 0; phase ^= 1; }
             }
             // leave only after every copy this CTA issued has landed (bounded)
             for (int st = (issued > p.stages ? issued - p.stages : 0); st < issued; ++st)
@@ -492,15 +742,36 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
         // works on one half of adjacent units: no divergence, no bank conflicts.
         const int su_cap = p.stage_rows * p.units;          // units of one sub-row in a full stage
         const int items_cap = 2 * p.subs * su_cap;
-        const int my_h = tid / (p.subs * su_cap);
+        int my_h = tid / (p.subs * su_cap);
         const int my_rem = tid - my_h * (p.subs * su_cap);
         const int my_s = my_rem / su_cap, my_su = my_rem - my_s * su_cap;
-        const int my_lr = my_su / p.units, my_u = my_su - my_lr * p.units;
+        const int my_lr = my_su / p.units;
+        int my_u = my_su - my_lr * p.units;
+        bool act_owner = tid < items_cap;   // this thread has an item, hence activations to hold
+        const int group = 2 * p.units;      // warp scheme: lanes per row
+        if (p.warp_rows) {
+            const int item = (tid & 31) & (group - 1);
+            my_h = item >= p.units ? 1 : 0;
+            my_u = item - my_h * p.units;
+            act_owner = true;
+        }
         ActHalf areg;
         if (MODE == RQ_ACT_INT8 && p.act_regs) {
-            // single token: this thread's 128 codes, steps and sums, straight from the scratch the
-            // quantiser wrote, kept in registers for the whole kernel
-            if (tid < items_cap) areg.load(p.act + ((size_t)tok0 * p.units + my_u) * kRecord, my_h);
+            // single token: this thread's 128 codes, steps and sums, kept in registers for the whole
+            // kernel. They come from the records an earlier launch left in the scratch, or (fused
+            // launches) from records this CTA makes of x right here, while its first weights fly.
+            if (p.fuse_step) {
+                quantise_to_smem<kConsumers>(p.x, p.sk, p.cols, p.fuse_step, act_smem, tid);
+                consumer_sync<kConsumers>();
+                if (act_owner) areg.load(act_smem + (size_t)my_u * kRecord, my_h);
+                if (blockIdx.x == 0 && p.act_out) {
+                    const uint4* src = (const uint4*)act_smem;
+                    uint4* dst = (uint4*)p.act_out;
+                    for (int i = tid; i < p.units * (kRecord / 16); i += kConsumers) dst[i] = src[i];
+                }
+            } else if (act_owner) {
+                areg.load(p.act + ((size_t)tok0 * p.units + my_u) * kRecord, my_h);
+            }
         } else if (MODE == RQ_ACT_FLOAT) {
             // stage the activations while the first weight stages are in flight
             for (int v = 0; v < p.act_vectors; ++v) {
@@ -536,35 +807,164 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
         }
         RQ_STAMP(1);
 
-        const int lane = tid & 31;
+        const int lane = tid & 31, warp = tid >> 5;
         bool dead = false;  // a wait ran out: no more waiting, the results are flagged invalid
         int seg = 0;
         int64_t r = row_begin;
-        for (int st = 0; r < row_end; ++st) {
-            while (seg + 1 < n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
-            const RqSegment& sg = table[seg];
-            const int64_t seg_end = sg.row_begin + sg.rows;
-            int64_t stop = r + p.stage_rows;
-            if (stop > seg_end) stop = seg_end;
-            if (stop > row_end) stop = row_end;
-            const int nr = (int)(stop - r);
-            const int64_t lr0 = r - sg.row_begin;
-            const int slot = st % p.stages;
-            if (!dead && !mbar_wait(&full_bar[slot], (st / p.stages) & 1)) { atomicExch(p.error_flag, 3); dead = true; }
-            RQ_STAMP(2 + 3 * st);
-            const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
-            float* part = partial + (size_t)(st & 1) * T * stage_items;
-            if (tid < items_cap && my_lr < nr && my_s < subs) {
-                const uint8_t* w = stage + (size_t)my_s * p.sub_main_bytes + (size_t)my_su * p.unit_bytes;
-                const uint16_t* sc = nullptr;
-                if (TYPE != RQ_Q4_K) {
-                    // where this sub-row's first d value sits inside its 16-byte-aligned copy
-                    const uintptr_t first = (uintptr_t)sg.scale[my_s] + (uintptr_t)(lr0 * row_scales * 2);
-                    sc = (const uint16_t*)(stage + (size_t)p.subs * p.sub_main_bytes + (size_t)my_s * p.sub_scale_bytes + (first & 15)) + (size_t)my_su * p.scales_per_unit;
+        int slot = 0;
+        uint32_t phase = 0;  // ring position and parity of the next stage
+        // A row's partial sums (its items, in shared memory) are added by eight adjacent lanes: each strides
+        // over the items, then a fixed xor tree joins the eight -- the same order, hence the same bits, on
+        // every run; sub-rows are joined by the epilogue in sub-row order. `first` = the task of this
+        // thread's lane group in the first sweep, `sweep` = tasks per sweep.
+        auto reduce_rows = [&](const float* part, const RqSegment& sg, int nr, int64_t lr0, int first, int sweep) {
+            const int l8 = lane & 7;
+            const int tasks = nr * T;
+            for (int base = 0; base < tasks; base += sweep) {  // uniform trip count: every lane takes part in the shuffles
+                const int task = base + first;
+                const bool live = task < tasks && tok0 + (task % T) < p.tokens;
+                const int lr = live ? task / T : 0, t = live ? task - lr * T : 0;
+                float out = 0.f, gate = 0.f;
+                for (int s = 0; s < subs; ++s) {
+                    const float* lo = part + t * stage_items + s * su_cap + lr * p.units;  // the row's half-0 partials
+                    const float* hi = lo + p.subs * su_cap;                                // and its half-1 partials
+                    float sum = 0.f;
+                    if (live)
+                        for (int j = l8; j < p.units; j += 8) sum += lo[j] + hi[j];
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    if (p.epilogue == RQ_EPI_GLU) { if (s == 0) gate = sum; else if (live && l8 == 0) out = rq_silu_portable(gate) * sum; }
+                    else if (p.epilogue == RQ_EPI_WSUM) out += sum * sg.coef[s];
+                    else out = sum;
                 }
-                if (MODE == RQ_ACT_INT8 && T == 1 && p.act_regs) {
-                    part[tid] = item_dot<TYPE, MODE>(w, sc, nullptr, areg, my_h);
-                } else {
+                if (live && l8 == 0) sg.y[(lr0 + lr) * p.yn + (int64_t)(tok0 + t) * p.yt] = out;
+            }
+        };
+        constexpr int kSweep = kConsumers / 8;  // row tasks per sweep of the consumer threads
+        if (MODE == RQ_ACT_INT8 && T == 1 && p.warp_rows) {
+            // ---- the warp scheme: no partial sums in shared memory, no CTA-wide barrier. A row's items are
+            // `group` adjacent lanes; a thread takes up to two rows of a stage (one per pass), holds their
+            // weights in registers, releases the stage, and the lanes of a row join their sums by an xor tree.
+            const int row_in_pass = warp * p.warp_rows + (lane / group);
+            const int rows_per_pass = NW * p.warp_rows;
+            const size_t my_off = (size_t)row_in_pass * row_bytes + (size_t)my_u * p.unit_bytes;
+            const size_t pass_bytes = (size_t)rows_per_pass * row_bytes;
+            const bool writer = (lane & (group - 1)) == 0;
+            while (r < row_end) {
+                if (!dead && !mbar_wait(&full_bar[slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                const int4 info = stage_info[slot];  // rows, segment, first local row, offset of the first d
+                const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+                ItemRegs<TYPE> wr[2];
+                bool have[2];
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int lr = row_in_pass + k * rows_per_pass;
+                    have[k] = k < p.rows_per_thread && lr < info.x;
+                    if (have[k]) {
+                        const uint16_t* sc = nullptr;
+                        if (TYPE != RQ_Q4_K) sc = (const uint16_t*)(stage + p.sub_main_bytes + info.w) + ((size_t)lr * p.units + my_u) * p.scales_per_unit;
+                        wr[k].load(stage + my_off + k * pass_bytes, sc, my_h);
+                    }
+                }
+                // the warp holds its weights in registers: the producer may refill the slot
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[slot]);
+                if (++slot == p.stages) { slot = 0; phase ^= 1; }
+                float v[2];
+#pragma unroll
+                for (int k = 0; k < 2; ++k) v[k] = have[k] ? dot_regs(wr[k], areg, my_h) : 0.f;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    if (off < group) {  // uniform over the launch
+                        v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+                        v[1] += __shfl_xor_sync(0xffffffffu, v[1], off);
+                    }
+                }
+                if (writer) {
+                    float* yb = table[info.y].y;
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)
+                        if (have[k]) yb[(int64_t)(info.z + row_in_pass + k * rows_per_pass) * p.yn + (int64_t)tok0 * p.yt] = v[k];
+                }
+                r += info.x;
+            }
+        } else if (MODE == RQ_ACT_INT8 && T == 1 && p.act_regs) {
+            // ---- register items, two stages per turn
+            constexpr int PAIR = TYPE == RQ_Q8_0 ? 1 : 2;
+            int buf = 0;
+            while (r < row_end) {
+                ItemRegs<TYPE> wr[PAIR];
+                bool have[PAIR];
+                int st_seg[PAIR], st_nr[PAIR];
+                int64_t st_lr0[PAIR];
+#pragma unroll
+                for (int k = 0; k < PAIR; ++k) {
+                    have[k] = false; st_nr[k] = 0; st_seg[k] = seg; st_lr0[k] = 0;
+                    if (r < row_end) {
+                        while (seg + 1 < n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
+                        const RqSegment& sg = table[seg];
+                        const int64_t seg_end = sg.row_begin + sg.rows;
+                        int64_t stop = r + p.stage_rows;
+                        if (stop > seg_end) stop = seg_end;
+                        if (stop > row_end) stop = row_end;
+                        const int nr = (int)(stop - r);
+                        const int64_t lr0 = r - sg.row_begin;
+                        st_seg[k] = seg; st_nr[k] = nr; st_lr0[k] = lr0;
+                        if (!dead && !mbar_wait(&full_bar[slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                        const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+                        have[k] = tid < items_cap && my_lr < nr && my_s < subs;
+                        if (have[k]) {
+                            const uint8_t* w = stage + (size_t)my_s * p.sub_main_bytes + (size_t)my_su * p.unit_bytes;
+                            const uint16_t* sc = nullptr;
+                            if (TYPE != RQ_Q4_K) {
+                                const uintptr_t first = (uintptr_t)sg.scale[my_s] + (uintptr_t)(lr0 * row_scales * 2);
+                                sc = (const uint16_t*)(stage + (size_t)p.subs * p.sub_main_bytes + (size_t)my_s * p.sub_scale_bytes + (first & 15)) + (size_t)my_su * p.scales_per_unit;
+                            }
+                            wr[k].load(w, sc, my_h);
+                        }
+                        // the warp holds its weights in registers: the producer may refill the slot
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&empty_bar[slot]);
+                        if (++slot == p.stages) { slot = 0; phase ^= 1; }
+                        r = stop;
+                    }
+                }
+                float* part = partial + (size_t)buf * PAIR * stage_items;
+                buf ^= 1;
+#pragma unroll
+                for (int k = 0; k < PAIR; ++k)
+                    if (have[k]) part[k * stage_items + tid] = dot_regs(wr[k], areg, my_h);
+                consumer_sync<kConsumers>();
+                // the rows of both stages, dealt to the warps in turn
+                reduce_rows(part, table[st_seg[0]], st_nr[0], st_lr0[0], tid >> 3, kSweep);
+                if (PAIR == 2 && st_nr[PAIR - 1] > 0) {
+                    const int shift = st_nr[0] % kSweep;  // carry the deal on where the first stage left it
+                    reduce_rows(part + stage_items, table[st_seg[PAIR - 1]], st_nr[PAIR - 1], st_lr0[PAIR - 1], ((tid >> 3) + kSweep - shift) % kSweep, kSweep);
+                }
+            }
+        } else {
+            for (int st = 0; r < row_end; ++st) {
+                while (seg + 1 < n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
+                const RqSegment& sg = table[seg];
+                const int64_t seg_end = sg.row_begin + sg.rows;
+                int64_t stop = r + p.stage_rows;
+                if (stop > seg_end) stop = seg_end;
+                if (stop > row_end) stop = row_end;
+                const int nr = (int)(stop - r);
+                const int64_t lr0 = r - sg.row_begin;
+                if (!dead && !mbar_wait(&full_bar[slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                RQ_STAMP(2 + 3 * st);
+                const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+                float* part = partial + (size_t)(st & 1) * T * stage_items;
+                if (tid < items_cap && my_lr < nr && my_s < subs) {
+                    const uint8_t* w = stage + (size_t)my_s * p.sub_main_bytes + (size_t)my_su * p.unit_bytes;
+                    const uint16_t* sc = nullptr;
+                    if (TYPE != RQ_Q4_K) {
+                        // where this sub-row's first d value sits inside its 16-byte-aligned copy
+                        const uintptr_t first = (uintptr_t)sg.scale[my_s] + (uintptr_t)(lr0 * row_scales * 2);
+                        sc = (const uint16_t*)(stage + (size_t)p.subs * p.sub_main_bytes + (size_t)my_s * p.sub_scale_bytes + (first & 15)) + (size_t)my_su * p.scales_per_unit;
+                    }
                     const uint8_t* a0 = act_smem + (size_t)sg.act[my_s] * p.act_bytes + (size_t)my_u * kRecord;
 #pragma unroll
                     for (int t = 0; t < T; ++t) {
@@ -573,31 +973,16 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 8 ? 2 : 1) rq_gemv_stream_
                         part[t * stage_items + tid] = item_dot<TYPE, MODE>(w, sc, ar, areg, my_h);
                     }
                 }
+                // this warp is done with the stage's weights: the producer may refill the slot
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[slot]);
+                if (++slot == p.stages) { slot = 0; phase ^= 1; }
+                RQ_STAMP(3 + 3 * st);
+                consumer_sync<kConsumers>();
+                RQ_STAMP(4 + 3 * st);
+                reduce_rows(part, sg, nr, lr0, tid >> 3, kSweep);
+                r = stop;
             }
-            // this warp is done with the stage's weights: the producer may refill the slot
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[slot]);
-            RQ_STAMP(3 + 3 * st);
-            consumer_sync<kConsumers>();
-            RQ_STAMP(4 + 3 * st);
-            // one thread per (row, token) adds the row's partials in sub-row, then item order
-            for (int i = tid; i < nr * T; i += kConsumers) {
-                const int lr = i / T, t = i - lr * T;
-                if (tok0 + t < p.tokens) {
-                    float out = 0.f, gate = 0.f;
-                    for (int s = 0; s < subs; ++s) {
-                        const float* lo = part + t * stage_items + s * su_cap + lr * p.units;  // the row's half-0 partials
-                        const float* hi = lo + p.subs * su_cap;                                // and its half-1 partials
-                        float sum = 0.f;
-                        for (int j = 0; j < p.units; ++j) sum += lo[j] + hi[j];
-                        if (p.epilogue == RQ_EPI_GLU) { if (s == 0) gate = sum; else out = rq_silu_portable(gate) * sum; }
-                        else if (p.epilogue == RQ_EPI_WSUM) out += sum * sg.coef[s];
-                        else out = sum;
-                    }
-                    sg.y[(lr0 + lr) * p.yn + (int64_t)(tok0 + t) * p.yt] = out;
-                }
-            }
-            r = stop;
         }
     }
 }
@@ -631,15 +1016,16 @@ int launch_stream(const StreamParams& p, int grid_x, size_t smem, cudaStream_t s
     return RQ_OK;
 }
 
-template <int TYPE, int MODE>
-int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s) {
+template <int TYPE, int MODE, int NW>
+int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s) {
     // Two CTAs share an SM (eight consumer warps and about 100 KB each): their barriers and waits
     // interleave, and when a CTA of one launch exits, a CTA of the next launch (programmatic
     // dependent launch) takes its place and prefetches weights while the other is still working.
     constexpr int kCtasPerSm = 2;
     constexpr size_t kSmemBudget = 104 * 1024;  // dynamic; the segment table and barriers are static
     constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
-    constexpr int NW = 8;  // consumer warps
+    // NW = consumer warps: seven, so that with the producer warp a CTA is eight warps and two CTAs per SM leave each
+    // thread 128 registers; eight (one CTA per SM then) only for rows too long for seven warps' worth of items.
     constexpr int kConsumers = NW * 32;
     p.act_bytes = ((size_t)p.units * kRecord + 127) & ~(size_t)127;
     int t = 1;
@@ -651,7 +1037,8 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
     }
     // single-token INT8 launches whose sub-rows all read vector 0 keep the activations in registers
     p.act_regs = (MODE == RQ_ACT_INT8 && t == 1 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr) ? 1 : 0;
-    if (p.act_regs) p.act_vectors = 0;  // nothing staged: the threads read the scratch directly
+    if (p.fuse_step && !p.act_regs) return RQ_ERR_UNSUPPORTED;  // the caller quantises with the standalone kernel instead
+    if (p.act_regs) p.act_vectors = p.fuse_step ? 1 : 0;        // fused: one token's records are made in shared memory; else nothing is staged
     if (p.act_bytes * p.act_vectors > 64 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
     const int ctas = sm_count * kCtasPerSm;
@@ -663,11 +1050,21 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
     int stage_rows = kConsumers / ipr;
     while (stage_rows > 1 && (int64_t)stage_rows * row_bytes * p.subs > 32 * 1024) --stage_rows;
     if (stage_rows > rows_per_cta) stage_rows = (int)rows_per_cta;
+    // The warp scheme: plain single-sub-row launches with register activations whose rows are a power
+    // of two of items, at most a warp's worth.
+    p.warp_rows = 0; p.rows_per_thread = 0;
+    if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && ipr <= 32 && (ipr & (ipr - 1)) == 0) {
+        p.warp_rows = 32 / ipr;
+        const int pass_rows = NW * p.warp_rows;
+        p.rows_per_thread = (int64_t)2 * pass_rows * row_bytes <= 34 * 1024 && rows_per_cta > pass_rows ? 2 : 1;
+        stage_rows = pass_rows * p.rows_per_thread;
+    }
     p.stage_rows = stage_rows;
     p.sub_main_bytes = ((size_t)stage_rows * row_bytes + 127) & ~(size_t)127;
     p.sub_scale_bytes = p.scales_per_unit ? (((size_t)stage_rows * p.units * p.scales_per_unit * 2 + 32 + 127) & ~(size_t)127) : 0;
     p.stage_bytes = (p.sub_main_bytes + p.sub_scale_bytes) * p.subs;
-    p.partial_bytes = ((size_t)2 * t * stage_rows * ipr * 4 + 127) & ~(size_t)127;
+    p.partial_bytes = ((size_t)2 * (t == 1 ? 2 : t) * stage_rows * ipr * 4 + 127) & ~(size_t)127;  // two buffers of T stages (of a pair of stages when T = 1)
+    if (p.warp_rows) p.partial_bytes = 0;
     const size_t fixed = p.act_bytes * p.act_vectors + p.partial_bytes;
     if (fixed + 2 * p.stage_bytes > kSmemBudget) return RQ_ERR_UNSUPPORTED;
     int stages = (int)((kSmemBudget - fixed) / p.stage_bytes);
@@ -676,6 +1073,12 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
     const size_t smem = fixed + (size_t)stages * p.stage_bytes;
     const int grid_x = (int)(p.rows < ctas ? p.rows : ctas);
     return t == 4 ? launch_stream<TYPE, MODE, 4, NW>(p, grid_x, smem, s) : launch_stream<TYPE, MODE, 1, NW>(p, grid_x, smem, s);
+}
+
+template <int TYPE, int MODE>
+int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s) {
+    if (2 * p.units * p.subs > 7 * 32) return dispatch_stream_nw<TYPE, MODE, 8>(p, sm_count, vectors_per_launch, s);
+    return dispatch_stream_nw<TYPE, MODE, 7>(p, sm_count, vectors_per_launch, s);
 }
 
 }  // namespace
@@ -699,7 +1102,7 @@ extern "C" int rq_trace_read(unsigned long long* host, int ctas) {
 // many slot vectors. Returns RQ_ERR_UNSUPPORTED (without error text) when the shape is not served.
 int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table, const RqSegment* inline_seg, int n_segments, int subs,
                      int epilogue, int64_t total_rows, const float* x, int64_t sk, int64_t st, int tokens, int vectors_per_launch,
-                     int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s) {
+                     int64_t yn, int64_t yt, int act_mode, const uint8_t* act, int fuse_step, uint8_t* act_out, cudaStream_t s) {
     if (cols % 256 || subs < 1 || subs > RQ_MAX_SUB) return RQ_ERR_UNSUPPORTED;
     if ((!table && n_segments > RQ_INLINE_SEGMENTS) || n_segments < 1 || n_segments > RQ_MAX_SEGMENTS) return RQ_ERR_UNSUPPORTED;
     StreamParams p;
@@ -709,6 +1112,7 @@ int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table
     p.n_segments = n_segments; p.subs = subs; p.epilogue = epilogue;
     p.rows = total_rows; p.cols = (int)cols; p.units = (int)(cols / 256);
     p.x = x; p.sk = sk; p.st = st; p.act = act; p.yn = yn; p.yt = yt; p.tokens = tokens;
+    p.fuse_step = act_mode == RQ_ACT_INT8 ? fuse_step : 0; p.act_out = act_out;
     p.error_flag = ctx->error_flag;
 #ifdef RQ_TRACE
     p.trace = rq_trace_buffer();
@@ -762,10 +1166,10 @@ int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* pla
 }
 
 int rq_launch_gemv_stream(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
-                          float* y, int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s) {
+                          float* y, int64_t yn, int64_t yt, int act_mode, const uint8_t* act, int fuse_step, uint8_t* act_out, cudaStream_t s) {
     RqSegment seg;
     memset(&seg, 0, sizeof(seg));
     seg.row_begin = 0; seg.rows = (int)w->rows; seg.y = y;
     seg.main[0] = w->main; seg.scale[0] = w->scale; seg.act[0] = 0; seg.coef[0] = 1.0f;
-    return rq_launch_stream(ctx, w->type, w->cols, nullptr, &seg, 1, 1, RQ_EPI_PLAIN, w->rows, x, sk, st, tokens, 0, yn, yt, act_mode, act, s);
+    return rq_launch_stream(ctx, w->type, w->cols, nullptr, &seg, 1, 1, RQ_EPI_PLAIN, w->rows, x, sk, st, tokens, 0, yn, yt, act_mode, act, fuse_step, act_out, s);
 }

@@ -117,10 +117,13 @@ int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* pla
                           const float* x, int64_t sk, int64_t st, int vectors, int64_t yn, int64_t yt, cudaStream_t s);
 int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table, const RqSegment* inline_seg, int n_segments, int subs,
                      int epilogue, int64_t total_rows, const float* x, int64_t sk, int64_t st, int tokens, int vectors_per_launch,
-                     int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s);
-// RQ_ERR_UNSUPPORTED (no error text) = shape not served by the streaming kernel
+                     int64_t yn, int64_t yt, int act_mode, const uint8_t* act, int fuse_step, uint8_t* act_out, cudaStream_t s);
+// RQ_ERR_UNSUPPORTED (no error text) = shape not served by the streaming kernel.
+// fuse_step = 32 / 256: an INT8 launch quantises x itself in its prologue (single token; nothing is
+// launched when the shape cannot be served that way) and leaves the records at act_out; 0: the
+// records are read from `act`.
 int rq_launch_gemv_stream(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,
-                          float* y, int64_t yn, int64_t yt, int act_mode, const uint8_t* act, cudaStream_t s);
+                          float* y, int64_t yn, int64_t yt, int act_mode, const uint8_t* act, int fuse_step, uint8_t* act_out, cudaStream_t s);
 
 // ---------------------------------------------------------------------------------
 // device helpers

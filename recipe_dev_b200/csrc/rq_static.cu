@@ -55,7 +55,7 @@ extern "C" int rq_matvec_int8_static(rq_ctx* ctx, const rq_weight* w, const floa
     cudaStream_t s = (cudaStream_t)stream;
     rc = rq_launch_act_quant(x, 1, w->cols, w->cols, 1, step, scratch, nullptr, s);
     if (rc) return rc;
-    rc = rq_launch_gemv_stream(ctx, w, x, 1, w->cols, 1, y, 1, w->rows, RQ_ACT_INT8, scratch, s);
+    rc = rq_launch_gemv_stream(ctx, w, x, 1, w->cols, 1, y, 1, w->rows, RQ_ACT_INT8, scratch, 0, nullptr, s);
     if (rc != RQ_ERR_UNSUPPORTED) return rc;
     return rq_launch_gemv_tiled_int8(ctx, w, 1, y, 1, w->rows, scratch, s);
 }
