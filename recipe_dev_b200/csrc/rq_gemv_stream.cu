@@ -57,6 +57,11 @@ struct StreamParams {
     int warp_rows;             // > 0: the warp scheme -- a row's 2 * units items are that many adjacent lanes (a power of two), a warp
                                // pass covers warp_rows = 32 / (2 * units) rows, and the lanes of a row join their sums by shuffles
     int rows_per_thread;       // warp scheme: passes per stage (1 or 2)
+    int row_warps;             // warp scheme: 1 = a row lies inside one warp; NW = every warp holds 32 / warp_rows lanes' worth of
+                               // each row of the pass, and the warps' sums meet in shared memory (the last warp to arrive adds them)
+    int sum_group, sum_chunks; // the order a row's item sums are added in when the shape has a warp scheme (so that a multi-token
+                               // launch gives each token the bits a single-token launch gives it): chunks of sum_group items, an
+                               // xor tree inside a chunk, chunks in order. sum_group = 0: items strided over eight lanes, then a tree
     int fuse_step;             // act_regs launches: 32 or 256 = quantise x in the prologue (no quantiser launch before), 0 = read `act`
     uint8_t* act_out;          // fused launches: CTA 0 leaves the records here for later INT8_CACHED calls
     const float* x; int64_t sk, st;   // FLOAT: vector v is x + v * st, element stride sk
@@ -649,10 +654,15 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
     // what the producer put into each ring slot: rows, segment, first row (local to the segment), and where the
     // first d value sits inside its 16-byte-aligned copy. Written before the copies are issued, read after they land.
     __shared__ int4 stage_info[kMaxStages];
+    // warp scheme with rows split over the warps: per stage in flight, each warp's sum of each row, and how many warps have
+    // delivered. A warp is never more than the ring's depth ahead of the slowest, so kMaxStages + 1 buffers never collide.
+    __shared__ float cross_sum[kMaxStages + 1][8][NW];
+    __shared__ int cross_count[kMaxStages + 1];
 
     RQ_STAMP(0);
     if (tid == 0) {
         for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NW); }
+        for (int s = 0; s <= kMaxStages; ++s) cross_count[s] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Programmatic dependent launch: the next kernel in the stream may start its own prologue now.
@@ -748,12 +758,12 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
         const int my_lr = my_su / p.units;
         int my_u = my_su - my_lr * p.units;
         bool act_owner = tid < items_cap;   // this thread has an item, hence activations to hold
-        const int group = 2 * p.units;      // warp scheme: lanes per row
+        const int group = p.warp_rows ? 32 / p.warp_rows : 32;  // warp scheme: lanes per row, the power of two that holds its 2 * units items
         if (p.warp_rows) {
-            const int item = (tid & 31) & (group - 1);
-            my_h = item >= p.units ? 1 : 0;
-            my_u = item - my_h * p.units;
-            act_owner = true;
+            const int item = ((tid & 31) & (group - 1)) + (p.row_warps > 1 ? (tid >> 5) * group : 0);
+            act_owner = item < 2 * p.units;   // a row whose items are no power of two leaves the group's last lanes idle
+            my_h = item >= p.units && act_owner ? 1 : 0;
+            my_u = act_owner ? item - my_h * p.units : 0;
         }
         ActHalf areg;
         if (MODE == RQ_ACT_INT8 && p.act_regs) {
@@ -829,11 +839,30 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                     const float* lo = part + t * stage_items + s * su_cap + lr * p.units;  // the row's half-0 partials
                     const float* hi = lo + p.subs * su_cap;                                // and its half-1 partials
                     float sum = 0.f;
-                    if (live)
-                        for (int j = l8; j < p.units; j += 8) sum += lo[j] + hi[j];
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    if (p.sum_group) {
+                        const int q = p.sum_group;
+                        for (int c = 0; c < p.sum_chunks; ++c) {
+                            float w4[4];
+#pragma unroll
+                            for (int m = 0; m < 4; ++m) {
+                                const int idx = c * q + l8 + 8 * m;  // item of the row: half-0 items first, then half-1
+                                w4[m] = (live && l8 + 8 * m < q && idx < 2 * p.units) ? (idx < p.units ? lo[idx] : hi[idx - p.units]) : 0.f;
+                            }
+                            if (q == 32) { w4[0] += w4[2]; w4[1] += w4[3]; }
+                            if (q >= 16) w4[0] += w4[1];
+                            float cs = w4[0];
+                            if (q > 4) cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+                            if (q > 2) cs += __shfl_xor_sync(0xffffffffu, cs, 2);
+                            cs += __shfl_xor_sync(0xffffffffu, cs, 1);
+                            sum = p.sum_chunks == 1 ? cs : sum + cs;
+                        }
+                    } else {
+                        if (live)
+                            for (int j = l8; j < p.units; j += 8) sum += lo[j] + hi[j];
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    }
                     if (p.epilogue == RQ_EPI_GLU) { if (s == 0) gate = sum; else if (live && l8 == 0) out = rq_silu_portable(gate) * sum; }
                     else if (p.epilogue == RQ_EPI_WSUM) out += sum * sg.coef[s];
                     else out = sum;
@@ -846,8 +875,10 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             // ---- the warp scheme: no partial sums in shared memory, no CTA-wide barrier. A row's items are
             // `group` adjacent lanes; a thread takes up to two rows of a stage (one per pass), holds their
             // weights in registers, releases the stage, and the lanes of a row join their sums by an xor tree.
-            const int row_in_pass = warp * p.warp_rows + (lane / group);
-            const int rows_per_pass = NW * p.warp_rows;
+            const bool split = p.row_warps > 1;
+            const int row_in_pass = (split ? 0 : warp * p.warp_rows) + (lane / group);
+            const int rows_per_pass = (split ? 1 : NW) * p.warp_rows;
+            int cross_buf = 0;
             const size_t my_off = (size_t)row_in_pass * row_bytes + (size_t)my_u * p.unit_bytes;
             const size_t pass_bytes = (size_t)rows_per_pass * row_bytes;
             const bool writer = (lane & (group - 1)) == 0;
@@ -860,7 +891,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
 #pragma unroll
                 for (int k = 0; k < 2; ++k) {
                     const int lr = row_in_pass + k * rows_per_pass;
-                    have[k] = k < p.rows_per_thread && lr < info.x;
+                    have[k] = k < p.rows_per_thread && lr < info.x && act_owner;
                     if (have[k]) {
                         const uint16_t* sc = nullptr;
                         if (TYPE != RQ_Q4_K) sc = (const uint16_t*)(stage + p.sub_main_bytes + info.w) + ((size_t)lr * p.units + my_u) * p.scales_per_unit;
@@ -881,11 +912,39 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                         v[1] += __shfl_xor_sync(0xffffffffu, v[1], off);
                     }
                 }
-                if (writer) {
-                    float* yb = table[info.y].y;
+                if (!split) {
+                    if (writer) {
+                        float* yb = table[info.y].y;
 #pragma unroll
-                    for (int k = 0; k < 2; ++k)
-                        if (have[k]) yb[(int64_t)(info.z + row_in_pass + k * rows_per_pass) * p.yn + (int64_t)tok0 * p.yt] = v[k];
+                        for (int k = 0; k < 2; ++k)
+                            if (have[k]) yb[(int64_t)(info.z + row_in_pass + k * rows_per_pass) * p.yn + (int64_t)tok0 * p.yt] = v[k];
+                    }
+                } else {
+                    // this warp's share of each row goes to shared memory; the warp that finds the others all
+                    // there adds the shares in warp order (whichever warp that is, the order is the same)
+                    if (writer) {
+#pragma unroll
+                        for (int k = 0; k < 2; ++k)
+                            if (k < p.rows_per_thread) cross_sum[cross_buf][row_in_pass + k * rows_per_pass][warp] = v[k];
+                    }
+                    __threadfence_block();
+                    __syncwarp();
+                    int arrived = 0;
+                    if (lane == 0) arrived = atomicAdd(&cross_count[cross_buf], 1);
+                    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                    if (arrived == NW - 1) {
+                        __threadfence_block();
+                        const int rows_here = info.x;
+                        if (lane < rows_here && lane < 8) {
+                            float out = 0.f;
+#pragma unroll
+                            for (int w = 0; w < NW; ++w) out += *(volatile float*)&cross_sum[cross_buf][lane][w];
+                            table[info.y].y[(int64_t)(info.z + lane) * p.yn + (int64_t)tok0 * p.yt] = out;
+                        }
+                        __syncwarp();
+                        if (lane == 0) cross_count[cross_buf] = 0;
+                    }
+                    if (++cross_buf > kMaxStages) cross_buf = 0;
                 }
                 r += info.x;
             }
@@ -1022,7 +1081,7 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     // interleave, and when a CTA of one launch exits, a CTA of the next launch (programmatic
     // dependent launch) takes its place and prefetches weights while the other is still working.
     constexpr int kCtasPerSm = 2;
-    constexpr size_t kSmemBudget = 104 * 1024;  // dynamic; the segment table and barriers are static
+    constexpr size_t kSmemBudget = 102 * 1024;  // dynamic; with the static tables (about 10 KB) and the 1 KB the system keeps per CTA, two CTAs fit an SM's 228 KB
     constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
     // NW = consumer warps: seven, so that with the producer warp a CTA is eight warps and two CTAs per SM leave each
     // thread 128 registers; eight (one CTA per SM then) only for rows too long for seven warps' worth of items.
@@ -1053,11 +1112,30 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     // The warp scheme: plain single-sub-row launches with register activations whose rows are a power
     // of two of items, at most a warp's worth.
     p.warp_rows = 0; p.rows_per_thread = 0;
-    if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && ipr <= 32 && (ipr & (ipr - 1)) == 0) {
-        p.warp_rows = 32 / ipr;
+    p.row_warps = 1;
+    p.sum_group = 0; p.sum_chunks = 1;
+    const bool warp_shape = MODE == RQ_ACT_INT8 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN;
+    const bool split_shape = ipr % NW == 0 && ipr / NW <= 32 && ipr / NW >= 8 && ((ipr / NW) & (ipr / NW - 1)) == 0;
+    if (warp_shape && ipr <= 32) {
+        p.sum_group = 2;
+        while (p.sum_group < ipr) p.sum_group <<= 1;
+    } else if (warp_shape && split_shape) {
+        p.sum_group = ipr / NW; p.sum_chunks = NW;
+    }
+    if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && ipr <= 32) {
+        int group = 2;
+        while (group < ipr) group <<= 1;
+        p.warp_rows = 32 / group;
         const int pass_rows = NW * p.warp_rows;
         p.rows_per_thread = (int64_t)2 * pass_rows * row_bytes <= 34 * 1024 && rows_per_cta > pass_rows ? 2 : 1;
         stage_rows = pass_rows * p.rows_per_thread;
+    } else if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && split_shape) {
+        // longer rows whose items split evenly over the warps, a power of two of lanes each (14336 inputs: 7 x 16)
+        const int group = ipr / NW;
+        p.warp_rows = 32 / group;
+        p.row_warps = NW;
+        p.rows_per_thread = (int64_t)2 * p.warp_rows * row_bytes <= 34 * 1024 && rows_per_cta > p.warp_rows ? 2 : 1;
+        stage_rows = p.warp_rows * p.rows_per_thread;
     }
     p.stage_rows = stage_rows;
     p.sub_main_bytes = ((size_t)stage_rows * row_bytes + 127) & ~(size_t)127;

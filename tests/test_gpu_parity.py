@@ -230,3 +230,42 @@ def test_matvec_multi_equals_single(rq_ctx, oracle, t, cols, mode, step):
     for y, ref in zip(ys, singles):
         assert np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
     rq_ctx.check()
+
+
+@pytest.mark.parametrize("step", [32, 256])
+@pytest.mark.parametrize("t,rows,cols", [(ol.Q4_K, 70, 4096), (ol.Q6_K, 33, 14336), (ol.Q6_K, 61, 2560), (ol.Q4_K, 50, 512), (ol.Q4_K, 9, 14336),
+                                         (ol.Q8_0, 40, 2048), (ol.Q4_0, 40, 1024), (ol.Q4_K, 21, 8192)])
+def test_int8_window_equals_positions_on_every_kernel_scheme(rq_ctx, oracle, t, rows, cols, step):
+    """The single-token int8 matvec runs one of three schemes by row length (a row inside a warp, a row
+    split over the warps, partial sums through shared memory); a multi-token window must give every
+    position the bits its own single-token call gives (suite.rs:343-371), whichever scheme that is."""
+    tokens = 3
+    blocks = oracle.quantize(t, oracle.normal(14, t + cols, rows * cols, 0.02))
+    x = oracle.normal(14, 7 + t, tokens * cols, 1.0).reshape(tokens, cols)
+    w = rq_ctx.weight_from_host(t, blocks, rows, cols)
+    y = rq_ctx.matvec(w, torch_cuda(x), act_mode=1, step=step).cpu().numpy()
+    # integer dots are exact; what is left is fp32 summation order over up to 14336 inputs
+    assert rel_err(y, oracle.matvec(t, blocks, rows, cols, x, ol.INT8, step)) <= 2e-4
+    for p in range(tokens):
+        one = rq_ctx.matvec(w, torch_cuda(x[p]), act_mode=1, step=step).cpu().numpy()
+        assert np.array_equal(one.view(np.uint32), y[p].view(np.uint32)), p
+        # the records the fused launch left behind serve a cached call with the same bits
+        again = rq_ctx.matvec(w, torch_cuda(x[p]), act_mode=2, step=step).cpu().numpy()
+        assert np.array_equal(one.view(np.uint32), again.view(np.uint32)), p
+    rq_ctx.check()
+
+
+@pytest.mark.parametrize("t,cols", [(ol.Q4_K, 4096), (ol.Q6_K, 14336), (ol.Q6_K, 2560)])
+def test_fused_quantiser_equals_standalone_quantiser(rq_ctx, oracle, t, cols):
+    """rq_matvec (int8) quantises x inside the matvec launch; rq_matvec_int8_static runs the standalone
+    quantiser kernel first. Same records, same kernel after them: the same bits."""
+    rows = 40
+    blocks = oracle.quantize(t, oracle.normal(15, t, rows * cols, 0.02))
+    x = oracle.normal(15, 1, cols, 1.0)
+    big = float(np.abs(x).max()) * 2
+    x[5], x[20] = big, -big  # a tie in magnitude inside one group: the first index wins
+    w = rq_ctx.weight_from_host(t, blocks, rows, cols)
+    for step in (32, 256):
+        fused = rq_ctx.matvec(w, torch_cuda(x), act_mode=1, step=step).cpu().numpy()
+        static = rq_ctx.matvec_int8_static(w, torch_cuda(x), step=step).cpu().numpy()
+        assert np.array_equal(fused.view(np.uint32), static.view(np.uint32))
