@@ -19,6 +19,7 @@
 // error code in the context's flag word and stops waiting (it keeps walking its loop, so the
 // CTA's barriers still balance); the CTA drains the copies it issued before it exits. A set
 // flag makes the next rq_check() fail.
+#include <stdlib.h>
 #include <string.h>
 
 #include "rq_internal.cuh"
@@ -46,6 +47,8 @@ struct StreamParams {
     RqSegment inline_seg[RQ_INLINE_SEGMENTS];
     int n_segments, subs, epilogue;
     int64_t rows;              // virtual rows of all segments
+    int64_t rows_quot; int rows_rem;  // rows / CTAs and rows % CTAs (launches whose row count the host knows): CTA b takes
+                               // rows_quot rows from b * rows_quot + min(b, rows_rem), one more when b < rows_rem
     int cols, units;           // units = cols / 256 per row
     int unit_bytes;            // bytes of one unit in the main plane: 144, 208, 256, 128
     int scales_per_unit;       // fp16 d values per unit in the scale plane: 0, 1, 8, 8
@@ -103,9 +106,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (global_ns() - t0 > kWaitLimitNs) return false;
     return true;
 }
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes),
-                 "r"(smem_u32(bar))
+// Weights are read once per launch: the copies carry an evict-first L2 policy, so the stream does not push
+// the activations, the outputs and the kernel's own code out of L2 between launches.
+__device__ __forceinline__ uint64_t evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst)), "l"(src),
+                 "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
                  : "memory");
 }
 template <int THREADS>
@@ -513,7 +523,7 @@ __device__ __forceinline__ float dot_regs(const ItemRegs<RQ_Q4_0>& r, const ActH
 
 // The int8 activation quantiser inside the matvec's prologue: the CTA's consumer threads turn the
 // `cols` inputs of one token into unit records in shared memory. A thread owns slices of sixteen
-// inputs (all its loads are issued before any arithmetic, so the prologue costs one trip to L2);
+// inputs, one slice per round, the next round's loads in flight while it works on this round's;
 // the two threads of a 32-value group, or the sixteen of a 256-value group, agree on the extreme
 // by shuffles. Same arithmetic as the standalone quantiser: the extreme is the FIRST input of
 // strictly largest magnitude, inverse = -127 / extreme, d = 1 / inverse (IEEE divides),
@@ -523,69 +533,69 @@ __device__ __forceinline__ void quantise_to_smem(const float* __restrict__ x, in
     constexpr int kRecord = RQ_ACT_RECORD_INT8;
     const int slices = cols >> 4;
     const bool vec = sk == 1 && ((uintptr_t)x & 15) == 0;
-    for (int base = 0; base < slices; base += 4 * THREADS) {
-        float v[4][16];
+    auto fetch = [&](int sl, float* v) {
+        if (sl < slices) {
+            if (vec) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int sl = base + i * THREADS + tid;
-            if (sl < slices) {
-                if (vec) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) *(float4*)&v[i][4 * j] = __ldg((const float4*)(x + 16 * (int64_t)sl) + j);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[i][j] = __ldg(x + (16 * (int64_t)sl + j) * sk);
-                }
+                for (int j = 0; j < 4; ++j) *(float4*)&v[4 * j] = __ldg((const float4*)(x + 16 * (int64_t)sl) + j);
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
+                for (int j = 0; j < 16; ++j) v[j] = __ldg(x + (16 * (int64_t)sl + j) * sk);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+    };
+    // one slice per thread per round; the next round's inputs are on their way while this round's are worked on
+    float cur[16], nxt[16];
+    fetch(tid, cur);
+#pragma unroll 1
+    for (int base = 0; base < slices; base += THREADS) {  // uniform over the CTA: every lane takes part in the shuffles
+        const int sl = base + tid;
+        fetch(sl + THREADS, nxt);
+        const int slot = sl & 15;                 // slice within its unit
+        float best = 0.f;
+        int best_at = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (fabsf(cur[j]) > fabsf(best)) { best = cur[j]; best_at = 16 * slot + j; }
+        const int reach = step == 32 ? 1 : 8;     // partners: lane ^ 1, or the sixteen lanes of the unit
+        for (int off = 1; off <= reach; off <<= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oa = __shfl_xor_sync(0xffffffffu, best_at, off);
+            const bool take = fabsf(ob) > fabsf(best) || (fabsf(ob) == fabsf(best) && oa < best_at);
+            if (take) { best = ob; best_at = oa; }
+        }
+        const bool nonzero = fabsf(best) > 0.f;
+        const float inverse = nonzero ? __fdiv_rn(-127.0f, best) : 0.f;
+        const float d = nonzero ? __fdiv_rn(1.0f, inverse) : 0.f;
+        uint32_t cw[4];
+        int sum = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                int code = __float2int_rn(__fmul_rn(cur[4 * j + b], inverse));
+                code = code < -128 ? -128 : (code > 127 ? 127 : code);
+                sum += code;
+                word |= (uint32_t)(code & 0xff) << (8 * b);
+            }
+            cw[j] = word;
+        }
+        const int pair_sum = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
+        if (sl < slices) {
+            uint8_t* rec = rec_base + (size_t)(sl >> 4) * kRecord;
+            *(uint4*)(rec + 16 * slot) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+            ((int16_t*)(rec + 288))[slot] = (int16_t)sum;
+            if ((slot & 1) == 0) {
+                ((float*)(rec + 256))[slot >> 1] = d;
+                ((int16_t*)(rec + 320))[slot >> 1] = (int16_t)pair_sum;
             }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (base + i * THREADS >= slices) break;  // uniform over the CTA
-            const int sl = base + i * THREADS + tid;
-            const int slot = sl & 15;                 // slice within its unit
-            float best = 0.f;
-            int best_at = 0x7fffffff;
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (fabsf(v[i][j]) > fabsf(best)) { best = v[i][j]; best_at = 16 * slot + j; }
-            const int reach = step == 32 ? 1 : 8;     // partners: lane ^ 1, or the sixteen lanes of the unit
-            for (int off = 1; off <= reach; off <<= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-                const int oa = __shfl_xor_sync(0xffffffffu, best_at, off);
-                const bool take = fabsf(ob) > fabsf(best) || (fabsf(ob) == fabsf(best) && oa < best_at);
-                if (take) { best = ob; best_at = oa; }
-            }
-            const bool nonzero = fabsf(best) > 0.f;
-            const float inverse = nonzero ? __fdiv_rn(-127.0f, best) : 0.f;
-            const float d = nonzero ? __fdiv_rn(1.0f, inverse) : 0.f;
-            uint32_t cw[4];
-            int sum = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t word = 0;
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    int code = __float2int_rn(__fmul_rn(v[i][4 * j + b], inverse));
-                    code = code < -128 ? -128 : (code > 127 ? 127 : code);
-                    sum += code;
-                    word |= (uint32_t)(code & 0xff) << (8 * b);
-                }
-                cw[j] = word;
-            }
-            const int pair_sum = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
-            if (sl < slices) {
-                uint8_t* rec = rec_base + (size_t)(sl >> 4) * kRecord;
-                *(uint4*)(rec + 16 * slot) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
-                ((int16_t*)(rec + 288))[slot] = (int16_t)sum;
-                if ((slot & 1) == 0) {
-                    ((float*)(rec + 256))[slot >> 1] = d;
-                    ((int16_t*)(rec + 320))[slot >> 1] = (int16_t)pair_sum;
-                }
-            }
-        }
+        for (int j = 0; j < 16; ++j) cur[j] = nxt[j];
     }
 }
 
@@ -660,47 +670,40 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
     __shared__ int cross_count[kMaxStages + 1];
 
     RQ_STAMP(0);
-    if (tid == 0) {
-        for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NW); }
-        for (int s = 0; s <= kMaxStages; ++s) cross_count[s] = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
     // Programmatic dependent launch: the next kernel in the stream may start its own prologue now.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    {
-        // A table in device memory may have been written by the kernel before this one: wait for it.
-        // An inline table came with the launch, and the weights are constants of the model, so the
-        // producer of a plain matvec streams weights while the previous kernel is still running.
-        if (p.table || p.plan) asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (p.plan && tid == 0) { plan_counts[0] = p.plan->n_segments; plan_counts[1] = p.plan->subs; plan_counts[2] = p.plan->total_rows; }
-        const int n_copy = p.plan ? p.plan->n_segments : p.n_segments;
-        const uint32_t* src = (const uint32_t*)(p.plan ? p.plan->seg : (p.table ? p.table : p.inline_seg));
-        uint32_t* dst = (uint32_t*)table;
-        const int words = (n_copy < RQ_MAX_SEGMENTS ? n_copy : RQ_MAX_SEGMENTS) * (int)(sizeof(RqSegment) / 4);
-        for (int i = tid; i < words; i += blockDim.x) dst[i] = src[i];
-    }
-    __syncthreads();
-    // counts: from the launch, or (planned launches) from the device-side plan, never above the launch's
-    const int n_segments = p.plan ? min(plan_counts[0], p.n_segments) : p.n_segments;
-    const int subs = p.plan ? min(plan_counts[1], p.subs) : p.subs;
-    const int64_t rows = p.plan ? min((int64_t)plan_counts[2], p.rows) : p.rows;
-    // this CTA's virtual rows: an even split, sizes differ by at most one
-    const int64_t row_begin = (rows * (int64_t)blockIdx.x) / gridDim.x;
-    const int64_t row_end = (rows * (int64_t)(blockIdx.x + 1)) / gridDim.x;
-
     const int tok0 = blockIdx.y * T;
+    // An inline table came with the launch and the weights are constants of the model: the producer of such a
+    // launch streams weights from its first instruction on, whatever the previous kernel is doing. A table or
+    // plan in device memory may have been written by the kernel before: it is read after griddepcontrol.wait.
+    const bool direct = p.table == nullptr && p.plan == nullptr;
+    int n_segments = p.n_segments, subs = p.subs;
+    int64_t row_begin = 0, row_end = 0;
+    auto split_rows = [&](int64_t rows) {
+        if (p.plan) {
+            row_begin = (rows * (int64_t)blockIdx.x) / gridDim.x;
+            row_end = (rows * (int64_t)(blockIdx.x + 1)) / gridDim.x;
+        } else {
+            const int b = (int)blockIdx.x;
+            row_begin = b * p.rows_quot + (b < p.rows_rem ? b : p.rows_rem);
+            row_end = row_begin + p.rows_quot + (b < p.rows_rem ? 1 : 0);
+        }
+    };
 
     if (tid >= kConsumers) {
-        // ---------------------------------------------------------------- producer warp
-        if (tid == kConsumers) {
-            int issued = 0, seg = 0;
-            int64_t r = row_begin;
-            int slot = 0;
-            uint32_t phase = 1;  // parity of the slot's previous round: the first round of the ring waits for nothing
-            for (int st = 0; r < row_end; ++st) {
-                while (seg + 1 < n_segments && r >= table[seg].row_begin + table[seg].rows) ++seg;
-                const RqSegment& sg = table[seg];
-                if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase)) { atomicExch(p.error_flag, 1); break; }
+        // ---------------------------------------------------------------- producer warp (lane 0 works)
+        int issued = 0, seg = 0, slot = 0, st = 0;
+        uint32_t phase = 1;  // parity of the slot's previous round: the first round of the ring waits for nothing
+        int64_t r = 0;
+        const RqSegment* segs = p.inline_seg;
+        bool failed = false;
+        const uint64_t policy = evict_first_policy();
+        // issues stages until `limit` have been issued or the rows run out
+        auto issue = [&](int limit) {
+            for (; r < row_end && st < limit && !failed; ++st) {
+                while (seg + 1 < n_segments && r >= segs[seg].row_begin + segs[seg].rows) ++seg;
+                const RqSegment& sg = segs[seg];
+                if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase)) { atomicExch(p.error_flag, 1); failed = true; break; }
                 const int64_t seg_end = sg.row_begin + sg.rows;
                 int64_t stop = r + p.stage_rows;
                 if (stop > seg_end) stop = seg_end;
@@ -726,27 +729,59 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                 if (p.trace && st < 16) p.trace[(size_t)blockIdx.x * 64 + 48 + st] = global_ns();
 #endif
                 for (int s = 0; s < subs; ++s) {
-                    bulk_g2s(dst + (size_t)s * p.sub_main_bytes, sg.main[s] + lr0 * row_bytes, main_bytes, &full_bar[slot]);
+                    bulk_g2s(dst + (size_t)s * p.sub_main_bytes, sg.main[s] + lr0 * row_bytes, main_bytes, &full_bar[slot], policy);
                     if (TYPE != RQ_Q4_K) {
                         const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
                         const uintptr_t last = first + (uintptr_t)nr * row_scales * 2;
                         const uintptr_t a0 = first & ~(uintptr_t)15, a1 = (last + 15) & ~(uintptr_t)15;
-                        bulk_g2s(dst + (size_t)p.subs * p.sub_main_bytes + (size_t)s * p.sub_scale_bytes, (const void*)a0, (uint32_t)(a1 - a0), &full_bar[slot]);
+                        bulk_g2s(dst + (size_t)p.subs * p.sub_main_bytes + (size_t)s * p.sub_scale_bytes, (const void*)a0, (uint32_t)(a1 - a0), &full_bar[slot], policy);
                     }
                 }
                 issued = st + 1;
                 r = stop;
                 if (++slot == p.stages) { slot = 0; phase ^= 1; }
             }
+        };
+        if (tid == kConsumers) {
+            for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NW); }
+            for (int s = 0; s <= kMaxStages; ++s) cross_count[s] = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            if (direct) {
+                // the first ring-full goes out before the CTA has even synchronised
+                split_rows(p.rows);
+                r = row_begin;
+                issue(p.stages);
+            }
+        }
+        __syncwarp();
+        __syncthreads();  // barriers initialised; the consumers have staged the table and their activations
+        if (tid == kConsumers) {
+            if (!direct) {
+                segs = table;
+                if (p.plan) { n_segments = min(plan_counts[0], p.n_segments); subs = min(plan_counts[1], p.subs); }
+                split_rows(p.plan ? min((int64_t)plan_counts[2], p.rows) : p.rows);
+                r = row_begin;
+            }
+            issue(0x7fffffff);
             // leave only after every copy this CTA issued has landed (bounded)
-            for (int st = (issued > p.stages ? issued - p.stages : 0); st < issued; ++st)
-                if (!mbar_wait(&full_bar[st % p.stages], (st / p.stages) & 1)) { atomicExch(p.error_flag, 2); break; }
+            for (int w = (issued > p.stages ? issued - p.stages : 0); w < issued; ++w)
+                if (!mbar_wait(&full_bar[w % p.stages], (w / p.stages) & 1)) { atomicExch(p.error_flag, 2); break; }
         }
     } else {
         // ---------------------------------------------------------------- consumers
         // Everything below reads what earlier kernels wrote (activations, tables) or writes what
         // they may still read (y): wait for them. The producer's weight copies are already running.
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        {
+            // the segment table sits in shared memory for the whole kernel
+            if (p.plan && tid == 0) { plan_counts[0] = p.plan->n_segments; plan_counts[1] = p.plan->subs; plan_counts[2] = p.plan->total_rows; }
+            const int n_copy = p.plan ? p.plan->n_segments : p.n_segments;
+            const uint32_t* src = (const uint32_t*)(p.plan ? p.plan->seg : (p.table ? p.table : p.inline_seg));
+            uint32_t* dst = (uint32_t*)table;
+            const int words = (n_copy < RQ_MAX_SEGMENTS ? n_copy : RQ_MAX_SEGMENTS) * (int)(sizeof(RqSegment) / 4);
+            for (int i = tid; i < words; i += kConsumers) dst[i] = src[i];
+        }
+        RQ_STAMP(41);
         // A thread's item is the same (half, sub-row, row slot, unit) in every stage: thread t takes
         // item t of the stage's grid [half][sub-row][row][unit]. Halves are outermost so that a warp
         // works on one half of adjacent units: no divergence, no bank conflicts.
@@ -772,7 +807,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             // launches) from records this CTA makes of x right here, while its first weights fly.
             if (p.fuse_step) {
                 quantise_to_smem<kConsumers>(p.x, p.sk, p.cols, p.fuse_step, act_smem, tid);
+                RQ_STAMP(45);
                 consumer_sync<kConsumers>();
+                RQ_STAMP(46);
                 if (act_owner) areg.load(act_smem + (size_t)my_u * kRecord, my_h);
                 if (blockIdx.x == 0 && p.act_out) {
                     const uint4* src = (const uint4*)act_smem;
@@ -815,7 +852,11 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             }
             consumer_sync<kConsumers>();
         }
+        __syncthreads();  // the producer has initialised the barriers; table and plan counts are in place
         RQ_STAMP(1);
+        // counts: from the launch, or (planned launches) from the device-side plan, never above the launch's
+        if (p.plan) { n_segments = min(plan_counts[0], p.n_segments); subs = min(plan_counts[1], p.subs); }
+        split_rows(p.plan ? min((int64_t)plan_counts[2], p.rows) : p.rows);
 
         const int lane = tid & 31, warp = tid >> 5;
         bool dead = false;  // a wait ran out: no more waiting, the results are flagged invalid
@@ -882,8 +923,14 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             const size_t my_off = (size_t)row_in_pass * row_bytes + (size_t)my_u * p.unit_bytes;
             const size_t pass_bytes = (size_t)rows_per_pass * row_bytes;
             const bool writer = (lane & (group - 1)) == 0;
+#ifdef RQ_TRACE
+            int trace_st = 0;
+#endif
             while (r < row_end) {
                 if (!dead && !mbar_wait(&full_bar[slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+#ifdef RQ_TRACE
+                RQ_STAMP(2 + 2 * trace_st);
+#endif
                 const int4 info = stage_info[slot];  // rows, segment, first local row, offset of the first d
                 const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
                 ItemRegs<TYPE> wr[2];
@@ -946,6 +993,10 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                     }
                     if (++cross_buf > kMaxStages) cross_buf = 0;
                 }
+#ifdef RQ_TRACE
+                RQ_STAMP(3 + 2 * trace_st);
+                ++trace_st;
+#endif
                 r += info.x;
             }
         } else if (MODE == RQ_ACT_INT8 && T == 1 && p.act_regs) {
@@ -1100,7 +1151,12 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     if (p.act_regs) p.act_vectors = p.fuse_step ? 1 : 0;        // fused: one token's records are made in shared memory; else nothing is staged
     if (p.act_bytes * p.act_vectors > 64 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
+#ifdef RQ_PROBE_CTAS
+    static const int probe_ctas = getenv("RQ_CTAS_PER_SM") ? atoi(getenv("RQ_CTAS_PER_SM")) : kCtasPerSm;
+    const int ctas = sm_count * probe_ctas;
+#else
     const int ctas = sm_count * kCtasPerSm;
+#endif
     const int64_t rows_per_cta = (p.rows + ctas - 1) / ctas;
     const int ipr = 2 * p.units * p.subs;  // items per virtual row
     p.units_shift = (p.units & (p.units - 1)) == 0 ? __builtin_ctz(p.units) : -1;
@@ -1150,6 +1206,7 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     p.stages = stages;
     const size_t smem = fixed + (size_t)stages * p.stage_bytes;
     const int grid_x = (int)(p.rows < ctas ? p.rows : ctas);
+    p.rows_quot = p.rows / grid_x; p.rows_rem = (int)(p.rows % grid_x);
     return t == 4 ? launch_stream<TYPE, MODE, 4, NW>(p, grid_x, smem, s) : launch_stream<TYPE, MODE, 1, NW>(p, grid_x, smem, s);
 }
 
