@@ -389,7 +389,9 @@ static int int8_records(rq_ctx* ctx, const char* who, const float* x, int64_t sk
 // *rc carries an allocation failure.
 static bool fused_int8(rq_ctx* ctx, int act_mode, int tokens, int64_t cols, int* rc) {
     *rc = RQ_OK;
-    if (act_mode != RQ_ACT_INT8 || tokens != 1 || cols % 256) return false;
+    // Every CTA of a fused launch reads all of x: beyond 8192 inputs that traffic (some 300 CTAs x 4 bytes x inputs)
+    // costs more than the quantiser launch it saves.
+    if (act_mode != RQ_ACT_INT8 || tokens != 1 || cols % 256 || cols > 8192) return false;
     *rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols));
     return *rc == RQ_OK;
 }

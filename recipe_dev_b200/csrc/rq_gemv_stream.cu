@@ -60,6 +60,9 @@ struct StreamParams {
     int warp_rows;             // > 0: the warp scheme -- a row's 2 * units items are that many adjacent lanes (a power of two), a warp
                                // pass covers warp_rows = 32 / (2 * units) rows, and the lanes of a row join their sums by shuffles
     int rows_per_thread;       // warp scheme: passes per stage (1 or 2)
+    int pieces, piece_rows;    // a stage lands as `pieces` copies with a barrier each (2 in the warp scheme with two passes: one per pass), piece_rows rows each
+    int window;                // the producer keeps at most this many pieces in flight: enough bytes to cover the memory latency at full
+                               // bandwidth, not more -- a deeper queue only delays everything else that reads memory (the activations)
     int row_warps;             // warp scheme: 1 = a row lies inside one warp; NW = every warp holds 32 / warp_rows lanes' worth of
                                // each row of the pass, and the warps' sums meet in shared memory (the last warp to arrive adds them)
     int sum_group, sum_chunks; // the order a row's item sums are added in when the shape has a warp scheme (so that a multi-token
@@ -642,11 +645,12 @@ __device__ float rq_tanh_portable(float xf) {
 __device__ __forceinline__ float rq_sigmoid_portable(float x) { return __fmul_rn(0.5f, __fadd_rn(rq_tanh_portable(__fmul_rn(0.5f, x)), 1.0f)); }
 __device__ __forceinline__ float rq_silu_portable(float x) { return __fmul_rn(x, rq_sigmoid_portable(x)); }
 
-template <int TYPE, int MODE, int T, int NW>
+// R = rows a thread takes per stage in the warp scheme (its weight registers): 2 only where the launch uses two
+template <int TYPE, int MODE, int T, int NW, int R>
 __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int kConsumers = NW * 32;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t full_bar[2 * kMaxStages];  // [slot][piece]
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
     uint8_t* act_smem = smem;                                              // activation vectors x units records
@@ -677,6 +681,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
     // launch streams weights from its first instruction on, whatever the previous kernel is doing. A table or
     // plan in device memory may have been written by the kernel before: it is read after griddepcontrol.wait.
     const bool direct = p.table == nullptr && p.plan == nullptr;
+    // fused launches: every warp of the CTA, the producer's included, takes part in quantising x
+    const bool fused = MODE == RQ_ACT_INT8 && p.act_regs && p.fuse_step != 0;
+    constexpr int kThreads = NW * 32 + 32;
     int n_segments = p.n_segments, subs = p.subs;
     int64_t row_begin = 0, row_end = 0;
     auto split_rows = [&](int64_t rows) {
@@ -692,7 +699,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
 
     if (tid >= kConsumers) {
         // ---------------------------------------------------------------- producer warp (lane 0 works)
-        int issued = 0, seg = 0, slot = 0, st = 0;
+        int issued = 0, seg = 0, slot = 0, st = 0, n_pieces = 0;
         uint32_t phase = 1;  // parity of the slot's previous round: the first round of the ring waits for nothing
         int64_t r = 0;
         const RqSegment* segs = p.inline_seg;
@@ -711,49 +718,70 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                 const int nr = (int)(stop - r);
                 const int64_t lr0 = r - sg.row_begin;  // first row, local to the segment
                 uint8_t* dst = ring + (size_t)slot * p.stage_bytes;
-                const uint32_t main_bytes = (uint32_t)(nr * row_bytes);
-                // bytes first, then the copies: the barrier must expect them before any can complete
-                uint32_t total = main_bytes * subs;
-                if (TYPE != RQ_Q4_K) {
-                    for (int s = 0; s < subs; ++s) {
-                        // the rows' d values, widened to whole 16-byte lines (the plane has slack past its end)
-                        const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
-                        const uintptr_t last = first + (uintptr_t)nr * row_scales * 2;
-                        total += (uint32_t)(((last + 15) & ~(uintptr_t)15) - (first & ~(uintptr_t)15));
-                    }
-                }
                 stage_info[slot] = make_int4(nr, seg, (int)lr0,
                                              TYPE != RQ_Q4_K ? (int)(((uintptr_t)sg.scale[0] + (uintptr_t)(lr0 * row_scales * 2)) & 15) : 0);
-                mbar_expect_tx(&full_bar[slot], total);
+                for (int k = 0; k < p.pieces; ++k) {
+                    // at most `window` pieces in flight: wait for the one issued `window` pieces ago
+                    if (n_pieces >= p.window) {
+                        const int old_piece = n_pieces - p.window, old_st = old_piece / p.pieces;
+                        if (!mbar_wait(&full_bar[2 * (old_st % p.stages) + (old_piece - old_st * p.pieces)], (old_st / p.stages) & 1)) { atomicExch(p.error_flag, 4); failed = true; break; }
+                    }
+                    ++n_pieces;
+                    uint64_t* bar = &full_bar[2 * slot + k];
+                    int rows_k = nr - k * p.piece_rows;
+                    rows_k = rows_k < 0 ? 0 : (rows_k > p.piece_rows ? p.piece_rows : rows_k);
+                    if (p.pieces == 1) rows_k = nr;
+                    const uint32_t main_bytes = (uint32_t)(rows_k * row_bytes);
+                    // bytes first, then the copies: the barrier must expect them before any can complete.
+                    // The d values of the whole stage travel with its first piece.
+                    uint32_t total = main_bytes * subs;
+                    if (TYPE != RQ_Q4_K && k == 0) {
+                        for (int s = 0; s < subs; ++s) {
+                            // the rows' d values, widened to whole 16-byte lines (the plane has slack past its end)
+                            const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
+                            const uintptr_t last = first + (uintptr_t)nr * row_scales * 2;
+                            total += (uint32_t)(((last + 15) & ~(uintptr_t)15) - (first & ~(uintptr_t)15));
+                        }
+                    }
+                    mbar_expect_tx(bar, total);
 #ifdef RQ_TRACE
-                if (p.trace && st < 16) p.trace[(size_t)blockIdx.x * 64 + 48 + st] = global_ns();
+                    if (p.trace && st < 16 && k == 0) p.trace[(size_t)blockIdx.x * 64 + 48 + st] = global_ns();
 #endif
-                for (int s = 0; s < subs; ++s) {
-                    bulk_g2s(dst + (size_t)s * p.sub_main_bytes, sg.main[s] + lr0 * row_bytes, main_bytes, &full_bar[slot], policy);
-                    if (TYPE != RQ_Q4_K) {
-                        const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
-                        const uintptr_t last = first + (uintptr_t)nr * row_scales * 2;
-                        const uintptr_t a0 = first & ~(uintptr_t)15, a1 = (last + 15) & ~(uintptr_t)15;
-                        bulk_g2s(dst + (size_t)p.subs * p.sub_main_bytes + (size_t)s * p.sub_scale_bytes, (const void*)a0, (uint32_t)(a1 - a0), &full_bar[slot], policy);
+                    const int64_t piece_off = (int64_t)k * p.piece_rows * row_bytes;
+                    for (int s = 0; s < subs; ++s) {
+                        if (main_bytes) bulk_g2s(dst + (size_t)s * p.sub_main_bytes + piece_off, sg.main[s] + lr0 * row_bytes + piece_off, main_bytes, bar, policy);
+                        if (TYPE != RQ_Q4_K && k == 0) {
+                            const uintptr_t first = (uintptr_t)sg.scale[s] + (uintptr_t)(lr0 * row_scales * 2);
+                            const uintptr_t last = first + (uintptr_t)nr * row_scales * 2;
+                            const uintptr_t a0 = first & ~(uintptr_t)15, a1 = (last + 15) & ~(uintptr_t)15;
+                            bulk_g2s(dst + (size_t)p.subs * p.sub_main_bytes + (size_t)s * p.sub_scale_bytes, (const void*)a0, (uint32_t)(a1 - a0), bar, policy);
+                        }
                     }
                 }
+                if (failed) break;
                 issued = st + 1;
                 r = stop;
                 if (++slot == p.stages) { slot = 0; phase ^= 1; }
             }
         };
         if (tid == kConsumers) {
-            for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NW); }
+            for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[2 * s], 1); mbar_init(&full_bar[2 * s + 1], 1); mbar_init(&empty_bar[s], NW); }
             for (int s = 0; s <= kMaxStages; ++s) cross_count[s] = 0;
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             if (direct) {
-                // the first ring-full goes out before the CTA has even synchronised
+                // the first window of copies goes out before the CTA has even synchronised (no waiting here:
+                // the consumers meet this thread at the barrier below)
                 split_rows(p.rows);
                 r = row_begin;
-                issue(p.stages);
+                const int early = p.window / p.pieces;
+                issue(early < 1 ? 1 : (early > p.stages ? p.stages : early));
             }
         }
         __syncwarp();
+        if (fused) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // x may come from the kernel before this one
+            quantise_to_smem<kThreads>(p.x, p.sk, p.cols, p.fuse_step, smem, tid);
+        }
         __syncthreads();  // barriers initialised; the consumers have staged the table and their activations
         if (tid == kConsumers) {
             if (!direct) {
@@ -765,23 +793,28 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             issue(0x7fffffff);
             // leave only after every copy this CTA issued has landed (bounded)
             for (int w = (issued > p.stages ? issued - p.stages : 0); w < issued; ++w)
-                if (!mbar_wait(&full_bar[w % p.stages], (w / p.stages) & 1)) { atomicExch(p.error_flag, 2); break; }
+                for (int k = 0; k < p.pieces; ++k)
+                    if (!mbar_wait(&full_bar[2 * (w % p.stages) + k], (w / p.stages) & 1)) { atomicExch(p.error_flag, 2); break; }
         }
     } else {
         // ---------------------------------------------------------------- consumers
         // Everything below reads what earlier kernels wrote (activations, tables) or writes what
         // they may still read (y): wait for them. The producer's weight copies are already running.
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        {
-            // the segment table sits in shared memory for the whole kernel
+        // The segment table sits in shared memory for the whole kernel. One that came with the launch is
+        // copied before the wait (it does not depend on the kernel before), one in device memory after.
+        auto stage_table = [&]() {
             if (p.plan && tid == 0) { plan_counts[0] = p.plan->n_segments; plan_counts[1] = p.plan->subs; plan_counts[2] = p.plan->total_rows; }
             const int n_copy = p.plan ? p.plan->n_segments : p.n_segments;
             const uint32_t* src = (const uint32_t*)(p.plan ? p.plan->seg : (p.table ? p.table : p.inline_seg));
             uint32_t* dst = (uint32_t*)table;
             const int words = (n_copy < RQ_MAX_SEGMENTS ? n_copy : RQ_MAX_SEGMENTS) * (int)(sizeof(RqSegment) / 4);
             for (int i = tid; i < words; i += kConsumers) dst[i] = src[i];
-        }
+        };
+        if (direct) stage_table();
         RQ_STAMP(41);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        RQ_STAMP(44);
+        if (!direct) stage_table();
         // A thread's item is the same (half, sub-row, row slot, unit) in every stage: thread t takes
         // item t of the stage's grid [half][sub-row][row][unit]. Halves are outermost so that a warp
         // works on one half of adjacent units: no divergence, no bank conflicts.
@@ -806,11 +839,12 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             // kernel. They come from the records an earlier launch left in the scratch, or (fused
             // launches) from records this CTA makes of x right here, while its first weights fly.
             if (p.fuse_step) {
-                quantise_to_smem<kConsumers>(p.x, p.sk, p.cols, p.fuse_step, act_smem, tid);
+                quantise_to_smem<kThreads>(p.x, p.sk, p.cols, p.fuse_step, act_smem, tid);
                 RQ_STAMP(45);
-                consumer_sync<kConsumers>();
+                __syncthreads();  // with the producer warp: records complete, barriers initialised
                 RQ_STAMP(46);
                 if (act_owner) areg.load(act_smem + (size_t)my_u * kRecord, my_h);
+                RQ_STAMP(47);
                 if (blockIdx.x == 0 && p.act_out) {
                     const uint4* src = (const uint4*)act_smem;
                     uint4* dst = (uint4*)p.act_out;
@@ -852,7 +886,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             }
             consumer_sync<kConsumers>();
         }
-        __syncthreads();  // the producer has initialised the barriers; table and plan counts are in place
+        if (!fused) __syncthreads();  // the producer has initialised the barriers; table and plan counts are in place
         RQ_STAMP(1);
         // counts: from the launch, or (planned launches) from the device-side plan, never above the launch's
         if (p.plan) { n_segments = min(plan_counts[0], p.n_segments); subs = min(plan_counts[1], p.subs); }
@@ -927,18 +961,20 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             int trace_st = 0;
 #endif
             while (r < row_end) {
-                if (!dead && !mbar_wait(&full_bar[slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                if (!dead && !mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
 #ifdef RQ_TRACE
                 RQ_STAMP(2 + 2 * trace_st);
 #endif
                 const int4 info = stage_info[slot];  // rows, segment, first local row, offset of the first d
                 const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
-                ItemRegs<TYPE> wr[2];
-                bool have[2];
+                ItemRegs<TYPE> wr[R];
+                bool have[R];
 #pragma unroll
-                for (int k = 0; k < 2; ++k) {
+                for (int k = 0; k < R; ++k) {
                     const int lr = row_in_pass + k * rows_per_pass;
-                    have[k] = k < p.rows_per_thread && lr < info.x && act_owner;
+                    // the second pass's rows are the stage's second piece
+                    if (k == 1 && p.pieces == 2 && !dead && !mbar_wait(&full_bar[2 * slot + 1], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                    have[k] = lr < info.x && act_owner;
                     if (have[k]) {
                         const uint16_t* sc = nullptr;
                         if (TYPE != RQ_Q4_K) sc = (const uint16_t*)(stage + p.sub_main_bytes + info.w) + ((size_t)lr * p.units + my_u) * p.scales_per_unit;
@@ -949,21 +985,21 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[slot]);
                 if (++slot == p.stages) { slot = 0; phase ^= 1; }
-                float v[2];
+                float v[R];
 #pragma unroll
-                for (int k = 0; k < 2; ++k) v[k] = have[k] ? dot_regs(wr[k], areg, my_h) : 0.f;
+                for (int k = 0; k < R; ++k) v[k] = have[k] ? dot_regs(wr[k], areg, my_h) : 0.f;
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) {
                     if (off < group) {  // uniform over the launch
-                        v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
-                        v[1] += __shfl_xor_sync(0xffffffffu, v[1], off);
+#pragma unroll
+                        for (int k = 0; k < R; ++k) v[k] += __shfl_xor_sync(0xffffffffu, v[k], off);
                     }
                 }
                 if (!split) {
                     if (writer) {
                         float* yb = table[info.y].y;
 #pragma unroll
-                        for (int k = 0; k < 2; ++k)
+                        for (int k = 0; k < R; ++k)
                             if (have[k]) yb[(int64_t)(info.z + row_in_pass + k * rows_per_pass) * p.yn + (int64_t)tok0 * p.yt] = v[k];
                     }
                 } else {
@@ -971,8 +1007,8 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                     // there adds the shares in warp order (whichever warp that is, the order is the same)
                     if (writer) {
 #pragma unroll
-                        for (int k = 0; k < 2; ++k)
-                            if (k < p.rows_per_thread) cross_sum[cross_buf][row_in_pass + k * rows_per_pass][warp] = v[k];
+                        for (int k = 0; k < R; ++k)
+                            cross_sum[cross_buf][row_in_pass + k * rows_per_pass][warp] = v[k];
                     }
                     __threadfence_block();
                     __syncwarp();
@@ -999,9 +1035,11 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
 #endif
                 r += info.x;
             }
+        } else if (R == 2) {
+            // two-row instantiations serve the warp scheme only
         } else if (MODE == RQ_ACT_INT8 && T == 1 && p.act_regs) {
-            // ---- register items, two stages per turn
-            constexpr int PAIR = TYPE == RQ_Q8_0 ? 1 : 2;
+            // ---- register items through shared-memory partial sums (rows the warp scheme does not take)
+            constexpr int PAIR = 1;
             int buf = 0;
             while (r < row_end) {
                 ItemRegs<TYPE> wr[PAIR];
@@ -1021,7 +1059,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                         const int nr = (int)(stop - r);
                         const int64_t lr0 = r - sg.row_begin;
                         st_seg[k] = seg; st_nr[k] = nr; st_lr0[k] = lr0;
-                        if (!dead && !mbar_wait(&full_bar[slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                        if (!dead && !mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
                         const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
                         have[k] = tid < items_cap && my_lr < nr && my_s < subs;
                         if (have[k]) {
@@ -1063,7 +1101,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                 if (stop > row_end) stop = row_end;
                 const int nr = (int)(stop - r);
                 const int64_t lr0 = r - sg.row_begin;
-                if (!dead && !mbar_wait(&full_bar[slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                if (!dead && !mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
                 RQ_STAMP(2 + 3 * st);
                 const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
                 float* part = partial + (size_t)(st & 1) * T * stage_items;
@@ -1097,9 +1135,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
     }
 }
 
-template <int TYPE, int MODE, int T, int NW>
+template <int TYPE, int MODE, int T, int NW, int R>
 int launch_stream(const StreamParams& p, int grid_x, size_t smem, cudaStream_t s) {
-    auto kernel = rq_gemv_stream_kernel<TYPE, MODE, T, NW>;
+    auto kernel = rq_gemv_stream_kernel<TYPE, MODE, T, NW, R>;
     static bool configured[64] = {};  // per instantiation and device: the opt-in to large dynamic shared memory
     int dev = 0;
     RQ_CUDA(cudaGetDevice(&dev));
@@ -1194,6 +1232,17 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
         stage_rows = p.warp_rows * p.rows_per_thread;
     }
     p.stage_rows = stage_rows;
+    p.pieces = 1; p.piece_rows = stage_rows;
+    if (p.warp_rows && p.rows_per_thread == 2) { p.pieces = 2; p.piece_rows = stage_rows / 2; }
+    {
+        // in flight per CTA: about 32 KB (two CTAs per SM: some 9 MB on the whole GPU, the memory latency at full bandwidth), two pieces at least
+        const int64_t piece_bytes = (int64_t)p.piece_rows * row_bytes * p.subs;
+        p.window = (int)((32 * 1024 + piece_bytes - 1) / piece_bytes);
+        if (p.window < 2) p.window = 2;
+#ifdef RQ_PROBE_CTAS
+        if (getenv("RQ_WINDOW_KB")) { p.window = (int)((atoi(getenv("RQ_WINDOW_KB")) * 1024 + piece_bytes - 1) / piece_bytes); if (p.window < 1) p.window = 1; }
+#endif
+    }
     p.sub_main_bytes = ((size_t)stage_rows * row_bytes + 127) & ~(size_t)127;
     p.sub_scale_bytes = p.scales_per_unit ? (((size_t)stage_rows * p.units * p.scales_per_unit * 2 + 32 + 127) & ~(size_t)127) : 0;
     p.stage_bytes = (p.sub_main_bytes + p.sub_scale_bytes) * p.subs;
@@ -1204,10 +1253,16 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     int stages = (int)((kSmemBudget - fixed) / p.stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     p.stages = stages;
+    if (p.window > stages * p.pieces - 1) p.window = stages * p.pieces - 1;  // the producer looks back at barriers of slots it has not re-armed yet
+    if (p.window < 1) p.window = 1;
     const size_t smem = fixed + (size_t)stages * p.stage_bytes;
     const int grid_x = (int)(p.rows < ctas ? p.rows : ctas);
     p.rows_quot = p.rows / grid_x; p.rows_rem = (int)(p.rows % grid_x);
-    return t == 4 ? launch_stream<TYPE, MODE, 4, NW>(p, grid_x, smem, s) : launch_stream<TYPE, MODE, 1, NW>(p, grid_x, smem, s);
+    if (t == 4) return launch_stream<TYPE, MODE, 4, NW, 1>(p, grid_x, smem, s);
+    if constexpr (MODE == RQ_ACT_INT8) {
+        if (p.rows_per_thread == 2) return launch_stream<TYPE, MODE, 1, NW, 2>(p, grid_x, smem, s);
+    }
+    return launch_stream<TYPE, MODE, 1, NW, 1>(p, grid_x, smem, s);
 }
 
 template <int TYPE, int MODE>
@@ -1221,13 +1276,17 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
 #ifdef RQ_TRACE
 // development builds: a device buffer of time stamps, read back with rq_trace_read()
 static unsigned long long* g_trace = nullptr;
+static int g_trace_launch = 0;
+// sixteen regions of 512 CTAs x 64 stamps: consecutive launches write consecutive regions
 unsigned long long* rq_trace_buffer() {
-    if (!g_trace) { cudaMalloc(&g_trace, 1024 * 64 * 8); cudaMemset(g_trace, 0, 1024 * 64 * 8); }
-    return g_trace;
+    if (!g_trace) { cudaMalloc(&g_trace, 16 * 512 * 64 * 8); cudaMemset(g_trace, 0, 16 * 512 * 64 * 8); }
+    return g_trace + (size_t)((g_trace_launch++) % 16) * 512 * 64;
 }
+extern "C" int rq_trace_reset() { g_trace_launch = 0; rq_trace_buffer(); g_trace_launch = 0; return (int)cudaMemset(g_trace, 0, 16 * 512 * 64 * 8); }
 extern "C" int rq_trace_read(unsigned long long* host, int ctas) {
     cudaDeviceSynchronize();
-    return (int)cudaMemcpy(host, rq_trace_buffer(), (size_t)ctas * 64 * 8, cudaMemcpyDeviceToHost);
+    if (!g_trace) return -1;
+    return (int)cudaMemcpy(host, g_trace, (size_t)ctas * 64 * 8, cudaMemcpyDeviceToHost);
 }
 #endif
 
