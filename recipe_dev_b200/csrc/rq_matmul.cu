@@ -1,29 +1,40 @@
 // Batched quantised matmul (prefill / multi-sequence decode) on the 5th-generation tensor cores.
 //
 // Y[t][n] = sum_k W[n][k] * X[t][k], W stored as GGUF blocks, fp32 activations kept as they are
-// (the FLOAT handling of a stored sum). A CTA owns a tile of 128 weight rows x 128 tokens:
-//   * four staging warps dequantise a 128 x 64 slice of W (bit-exact values, as rq_dequant gives
-//     them) and convert it, and the matching 128 x 64 slice of X, to fp16 PAIRS hi + lo with
-//     hi = fp16(v), lo = fp16(v - hi): together 22 mantissa bits, so nothing of the fp32 inputs that
-//     matters at the 1e-3 bar is lost. The four tiles go to shared memory in the 128-byte-swizzled
-//     K-major layout the tensor core reads;
-//   * one warp issues tcgen05.mma (kind::f16, M = 128, N = 128, K = 16) three times per 16-wide
-//     slice: A_hi B_hi + A_hi B_lo + A_lo B_hi, accumulating in fp32 in TMEM (the dropped
-//     A_lo B_lo term is 2^-22 relative); tcgen05.commit releases the stage and, at the end, signals
-//     the epilogue;
-//   * the staging warps read the 128 x 128 fp32 accumulator back with tcgen05.ld and store Y.
+// (the FLOAT handling of a stored sum).
+//
+// Operands reach the tensor core as fp16 PAIRS hi + lo with hi = fp16(v), lo = fp16(v - hi):
+// together 22 mantissa bits, so nothing of the fp32 inputs that matters at the 1e-3 bar is lost.
+// Three products are issued per 16-wide slice, A_hi B_hi + A_hi B_lo + A_lo B_hi (the dropped
+// A_lo B_lo term is 2^-22 relative).
+//
+//   * a small kernel splits X once into hi and lo tiles, already in the 128-byte-swizzled K-major
+//     image the tensor core reads, so the main kernel fetches a tile with one bulk copy;
+//   * a CTA owns 128 weight rows x BN tokens (BN = 32, 64 or 128). Eight staging warps dequantise
+//     128 x 64 slices of W (bit-exact values, as rq_dequant gives them; the next slice's bytes are
+//     fetched while this one is converted) into swizzled hi / lo tiles in shared memory;
+//   * one thread issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16). The tensor core adds
+//     into its fp32 accumulator by TRUNCATION, a bias that grows with the length of the chain
+//     (measured: 1.2e-5 relative at K = 4096). So the large term A_hi B_hi is accumulated in
+//     tensor memory only over one 64-wide slice (four instructions), into one of two
+//     accumulators in turn, and eight drain warps add each finished slice into fp32 registers
+//     with round-to-nearest adds while the tensor core works on the next. The two cross terms,
+//     2^-11 of the result, stay in a third accumulator for the whole K.
 // Three stages of 64 KB keep dequantisation ahead of the tensor core.
 //
 // Every wait is bounded in time; a wait that runs out records a code in the context's error word,
-// the thread stops waiting and the CTA still frees its TMEM before it exits.
+// the thread stops waiting and the CTA still frees its tensor memory before it exits.
 #include "rq_internal.cuh"
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, kStages = 3;
-constexpr int kStagers = 128, kThreadsMM = 160;
-constexpr int kTileBytes = BM * BK * 2;            // one fp16 tile: 16 KB
-constexpr int kStageBytes = 4 * kTileBytes;        // A_hi | A_lo | B_hi | B_lo
+constexpr int BM = 128, BK = 64, kStages = 3;
+constexpr int kStageWarps = 8, kDrainWarps = 8;
+constexpr int kStagers = kStageWarps * 32;
+constexpr int kMmaWarp = kStageWarps + kDrainWarps, kCopyWarp = kMmaWarp + 1;
+constexpr int kThreadsMM = (kCopyWarp + 1) * 32;
+constexpr int kTileBytes = BM * BK * 2;            // one fp16 tile of 128 rows: 16 KB
+constexpr int kStageBytes = 4 * kTileBytes;        // A_hi | A_lo | B_hi | B_lo (B tiles of BN rows, at most 128)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct MatmulParams {
@@ -31,8 +42,8 @@ struct MatmulParams {
     const uint16_t* scale;
     int64_t rows;
     int cols;
-    const float* x; int64_t sk, st;
-    int x_vec;  // token rows are contiguous and 16-byte aligned: 128-bit loads
+    const uint8_t* xs;  // the split activations: [token tile][k slice][hi | lo][bn rows x 128 bytes, swizzled]
+    int bn;             // tokens per tile
     int tokens;
     float* y; int64_t yn, yt;
     int* error_flag;
@@ -42,6 +53,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)); }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
@@ -54,6 +68,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (global_ns() - t0 > kWaitLimitNs) return false;
     return true;
 }
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes),
+                 "r"(smem_u32(bar))
+                 : "memory");
+}
 
 // K-major, 128-byte-swizzled operand tile of 128-byte rows: rows 128 bytes apart, groups of eight
 // rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type SWIZZLE_128B.
@@ -65,94 +84,27 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
     return d;
 }
-// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = BN
-constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = bn
+__device__ __forceinline__ uint32_t instr_desc(int bn) { return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24); }
 
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate), "r"(0u)
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-
-// 64 consecutive values of one row, starting at k0 (a multiple of 64): the same bits rq_dequant gives.
-template <int TYPE>
-__device__ __forceinline__ void row_values(const MatmulParams& p, int64_t row, int k0, float* v) {
-    if (TYPE == RQ_Q4_K) {
-        const int b = k0 >> 8, pr = (k0 & 255) >> 6;
-        const uint8_t* blk = p.main + (row * (p.cols >> 8) + b) * 144;
-        const uint4 hdr = __ldg((const uint4*)blk);
-        const uint4 q0 = __ldg((const uint4*)(blk + 16 + 32 * pr)), q1 = __ldg((const uint4*)(blk + 32 + 32 * pr));
-        int sc_lo, mn_lo, sc_hi, mn_hi;
-        rq_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pr, sc_lo, mn_lo);
-        rq_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pr + 1, sc_hi, mn_hi);
-        const float d = rq_h2f((uint16_t)(hdr.x & 0xffff)), dmin = rq_h2f((uint16_t)(hdr.x >> 16));
-        const float step_lo = __fmul_rn(d, (float)sc_lo), base_lo = __fmul_rn(dmin, (float)mn_lo);
-        const float step_hi = __fmul_rn(d, (float)sc_hi), base_hi = __fmul_rn(dmin, (float)mn_hi);
-        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t byte = (w[j] >> (8 * i)) & 0xff;
-                v[4 * j + i] = __fsub_rn(__fmul_rn(step_lo, (float)(byte & 15)), base_lo);
-                v[32 + 4 * j + i] = __fsub_rn(__fmul_rn(step_hi, (float)(byte >> 4)), base_hi);
-            }
-    } else if (TYPE == RQ_Q6_K) {
-        const int b = k0 >> 8, j64 = (k0 & 255) >> 6, ch = j64 >> 1, sel = j64 & 1;  // groups 2 sel, 2 sel + 1 of chunk ch
-        const int64_t nb = p.cols >> 8;
-        const uint8_t* body = p.main + (row * nb + b) * 208;
-        const float d = rq_h2f(__ldg(p.scale + row * nb + b));
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {   // group g = 2 sel + half: ql line 32 * (g & 1) = 32 * half, nibble g / 2 = sel
-            const int g = 2 * sel + half;
-#pragma unroll
-            for (int q4 = 0; q4 < 2; ++q4) {     // sixteen values at a time
-                const uint4 ql = __ldg((const uint4*)(body + 64 * ch + 32 * half + 16 * q4));
-                const uint4 qh = __ldg((const uint4*)(body + 128 + 32 * ch + 16 * q4));
-                const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
-                const int scale = (int8_t)__ldg(body + 192 + 8 * ch + 2 * g + q4);
-                const float scaled = __fmul_rn(d, (float)scale);
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int lo = (lw[j] >> (8 * i + 4 * sel)) & 15, hi = (hw[j] >> (8 * i + 2 * g)) & 3;
-                        v[32 * half + 16 * q4 + 4 * j + i] = __fmul_rn(scaled, (float)((lo | (hi << 4)) - 32));
-                    }
-            }
-        }
-    } else if (TYPE == RQ_Q8_0) {
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-            const float d = rq_h2f(__ldg(p.scale + row * (p.cols >> 5) + (k0 >> 5) + blk));
-            const uint4 a = __ldg((const uint4*)(p.main + row * p.cols + k0 + 32 * blk)), c = __ldg((const uint4*)(p.main + row * p.cols + k0 + 32 * blk + 16));
-            const uint32_t w[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) v[32 * blk + 4 * j + i] = __fmul_rn((float)(int8_t)(w[j] >> (8 * i)), d);
-        }
-    } else {
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-            const float d = rq_h2f(__ldg(p.scale + row * (p.cols >> 5) + (k0 >> 5) + blk));
-            const uint4 a = __ldg((const uint4*)(p.main + row * (p.cols >> 1) + ((k0 >> 5) + blk) * 16));
-            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t byte = (w[j] >> (8 * i)) & 0xff;
-                    v[32 * blk + 4 * j + i] = __fmul_rn((float)((int)(byte & 15) - 8), d);
-                    v[32 * blk + 16 + 4 * j + i] = __fmul_rn((float)((int)(byte >> 4) - 8), d);
-                }
-        }
-    }
+// sixteen fp32 columns of this warp's 32 accumulator rows
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // Weights are scaled by 2^8 before the split and the accumulator by 2^-8 after: a weight of 0.02
@@ -161,22 +113,157 @@ __device__ __forceinline__ void row_values(const MatmulParams& p, int64_t row, i
 // weights are orders of magnitude below that.)
 constexpr float kWeightScale = 256.0f, kWeightUnscale = 1.0f / 256.0f;
 
-// Splits 64 fp32 values (times `scale`) into fp16 hi and lo and writes the row into the two swizzled tiles.
-__device__ __forceinline__ void store_row_split(const float* v, float scale, uint8_t* tile_hi, uint8_t* tile_lo, int row) {
+// Eight fp32 values (times `scale`) as one 16-byte chunk of fp16 hi and one of fp16 lo.
+__device__ __forceinline__ void split8(const float* v, float scale, uint4& hi, uint4& lo) {
+    uint32_t hw[4], lw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float a = v[2 * j] * scale, b = v[2 * j + 1] * scale;
+        const __half2 h2 = __floats2half2_rn(a, b);
+        const float2 back = __half22float2(h2);
+        const __half2 l2 = __floats2half2_rn(a - back.x, b - back.y);
+        hw[j] = *(const uint32_t*)&h2;
+        lw[j] = *(const uint32_t*)&l2;
+    }
+    hi = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+    lo = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+}
+// Swizzle<3,4,3>: the 16-byte chunk index of a 128-byte row, xor the row within its group of eight
+__device__ __forceinline__ int swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+// ------------------------------------------------------------------------------------------
+// The raw bytes behind 32 consecutive values of one row (`half` 0 or 1 of a 64-wide slice at k0),
+// fetched one slice ahead, and their dequantisation: the same bits rq_dequant gives.
+// ------------------------------------------------------------------------------------------
+template <int TYPE> struct RawHalf;
+template <> struct RawHalf<RQ_Q4_K> {
+    uint4 hdr, q0, q1;
+    __device__ __forceinline__ void load(const MatmulParams& p, int64_t row, int k0, int) {
+        const uint8_t* blk = p.main + (row * (p.cols >> 8) + (k0 >> 8)) * 144;
+        const int pr = (k0 & 255) >> 6;
+        hdr = __ldg((const uint4*)blk);
+        q0 = __ldg((const uint4*)(blk + 16 + 32 * pr));
+        q1 = __ldg((const uint4*)(blk + 32 + 32 * pr));
+    }
+    __device__ __forceinline__ void decode(int k0, int half, float* v) const {
+        const int pr = (k0 & 255) >> 6;
+        int sc, mn;
+        rq_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pr + half, sc, mn);
+        const float d = rq_h2f((uint16_t)(hdr.x & 0xffff)), dmin = rq_h2f((uint16_t)(hdr.x >> 16));
+        const float step = __fmul_rn(d, (float)sc), base = __fmul_rn(dmin, (float)mn);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const int shift = 4 * half;  // sub-block 2 pr in the low nibbles, 2 pr + 1 in the high
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[4 * j + i] = __fsub_rn(__fmul_rn(step, (float)((w[j] >> (8 * i + shift)) & 15)), base);
+    }
+};
+template <> struct RawHalf<RQ_Q6_K> {
+    uint4 ql[2], qh[2];
+    uint32_t scales;  // two int8 scales
+    uint32_t d16;
+    __device__ __forceinline__ void load(const MatmulParams& p, int64_t row, int k0, int half) {
+        const int64_t nb = p.cols >> 8;
+        const int j64 = (k0 & 255) >> 6, ch = j64 >> 1, sel = j64 & 1, g = 2 * sel + half;
+        const uint8_t* body = p.main + (row * nb + (k0 >> 8)) * 208;
+        ql[0] = __ldg((const uint4*)(body + 64 * ch + 32 * half));
+        ql[1] = __ldg((const uint4*)(body + 64 * ch + 32 * half + 16));
+        qh[0] = __ldg((const uint4*)(body + 128 + 32 * ch));
+        qh[1] = __ldg((const uint4*)(body + 128 + 32 * ch + 16));
+        scales = __ldg((const uint16_t*)(body + 192 + 8 * ch + 2 * g));
+        d16 = __ldg(p.scale + row * nb + (k0 >> 8));
+    }
+    __device__ __forceinline__ void decode(int k0, int half, float* v) const {
+        const int j64 = (k0 & 255) >> 6, sel = j64 & 1, g = 2 * sel + half;  // group g of its chunk: ql line 32 * half, nibble sel
+        const float d = rq_h2f((uint16_t)d16);
+#pragma unroll
+        for (int q4 = 0; q4 < 2; ++q4) {  // sixteen values at a time
+            const uint32_t lw[4] = {ql[q4].x, ql[q4].y, ql[q4].z, ql[q4].w}, hw[4] = {qh[q4].x, qh[q4].y, qh[q4].z, qh[q4].w};
+            const int scale = (int)(int8_t)(scales >> (8 * q4));
+            const float scaled = __fmul_rn(d, (float)scale);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int lo = (lw[j] >> (8 * i + 4 * sel)) & 15, hi = (hw[j] >> (8 * i + 2 * g)) & 3;
+                    v[16 * q4 + 4 * j + i] = __fmul_rn(scaled, (float)((lo | (hi << 4)) - 32));
+                }
+        }
+    }
+};
+template <> struct RawHalf<RQ_Q8_0> {
+    uint4 a, c;
+    uint32_t d16;
+    __device__ __forceinline__ void load(const MatmulParams& p, int64_t row, int k0, int half) {
+        const int64_t at = row * p.cols + k0 + 32 * half;
+        a = __ldg((const uint4*)(p.main + at));
+        c = __ldg((const uint4*)(p.main + at + 16));
+        d16 = __ldg(p.scale + row * (p.cols >> 5) + (k0 >> 5) + half);
+    }
+    __device__ __forceinline__ void decode(int, int, float* v) const {
+        const float d = rq_h2f((uint16_t)d16);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[4 * j + i] = __fmul_rn((float)(int8_t)(w[j] >> (8 * i)), d);
+    }
+};
+template <> struct RawHalf<RQ_Q4_0> {
+    uint4 a;
+    uint32_t d16;
+    __device__ __forceinline__ void load(const MatmulParams& p, int64_t row, int k0, int half) {
+        a = __ldg((const uint4*)(p.main + row * (p.cols >> 1) + ((k0 >> 5) + half) * 16));
+        d16 = __ldg(p.scale + row * (p.cols >> 5) + (k0 >> 5) + half);
+    }
+    __device__ __forceinline__ void decode(int, int, float* v) const {
+        const float d = rq_h2f((uint16_t)d16);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t byte = (w[j] >> (8 * i)) & 0xff;
+                v[4 * j + i] = __fmul_rn((float)((int)(byte & 15) - 8), d);
+                v[16 + 4 * j + i] = __fmul_rn((float)((int)(byte >> 4) - 8), d);
+            }
+    }
+};
+
+// ------------------------------------------------------------------------------------------
+// X -> fp16 hi / lo tiles in the tensor core's swizzled image. grid (k slices, token tiles),
+// one thread per token row of the tile; rows past the last token are zero.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) rq_split_x_kernel(const float* __restrict__ x, int64_t sk, int64_t st, int tokens, int bn, uint8_t* __restrict__ xs) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int ks = blockIdx.x, nt = blockIdx.y, r = threadIdx.x;
+    if (r >= bn) return;
+    const int token = nt * bn + r;
+    uint8_t* hi = xs + ((size_t)nt * gridDim.x + ks) * 2 * (size_t)bn * 128;
+    uint8_t* lo = hi + (size_t)bn * 128;
+    const bool vec = sk == 1 && (st & 3) == 0 && ((uintptr_t)x & 15) == 0;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-        uint32_t hw[4], lw[4];
+        float v[8];
+        if (token < tokens) {
+            const float* src = x + (int64_t)token * st + (int64_t)(ks * BK + 8 * c) * sk;
+            if (vec) {
+                *(float4*)v = __ldg((const float4*)src);
+                *(float4*)(v + 4) = __ldg((const float4*)src + 1);
+            } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float a = v[8 * c + 2 * j] * scale, b = v[8 * c + 2 * j + 1] * scale;
-            const __half ha = __float2half_rn(a), hb = __float2half_rn(b);
-            const __half la = __float2half_rn(a - __half2float(ha)), lb = __float2half_rn(b - __half2float(hb));
-            hw[j] = (uint32_t)__half_as_ushort(ha) | ((uint32_t)__half_as_ushort(hb) << 16);
-            lw[j] = (uint32_t)__half_as_ushort(la) | ((uint32_t)__half_as_ushort(lb) << 16);
+                for (int j = 0; j < 8; ++j) v[j] = __ldg(src + j * sk);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
         }
-        const int off = row * 128 + ((c ^ (row & 7)) << 4);  // Swizzle<3,4,3>: the 16-byte chunk index xor the row within its group of eight
-        *(uint4*)(tile_hi + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-        *(uint4*)(tile_lo + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        uint4 h, l;
+        split8(v, 1.0f, h, l);
+        *(uint4*)(hi + swizzled(r, c)) = h;
+        *(uint4*)(lo + swizzled(r, c)) = l;
     }
 }
 
@@ -184,112 +271,151 @@ template <int TYPE>
 __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_constant__ MatmulParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzled tiles want 1024-byte alignment
-    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], done_bar;
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full[2], acc_empty[2], done_bar;
     __shared__ uint32_t tmem_base_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t m0 = (int64_t)blockIdx.x * BM;
-    const int n0 = blockIdx.y * BN;
+    const int nt = blockIdx.y, n0 = nt * p.bn;
     const int k_steps = p.cols / BK;
+    const int bn = p.bn;
+    // tensor memory: two accumulators for the hi x hi term, one for the cross terms: 3 bn columns, allocated as a power of two
+    const uint32_t tmem_cols = bn == 128 ? 512u : (bn == 64 ? 256u : 128u);
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], kStagers); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], kStagers + 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kDrainWarps); }
         mbar_init(&done_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
-        // 128 fp32 accumulator columns of tensor memory for this CTA
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)BN) : "memory");
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
 
-    if (warp < 4) {
-        // ------------------------------------------------------------ staging warps
-        const int64_t row = m0 + tid < p.rows ? m0 + tid : p.rows - 1;  // rows past the end are computed and dropped
-        const int token = n0 + tid;
-        const bool live_token = token < p.tokens;
-        const float* xt = p.x + (int64_t)(live_token ? token : 0) * p.st;
+    if (warp < kStageWarps) {
+        // ------------------------------------------------------------ staging warps: W -> hi / lo tiles
+        const int r = tid & 127, half = tid >> 7;  // a row of the tile, and which 32 of the slice's 64 values
+        const int64_t row = m0 + r < p.rows ? m0 + r : p.rows - 1;  // rows past the end are computed and dropped
         bool dead = false;
+        RawHalf<TYPE> cur, nxt;
+        cur.load(p, row, 0, half);
         for (int ks = 0; ks < k_steps; ++ks) {
             const int slot = ks % kStages;
+            if (ks + 1 < k_steps) nxt.load(p, row, (ks + 1) * BK, half);
+            float v[32];
+            cur.decode(ks * BK, half, v);
             if (ks >= kStages && !dead && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 11); dead = true; }
-            uint8_t* stage = smem + (size_t)slot * kStageBytes;
-            float v[64];
-            row_values<TYPE>(p, row, ks * BK, v);
-            store_row_split(v, kWeightScale, stage, stage + kTileBytes, tid);
-            if (live_token) {
-                if (p.x_vec) {
+            uint8_t* a_hi = smem + (size_t)slot * kStageBytes;
+            uint8_t* a_lo = a_hi + kTileBytes;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) *(float4*)(v + 4 * j) = __ldg((const float4*)(xt + ks * BK) + j);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 64; ++j) v[j] = __ldg(xt + (int64_t)(ks * BK + j) * p.sk);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 64; ++j) v[j] = 0.0f;
+            for (int c = 0; c < 4; ++c) {
+                uint4 h, l;
+                split8(v + 8 * c, kWeightScale, h, l);
+                const int off = swizzled(r, 4 * half + c);
+                *(uint4*)(a_hi + off) = h;
+                *(uint4*)(a_lo + off) = l;
             }
-            store_row_split(v, 1.0f, stage + 2 * kTileBytes, stage + 3 * kTileBytes, tid);
             // the tensor core reads shared memory through the async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(&full_bar[slot]);
+            cur = nxt;
         }
-        // ------------------------------------------------------------ epilogue
+    } else if (warp < kMmaWarp) {
+        // ------------------------------------------------------------ drain warps: tensor memory -> fp32 registers -> Y
+        // warp w may read accumulator rows 32 (w % 4) ..; the eight warps split the columns in two
+        const int dw = warp - kStageWarps, quarter = warp & 3, chalf = dw >> 2;
+        const int cols_here = bn >> 1, col0 = chalf * cols_here;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        bool dead = false;
+        for (int ks = 0; ks < k_steps; ++ks) {
+            const int b = ks & 1;
+            if (!dead && !mbar_wait(&acc_full[b], (ks >> 1) & 1)) { atomicExch(p.error_flag, 14); dead = true; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (16 * c < cols_here) {
+                    uint32_t t[16];
+                    tmem_ld16(tmem_base + lane_base + (uint32_t)(b * bn + col0 + 16 * c), t);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[16 * c + j] += __uint_as_float(t[j]);
+                }
+            }
+            // this warp has read the accumulator: the tensor core may overwrite it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);
+        }
         if (!dead && !mbar_wait(&done_bar, 0)) { atomicExch(p.error_flag, 12); dead = true; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int64_t out_row = m0 + warp * 32 + lane;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t r[32];
-            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
-                "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-                  "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-                  "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-                  "=r"(r[31])
-                : "r"(taddr));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (out_row < p.rows && !dead) {
+        const int64_t out_row = m0 + quarter * 32 + lane;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int t = n0 + c0 + j;
-                    if (t < p.tokens) p.y[out_row * p.yn + (int64_t)t * p.yt] = __uint_as_float(r[j]) * kWeightUnscale;
+        for (int c = 0; c < 4; ++c) {
+            if (16 * c < cols_here) {
+                uint32_t t[16];
+                tmem_ld16(tmem_base + lane_base + (uint32_t)(2 * bn + col0 + 16 * c), t);  // the cross terms
+                if (out_row < p.rows && !dead) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int token = n0 + col0 + 16 * c + j;
+                        if (token < p.tokens) p.y[out_row * p.yn + (int64_t)token * p.yt] = (acc[16 * c + j] + __uint_as_float(t[j])) * kWeightUnscale;
+                    }
                 }
             }
         }
-    } else {
-        // ------------------------------------------------------------ MMA warp
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------ MMA warp (lane 0 issues)
         bool dead = false;
+        const uint32_t idesc = instr_desc(bn);
         for (int ks = 0; ks < k_steps; ++ks) {
-            const int slot = ks % kStages;
+            const int slot = ks % kStages, b = ks & 1;
             if (!dead && !mbar_wait(&full_bar[slot], (ks / kStages) & 1)) { atomicExch(p.error_flag, 13); dead = true; }
+            if (ks >= 2 && !dead && !mbar_wait(&acc_empty[b], ((ks >> 1) - 1) & 1)) { atomicExch(p.error_flag, 15); dead = true; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0 && !dead) {
                 const uint32_t base = smem_u32(smem + (size_t)slot * kStageBytes);
                 const uint64_t a_hi = smem_desc(base), a_lo = smem_desc(base + kTileBytes);
-                const uint64_t b_hi = smem_desc(base + 2 * kTileBytes), b_lo = smem_desc(base + 3 * kTileBytes);
+                const uint64_t b_hi = smem_desc(base + 2 * kTileBytes), b_lo = smem_desc(base + 2 * kTileBytes + bn * 128);
+                const uint32_t acc_main = tmem_base + (uint32_t)(b * bn), acc_cross = tmem_base + (uint32_t)(2 * bn);
 #pragma unroll
                 for (int kk = 0; kk < BK / 16; ++kk) {
                     const uint64_t adv = (uint64_t)(kk * 2);  // 32 bytes along K, in 16-byte units of the start address
-                    mma_f16(tmem_base, a_hi + adv, b_hi + adv, (ks | kk) ? 1u : 0u);
-                    mma_f16(tmem_base, a_hi + adv, b_lo + adv, 1u);
-                    mma_f16(tmem_base, a_lo + adv, b_hi + adv, 1u);
+                    mma_f16(acc_main, a_hi + adv, b_hi + adv, idesc, kk ? 1u : 0u);       // a fresh sum for every slice
+                    mma_f16(acc_cross, a_hi + adv, b_lo + adv, idesc, (ks | kk) ? 1u : 0u);
+                    mma_f16(acc_cross, a_lo + adv, b_hi + adv, idesc, 1u);
                 }
-                mma_commit(&empty_bar[slot]);          // the stage is free once these have read it
+                mma_commit(&empty_bar[slot]);  // the stage is free once these have read it
+                mma_commit(&acc_full[b]);      // and the slice's sum is complete
                 if (ks == k_steps - 1) mma_commit(&done_bar);
             }
             __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------ copy warp (lane 0): the split X tiles
+        if (lane == 0) {
+            // the activation tiles were written by the kernel before this one
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            const uint32_t bytes = 2u * (uint32_t)bn * 128u;
+            const uint8_t* src = p.xs + (size_t)nt * k_steps * bytes;
+            for (int ks = 0; ks < k_steps; ++ks) {
+                const int slot = ks % kStages;
+                if (ks >= kStages && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 16); break; }
+                mbar_expect_tx(&full_bar[slot], bytes);
+                bulk_g2s(smem + (size_t)slot * kStageBytes + 2 * kTileBytes, src + (size_t)ks * bytes, bytes, &full_bar[slot]);
+            }
         }
     }
     // free the tensor memory: everyone is past its use
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    if (warp == kMmaWarp) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
 }
 
 template <int TYPE>
@@ -303,9 +429,17 @@ int launch_mm(const MatmulParams& p, cudaStream_t s) {
         RQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    dim3 grid((unsigned)((p.rows + BM - 1) / BM), (unsigned)((p.tokens + BN - 1) / BN));
-    kernel<<<grid, kThreadsMM, smem, s>>>(p);
-    RQ_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((p.rows + BM - 1) / BM), (unsigned)((p.tokens + p.bn - 1) / p.bn));
+    cfg.blockDim = dim3(kThreadsMM);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return RQ_OK;
 }
 
@@ -315,8 +449,27 @@ int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk
     if (w->cols % BK) return RQ_ERR_UNSUPPORTED;
     MatmulParams p;
     p.main = w->main; p.scale = w->scale; p.rows = w->rows; p.cols = (int)w->cols;
-    p.x = x; p.sk = sk; p.st = st; p.tokens = tokens; p.y = y;
-    p.x_vec = (sk == 1 && (st % 4 == 0 || tokens == 1) && ((uintptr_t)x % 16) == 0) ? 1 : 0; p.yn = yn; p.yt = yt; p.error_flag = ctx->error_flag;
+    p.bn = tokens <= 32 ? 32 : (tokens <= 64 ? 64 : 128);
+    p.tokens = tokens; p.y = y; p.yn = yn; p.yt = yt; p.error_flag = ctx->error_flag;
+    // the split activations live in the context's scratch (whatever int8 records it held are gone)
+    const int n_tiles = (tokens + p.bn - 1) / p.bn, k_steps = p.cols / BK;
+    const size_t bytes = (size_t)n_tiles * k_steps * 2 * p.bn * 128;
+    int rc = rq_ensure_act_scratch(ctx, bytes);
+    if (rc) return rc;
+    ctx->act_cols = 0;
+    p.xs = ctx->act_scratch;
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)k_steps, (unsigned)n_tiles);
+        cfg.blockDim = dim3(128);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_split_x_kernel, x, sk, st, tokens, p.bn, ctx->act_scratch));
+    }
     switch (w->type) {
         case RQ_Q4_K: return launch_mm<RQ_Q4_K>(p, s);
         case RQ_Q6_K: return launch_mm<RQ_Q6_K>(p, s);
