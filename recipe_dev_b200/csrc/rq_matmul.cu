@@ -46,6 +46,8 @@ struct MatmulParams {
     int bn;             // tokens per tile
     int tokens;
     float* y; int64_t yn, yt;
+    int ks_per_split;   // 64-wide slices per CTA along K (gridDim.z CTAs share a tile's K)
+    float* partial;     // gridDim.z > 1: [split][token][row] sums, added in split order by rq_sum_splits_kernel
     int* error_flag;
 };
 
@@ -61,10 +63,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// a try_wait that lets the hardware park the thread for up to `ns` (it wakes when the phase completes)
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+                 : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
-    while (!mbar_try_wait(bar, parity))
+    while (!mbar_try_wait_parked(bar, parity, 2000u))  // parked waits do not eat the staging warps' issue slots
         if (global_ns() - t0 > kWaitLimitNs) return false;
     return true;
 }
@@ -154,9 +165,15 @@ template <> struct RawHalf<RQ_Q4_K> {
         const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         const int shift = 4 * half;  // sub-block 2 pr in the low nibbles, 2 pr + 1 in the high
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t nib = (w[j] >> shift) & 0x0F0F0F0Fu;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) v[4 * j + i] = __fsub_rn(__fmul_rn(step, (float)((w[j] >> (8 * i + shift)) & 15)), base);
+            for (int i = 0; i < 4; ++i) {
+                // 0x4B0000nn is 2^23 + nn: the nibble as a float without the conversion unit
+                const float q = __uint_as_float(__byte_perm(nib, 0x4B000000u, 0x7650 + i)) - 8388608.0f;
+                v[4 * j + i] = __fsub_rn(__fmul_rn(step, q), base);
+            }
+        }
     }
 };
 template <> struct RawHalf<RQ_Q6_K> {
@@ -267,6 +284,19 @@ __global__ void __launch_bounds__(128) rq_split_x_kernel(const float* __restrict
     }
 }
 
+// y[row][token] = the splits' sums added in split order (the same bits on every run)
+__global__ void __launch_bounds__(256) rq_sum_splits_kernel(const float* __restrict__ partial, int splits, int64_t rows, int tokens, float* __restrict__ y, int64_t yn, int64_t yt) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int64_t total = rows * tokens;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t token = i / rows, row = i - token * rows;
+        float sum = 0.f;
+        for (int z = 0; z < splits; ++z) sum += partial[(size_t)z * total + i];
+        y[row * yn + token * yt] = sum;
+    }
+}
+
 template <int TYPE>
 __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_constant__ MatmulParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -276,7 +306,9 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t m0 = (int64_t)blockIdx.x * BM;
     const int nt = blockIdx.y, n0 = nt * p.bn;
-    const int k_steps = p.cols / BK;
+    const int k_first = blockIdx.z * p.ks_per_split;  // this CTA's slices of K
+    const int k_steps = min(p.ks_per_split, p.cols / BK - k_first);
+    const int k_total = p.cols / BK;
     const int bn = p.bn;
     // tensor memory: two accumulators for the hi x hi term, one for the cross terms: 3 bn columns, allocated as a power of two
     const uint32_t tmem_cols = bn == 128 ? 512u : (bn == 64 ? 256u : 128u);
@@ -303,12 +335,12 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
         const int64_t row = m0 + r < p.rows ? m0 + r : p.rows - 1;  // rows past the end are computed and dropped
         bool dead = false;
         RawHalf<TYPE> cur, nxt;
-        cur.load(p, row, 0, half);
+        cur.load(p, row, k_first * BK, half);
         for (int ks = 0; ks < k_steps; ++ks) {
             const int slot = ks % kStages;
-            if (ks + 1 < k_steps) nxt.load(p, row, (ks + 1) * BK, half);
+            if (ks + 1 < k_steps) nxt.load(p, row, (k_first + ks + 1) * BK, half);
             float v[32];
-            cur.decode(ks * BK, half, v);
+            cur.decode((k_first + ks) * BK, half, v);
             if (ks >= kStages && !dead && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 11); dead = true; }
             uint8_t* a_hi = smem + (size_t)slot * kStageBytes;
             uint8_t* a_lo = a_hi + kTileBytes;
@@ -365,7 +397,11 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int token = n0 + col0 + 16 * c + j;
-                        if (token < p.tokens) p.y[out_row * p.yn + (int64_t)token * p.yt] = (acc[16 * c + j] + __uint_as_float(t[j])) * kWeightUnscale;
+                        const float out = (acc[16 * c + j] + __uint_as_float(t[j])) * kWeightUnscale;
+                        if (token < p.tokens) {
+                            if (gridDim.z == 1) p.y[out_row * p.yn + (int64_t)token * p.yt] = out;
+                            else p.partial[((size_t)blockIdx.z * p.tokens + token) * p.rows + out_row] = out;
+                        }
                     }
                 }
             }
@@ -403,7 +439,7 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
             // the activation tiles were written by the kernel before this one
             asm volatile("griddepcontrol.wait;" ::: "memory");
             const uint32_t bytes = 2u * (uint32_t)bn * 128u;
-            const uint8_t* src = p.xs + (size_t)nt * k_steps * bytes;
+            const uint8_t* src = p.xs + ((size_t)nt * k_total + k_first) * bytes;
             for (int ks = 0; ks < k_steps; ++ks) {
                 const int slot = ks % kStages;
                 if (ks >= kStages && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 16); break; }
@@ -430,7 +466,7 @@ int launch_mm(const MatmulParams& p, cudaStream_t s) {
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((p.rows + BM - 1) / BM), (unsigned)((p.tokens + p.bn - 1) / p.bn));
+    cfg.gridDim = dim3((unsigned)((p.rows + BM - 1) / BM), (unsigned)((p.tokens + p.bn - 1) / p.bn), (unsigned)((p.cols / BK + p.ks_per_split - 1) / p.ks_per_split));
     cfg.blockDim = dim3(kThreadsMM);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
@@ -454,10 +490,23 @@ int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk
     // the split activations live in the context's scratch (whatever int8 records it held are gone)
     const int n_tiles = (tokens + p.bn - 1) / p.bn, k_steps = p.cols / BK;
     const size_t bytes = (size_t)n_tiles * k_steps * 2 * p.bn * 128;
-    int rc = rq_ensure_act_scratch(ctx, bytes);
+    // Few tiles and a long K: several CTAs share a tile's K (at least sixteen slices each) so that the whole GPU
+    // dequantises, and a second kernel adds their sums.
+    const int64_t tiles = ((w->rows + BM - 1) / BM) * n_tiles;
+    int splits = 1;
+    if (tiles < ctx->sm_count) {
+        splits = (int)(ctx->sm_count / tiles);
+        if (splits > k_steps / 16) splits = k_steps / 16;
+        if (splits < 1) splits = 1;
+    }
+    p.ks_per_split = (k_steps + splits - 1) / splits;
+    splits = (k_steps + p.ks_per_split - 1) / p.ks_per_split;
+    const size_t partial_bytes = splits > 1 ? (size_t)splits * tokens * w->rows * 4 : 0;
+    int rc = rq_ensure_act_scratch(ctx, bytes + partial_bytes);
     if (rc) return rc;
     ctx->act_cols = 0;
     p.xs = ctx->act_scratch;
+    p.partial = splits > 1 ? (float*)(ctx->act_scratch + bytes) : nullptr;
     {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)k_steps, (unsigned)n_tiles);
@@ -471,10 +520,23 @@ int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk
         RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_split_x_kernel, x, sk, st, tokens, p.bn, ctx->act_scratch));
     }
     switch (w->type) {
-        case RQ_Q4_K: return launch_mm<RQ_Q4_K>(p, s);
-        case RQ_Q6_K: return launch_mm<RQ_Q6_K>(p, s);
-        case RQ_Q8_0: return launch_mm<RQ_Q8_0>(p, s);
-        case RQ_Q4_0: return launch_mm<RQ_Q4_0>(p, s);
+        case RQ_Q4_K: rc = launch_mm<RQ_Q4_K>(p, s); break;
+        case RQ_Q6_K: rc = launch_mm<RQ_Q6_K>(p, s); break;
+        case RQ_Q8_0: rc = launch_mm<RQ_Q8_0>(p, s); break;
+        case RQ_Q4_0: rc = launch_mm<RQ_Q4_0>(p, s); break;
         default: return RQ_ERR_UNSUPPORTED;
     }
+    if (rc || splits == 1) return rc;
+    cudaLaunchConfig_t cfg = {};
+    const int64_t total = w->rows * tokens;
+    cfg.gridDim = dim3((unsigned)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184));
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_sum_splits_kernel, (const float*)p.partial, splits, (int64_t)w->rows, tokens, y, yn, yt));
+    return RQ_OK;
 }
