@@ -177,6 +177,7 @@ def workload_config(args, layers):
     return {"workload": "llama-8B-shaped decode layer, batch 1: q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096 Q4_K; down 4096x14336 Q6_K",
             "activation_mode": "int8 records, step 32 (recipe default profile)" if args.act == "int8" else "fp32 activations as they are",
             "layers_in_rotation": layers, "l2": "inputs larger than L2: each step reads a different layer of a stack larger than 1 GB",
+            "timing": "the K timed steps are one CUDA graph, replayed once untimed (its first launch uploads it) after the W warm-up steps, then timed with CUDA events",
             "algorithmic_bytes_per_step": LAYER_BYTES, "multi_gpu": "replicas only (the decode layer is unsharded)"}
 
 
@@ -265,6 +266,7 @@ def run_ours(args):
 
     # ---- device-resident timing: exactly K steps after W warm-up steps -----------------
     warm_graph.replay()
+    timed_graph.replay()  # untimed: the first launch of a graph also uploads it to the device
     sampler = ClockSampler(local)
     barrier()
     if rank == 0:
@@ -346,8 +348,8 @@ def run_ours(args):
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": dom_us, "algorithmic_bytes_per_launch": dom_bytes,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the same kernel over one of the two
-                     # row sets (14336 x 4096: 33,079,808 bytes), scaled to the launch's two row sets
-                     "traffic": 2 * 33_079_808, "traffic_source": "profiles/rq_gemv_stream_q4k_14336x4096_int8.md, x2 row sets"},
+                     # row sets (14336 x 4096: 33.10 MB read, nothing written), scaled to the launch's two row sets
+                     "traffic": 2 * 33_101_300, "traffic_source": "profiles/rq_gemv_stream_q4k_14336x4096_int8.md, x2 row sets"},
         "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": sum(4 * c for _, _, _, c, _ in LAYER), "d2h_bytes_per_step": sum(4 * r for _, _, r, _, _ in LAYER),
                 "ms_per_step": 1e3 * e2e_s / args.steps, "call": "rq_matvec_host x 7 per step (host x in, host y out)"},
@@ -402,6 +404,23 @@ def run_case(args):
     y = torch.empty(tokens, rows, device="cuda")
     stream = torch.cuda.current_stream()
     cached = 2 if mode == rq.ACT_INT8 else mode
+    if args.matmul:
+        # the batched entry point: time per call (the activation split and, for split K, the sum kernel included)
+        for i in range(args.warmup):
+            ctx.matmul(ws[i % len(ws)], x, y, act_mode=mode, step=32, stream=stream)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(args.steps):
+            ctx.matmul(ws[(args.warmup + i) % len(ws)], x, y, act_mode=mode, step=32, stream=stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        us = 1e3 * e0.elapsed_time(e1) / args.steps
+        flops = 2.0 * rows * cols * tokens
+        print(json.dumps({"case": args.case, "entry": "rq_matmul", "us_per_call": us, "TFLOPs_useful": flops / us / 1e6, "TFLOPs_issued_fp16": 3 * flops / us / 1e6,
+                          "calls": args.steps, "weight_copies": args.layers}), flush=True)
+        ctx.check()
+        return
     ctx.matvec(ws[0], x, y, act_mode=mode, step=32, stream=stream)
     for i in range(args.warmup):
         ctx.matvec(ws[i % len(ws)], x, y, act_mode=cached, step=32, stream=stream)
@@ -542,6 +561,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-sharded", dest="sharded", action="store_false", help="skip the row-split LM head and expert-parallel MoE configs")
     ap.add_argument("--graph", action="store_true", help="--case: replay the launches as one CUDA graph")
+    ap.add_argument("--matmul", action="store_true", help="--case: the batched tensor-core entry point (rq_matmul) instead of rq_matvec")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -855,13 +855,29 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             }
         } else if (MODE == RQ_ACT_FLOAT) {
             // stage the activations while the first weight stages are in flight
-            for (int v = 0; v < p.act_vectors; ++v) {
-                uint8_t* base = act_smem + v * p.act_bytes;
-                const int vec = tok0 + v;  // plain: token; expert banks: slot vector (one token per launch)
-                const bool live = p.act_vectors > T || vec < p.tokens;
-                const float* src = p.x + (int64_t)(live ? vec : tok0) * p.st;
-                for (int k = tid; k < p.cols; k += kConsumers)
-                    ((float*)(base + (size_t)(k >> 8) * kRecord))[k & 255] = live ? __ldg(src + (int64_t)k * p.sk) : 0.0f;
+            // all vectors as one flat range, eight loads in flight per thread: the copy costs a few trips to L2, not one per element
+            const int total = p.act_vectors * p.cols;
+            for (int base_i = tid; base_i < total; base_i += 8 * kConsumers) {
+                float got[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int i = base_i + j * kConsumers;
+                    got[j] = 0.0f;
+                    if (i < total) {
+                        const int v = i / p.cols, k = i - v * p.cols;
+                        const int vec = tok0 + v;  // plain: token; expert banks: slot vector (one token per launch)
+                        const bool live = p.act_vectors > T || vec < p.tokens;
+                        if (live) got[j] = __ldg(p.x + (int64_t)vec * p.st + (int64_t)k * p.sk);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int i = base_i + j * kConsumers;
+                    if (i < total) {
+                        const int v = i / p.cols, k = i - v * p.cols;
+                        ((float*)(act_smem + v * p.act_bytes + (size_t)(k >> 8) * kRecord))[k & 255] = got[j];
+                    }
+                }
             }
             consumer_sync<kConsumers>();
             for (int v = 0; v < p.act_vectors; ++v) {
@@ -877,12 +893,28 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             consumer_sync<kConsumers>();
         } else {
             const size_t src_bytes = (size_t)p.units * kRecord;
-            for (int v = 0; v < p.act_vectors; ++v) {
-                const int vec = tok0 + v;
-                const bool live = p.act_vectors > T || vec < p.tokens;
-                const uint4* src = (const uint4*)(p.act + (size_t)(live ? vec : tok0) * src_bytes);
-                uint4* dst = (uint4*)(act_smem + v * p.act_bytes);
-                for (int i = tid; i < (int)(src_bytes / 16); i += kConsumers) dst[i] = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+            const int per_vec = (int)(src_bytes / 16), total = p.act_vectors * per_vec;
+            for (int base_i = tid; base_i < total; base_i += 4 * kConsumers) {  // four 16-byte loads in flight per thread
+                uint4 got[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = base_i + j * kConsumers;
+                    got[j] = make_uint4(0, 0, 0, 0);
+                    if (i < total) {
+                        const int v = i / per_vec, e = i - v * per_vec;
+                        const int vec = tok0 + v;
+                        const bool live = p.act_vectors > T || vec < p.tokens;
+                        if (live) got[j] = __ldg((const uint4*)(p.act + (size_t)vec * src_bytes) + e);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = base_i + j * kConsumers;
+                    if (i < total) {
+                        const int v = i / per_vec, e = i - v * per_vec;
+                        ((uint4*)(act_smem + v * p.act_bytes))[e] = got[j];
+                    }
+                }
             }
             consumer_sync<kConsumers>();
         }

@@ -114,6 +114,20 @@ __device__ __forceinline__ float sigmoid_portable(float x) { return __fmul_rn(0.
 // ---- routing: one CTA per token ------------------------------------------------------------
 constexpr int kRouteThreads = 256;
 
+// Sums are added in expert order by one thread (the order is part of the result's bits); maxima and the
+// top-k picks do not depend on order and are found by the whole CTA. A NaN among the scores or keys makes
+// "greater than" order-dependent, so such a token takes the one-thread path throughout.
+__device__ __forceinline__ float block_max(float v, float* scratch, int tid) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    __syncthreads();
+    if ((tid & 31) == 0) scratch[tid >> 5] = v;
+    __syncthreads();
+    float m = scratch[0];
+    for (int w = 1; w < kRouteThreads / 32; ++w) m = fmaxf(m, scratch[w]);
+    return m;
+}
+
 __global__ void __launch_bounds__(kRouteThreads) rq_route_kernel(const float* __restrict__ scores, int64_t se, int64_t st, int experts, int top,
                                                                 int sigmoid, int renorm, const float* __restrict__ bias,
                                                                 float* __restrict__ weights, int64_t we, int64_t wt) {
@@ -122,57 +136,110 @@ __global__ void __launch_bounds__(kRouteThreads) rq_route_kernel(const float* __
     float* val = sm + experts;
     float* key = sm + 2 * experts;
     int* mark = (int*)(sm + 3 * experts);
-    __shared__ float s_max, s_total;
-    __shared__ int s_best;
+    __shared__ float s_max, s_total, s_wmax[kRouteThreads / 32], s_wkey[kRouteThreads / 32];
+    __shared__ int s_best, s_widx[kRouteThreads / 32];
     const int t = blockIdx.x, tid = threadIdx.x;
     const bool sig = sigmoid != 0, every = renorm == 0, divide = renorm != 0 || !sig;
-    for (int e = tid; e < experts; e += kRouteThreads) { raw[e] = scores[e * se + t * st]; mark[e] = 0; }
-    __syncthreads();
-    // the maximum over every expert (first wins a tie; the value is what matters) and the total
-    if (tid == 0) {
-        float mx = raw[0];
-        for (int e = 1; e < experts; ++e) if (raw[e] > mx) mx = raw[e];
-        s_max = mx;
+    const float kLowest = __int_as_float(0xff800000);  // -inf
+    int nan_here = 0;
+    for (int e = tid; e < experts; e += kRouteThreads) {
+        const float v = scores[e * se + t * st];
+        raw[e] = v; mark[e] = 0;
+        nan_here |= (v != v) || (bias && bias[e] != bias[e]);
     }
-    __syncthreads();
+    const bool ordered = __syncthreads_or(nan_here) != 0;  // a NaN somewhere: every step in index order by one thread
+    // the maximum over every expert
+    if (ordered) {
+        if (tid == 0) {
+            float mx = raw[0];
+            for (int e = 1; e < experts; ++e) if (raw[e] > mx) mx = raw[e];
+            s_max = mx;
+        }
+        __syncthreads();
+    } else {
+        float mx = kLowest;
+        for (int e = tid; e < experts; e += kRouteThreads) mx = fmaxf(mx, raw[e]);
+        mx = block_max(mx, s_wmax, tid);
+        if (tid == 0) s_max = mx;
+        __syncthreads();
+    }
     for (int e = tid; e < experts; e += kRouteThreads) val[e] = topk_score(raw[e], s_max, sig);
     __syncthreads();
     if (tid == 0) {
         float total = 0.0f;
+#pragma unroll 8
         for (int e = 0; e < experts; ++e) total = __fadd_rn(total, val[e]);
         s_total = total;
     }
     __syncthreads();
     // selection key: the raw score, or the probability over every expert plus the expert's bias
-    for (int e = tid; e < experts; e += kRouteThreads)
-        key[e] = bias ? __fadd_rn(sig ? val[e] : __fdiv_rn(val[e], s_total), bias[e]) : raw[e];
-    __syncthreads();
+    int key_nan = 0;
+    for (int e = tid; e < experts; e += kRouteThreads) {
+        const float k = bias ? __fadd_rn(sig ? val[e] : __fdiv_rn(val[e], s_total), bias[e]) : raw[e];
+        key[e] = k;
+        key_nan |= k != k;
+    }
+    const bool ordered_pick = __syncthreads_or(key_nan) != 0 || ordered;
     // pick `top` times the unmarked expert of strictly greatest key; ties go to the lowest index
     for (int pick = 0; pick < top; ++pick) {
-        if (tid == 0) {
-            int best = -1;
-            float best_key = 0.0f;
-            for (int e = 0; e < experts; ++e)
-                if (!mark[e] && (best == -1 || key[e] > best_key)) { best = e; best_key = key[e]; }
-            s_best = best;
+        if (ordered_pick) {
+            if (tid == 0) {
+                int best = -1;
+                float best_key = 0.0f;
+                for (int e = 0; e < experts; ++e)
+                    if (!mark[e] && (best == -1 || key[e] > best_key)) { best = e; best_key = key[e]; }
+                if (best >= 0) mark[best] = 1;
+            }
+            __syncthreads();
+        } else {
+            int best = 0x7fffffff;
+            float best_key = kLowest;
+            for (int e = tid; e < experts; e += kRouteThreads)
+                if (!mark[e] && (best == 0x7fffffff || key[e] > best_key)) { best = e; best_key = key[e]; }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ok = __shfl_xor_sync(0xffffffffu, best_key, off);
+                const int oi = __shfl_xor_sync(0xffffffffu, best, off);
+                if (oi != 0x7fffffff && (best == 0x7fffffff || ok > best_key || (ok == best_key && oi < best))) { best = oi; best_key = ok; }
+            }
+            if ((tid & 31) == 0) { s_wkey[tid >> 5] = best_key; s_widx[tid >> 5] = best; }
+            __syncthreads();
+            if (tid == 0) {
+                for (int w = 1; w < kRouteThreads / 32; ++w) {
+                    const float ok = s_wkey[w];
+                    const int oi = s_widx[w];
+                    if (oi != 0x7fffffff && (best == 0x7fffffff || ok > best_key || (ok == best_key && oi < best))) { best = oi; best_key = ok; }
+                }
+                if (best != 0x7fffffff) mark[best] = 1;
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        if (tid == 0 && s_best >= 0) mark[s_best] = 1;
-        __syncthreads();
     }
     // the maximum and the total over the kept experts (or every expert without renormalising)
-    if (tid == 0) {
-        float mx = 0.0f;
-        bool first = true;
-        for (int e = 0; e < experts; ++e)
-            if ((mark[e] || every) && (first || raw[e] > mx)) { mx = raw[e]; first = false; }
-        s_max = mx;
+    if (ordered) {
+        if (tid == 0) {
+            float mx = 0.0f;
+            bool first = true;
+            for (int e = 0; e < experts; ++e)
+                if ((mark[e] || every) && (first || raw[e] > mx)) { mx = raw[e]; first = false; }
+            s_max = mx;
+        }
+        __syncthreads();
+    } else {
+        float mx = kLowest;
+        int any = 0;
+        for (int e = tid; e < experts; e += kRouteThreads)
+            if (mark[e] || every) { mx = fmaxf(mx, raw[e]); any = 1; }
+        mx = block_max(mx, s_wmax, tid);
+        const bool some = __syncthreads_or(any) != 0;
+        if (tid == 0) s_max = some ? mx : 0.0f;
+        __syncthreads();
     }
-    __syncthreads();
     for (int e = tid; e < experts; e += kRouteThreads) val[e] = topk_score(raw[e], s_max, sig);
     __syncthreads();
     if (tid == 0) {
         float total = 0.0f;
+#pragma unroll 8
         for (int e = 0; e < experts; ++e) total = __fadd_rn(total, (mark[e] || every) ? val[e] : 0.0f);
         s_total = total;
     }
