@@ -305,8 +305,8 @@ def run_ours(args):
     def layer_pass_host(li):
         ws = layers[li % n_layers]
         out = None
-        for (name, t, rows, cols, shares), w in zip(LAYER, ws):
-            out = ctx.matvec_host(w, hx[cols], act_mode=mode, step=step)
+        for g in GROUPS:  # one host call per group of projections that read the same x
+            out = ctx.matvec_multi_host([ws[j] for j in g], hx[LAYER[g[0]][3]], act_mode=mode, step=step)
         return out
     for i in range(min(args.warmup, 3)):
         layer_pass_host(i)
@@ -352,7 +352,7 @@ def run_ours(args):
                      "traffic": 2 * 33_101_300, "traffic_source": "profiles/rq_gemv_stream_q4k_14336x4096_int8.md, x2 row sets"},
         "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": sum(4 * c for _, _, _, c, _ in LAYER), "d2h_bytes_per_step": sum(4 * r for _, _, r, _, _ in LAYER),
-                "ms_per_step": 1e3 * e2e_s / args.steps, "call": "rq_matvec_host x 7 per step (host x in, host y out)"},
+                "ms_per_step": 1e3 * e2e_s / args.steps, "call": "rq_matvec_multi_host x 4 per step (q/k/v, o, gate/up, down: host x in, host y out)"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }

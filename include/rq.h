@@ -123,6 +123,12 @@ int rq_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t x_k_strid
 int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host_x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
                    float* host_y, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step);
 
+/* rq_matvec_multi with HOST buffers: x goes in once, the n matrices run as one launch, the outputs come
+ * back in one copy, one synchronisation. What a host without device buffers calls for sibling
+ * projections (q/k/v, gate/up; Placed::infer, recipe.rs:21314-21490). */
+int rq_matvec_multi_host(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* host_x, int64_t x_k_stride, int64_t x_t_stride,
+                         int tokens, float* const* host_ys, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step);
+
 /* The INT8 product of one contiguous column (x[cols] -> y[rows]) for callers that cannot allocate.
  * No counterpart in the reference: there the host owns every arena and kernels never allocate, so
  * the question does not arise; here rq_matvec grows a scratch buffer with cudaMalloc on demand.

@@ -54,6 +54,7 @@ def _declare(lib) -> None:
         "rq_matmul": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
         "rq_matvec_multi": (i32, [p, i32, p, f32p, i64, i64, i32, p, i64, i64, i32, i32, p]),
         "rq_matvec_host": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32]),
+        "rq_matvec_multi_host": (i32, [p, i32, p, f32p, i64, i64, i32, p, i64, i64, i32, i32]),
         "rq_quantize_activations": (i32, [p, f32p, i64, i64, i64, i32, i32, p, p]),
         "rq_matvec_int8_static": (i32, [p, p, f32p, f32p, i32, p]),
     }
@@ -285,6 +286,21 @@ class Context:
         y = np.empty((tokens, w.rows), dtype=np.float32)
         _check(self.lib.rq_matvec_host(self.handle, w.handle, x2.ctypes.data, 1, x2.shape[1], tokens, y.ctypes.data, 1, w.rows, act_mode, step))
         return y[0] if single else y
+
+    def matvec_multi_host(self, ws, x: np.ndarray, act_mode: int = ACT_FLOAT, step: int = 32):
+        """Host buffers in and out for several weights that read one x ([cols] or [tokens, cols]): a list of outputs."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        single = x.ndim == 1
+        x2 = x[None, :] if single else x
+        tokens, n = x2.shape[0], len(ws)
+        total = sum(w.rows for w in ws)
+        plane = np.empty((tokens, total), dtype=np.float32)  # the outputs share one token stride: slices of one plane
+        offs = np.cumsum([0] + [w.rows for w in ws])
+        wa = (C.c_void_p * n)(*[w.handle for w in ws])
+        ya = (C.c_void_p * n)(*[plane.ctypes.data + 4 * int(o) for o in offs[:-1]])
+        _check(self.lib.rq_matvec_multi_host(self.handle, n, wa, x2.ctypes.data, 1, x2.shape[1], tokens, ya, 1, total, act_mode, step))
+        ys = [plane[:, int(offs[i]):int(offs[i + 1])] for i in range(n)]
+        return [y[0] for y in ys] if single else ys
 
     def matvec_int8_static(self, w: Weight, x, y=None, step: int = 32, stream=None):
         """The INT8 product of one contiguous column through the entry point that allocates nothing

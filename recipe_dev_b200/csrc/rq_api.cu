@@ -312,6 +312,48 @@ extern "C" int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host
     return RQ_OK;
 }
 
+extern "C" int rq_matvec_multi_host(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* host_x, int64_t sk, int64_t st, int tokens,
+                                    float* const* host_ys, int64_t yn, int64_t yt, int act_mode, int step) {
+    if (!ctx || !ws || !host_ys || n < 1) return rq_fail(RQ_ERR_INVALID, "rq_matvec_multi_host: null argument or no matrices");
+    if (n > 16) return rq_fail(RQ_ERR_LIMIT, "rq_matvec_multi_host: %d matrices, at most 16", n);
+    int64_t total_rows = 0;
+    for (int i = 0; i < n; ++i) {
+        int rc = check_matvec("rq_matvec_multi_host", ctx, ws[i], host_x, host_ys[i], tokens, act_mode, step);
+        if (rc) return rc;
+        if (ws[i]->type != ws[0]->type || ws[i]->cols != ws[0]->cols)
+            return rq_fail(RQ_ERR_INVALID, "rq_matvec_multi_host: matrix %d differs from matrix 0 in format or width (they must read one activation column)", i);
+        total_rows += ws[i]->rows;
+    }
+    if (sk <= 0 || yn <= 0 || (tokens > 1 && (st <= 0 || yt <= 0))) return rq_fail(RQ_ERR_INVALID, "rq_matvec_multi_host: strides must be positive");
+    DeviceGuard guard(ctx->device);
+    const int64_t cols = ws[0]->cols;
+    // x token-major in pinned memory; the outputs as one [tokens, all rows] plane, matrix i at its row offset
+    size_t xb = (size_t)tokens * (size_t)cols * 4, yb = (size_t)tokens * (size_t)total_rows * 4;
+    int rc = ensure_buffer(&ctx->stage_x, &ctx->stage_x_bytes, &ctx->pin_x, &ctx->pin_x_bytes, xb);
+    if (rc) return rc;
+    rc = ensure_buffer(&ctx->stage_y, &ctx->stage_y_bytes, &ctx->pin_y, &ctx->pin_y_bytes, yb);
+    if (rc) return rc;
+    for (int t = 0; t < tokens; ++t)
+        for (int64_t k = 0; k < cols; ++k) ctx->pin_x[(size_t)t * cols + k] = host_x[k * sk + t * st];
+    RQ_CUDA(cudaMemcpyAsync(ctx->stage_x, ctx->pin_x, xb, cudaMemcpyHostToDevice, ctx->stream));
+    float* dev_ys[16];
+    int64_t at = 0;
+    for (int i = 0; i < n; ++i) { dev_ys[i] = ctx->stage_y + at; at += ws[i]->rows; }
+    rc = rq_launch_gemv_multi(ctx, n, ws, ctx->stage_x, 1, cols, tokens, dev_ys, 1, total_rows, act_mode, step, ctx->stream);
+    if (rc) return rc;
+    RQ_CUDA(cudaMemcpyAsync(ctx->pin_y, ctx->stage_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    RQ_CUDA(cudaMemcpyAsync(ctx->pin_flag, ctx->error_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    RQ_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (*ctx->pin_flag) return rq_check(ctx);
+    at = 0;
+    for (int i = 0; i < n; ++i) {
+        for (int t = 0; t < tokens; ++t)
+            for (int64_t r = 0; r < ws[i]->rows; ++r) host_ys[i][r * yn + t * yt] = ctx->pin_y[(size_t)t * total_rows + at + r];
+        at += ws[i]->rows;
+    }
+    return RQ_OK;
+}
+
 extern "C" int rq_quantize_activations(rq_ctx* ctx, const float* x, int64_t sk, int64_t st, int64_t cols, int tokens,
                                        int step, void* dev_records, void* stream) {
     if (!ctx || !x || !dev_records) return rq_fail(RQ_ERR_INVALID, "rq_quantize_activations: null argument");

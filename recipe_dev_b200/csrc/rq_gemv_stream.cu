@@ -60,6 +60,11 @@ struct StreamParams {
     int warp_rows;             // > 0: the warp scheme -- a row's 2 * units items are that many adjacent lanes (a power of two), a warp
                                // pass covers warp_rows = 32 / (2 * units) rows, and the lanes of a row join their sums by shuffles
     int rows_per_thread;       // warp scheme: passes per stage (1 or 2)
+    int interleaved;           // warp-scheme launches with an inline table: CTA b takes stages b, b + CTAs, b + 2 CTAs, ... of the launch
+                               // (at any moment the CTAs read one moving window of memory; measured a little faster than a contiguous
+                               // range per CTA). Claiming stages from a global ticket counter instead was tried and is slower: under
+                               // load an atomic's round trip outlasts a stage.
+    int total_stages, seg_stage_begin[RQ_INLINE_SEGMENTS + 1];  // interleaved: stages of the launch, and where each segment's stages begin
     int pieces, piece_rows;    // a stage lands as `pieces` copies with a barrier each (2 in the warp scheme with two passes: one per pass), piece_rows rows each
     int window;                // the producer keeps at most this many pieces in flight: enough bytes to cover the memory latency at full
                                // bandwidth, not more -- a deeper queue only delays everything else that reads memory (the activations)
@@ -706,17 +711,33 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
         bool failed = false;
         const uint64_t policy = evict_first_policy();
         // issues stages until `limit` have been issued or the rows run out
+        const int grid = (int)gridDim.x;
+        int my_stage = (int)blockIdx.x;  // interleaved launches: the stage to issue next
         auto issue = [&](int limit) {
-            for (; r < row_end && st < limit && !failed; ++st) {
-                while (seg + 1 < n_segments && r >= segs[seg].row_begin + segs[seg].rows) ++seg;
+            for (; st < limit && !failed; ++st) {
+                int nr;
+                int64_t lr0;  // first row, local to the segment
+                if (p.interleaved) {
+                    if (my_stage >= p.total_stages) break;
+                    seg = 0;
+                    while (seg + 1 < n_segments && my_stage >= p.seg_stage_begin[seg + 1]) ++seg;
+                    lr0 = (int64_t)(my_stage - p.seg_stage_begin[seg]) * p.stage_rows;
+                    const int64_t left = segs[seg].rows - lr0;
+                    nr = (int)(left < p.stage_rows ? left : p.stage_rows);
+                    my_stage += grid;
+                } else {
+                    if (r >= row_end) break;
+                    while (seg + 1 < n_segments && r >= segs[seg].row_begin + segs[seg].rows) ++seg;
+                    const int64_t seg_end = segs[seg].row_begin + segs[seg].rows;
+                    int64_t stop = r + p.stage_rows;
+                    if (stop > seg_end) stop = seg_end;
+                    if (stop > row_end) stop = row_end;
+                    nr = (int)(stop - r);
+                    lr0 = r - segs[seg].row_begin;
+                    r = stop;
+                }
                 const RqSegment& sg = segs[seg];
                 if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase)) { atomicExch(p.error_flag, 1); failed = true; break; }
-                const int64_t seg_end = sg.row_begin + sg.rows;
-                int64_t stop = r + p.stage_rows;
-                if (stop > seg_end) stop = seg_end;
-                if (stop > row_end) stop = row_end;
-                const int nr = (int)(stop - r);
-                const int64_t lr0 = r - sg.row_begin;  // first row, local to the segment
                 uint8_t* dst = ring + (size_t)slot * p.stage_bytes;
                 stage_info[slot] = make_int4(nr, seg, (int)lr0,
                                              TYPE != RQ_Q4_K ? (int)(((uintptr_t)sg.scale[0] + (uintptr_t)(lr0 * row_scales * 2)) & 15) : 0);
@@ -760,7 +781,6 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                 }
                 if (failed) break;
                 issued = st + 1;
-                r = stop;
                 if (++slot == p.stages) { slot = 0; phase ^= 1; }
             }
         };
@@ -791,6 +811,15 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                 r = row_begin;
             }
             issue(0x7fffffff);
+            if (p.warp_rows && !failed) {
+                // the warp scheme's consumers read what each slot holds from stage_info: a stage of no rows ends their loop
+                if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase)) { atomicExch(p.error_flag, 1); failed = true; }
+                else {
+                    stage_info[slot] = make_int4(0, 0, 0, 0);
+                    for (int k = 0; k < p.pieces; ++k) mbar_expect_tx(&full_bar[2 * slot + k], 0);
+                    issued = ++st;
+                }
+            }
             // leave only after every copy this CTA issued has landed (bounded)
             for (int w = (issued > p.stages ? issued - p.stages : 0); w < issued; ++w)
                 for (int k = 0; k < p.pieces; ++k)
@@ -992,12 +1021,14 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
 #ifdef RQ_TRACE
             int trace_st = 0;
 #endif
-            while (r < row_end) {
-                if (!dead && !mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+            while (true) {
+                if (!mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                if (dead) break;
 #ifdef RQ_TRACE
                 RQ_STAMP(2 + 2 * trace_st);
 #endif
                 const int4 info = stage_info[slot];  // rows, segment, first local row, offset of the first d
+                if (info.x == 0) break;               // the producer has no more rows for this CTA
                 const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
                 ItemRegs<TYPE> wr[R];
                 bool have[R];
@@ -1065,7 +1096,6 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
                 RQ_STAMP(3 + 2 * trace_st);
                 ++trace_st;
 #endif
-                r += info.x;
             }
         } else if (R == 2) {
             // two-row instantiations serve the warp scheme only
@@ -1290,6 +1320,14 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     const size_t smem = fixed + (size_t)stages * p.stage_bytes;
     const int grid_x = (int)(p.rows < ctas ? p.rows : ctas);
     p.rows_quot = p.rows / grid_x; p.rows_rem = (int)(p.rows % grid_x);
+    p.interleaved = 0;
+    if (p.warp_rows && p.table == nullptr && p.plan == nullptr && p.n_segments <= RQ_INLINE_SEGMENTS) {
+        p.interleaved = 1;
+        int at = 0;
+        for (int i = 0; i < p.n_segments; ++i) { p.seg_stage_begin[i] = at; at += (p.inline_seg[i].rows + stage_rows - 1) / stage_rows; }
+        for (int i = p.n_segments; i <= RQ_INLINE_SEGMENTS; ++i) p.seg_stage_begin[i] = at;
+        p.total_stages = at;
+    }
     if (t == 4) return launch_stream<TYPE, MODE, 4, NW, 1>(p, grid_x, smem, s);
     if constexpr (MODE == RQ_ACT_INT8) {
         if (p.rows_per_thread == 2) return launch_stream<TYPE, MODE, 1, NW, 2>(p, grid_x, smem, s);

@@ -269,3 +269,19 @@ def test_fused_quantiser_equals_standalone_quantiser(rq_ctx, oracle, t, cols):
         fused = rq_ctx.matvec(w, torch_cuda(x), act_mode=1, step=step).cpu().numpy()
         static = rq_ctx.matvec_int8_static(w, torch_cuda(x), step=step).cpu().numpy()
         assert np.array_equal(fused.view(np.uint32), static.view(np.uint32))
+
+
+def test_matvec_multi_host_equals_single_host_calls(rq_ctx, oracle):
+    """Sibling projections through host buffers in one call: the bits of one rq_matvec_host call per matrix."""
+    t, cols = ol.Q4_K, 1024
+    rows = [96, 32, 40]
+    ws = [rq_ctx.weight_from_host(t, oracle.quantize(t, oracle.normal(31, i, r * cols, 0.02)), r, cols) for i, r in enumerate(rows)]
+    for tokens in (1, 3):
+        x = oracle.normal(31, 9, tokens * cols, 1.0).reshape(tokens, cols)
+        xs = x[0] if tokens == 1 else x
+        for mode in (0, 1):
+            got = rq_ctx.matvec_multi_host(ws, xs, act_mode=mode, step=32)
+            for w, y in zip(ws, got):
+                one = rq_ctx.matvec_host(w, xs, act_mode=mode, step=32)
+                assert np.array_equal(np.ascontiguousarray(y).view(np.uint32), one.view(np.uint32))
+    rq_ctx.check()
