@@ -788,7 +788,23 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[2 * s], 1); mbar_init(&full_bar[2 * s + 1], 1); mbar_init(&empty_bar[s], NW); }
             for (int s = 0; s <= kMaxStages; ++s) cross_count[s] = 0;
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            if (direct) {
+            if (!direct) {
+                // the table or plan is in device memory and may come from the kernel before: wait for that one, then read it
+                // from there (the consumers are copying it to shared memory meanwhile)
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                int64_t rows = p.rows;
+                if (p.plan) {
+                    segs = p.plan->seg;
+                    n_segments = min(p.plan->n_segments, p.n_segments); subs = min(p.plan->subs, p.subs);
+                    rows = min((int64_t)p.plan->total_rows, p.rows);
+                } else {
+                    segs = p.table;
+                }
+                split_rows(rows);
+                r = row_begin;
+                const int early = p.window / p.pieces;
+                issue(early < 1 ? 1 : (early > p.stages ? p.stages : early));
+            } else {
                 // the first window of copies goes out before the CTA has even synchronised (no waiting here:
                 // the consumers meet this thread at the barrier below)
                 split_rows(p.rows);
@@ -804,12 +820,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
         }
         __syncthreads();  // barriers initialised; the consumers have staged the table and their activations
         if (tid == kConsumers) {
-            if (!direct) {
-                segs = table;
-                if (p.plan) { n_segments = min(plan_counts[0], p.n_segments); subs = min(plan_counts[1], p.subs); }
-                split_rows(p.plan ? min((int64_t)plan_counts[2], p.rows) : p.rows);
-                r = row_begin;
-            }
+            if (!direct) segs = table;  // the same entries, now in shared memory
             issue(0x7fffffff);
             if (p.warp_rows && !failed) {
                 // the warp scheme's consumers read what each slot holds from stage_info: a stage of no rows ends their loop
@@ -833,7 +844,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
         // copied before the wait (it does not depend on the kernel before), one in device memory after.
         auto stage_table = [&]() {
             if (p.plan && tid == 0) { plan_counts[0] = p.plan->n_segments; plan_counts[1] = p.plan->subs; plan_counts[2] = p.plan->total_rows; }
-            const int n_copy = p.plan ? p.plan->n_segments : p.n_segments;
+            const int n_copy = p.n_segments;  // a planned launch copies its maximum: no trip to memory for the count first
             const uint32_t* src = (const uint32_t*)(p.plan ? p.plan->seg : (p.table ? p.table : p.inline_seg));
             uint32_t* dst = (uint32_t*)table;
             const int words = (n_copy < RQ_MAX_SEGMENTS ? n_copy : RQ_MAX_SEGMENTS) * (int)(sizeof(RqSegment) / 4);
@@ -844,6 +855,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
         asm volatile("griddepcontrol.wait;" ::: "memory");
         RQ_STAMP(44);
         if (!direct) stage_table();
+        RQ_STAMP(43);
         // A thread's item is the same (half, sub-row, row slot, unit) in every stage: thread t takes
         // item t of the stage's grid [half][sub-row][row][unit]. Halves are outermost so that a warp
         // works on one half of adjacent units: no divergence, no bank conflicts.
@@ -884,39 +896,47 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_
             }
         } else if (MODE == RQ_ACT_FLOAT) {
             // stage the activations while the first weight stages are in flight
-            // all vectors as one flat range, eight loads in flight per thread: the copy costs a few trips to L2, not one per element
+            // all vectors as one flat range, sixteen loads in flight per thread: the copy costs a few trips to L2, not one per
+            // element. (vector, input) of a flat index advance by subtraction: no division in the loop.
             const int total = p.act_vectors * p.cols;
-            for (int base_i = tid; base_i < total; base_i += 8 * kConsumers) {
-                float got[8];
+            int v0 = tid / p.cols, k0 = tid - v0 * p.cols;
+            const int adv_v = kConsumers / p.cols, adv_k = kConsumers - adv_v * p.cols;  // one step of kConsumers
+            for (int base_i = tid; base_i < total; base_i += 16 * kConsumers) {
+                float got[16];
+                int v = v0, k = k0;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int i = base_i + j * kConsumers;
+                for (int j = 0; j < 16; ++j) {
                     got[j] = 0.0f;
-                    if (i < total) {
-                        const int v = i / p.cols, k = i - v * p.cols;
+                    if (base_i + j * kConsumers < total) {
                         const int vec = tok0 + v;  // plain: token; expert banks: slot vector (one token per launch)
                         const bool live = p.act_vectors > T || vec < p.tokens;
                         if (live) got[j] = __ldg(p.x + (int64_t)vec * p.st + (int64_t)k * p.sk);
                     }
+                    v += adv_v; k += adv_k;
+                    if (k >= p.cols) { k -= p.cols; ++v; }
                 }
+                v = v0; k = k0;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int i = base_i + j * kConsumers;
-                    if (i < total) {
-                        const int v = i / p.cols, k = i - v * p.cols;
-                        ((float*)(act_smem + v * p.act_bytes + (size_t)(k >> 8) * kRecord))[k & 255] = got[j];
-                    }
+                for (int j = 0; j < 16; ++j) {
+                    if (base_i + j * kConsumers < total) ((float*)(act_smem + v * p.act_bytes + (size_t)(k >> 8) * kRecord))[k & 255] = got[j];
+                    v += adv_v; k += adv_k;
+                    if (k >= p.cols) { k -= p.cols; ++v; }
                 }
+                v0 = v; k0 = k;
             }
+            RQ_STAMP(45);
             consumer_sync<kConsumers>();
-            for (int v = 0; v < p.act_vectors; ++v) {
-                uint8_t* base = act_smem + v * p.act_bytes;
-                for (int s = tid; s < (p.cols >> 4); s += kConsumers) {
-                    float* rec = (float*)(base + (size_t)(s >> 4) * kRecord);
+            RQ_STAMP(46);
+            {
+                // the sums of every 16-input slice of every vector, dealt flat over the threads
+                const int per_vec = p.cols >> 4, slices = p.act_vectors * per_vec;
+                for (int i = tid; i < slices; i += kConsumers) {
+                    const int v = i / per_vec, s2 = i - v * per_vec;
+                    float* rec = (float*)(act_smem + v * p.act_bytes + (size_t)(s2 >> 4) * kRecord);
                     float acc = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) acc += rec[16 * (s & 15) + i];
-                    rec[256 + (s & 15)] = acc;
+                    for (int q = 0; q < 16; ++q) acc += rec[16 * (s2 & 15) + q];
+                    rec[256 + (s2 & 15)] = acc;
                 }
             }
             consumer_sync<kConsumers>();

@@ -279,16 +279,28 @@ __global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const floa
         if (tid == 0) s_gate = sigmoid_portable(red[0]);
         __syncthreads();
     }
-    if (tid == 0) {
-        RqPlan* pa = plans + 2 * t;
-        RqPlan* pb = pa + 1;
-        const int slots_max = top + 1;
-        float* ht = h + (size_t)t * slots_max * b.ffn;
-        int n = 0;
-        // routed experts that live here, in ascending index
-        for (int e = b.expert_first; e < b.expert_first + b.expert_count && n < top; ++e) {
-            const float w = routing[e * re + t * rt];
-            if (w == 0.0f) continue;
+    RqPlan* pa = plans + 2 * t;
+    RqPlan* pb = pa + 1;
+    const int slots_max = top + 1;
+    float* ht = h + (size_t)t * slots_max * b.ffn;
+    // Routed experts that live here take slots in ascending expert index. Every thread looks at one expert
+    // per sweep; a selected expert's slot is the number of selected experts before it (ballots and counts).
+    __shared__ int s_warp_count[8];
+    __shared__ int s_base;
+    if (tid == 0) s_base = 0;
+    __syncthreads();
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int e0 = b.expert_first; e0 < b.expert_first + b.expert_count; e0 += 256) {
+        const int e = e0 + tid;
+        const bool in = e < b.expert_first + b.expert_count;
+        const float w = in ? routing[e * re + t * rt] : 0.0f;
+        const bool sel = in && w != 0.0f;
+        const unsigned ballot = __ballot_sync(0xffffffffu, sel);
+        if (lane == 0) s_warp_count[warp] = __popc(ballot);
+        __syncthreads();
+        int n = s_base + __popc(ballot & ((1u << lane) - 1u));
+        for (int w2 = 0; w2 < warp; ++w2) n += s_warp_count[w2];
+        if (sel && n < top) {
             const int le = e - b.expert_first;
             RqSegment& sa = pa->seg[n];
             sa.row_begin = n * b.ffn; sa.rows = b.ffn; sa.y = ht + (size_t)n * b.ffn;
@@ -300,8 +312,13 @@ __global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const floa
             sb.main[n] = b.down + (size_t)le * b.hidden * dn_row_main;
             sb.scale[n] = b.down_sc ? b.down_sc + (size_t)le * b.hidden * dn_row_sc : nullptr;
             sb.act[n] = n; sb.coef[n] = w;
-            ++n;
         }
+        __syncthreads();
+        if (tid == 0) { int total = 0; for (int w2 = 0; w2 < 8; ++w2) total += s_warp_count[w2]; s_base += total; }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        int n = s_base < top ? s_base : top;
         if (b.has_shared && include_shared) {
             RqSegment& sa = pa->seg[n];
             sa.row_begin = n * b.ffn; sa.rows = b.ffn; sa.y = ht + (size_t)n * b.ffn;
@@ -318,7 +335,6 @@ __global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const floa
     }
     // a token nothing here is routed to still owes zeros (the caller sums the ranks' outputs)
     __syncthreads();
-    const RqPlan* pb = plans + 2 * t + 1;
     if (pb->total_rows == 0)
         for (int r = tid; r < b.hidden; r += 256) y[r * yn + (int64_t)t * yt] = 0.0f;
 }
