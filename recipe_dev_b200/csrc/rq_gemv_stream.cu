@@ -652,7 +652,7 @@ __device__ __forceinline__ float rq_silu_portable(float x) { return __fmul_rn(x,
 
 // R = rows a thread takes per stage in the warp scheme (its weight registers): 2 only where the launch uses two
 template <int TYPE, int MODE, int T, int NW, int R>
-__global__ void __launch_bounds__(NW * 32 + 32, NW <= 7 ? 2 : 1) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+__global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1)) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int kConsumers = NW * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[2 * kMaxStages];  // [slot][piece]
@@ -1246,13 +1246,28 @@ int launch_stream(const StreamParams& p, int grid_x, size_t smem, cudaStream_t s
     return RQ_OK;
 }
 
+// How a row of `ipr` items is laid on lanes by the single-token int8 schemes (and hence the order its item sums are
+// added in, whatever kernel runs): `group` adjacent lanes per row inside a warp, the row spread over `chunks` warps.
+// chunks = 1: the row lies in one warp (a power of two of items, or padded up to one); 7 / 5 / 8: rows of 7, 5 or 8
+// times a power of two of items (14336, 2560, 32768 inputs) with as many consumer warps. group = 0: no such layout.
+static void row_layout(int ipr, int* group, int* chunks) {
+    auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
+    *group = 0; *chunks = 1;
+    if (ipr <= 32 && pow2(ipr)) { *group = ipr; return; }
+    if (ipr % 7 == 0 && pow2(ipr / 7) && ipr / 7 >= 8 && ipr / 7 <= 32) { *group = ipr / 7; *chunks = 7; return; }
+    if (ipr % 5 == 0 && pow2(ipr / 5) && ipr / 5 >= 4 && ipr / 5 <= 32) { *group = ipr / 5; *chunks = 5; return; }
+    if (ipr == 256) { *group = 32; *chunks = 8; return; }
+    if (ipr <= 32) { *group = 2; while (*group < ipr) *group <<= 1; }
+}
+
 template <int TYPE, int MODE, int NW>
 int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s) {
     // Two CTAs share an SM (eight consumer warps and about 100 KB each): their barriers and waits
     // interleave, and when a CTA of one launch exits, a CTA of the next launch (programmatic
     // dependent launch) takes its place and prefetches weights while the other is still working.
-    constexpr int kCtasPerSm = 2;
-    constexpr size_t kSmemBudget = 102 * 1024;  // dynamic; with the static tables (about 10 KB) and the 1 KB the system keeps per CTA, two CTAs fit an SM's 228 KB
+    constexpr int kCtasPerSm = NW == 5 ? 3 : 2;  // five consumer warps: three CTAs of six warps per SM
+    // dynamic; with the static tables (about 10 KB) and the 1 KB the system keeps per CTA, two (three) CTAs fit an SM's 228 KB
+    constexpr size_t kSmemBudget = NW == 5 ? 64 * 1024 : 102 * 1024;
     constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
     // NW = consumer warps: seven, so that with the producer warp a CTA is eight warps and two CTAs per SM leave each
     // thread 128 registers; eight (one CTA per SM then) only for rows too long for seven warps' worth of items.
@@ -1291,26 +1306,22 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     p.row_warps = 1;
     p.sum_group = 0; p.sum_chunks = 1;
     const bool warp_shape = MODE == RQ_ACT_INT8 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN;
-    const bool split_shape = ipr % NW == 0 && ipr / NW <= 32 && ipr / NW >= 8 && ((ipr / NW) & (ipr / NW - 1)) == 0;
-    if (warp_shape && ipr <= 32) {
-        p.sum_group = 2;
-        while (p.sum_group < ipr) p.sum_group <<= 1;
-    } else if (warp_shape && split_shape) {
-        p.sum_group = ipr / NW; p.sum_chunks = NW;
-    }
-    if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && ipr <= 32) {
-        int group = 2;
-        while (group < ipr) group <<= 1;
+    int layout_group = 0, layout_chunks = 1;
+    row_layout(ipr, &layout_group, &layout_chunks);
+    const bool split_shape = layout_chunks > 1 && layout_chunks == NW;
+    if (warp_shape && layout_group) { p.sum_group = layout_group; p.sum_chunks = layout_chunks; }
+    if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && layout_group && layout_chunks == 1) {
+        const int group = layout_group;
         p.warp_rows = 32 / group;
         const int pass_rows = NW * p.warp_rows;
         p.rows_per_thread = (int64_t)2 * pass_rows * row_bytes <= 34 * 1024 && rows_per_cta > pass_rows ? 2 : 1;
         stage_rows = pass_rows * p.rows_per_thread;
     } else if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && split_shape) {
         // longer rows whose items split evenly over the warps, a power of two of lanes each (14336 inputs: 7 x 16)
-        const int group = ipr / NW;
+        const int group = layout_group;
         p.warp_rows = 32 / group;
         p.row_warps = NW;
-        p.rows_per_thread = (int64_t)2 * p.warp_rows * row_bytes <= 34 * 1024 && rows_per_cta > p.warp_rows ? 2 : 1;
+        p.rows_per_thread = (int64_t)2 * p.warp_rows * row_bytes <= 34 * 1024 && rows_per_cta > p.warp_rows && 2 * p.warp_rows <= 8 ? 2 : 1;
         stage_rows = p.warp_rows * p.rows_per_thread;
     }
     p.stage_rows = stage_rows;
@@ -1357,7 +1368,15 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
 
 template <int TYPE, int MODE>
 int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s) {
-    if (2 * p.units * p.subs > 7 * 32) return dispatch_stream_nw<TYPE, MODE, 8>(p, sm_count, vectors_per_launch, s);
+    const int ipr = 2 * p.units * p.subs;
+    if (ipr > 7 * 32) return dispatch_stream_nw<TYPE, MODE, 8>(p, sm_count, vectors_per_launch, s);
+    if constexpr (MODE == RQ_ACT_INT8) {
+        // rows of 5 x 2^k items (2560 inputs): single-token launches run five consumer warps, three CTAs per SM
+        int group = 0, chunks = 1;
+        row_layout(ipr, &group, &chunks);
+        if (chunks == 5 && p.tokens == 1 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN)
+            return dispatch_stream_nw<TYPE, MODE, 5>(p, sm_count, vectors_per_launch, s);
+    }
     return dispatch_stream_nw<TYPE, MODE, 7>(p, sm_count, vectors_per_launch, s);
 }
 
