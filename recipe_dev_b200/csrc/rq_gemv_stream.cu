@@ -161,6 +161,12 @@ __device__ __forceinline__ void load16f(const float* src, float* dst) {
     for (int j = 0; j < 4; ++j) *(float4*)(dst + 4 * j) = *(const float4*)(src + 4 * j);
 }
 
+// Two spellings the compiler might otherwise contract differently at different call sites (a row must have
+// the same bits whichever path computes it): a - b * c as one fused operation, and a * b - c * d with the
+// products rounded first.
+__device__ __forceinline__ float minus_scaled(float a, float b, float c) { return fmaf(-b, c, a); }
+__device__ __forceinline__ float diff_of_products(float a, float b, float c, float d) { return __fsub_rn(__fmul_rn(a, b), __fmul_rn(c, d)); }
+
 // Activations of one token in shared memory: one padded record per 256 inputs.
 //   INT8  (336 bytes): codes[256] int8 | d[8] fp32 @256 | sum16[16] int16 @288 | sum32[8] int16 @320
 //          d = the step of each 32-value group, sum16 / sum32 = the sum of the codes of each
@@ -253,7 +259,7 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
                 acc_m = fmaf((float)mn_hi, xs4.z + xs4.w, acc_m);
             }
         }
-        return d * acc_s - dmin * acc_m;
+        return diff_of_products(d, acc_s, dmin, acc_m);
     } else if (TYPE == RQ_Q6_K) {
         // half h = the 128-value chunk h: ql lines 64h.., qh lines 128 + 32h.., scales 8h..8h+7
         const float d = rq_h2f(sc[0]);
@@ -302,9 +308,9 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
                     }
                     float xv[16];
                     load16f(xf + k_lo, xv);
-                    float dl = dot16f(lo[0], lo[1], lo[2], lo[3], xv) - 32.0f * xsum[k_lo >> 4];
+                    float dl = minus_scaled(dot16f(lo[0], lo[1], lo[2], lo[3], xv), 32.0f, xsum[k_lo >> 4]);
                     load16f(xf + k_hi, xv);
-                    float dh = dot16f(hi[0], hi[1], hi[2], hi[3], xv) - 32.0f * xsum[k_hi >> 4];
+                    float dh = minus_scaled(dot16f(hi[0], hi[1], hi[2], hi[3], xv), 32.0f, xsum[k_hi >> 4]);
                     acc = fmaf((float)sc_lo, dl, acc);
                     acc = fmaf((float)sc_hi, dh, acc);
                 }
@@ -335,7 +341,7 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
                 float dot = dot16f(q0.x ^ 0x80808080u, q0.y ^ 0x80808080u, q0.z ^ 0x80808080u, q0.w ^ 0x80808080u, xv);
                 load16f(xf + 32 * b + 16, xv);
                 dot += dot16f(q1.x ^ 0x80808080u, q1.y ^ 0x80808080u, q1.z ^ 0x80808080u, q1.w ^ 0x80808080u, xv);
-                acc = fmaf(d, dot - 128.0f * (xsum[2 * b] + xsum[2 * b + 1]), acc);
+                acc = fmaf(d, minus_scaled(dot, 128.0f, xsum[2 * b] + xsum[2 * b + 1]), acc);
             }
         }
         return acc;
@@ -365,7 +371,7 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
                 float dot = dot16f(qw[0] & 0x0F0F0F0Fu, qw[1] & 0x0F0F0F0Fu, qw[2] & 0x0F0F0F0Fu, qw[3] & 0x0F0F0F0Fu, xv);
                 load16f(xf + 32 * b + 16, xv);
                 dot += dot16f((qw[0] >> 4) & 0x0F0F0F0Fu, (qw[1] >> 4) & 0x0F0F0F0Fu, (qw[2] >> 4) & 0x0F0F0F0Fu, (qw[3] >> 4) & 0x0F0F0F0Fu, xv);
-                acc = fmaf(d, dot - 8.0f * (xsum[2 * b] + xsum[2 * b + 1]), acc);
+                acc = fmaf(d, minus_scaled(dot, 8.0f, xsum[2 * b] + xsum[2 * b + 1]), acc);
             }
         }
         return acc;
@@ -452,7 +458,7 @@ __device__ __forceinline__ float dot_regs(const ItemRegs<RQ_Q4_K>& r, const ActH
         acc_m = fmaf(a.dg[2 * pp], mn[2 * pp], acc_m);
         acc_m = fmaf(a.dg[2 * pp + 1], mn[2 * pp + 1], acc_m);
     }
-    return d * acc_s - dmin * acc_m;
+    return diff_of_products(d, acc_s, dmin, acc_m);
 }
 
 __device__ __forceinline__ float dot_regs(const ItemRegs<RQ_Q6_K>& r, const ActHalf& a, const int) {
@@ -527,6 +533,161 @@ __device__ __forceinline__ float dot_regs(const ItemRegs<RQ_Q4_0>& r, const ActH
         acc = fmaf(a.d8[b] * d, (float)dot, acc);
     }
     return acc;
+}
+
+// ------------------------------------------------------------------------------------------
+// fp32 activations in the warp scheme: the weights of the thread's R rows sit in registers, the
+// item's 128 inputs come from the unit record in shared memory sixteen at a time, and each
+// sixteen serve all R rows. Per row the operations and their order are item_dot's, so a row has
+// the same bits whichever path computes it.
+// ------------------------------------------------------------------------------------------
+template <int R>
+__device__ __forceinline__ void dot_regs_float(const ItemRegs<RQ_Q4_K> (&r)[R], const bool (&have)[R], const uint8_t* __restrict__ ar, const int h, float (&out)[R]) {
+    const float* xf = (const float*)ar + 128 * h;
+    const float* xsum = (const float*)ar + 256 + 8 * h;
+    float acc_s[R], acc_m[R];
+    uint32_t scw[R], mnw[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+        const uint4 hdr = r[k].hdr;
+        scw[k] = h == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u));
+        mnw[k] = h == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u));
+        acc_s[k] = 0.f; acc_m[k] = 0.f;
+    }
+#pragma unroll
+    for (int pp = 0; pp < 2; ++pp) {
+        float dl[R], dh[R], xl[16];
+        const float* xs = xf + 64 * pp;
+        load16f(xs, xl);
+#pragma unroll
+        for (int k = 0; k < R; ++k) { const uint4 q = r[k].q[2 * pp]; dl[k] = dot16f(q.x & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu, q.z & 0x0F0F0F0Fu, q.w & 0x0F0F0F0Fu, xl); }
+        load16f(xs + 16, xl);
+#pragma unroll
+        for (int k = 0; k < R; ++k) { const uint4 q = r[k].q[2 * pp + 1]; dl[k] += dot16f(q.x & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu, q.z & 0x0F0F0F0Fu, q.w & 0x0F0F0F0Fu, xl); }
+        load16f(xs + 32, xl);
+#pragma unroll
+        for (int k = 0; k < R; ++k) { const uint4 q = r[k].q[2 * pp]; dh[k] = dot16f((q.x >> 4) & 0x0F0F0F0Fu, (q.y >> 4) & 0x0F0F0F0Fu, (q.z >> 4) & 0x0F0F0F0Fu, (q.w >> 4) & 0x0F0F0F0Fu, xl); }
+        load16f(xs + 48, xl);
+#pragma unroll
+        for (int k = 0; k < R; ++k) { const uint4 q = r[k].q[2 * pp + 1]; dh[k] += dot16f((q.x >> 4) & 0x0F0F0F0Fu, (q.y >> 4) & 0x0F0F0F0Fu, (q.z >> 4) & 0x0F0F0F0Fu, (q.w >> 4) & 0x0F0F0F0Fu, xl); }
+        const float4 xs4 = *(const float4*)(xsum + 4 * pp);
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            const int sc_lo = (scw[k] >> (16 * pp)) & 0xff, sc_hi = (scw[k] >> (16 * pp + 8)) & 0xff;
+            const int mn_lo = (mnw[k] >> (16 * pp)) & 0xff, mn_hi = (mnw[k] >> (16 * pp + 8)) & 0xff;
+            acc_s[k] = fmaf((float)sc_lo, dl[k], acc_s[k]);
+            acc_s[k] = fmaf((float)sc_hi, dh[k], acc_s[k]);
+            acc_m[k] = fmaf((float)mn_lo, xs4.x + xs4.y, acc_m[k]);
+            acc_m[k] = fmaf((float)mn_hi, xs4.z + xs4.w, acc_m[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+        const float d = rq_h2f((uint16_t)(r[k].hdr.x & 0xffff)), dmin = rq_h2f((uint16_t)(r[k].hdr.x >> 16));
+        out[k] = have[k] ? diff_of_products(d, acc_s[k], dmin, acc_m[k]) : 0.f;
+    }
+}
+
+template <int R>
+__device__ __forceinline__ void dot_regs_float(const ItemRegs<RQ_Q6_K> (&r)[R], const bool (&have)[R], const uint8_t* __restrict__ ar, const int h, float (&out)[R]) {
+    const float* xf = (const float*)ar + 128 * h;
+    const float* xsum = (const float*)ar + 256 + 8 * h;
+    float acc[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) acc[k] = 0.f;
+#pragma unroll
+    for (int wh = 0; wh < 2; ++wh) {
+#pragma unroll
+        for (int gl = 0; gl < 2; ++gl) {
+            const int s_lo = 2 * gl + wh, s_hi = s_lo + 4;
+            const int k_lo = 32 * gl + 16 * wh, k_hi = k_lo + 64;  // within the chunk
+            float xv[16], dl[R], dh[R];
+            load16f(xf + k_lo, xv);
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const uint4 ql4 = r[k].ql[2 * gl + wh], qh4 = r[k].qh[wh];
+                const uint32_t ql[4] = {ql4.x, ql4.y, ql4.z, ql4.w}, qh[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
+                uint32_t lo[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) lo[j] = (ql[j] & 0x0F0F0F0Fu) | (((qh[j] >> (2 * gl)) & 0x03030303u) << 4);
+                dl[k] = minus_scaled(dot16f(lo[0], lo[1], lo[2], lo[3], xv), 32.0f, xsum[k_lo >> 4]);
+            }
+            load16f(xf + k_hi, xv);
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const uint4 ql4 = r[k].ql[2 * gl + wh], qh4 = r[k].qh[wh];
+                const uint32_t ql[4] = {ql4.x, ql4.y, ql4.z, ql4.w}, qh[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
+                uint32_t hi[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) hi[j] = ((ql[j] >> 4) & 0x0F0F0F0Fu) | (((qh[j] >> (2 * gl + 4)) & 0x03030303u) << 4);
+                dh[k] = minus_scaled(dot16f(hi[0], hi[1], hi[2], hi[3], xv), 32.0f, xsum[k_hi >> 4]);
+            }
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const uint32_t scales[2] = {r[k].sc.x, r[k].sc.y};
+                const int sc_lo = (int)(int8_t)(scales[s_lo >> 2] >> (8 * (s_lo & 3)));
+                const int sc_hi = (int)(int8_t)(scales[s_hi >> 2] >> (8 * (s_hi & 3)));
+                acc[k] = fmaf((float)sc_lo, dl[k], acc[k]);
+                acc[k] = fmaf((float)sc_hi, dh[k], acc[k]);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) out[k] = have[k] ? rq_h2f((uint16_t)r[k].d16) * acc[k] : 0.f;
+}
+
+template <int R>
+__device__ __forceinline__ void dot_regs_float(const ItemRegs<RQ_Q8_0> (&r)[R], const bool (&have)[R], const uint8_t* __restrict__ ar, const int h, float (&out)[R]) {
+    const float* xf = (const float*)ar + 128 * h;
+    const float* xsum = (const float*)ar + 256 + 8 * h;
+    float acc[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) acc[k] = 0.f;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        float xv[16], dot[R];
+        load16f(xf + 32 * b, xv);
+#pragma unroll
+        for (int k = 0; k < R; ++k) { const uint4 q0 = r[k].q[2 * b]; dot[k] = dot16f(q0.x ^ 0x80808080u, q0.y ^ 0x80808080u, q0.z ^ 0x80808080u, q0.w ^ 0x80808080u, xv); }
+        load16f(xf + 32 * b + 16, xv);
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            const uint4 q1 = r[k].q[2 * b + 1];
+            dot[k] += dot16f(q1.x ^ 0x80808080u, q1.y ^ 0x80808080u, q1.z ^ 0x80808080u, q1.w ^ 0x80808080u, xv);
+            const uint32_t dw[2] = {r[k].dd.x, r[k].dd.y};
+            const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
+            acc[k] = fmaf(d, minus_scaled(dot[k], 128.0f, xsum[2 * b] + xsum[2 * b + 1]), acc[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) out[k] = have[k] ? acc[k] : 0.f;
+}
+
+template <int R>
+__device__ __forceinline__ void dot_regs_float(const ItemRegs<RQ_Q4_0> (&r)[R], const bool (&have)[R], const uint8_t* __restrict__ ar, const int h, float (&out)[R]) {
+    const float* xf = (const float*)ar + 128 * h;
+    const float* xsum = (const float*)ar + 256 + 8 * h;
+    float acc[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) acc[k] = 0.f;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        float xv[16], dot[R];
+        load16f(xf + 32 * b, xv);
+#pragma unroll
+        for (int k = 0; k < R; ++k) { const uint4 q = r[k].q[b]; dot[k] = dot16f(q.x & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu, q.z & 0x0F0F0F0Fu, q.w & 0x0F0F0F0Fu, xv); }
+        load16f(xf + 32 * b + 16, xv);
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            const uint4 q = r[k].q[b];
+            dot[k] += dot16f((q.x >> 4) & 0x0F0F0F0Fu, (q.y >> 4) & 0x0F0F0F0Fu, (q.z >> 4) & 0x0F0F0F0Fu, (q.w >> 4) & 0x0F0F0F0Fu, xv);
+            const uint32_t dw[2] = {r[k].dd.x, r[k].dd.y};
+            const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
+            acc[k] = fmaf(d, minus_scaled(dot[k], 8.0f, xsum[2 * b] + xsum[2 * b + 1]), acc[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) out[k] = have[k] ? acc[k] : 0.f;
 }
 
 // The int8 activation quantiser inside the matvec's prologue: the CTA's consumer threads turn the
@@ -1027,7 +1188,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             }
         };
         constexpr int kSweep = kConsumers / 8;  // row tasks per sweep of the consumer threads
-        if (MODE == RQ_ACT_INT8 && T == 1 && p.warp_rows) {
+        if (T == 1 && p.warp_rows) {
             // ---- the warp scheme: no partial sums in shared memory, no CTA-wide barrier. A row's items are
             // `group` adjacent lanes; a thread takes up to two rows of a stage (one per pass), holds their
             // weights in registers, releases the stage, and the lanes of a row join their sums by an xor tree.
@@ -1069,8 +1230,12 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 if (lane == 0) mbar_arrive(&empty_bar[slot]);
                 if (++slot == p.stages) { slot = 0; phase ^= 1; }
                 float v[R];
+                if (MODE == RQ_ACT_INT8) {
 #pragma unroll
-                for (int k = 0; k < R; ++k) v[k] = have[k] ? dot_regs(wr[k], areg, my_h) : 0.f;
+                    for (int k = 0; k < R; ++k) v[k] = have[k] ? dot_regs(wr[k], areg, my_h) : 0.f;
+                } else {
+                    dot_regs_float<R>(wr, have, act_smem + (size_t)my_u * kRecord, my_h, v);
+                }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) {
                     if (off < group) {  // uniform over the launch
@@ -1305,18 +1470,20 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     p.warp_rows = 0; p.rows_per_thread = 0;
     p.row_warps = 1;
     p.sum_group = 0; p.sum_chunks = 1;
-    const bool warp_shape = MODE == RQ_ACT_INT8 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN;
+    const bool warp_shape = vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN;
+    // single-token launches that run a warp scheme: int8 with register activations, fp32 with the token's record in shared memory
+    const bool warp_launch = warp_shape && (p.act_regs || (MODE == RQ_ACT_FLOAT && t == 1));
     int layout_group = 0, layout_chunks = 1;
     row_layout(ipr, &layout_group, &layout_chunks);
     const bool split_shape = layout_chunks > 1 && layout_chunks == NW;
     if (warp_shape && layout_group) { p.sum_group = layout_group; p.sum_chunks = layout_chunks; }
-    if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && layout_group && layout_chunks == 1) {
+    if (warp_launch && layout_group && layout_chunks == 1) {
         const int group = layout_group;
         p.warp_rows = 32 / group;
         const int pass_rows = NW * p.warp_rows;
         p.rows_per_thread = (int64_t)2 * pass_rows * row_bytes <= 34 * 1024 && rows_per_cta > pass_rows ? 2 : 1;
         stage_rows = pass_rows * p.rows_per_thread;
-    } else if (p.act_regs && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN && split_shape) {
+    } else if (warp_launch && split_shape) {
         // longer rows whose items split evenly over the warps, a power of two of lanes each (14336 inputs: 7 x 16)
         const int group = layout_group;
         p.warp_rows = 32 / group;
@@ -1360,9 +1527,7 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
         p.total_stages = at;
     }
     if (t == 4) return launch_stream<TYPE, MODE, 4, NW, 1>(p, grid_x, smem, s);
-    if constexpr (MODE == RQ_ACT_INT8) {
-        if (p.rows_per_thread == 2) return launch_stream<TYPE, MODE, 1, NW, 2>(p, grid_x, smem, s);
-    }
+    if (p.rows_per_thread == 2) return launch_stream<TYPE, MODE, 1, NW, 2>(p, grid_x, smem, s);
     return launch_stream<TYPE, MODE, 1, NW, 1>(p, grid_x, smem, s);
 }
 
