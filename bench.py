@@ -462,20 +462,41 @@ def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
     stream = torch.cuda.current_stream()
 
     def timed(fn, reps):
+        """Mean device time of fn, max over ranks. The reps are captured into one CUDA graph (kernels and the NCCL
+        collective alike), so the host's launch rate is not what is measured; if capture is refused the reps run eagerly."""
         for _ in range(3):
             fn()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
+        graph = None
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(reps):
+                    fn()
+            g.replay()  # the first launch uploads the graph
+            torch.cuda.synchronize()
+            graph = g
+        except Exception as exc:  # noqa: BLE001 - any capture failure falls back to eager timing
+            print(f"bench.py: graph capture of a sharded step failed ({type(exc).__name__}: {exc}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for _ in range(reps):
-            fn()
+        if graph is not None:
+            graph.replay()
+        else:
+            for _ in range(reps):
+                fn()
         e1.record(stream)
         torch.cuda.synchronize()
         us = torch.tensor([1e3 * e0.elapsed_time(e1) / reps], device=device, dtype=torch.float64)
         if dist is not None:
             dist.all_reduce(us, op=dist.ReduceOp.MAX)
+        timed.graphed = graph is not None
         return float(us[0])
 
     # ---- LM head: rows [first, first + count) of 262144 x 2560 Q6_K on this rank
@@ -502,7 +523,8 @@ def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
         us = timed(head_step, max(10, steps // 10))
         nbytes = rows * (cols // 256) * 210 + 4 * cols * tokens + 4 * rows * tokens
         out[f"lm_head_q6k_262144x2560_batch{tokens}"] = {"us": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes": nbytes,
-                                                         "rows_per_gpu": count, "collective": "all_gather fp32 logits" if world > 1 else "none"}
+                                                         "rows_per_gpu": count, "collective": "all_gather fp32 logits" if world > 1 else "none",
+                                                         "launch": "cuda graph" if timed.graphed else "eager"}
     for w in copies:
         w.free()
     del copies
@@ -543,7 +565,8 @@ def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
         loads = sharded.routed_bytes_per_rank(ctx.moe_route(scores, top), experts, world, expert_bytes)
         out[f"moe_q4k_256e_top8_batch{tokens}"] = {"us": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes": nbytes, "experts_per_gpu": ec,
                                                   "routed_bytes_per_rank_min_max": [min(loads), max(loads)],
-                                                  "collective": "all_reduce fp32 [hidden, tokens]" if world > 1 else "none"}
+                                                  "collective": "all_reduce fp32 [hidden, tokens]" if world > 1 else "none",
+                                                  "launch": "cuda graph" if timed.graphed else "eager"}
     ctx.check()
     bank.free()
     return out

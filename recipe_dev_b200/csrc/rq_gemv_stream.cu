@@ -44,6 +44,9 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait on an mbar
 struct StreamParams {
     const RqSegment* table;    // device memory, or null: use `inline_seg`
     const RqPlan* plan;        // device memory written by an earlier kernel: table and counts come from it
+    int plan_count;            // > 1: a batch of planned launches in one -- grid row y reads plan[y * plan_stride] and the
+    int plan_stride;           //      activations at x + y * x_plan_stride (one token of an expert bank per grid row)
+    int64_t x_plan_stride;
     RqSegment inline_seg[RQ_INLINE_SEGMENTS];
     int n_segments, subs, epilogue;
     int64_t rows;              // virtual rows of all segments
@@ -842,7 +845,10 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
     RQ_STAMP(0);
     // Programmatic dependent launch: the next kernel in the stream may start its own prologue now.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int tok0 = blockIdx.y * T;
+    const int batch_row = p.plan_count > 1 ? (int)blockIdx.y : 0;
+    const RqPlan* const plan = p.plan ? p.plan + (size_t)batch_row * p.plan_stride : nullptr;
+    const float* const xbase = p.x + (size_t)batch_row * p.x_plan_stride;
+    const int tok0 = p.plan_count > 1 ? 0 : blockIdx.y * T;
     // An inline table came with the launch and the weights are constants of the model: the producer of such a
     // launch streams weights from its first instruction on, whatever the previous kernel is doing. A table or
     // plan in device memory may have been written by the kernel before: it is read after griddepcontrol.wait.
@@ -955,9 +961,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 int64_t rows = p.rows;
                 if (p.plan) {
-                    segs = p.plan->seg;
-                    n_segments = min(p.plan->n_segments, p.n_segments); subs = min(p.plan->subs, p.subs);
-                    rows = min((int64_t)p.plan->total_rows, p.rows);
+                    segs = plan->seg;
+                    n_segments = min(plan->n_segments, p.n_segments); subs = min(plan->subs, p.subs);
+                    rows = min((int64_t)plan->total_rows, p.rows);
                 } else {
                     segs = p.table;
                 }
@@ -1004,9 +1010,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
         // The segment table sits in shared memory for the whole kernel. One that came with the launch is
         // copied before the wait (it does not depend on the kernel before), one in device memory after.
         auto stage_table = [&]() {
-            if (p.plan && tid == 0) { plan_counts[0] = p.plan->n_segments; plan_counts[1] = p.plan->subs; plan_counts[2] = p.plan->total_rows; }
+            if (p.plan && tid == 0) { plan_counts[0] = plan->n_segments; plan_counts[1] = plan->subs; plan_counts[2] = plan->total_rows; }
             const int n_copy = p.n_segments;  // a planned launch copies its maximum: no trip to memory for the count first
-            const uint32_t* src = (const uint32_t*)(p.plan ? p.plan->seg : (p.table ? p.table : p.inline_seg));
+            const uint32_t* src = (const uint32_t*)(p.plan ? plan->seg : (p.table ? p.table : p.inline_seg));
             uint32_t* dst = (uint32_t*)table;
             const int words = (n_copy < RQ_MAX_SEGMENTS ? n_copy : RQ_MAX_SEGMENTS) * (int)(sizeof(RqSegment) / 4);
             for (int i = tid; i < words; i += kConsumers) dst[i] = src[i];
@@ -1071,7 +1077,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                     if (base_i + j * kConsumers < total) {
                         const int vec = tok0 + v;  // plain: token; expert banks: slot vector (one token per launch)
                         const bool live = p.act_vectors > T || vec < p.tokens;
-                        if (live) got[j] = __ldg(p.x + (int64_t)vec * p.st + (int64_t)k * p.sk);
+                        if (live) got[j] = __ldg(xbase + (int64_t)vec * p.st + (int64_t)k * p.sk);
                     }
                     v += adv_v; k += adv_k;
                     if (k >= p.cols) { k -= p.cols; ++v; }
@@ -1398,7 +1404,7 @@ int launch_stream(const StreamParams& p, int grid_x, size_t smem, cudaStream_t s
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid_x, (unsigned)((p.tokens + T - 1) / T));
+    cfg.gridDim = dim3((unsigned)grid_x, (unsigned)(p.plan_count > 1 ? p.plan_count : (p.tokens + T - 1) / T));
     cfg.blockDim = dim3(NW * 32 + 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
@@ -1453,10 +1459,11 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
 #ifdef RQ_PROBE_CTAS
     static const int probe_ctas = getenv("RQ_CTAS_PER_SM") ? atoi(getenv("RQ_CTAS_PER_SM")) : kCtasPerSm;
-    const int ctas = sm_count * probe_ctas;
+    int ctas = sm_count * probe_ctas;
 #else
-    const int ctas = sm_count * kCtasPerSm;
+    int ctas = sm_count * kCtasPerSm;
 #endif
+    if (p.plan_count > 1) { ctas /= p.plan_count; if (ctas < 1) ctas = 1; }  // the batch's grid rows share the GPU
     const int64_t rows_per_cta = (p.rows + ctas - 1) / ctas;
     const int ipr = 2 * p.units * p.subs;  // items per virtual row
     p.units_shift = (p.units & (p.units - 1)) == 0 ? __builtin_ctz(p.units) : -1;
@@ -1603,13 +1610,15 @@ int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table
 }
 
 // A launch whose segment table and counts a kernel wrote into `plan` (device memory): the host
-// sizes the launch for the maxima. FLOAT activations only: vector v is x + v * st.
-int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* plan, int max_segments, int max_subs, int epilogue, int64_t max_rows,
-                          const float* x, int64_t sk, int64_t st, int vectors, int64_t yn, int64_t yt, cudaStream_t s) {
+// sizes the launch for the maxima. FLOAT activations only: vector v is x + v * st. plan_count > 1 runs
+// that many planned launches as the grid rows of one: row y reads plan[y * plan_stride] and x + y * x_plan_stride.
+int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* plan, int plan_count, int plan_stride, int max_segments, int max_subs,
+                          int epilogue, int64_t max_rows, const float* x, int64_t x_plan_stride, int64_t sk, int64_t st, int vectors, int64_t yn, int64_t yt,
+                          cudaStream_t s) {
     if (cols % 256 || max_subs < 1 || max_subs > RQ_MAX_SUB || max_segments < 1 || max_segments > RQ_MAX_SEGMENTS || vectors < 1) return RQ_ERR_UNSUPPORTED;
     StreamParams p;
     memset(&p, 0, sizeof(p));
-    p.plan = plan;
+    p.plan = plan; p.plan_count = plan_count; p.plan_stride = plan_stride; p.x_plan_stride = x_plan_stride;
     p.n_segments = max_segments; p.subs = max_subs; p.epilogue = epilogue;
     p.rows = max_rows; p.cols = (int)cols; p.units = (int)(cols / 256);
     p.x = x; p.sk = sk; p.st = st; p.yn = yn; p.yt = yt; p.tokens = 1;

@@ -113,8 +113,9 @@ struct RqPlan {
     int pad;
     RqSegment seg[RQ_MAX_SEGMENTS];
 };
-int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* plan, int max_segments, int max_subs, int epilogue, int64_t max_rows,
-                          const float* x, int64_t sk, int64_t st, int vectors, int64_t yn, int64_t yt, cudaStream_t s);
+int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* plan, int plan_count, int plan_stride, int max_segments, int max_subs,
+                          int epilogue, int64_t max_rows, const float* x, int64_t x_plan_stride, int64_t sk, int64_t st, int vectors, int64_t yn, int64_t yt,
+                          cudaStream_t s);
 int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table, const RqSegment* inline_seg, int n_segments, int subs,
                      int epilogue, int64_t total_rows, const float* x, int64_t sk, int64_t st, int tokens, int vectors_per_launch,
                      int64_t yn, int64_t yt, int act_mode, const uint8_t* act, int fuse_step, uint8_t* act_out, cudaStream_t s);

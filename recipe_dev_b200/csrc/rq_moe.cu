@@ -486,17 +486,16 @@ extern "C" int rq_moe_forward(rq_ctx* ctx, rq_moe* m, const float* x, int64_t x_
     rq_moe_plan_kernel<<<tokens, 256, 0, s>>>(view_of(m), routing, routing_e_stride, routing_t_stride, x, x_k_stride, x_t_stride, top_k, include_shared,
                                               m->plans, m->h, y, y_n_stride, y_t_stride);
     RQ_CUDA(cudaGetLastError());
-    for (int t = 0; t < tokens; ++t) {
-        // expert gate and up rows against the token's x, h = silu(g) * u per slot
-        int rc = rq_launch_stream_plan(ctx, m->type, m->hidden, m->plans + 2 * t, slots, 2, RQ_EPI_GLU, (int64_t)slots * m->ffn, x + t * x_t_stride,
-                                       x_k_stride, 0, 1, 1, 0, s);
-        if (rc == RQ_ERR_UNSUPPORTED) return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: hidden=%d is beyond what the streaming kernel holds", m->hidden);
-        if (rc) return rc;
-        // expert down rows, one sub-row per slot against that slot's h, summed with the routing weights
-        rc = rq_launch_stream_plan(ctx, m->type, m->ffn, m->plans + 2 * t + 1, 1, slots, RQ_EPI_WSUM, m->hidden, m->h + (size_t)t * slots * m->ffn, 1, m->ffn,
-                                   slots, y_n_stride, 0, s);
-        if (rc == RQ_ERR_UNSUPPORTED) return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: ffn=%d with %d slots is beyond what the streaming kernel holds", m->ffn, slots);
-        if (rc) return rc;
-    }
+    // All tokens in two launches: grid row t of each reads token t's plan and activations.
+    // expert gate and up rows against the token's x, h = silu(g) * u per slot
+    int rc = rq_launch_stream_plan(ctx, m->type, m->hidden, m->plans, tokens, 2, slots, 2, RQ_EPI_GLU, (int64_t)slots * m->ffn, x, x_t_stride, x_k_stride, 0,
+                                   1, 1, 0, s);
+    if (rc == RQ_ERR_UNSUPPORTED) return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: hidden=%d is beyond what the streaming kernel holds", m->hidden);
+    if (rc) return rc;
+    // expert down rows, one sub-row per slot against that slot's h, summed with the routing weights
+    rc = rq_launch_stream_plan(ctx, m->type, m->ffn, m->plans + 1, tokens, 2, 1, slots, RQ_EPI_WSUM, m->hidden, m->h, (int64_t)slots * m->ffn, 1, m->ffn, slots,
+                               y_n_stride, 0, s);
+    if (rc == RQ_ERR_UNSUPPORTED) return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: ffn=%d with %d slots is beyond what the streaming kernel holds", m->ffn, slots);
+    if (rc) return rc;
     return RQ_OK;
 }
