@@ -285,3 +285,50 @@ def test_matvec_multi_host_equals_single_host_calls(rq_ctx, oracle):
                 one = rq_ctx.matvec_host(w, xs, act_mode=mode, step=32)
                 assert np.array_equal(np.ascontiguousarray(y).view(np.uint32), one.view(np.uint32))
     rq_ctx.check()
+
+
+EDGE_SHAPES = [
+    # (type, rows, cols): every row layout of the streaming kernel, with row counts around the stage sizes
+    (ol.Q4_K, 1, 256), (ol.Q4_K, 3, 512), (ol.Q4_K, 29, 1024), (ol.Q6_K, 57, 2048), (ol.Q4_K, 15, 4096), (ol.Q4_K, 113, 4096),
+    (ol.Q6_K, 5, 14336), (ol.Q4_K, 2, 7168), (ol.Q6_K, 41, 5120), (ol.Q4_K, 9, 1280), (ol.Q6_K, 8, 2560), (ol.Q4_K, 3, 32768),
+    (ol.Q4_K, 6, 8192), (ol.Q8_0, 23, 4096), (ol.Q4_0, 31, 2560), (ol.Q8_0, 2, 14336), (ol.Q4_K, 300, 768), (ol.Q6_K, 1, 3072),
+]
+
+
+@pytest.mark.parametrize("t,rows,cols", EDGE_SHAPES)
+def test_matvec_every_row_layout_and_ragged_row_counts(rq_ctx, oracle, t, rows, cols):
+    """Widths that take the in-warp layout (powers of two, padded), the split layouts (7, 5 and 8 warps) and the
+    shared-memory partial sums, with row counts that leave stages and CTAs partly empty; both activation modes,
+    one token and a window of three."""
+    blocks = oracle.quantize(t, oracle.normal(41, t + cols, rows * cols, 0.02))
+    x = oracle.normal(41, 3 + t, 3 * cols, 1.0).reshape(3, cols)
+    w = rq_ctx.weight_from_host(t, blocks, rows, cols)
+    for mode, omode in ((1, ol.INT8), (0, ol.FLOAT_RUN)):
+        ref = oracle.matvec(t, blocks, rows, cols, x, omode, 32)
+        y = rq_ctx.matvec(w, torch_cuda(x), act_mode=mode, step=32).cpu().numpy()
+        assert rel_err(y, ref) <= TOL, (mode, "window")
+        for p in range(3):
+            one = rq_ctx.matvec(w, torch_cuda(x[p]), act_mode=mode, step=32).cpu().numpy()
+            assert rel_err(one, ref[p]) <= TOL, (mode, p)
+            assert np.array_equal(one.view(np.uint32), y[p].view(np.uint32)), (mode, p)
+    rq_ctx.check()
+
+
+def test_matvec_multi_ragged_segments(rq_ctx, oracle):
+    """Four matrices of unequal, awkward row counts in one launch: stages never straddle a matrix."""
+    t, cols = ol.Q4_K, 4096
+    rows = [1, 33, 14, 200]
+    bl = [oracle.quantize(t, oracle.normal(42, i, r * cols, 0.02)) for i, r in enumerate(rows)]
+    ws = [rq_ctx.weight_from_host(t, b, r, cols) for b, r in zip(bl, rows)]
+    x = oracle.normal(42, 9, cols, 1.0)
+    import torch
+
+    for mode in (1, 0):
+        plane = torch.zeros(sum(rows), dtype=torch.float32, device="cuda")
+        offs = np.cumsum([0] + rows)
+        ys = [plane[int(offs[i]):int(offs[i + 1])] for i in range(4)]
+        rq_ctx.matvec_multi(ws, torch_cuda(x), ys, act_mode=mode, step=32)
+        for w, y in zip(ws, ys):
+            one = rq_ctx.matvec(w, torch_cuda(x), act_mode=mode, step=32)
+            assert torch.equal(one, y)
+    rq_ctx.check()
