@@ -3,46 +3,38 @@
 // Y[t][n] = sum_k W[n][k] * X[t][k], W stored as GGUF blocks, fp32 activations kept as they are
 // (the FLOAT handling of a stored sum).
 //
-// A stored weight is an integer CODE times a factor that is constant over a block of 32 (Q6_K: 16)
-// inputs, less (Q4_K) a per-block minimum. The tensor core multiplies the CODES -- small integers,
-// exact in fp16, unpacked from the blocks with a byte permute and one exact subtraction each -- with
-// X split into fp16 pairs hi + lo (hi = fp16(x), lo = fp16(x - hi): 22 mantissa bits), and the
-// per-block factors are applied when the block's sum leaves tensor memory:
+// Operands reach the tensor core as fp16 PAIRS hi + lo with hi = fp16(v), lo = fp16(v - hi):
+// together 22 mantissa bits, so nothing of the fp32 inputs that matters at the 1e-3 bar is lost.
+// Three products are issued per 16-wide slice, A_hi B_hi + A_hi B_lo + A_lo B_hi (the dropped
+// A_lo B_lo term is 2^-22 relative).
 //
-//   * rq_split_x_kernel splits X once into hi / lo tiles laid out as the 128-byte-swizzled K-major image
-//     the tensor core reads, plus the sums of x over every 32 inputs (the Q4_K minimum term), so the
-//     main kernel fetches a token tile of a 64-wide slice with one bulk copy;
-//   * a CTA owns 128 weight rows x BN tokens (BN = 32, 64, 128). Eight staging warps unpack 128 x 64
-//     slices of W into one swizzled tile of codes and a small table of factors (the next slice's bytes
-//     are fetched while this one is unpacked);
-//   * one thread issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16), two per 16 inputs (codes x hi,
-//     codes x lo), into a FRESH accumulator for every block of 32 (16) inputs, four accumulators in
-//     rotation, committing each to an mbarrier;
-//   * eight drain warps read each finished block sum with tcgen05.ld and fold it into fp32 registers:
-//     acc = fma(factor, sum, acc), and for Q4_K acc = fma(-minimum, sum of x, acc). Long sums are
-//     therefore added with round-to-nearest adds in registers; the tensor core's own fp32 accumulation
-//     truncates (measured: a sum kept in tensor memory over K = 4096 is 1.2e-5 low), which is harmless
-//     over the two or four instructions of one block.
-// Shapes with few 128-row tiles and a long K split K over CTAs; a second kernel adds their sums in
-// split order.
+//   * a small kernel splits X once into hi and lo tiles, already in the 128-byte-swizzled K-major
+//     image the tensor core reads, so the main kernel fetches a tile with one bulk copy;
+//   * a CTA owns 128 weight rows x BN tokens (BN = 32, 64 or 128). Eight staging warps dequantise
+//     128 x 64 slices of W (bit-exact values, as rq_dequant gives them; the next slice's bytes are
+//     fetched while this one is converted) into swizzled hi / lo tiles in shared memory;
+//   * one thread issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16). The tensor core adds
+//     into its fp32 accumulator by TRUNCATION, a bias that grows with the length of the chain
+//     (measured: 1.2e-5 relative at K = 4096). So the large term A_hi B_hi is accumulated in
+//     tensor memory only over one 64-wide slice (four instructions), into one of two
+//     accumulators in turn, and eight drain warps add each finished slice into fp32 registers
+//     with round-to-nearest adds while the tensor core works on the next. The two cross terms,
+//     2^-11 of the result, stay in a third accumulator for the whole K.
+// Three stages of 64 KB keep dequantisation ahead of the tensor core.
 //
 // Every wait is bounded in time; a wait that runs out records a code in the context's error word,
 // the thread stops waiting and the CTA still frees its tensor memory before it exits.
 #include "rq_internal.cuh"
 
-#include <cuda_fp16.h>
-
 namespace {
 
-constexpr int BM = 128, BK = 64, kStages = 4, kAccs = 4;
+constexpr int BM = 128, BK = 64, kStages = 3;
 constexpr int kStageWarps = 8, kDrainWarps = 8;
 constexpr int kStagers = kStageWarps * 32;
 constexpr int kMmaWarp = kStageWarps + kDrainWarps, kCopyWarp = kMmaWarp + 1;
 constexpr int kThreadsMM = (kCopyWarp + 1) * 32;
-constexpr int kTileBytes = BM * BK * 2;               // the fp16 code tile of 128 rows: 16 KB
-constexpr int kFactorOffset = kTileBytes + 128 * 264;  // after the X image of at most 128 tokens (hi | lo | sums)
-constexpr int kStageBytes = 52 * 1024;                 // codes | X image | factors [128 rows][2] float2
-static_assert(kFactorOffset + 128 * 2 * 8 <= kStageBytes, "a stage holds its tiles and tables");
+constexpr int kTileBytes = BM * BK * 2;            // one fp16 tile of 128 rows: 16 KB
+constexpr int kStageBytes = 4 * kTileBytes;        // A_hi | A_lo | B_hi | B_lo (B tiles of BN rows, at most 128)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct MatmulParams {
@@ -83,7 +75,7 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
-    while (!mbar_try_wait_parked(bar, parity, 100u))
+    while (!mbar_try_wait_parked(bar, parity, 2000u))  // parked waits do not eat the staging warps' issue slots
         if (global_ns() - t0 > kWaitLimitNs) return false;
     return true;
 }
@@ -126,26 +118,33 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Weights are scaled by 2^8 before the split and the accumulator by 2^-8 after: a weight of 0.02
+// leaves a residual near 1e-5, which fp16 could only hold as a subnormal with a few bits; scaled, the
+// residual keeps its eleven. (Weights of magnitude 255 and more would overflow fp16; GGUF model
+// weights are orders of magnitude below that.)
+constexpr float kWeightScale = 256.0f, kWeightUnscale = 1.0f / 256.0f;
+
+// Eight fp32 values (times `scale`) as one 16-byte chunk of fp16 hi and one of fp16 lo.
+__device__ __forceinline__ void split8(const float* v, float scale, uint4& hi, uint4& lo) {
+    uint32_t hw[4], lw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float a = v[2 * j] * scale, b = v[2 * j + 1] * scale;
+        const __half2 h2 = __floats2half2_rn(a, b);
+        const float2 back = __half22float2(h2);
+        const __half2 l2 = __floats2half2_rn(a - back.x, b - back.y);
+        hw[j] = *(const uint32_t*)&h2;
+        lw[j] = *(const uint32_t*)&l2;
+    }
+    hi = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+    lo = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+}
 // Swizzle<3,4,3>: the 16-byte chunk index of a 128-byte row, xor the row within its group of eight
 __device__ __forceinline__ int swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
-// Four unsigned bytes (each below 1024) as two half2 words holding byte - bias: 0x64bb is the fp16 number
-// 1024 + bb, exactly, so a byte becomes a half by a byte permute and one exact subtraction.
-__device__ __forceinline__ void bytes_to_half4(uint32_t bytes, uint32_t bias_h2, uint32_t& lo_pair, uint32_t& hi_pair) {
-    const uint32_t a = __byte_perm(bytes, 0x64646464u, 0x4140), b = __byte_perm(bytes, 0x64646464u, 0x4342);
-    const __half2 ra = __hsub2(*(const __half2*)&a, *(const __half2*)&bias_h2), rb = __hsub2(*(const __half2*)&b, *(const __half2*)&bias_h2);
-    lo_pair = *(const uint32_t*)&ra; hi_pair = *(const uint32_t*)&rb;
-}
-
 // ------------------------------------------------------------------------------------------
 // The raw bytes behind 32 consecutive values of one row (`half` 0 or 1 of a 64-wide slice at k0),
-// fetched one slice ahead. unpack() turns them into the 32 integer CODES of the values as fp16
-// (exact: codes are small integers) and the fp32 factors that make values of codes:
-//   Q4_K   value = f[0] * code - f[1]          (f[0] = d * sc, f[1] = dmin * m, one pair per 32 values)
-//   Q6_K   value = f[i] * code, i = 0, 1       (f[i] = d * scale of each 16 values; code = q - 32)
-//   Q8_0   value = f[0] * code                 (code = the int8)
-//   Q4_0   value = f[0] * code                 (code = nibble - 8)
-// The products d * sc etc. are exact in fp32, as in rq_dequant.
+// fetched one slice ahead, and their dequantisation: the same bits rq_dequant gives.
 // ------------------------------------------------------------------------------------------
 template <int TYPE> struct RawHalf;
 template <> struct RawHalf<RQ_Q4_K> {
@@ -157,16 +156,24 @@ template <> struct RawHalf<RQ_Q4_K> {
         q0 = __ldg((const uint4*)(blk + 16 + 32 * pr));
         q1 = __ldg((const uint4*)(blk + 32 + 32 * pr));
     }
-    __device__ __forceinline__ void unpack(int k0, int half, uint32_t* h2, float* f) const {
+    __device__ __forceinline__ void decode(int k0, int half, float* v) const {
         const int pr = (k0 & 255) >> 6;
         int sc, mn;
         rq_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pr + half, sc, mn);
-        f[0] = __fmul_rn(rq_h2f((uint16_t)(hdr.x & 0xffff)), (float)sc);
-        f[1] = __fmul_rn(rq_h2f((uint16_t)(hdr.x >> 16)), (float)mn);
+        const float d = rq_h2f((uint16_t)(hdr.x & 0xffff)), dmin = rq_h2f((uint16_t)(hdr.x >> 16));
+        const float step = __fmul_rn(d, (float)sc), base = __fmul_rn(dmin, (float)mn);
         const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         const int shift = 4 * half;  // sub-block 2 pr in the low nibbles, 2 pr + 1 in the high
 #pragma unroll
-        for (int j = 0; j < 8; ++j) bytes_to_half4((w[j] >> shift) & 0x0F0F0F0Fu, 0x64006400u, h2[2 * j], h2[2 * j + 1]);
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t nib = (w[j] >> shift) & 0x0F0F0F0Fu;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // 0x4B0000nn is 2^23 + nn: the nibble as a float without the conversion unit
+                const float q = __uint_as_float(__byte_perm(nib, 0x4B000000u, 0x7650 + i)) - 8388608.0f;
+                v[4 * j + i] = __fsub_rn(__fmul_rn(step, q), base);
+            }
+        }
     }
 };
 template <> struct RawHalf<RQ_Q6_K> {
@@ -184,19 +191,21 @@ template <> struct RawHalf<RQ_Q6_K> {
         scales = __ldg((const uint16_t*)(body + 192 + 8 * ch + 2 * g));
         d16 = __ldg(p.scale + row * nb + (k0 >> 8));
     }
-    __device__ __forceinline__ void unpack(int k0, int half, uint32_t* h2, float* f) const {
+    __device__ __forceinline__ void decode(int k0, int half, float* v) const {
         const int j64 = (k0 & 255) >> 6, sel = j64 & 1, g = 2 * sel + half;  // group g of its chunk: ql line 32 * half, nibble sel
         const float d = rq_h2f((uint16_t)d16);
-        f[0] = __fmul_rn(d, (float)(int)(int8_t)(scales & 0xff));
-        f[1] = __fmul_rn(d, (float)(int)(int8_t)(scales >> 8));
 #pragma unroll
         for (int q4 = 0; q4 < 2; ++q4) {  // sixteen values at a time
             const uint32_t lw[4] = {ql[q4].x, ql[q4].y, ql[q4].z, ql[q4].w}, hw[4] = {qh[q4].x, qh[q4].y, qh[q4].z, qh[q4].w};
+            const int scale = (int)(int8_t)(scales >> (8 * q4));
+            const float scaled = __fmul_rn(d, (float)scale);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t code = ((lw[j] >> (4 * sel)) & 0x0F0F0F0Fu) | (((hw[j] >> (2 * g)) & 0x03030303u) << 4);
-                bytes_to_half4(code, 0x64206420u, h2[8 * q4 + 2 * j], h2[8 * q4 + 2 * j + 1]);  // code - 32
-            }
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int lo = (lw[j] >> (8 * i + 4 * sel)) & 15, hi = (hw[j] >> (8 * i + 2 * g)) & 3;
+                    v[16 * q4 + 4 * j + i] = __fmul_rn(scaled, (float)((lo | (hi << 4)) - 32));
+                }
         }
     }
 };
@@ -209,12 +218,13 @@ template <> struct RawHalf<RQ_Q8_0> {
         c = __ldg((const uint4*)(p.main + at + 16));
         d16 = __ldg(p.scale + row * (p.cols >> 5) + (k0 >> 5) + half);
     }
-    __device__ __forceinline__ void unpack(int, int, uint32_t* h2, float* f) const {
-        f[0] = rq_h2f((uint16_t)d16);
-        f[1] = 0.f;
+    __device__ __forceinline__ void decode(int, int, float* v) const {
+        const float d = rq_h2f((uint16_t)d16);
         const uint32_t w[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) bytes_to_half4(w[j] ^ 0x80808080u, 0x64806480u, h2[2 * j], h2[2 * j + 1]);  // (int8 + 128) - 128
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[4 * j + i] = __fmul_rn((float)(int8_t)(w[j] >> (8 * i)), d);
     }
 };
 template <> struct RawHalf<RQ_Q4_0> {
@@ -224,38 +234,33 @@ template <> struct RawHalf<RQ_Q4_0> {
         a = __ldg((const uint4*)(p.main + row * (p.cols >> 1) + ((k0 >> 5) + half) * 16));
         d16 = __ldg(p.scale + row * (p.cols >> 5) + (k0 >> 5) + half);
     }
-    __device__ __forceinline__ void unpack(int, int, uint32_t* h2, float* f) const {
-        f[0] = rq_h2f((uint16_t)d16);
-        f[1] = 0.f;
+    __device__ __forceinline__ void decode(int, int, float* v) const {
+        const float d = rq_h2f((uint16_t)d16);
         const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            bytes_to_half4(w[j] & 0x0F0F0F0Fu, 0x64086408u, h2[2 * j], h2[2 * j + 1]);                  // values 4j .. 4j+3: low nibbles - 8
-            bytes_to_half4((w[j] >> 4) & 0x0F0F0F0Fu, 0x64086408u, h2[8 + 2 * j], h2[8 + 2 * j + 1]);   // values 16+4j ..: high nibbles - 8
-        }
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t byte = (w[j] >> (8 * i)) & 0xff;
+                v[4 * j + i] = __fmul_rn((float)((int)(byte & 15) - 8), d);
+                v[16 + 4 * j + i] = __fmul_rn((float)((int)(byte >> 4) - 8), d);
+            }
     }
 };
-// values per scale factor: a drain of the accumulator per this many inputs
-template <int TYPE> struct BlockOf { static constexpr int value = TYPE == RQ_Q6_K ? 16 : 32; };
 
 // ------------------------------------------------------------------------------------------
-// X -> fp16 hi / lo tiles in the tensor core's swizzled image, plus the sums of x over each 32 inputs
-// (the Q4_K minimum term). grid (k slices, token tiles), one thread per token row of the tile; rows
-// past the last token are zero. Image of one (tile, slice): hi [bn x 128 B] | lo [bn x 128 B] | sums [2][bn] fp32.
+// X -> fp16 hi / lo tiles in the tensor core's swizzled image. grid (k slices, token tiles),
+// one thread per token row of the tile; rows past the last token are zero.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ size_t x_image_bytes(int bn) { return (size_t)bn * 256 + (size_t)bn * 8; }
-
 __global__ void __launch_bounds__(128) rq_split_x_kernel(const float* __restrict__ x, int64_t sk, int64_t st, int tokens, int bn, uint8_t* __restrict__ xs) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int ks = blockIdx.x, nt = blockIdx.y, r = threadIdx.x;
     if (r >= bn) return;
     const int token = nt * bn + r;
-    uint8_t* hi = xs + ((size_t)nt * gridDim.x + ks) * x_image_bytes(bn);
+    uint8_t* hi = xs + ((size_t)nt * gridDim.x + ks) * 2 * (size_t)bn * 128;
     uint8_t* lo = hi + (size_t)bn * 128;
-    float* sums = (float*)(hi + (size_t)bn * 256);
     const bool vec = sk == 1 && (st & 3) == 0 && ((uintptr_t)x & 15) == 0;
-    float s32[2] = {0.f, 0.f};
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         float v[8];
@@ -272,22 +277,11 @@ __global__ void __launch_bounds__(128) rq_split_x_kernel(const float* __restrict
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.f;
         }
-        uint32_t hw[4], lw[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const __half2 h2 = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-            const float2 back = __half22float2(h2);
-            const __half2 l2 = __floats2half2_rn(v[2 * j] - back.x, v[2 * j + 1] - back.y);
-            hw[j] = *(const uint32_t*)&h2;
-            lw[j] = *(const uint32_t*)&l2;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) s32[c >> 2] += v[j];
-        *(uint4*)(hi + swizzled(r, c)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-        *(uint4*)(lo + swizzled(r, c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        uint4 h, l;
+        split8(v, 1.0f, h, l);
+        *(uint4*)(hi + swizzled(r, c)) = h;
+        *(uint4*)(lo + swizzled(r, c)) = l;
     }
-    sums[r] = s32[0];
-    sums[bn + r] = s32[1];
 }
 
 // y[row][token] = the splits' sums added in split order (the same bits on every run)
@@ -305,11 +299,9 @@ __global__ void __launch_bounds__(256) rq_sum_splits_kernel(const float* __restr
 
 template <int TYPE>
 __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_constant__ MatmulParams p) {
-    constexpr int BLK = BlockOf<TYPE>::value;  // inputs per scale factor
-    constexpr int NBLK = BK / BLK;             // accumulator drains per 64-wide slice
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzled tiles want 1024-byte alignment
-    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full[kAccs], acc_empty[kAccs];
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full[2], acc_empty[2], done_bar;
     __shared__ uint32_t tmem_base_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t m0 = (int64_t)blockIdx.x * BM;
@@ -318,12 +310,13 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
     const int k_steps = min(p.ks_per_split, p.cols / BK - k_first);
     const int k_total = p.cols / BK;
     const int bn = p.bn;
-    // tensor memory: kAccs accumulators of bn fp32 columns, allocated as a power of two
+    // tensor memory: two accumulators for the hi x hi term, one for the cross terms: 3 bn columns, allocated as a power of two
     const uint32_t tmem_cols = bn == 128 ? 512u : (bn == 64 ? 256u : 128u);
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], kStagers + 1); mbar_init(&empty_bar[s], 1 + kDrainWarps); }
-        for (int b = 0; b < kAccs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kDrainWarps); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], kStagers + 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kDrainWarps); }
+        mbar_init(&done_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kMmaWarp) {
@@ -337,37 +330,32 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
     const uint32_t tmem_base = tmem_base_slot;
 
     if (warp < kStageWarps) {
-        // ------------------------------------------------------------ staging warps: W -> code tile + factors
+        // ------------------------------------------------------------ staging warps: W -> hi / lo tiles
         const int r = tid & 127, half = tid >> 7;  // a row of the tile, and which 32 of the slice's 64 values
         const int64_t row = m0 + r < p.rows ? m0 + r : p.rows - 1;  // rows past the end are computed and dropped
         bool dead = false;
-        // the raw bytes of the next kPrefetch slices are in flight (in registers) while one is unpacked: a load from
-        // HBM under load takes about a microsecond, several slices' worth of unpacking
-        constexpr int kPrefetch = 4;
-        RawHalf<TYPE> ring[kPrefetch];
+        RawHalf<TYPE> cur, nxt;
+        cur.load(p, row, k_first * BK, half);
+        for (int ks = 0; ks < k_steps; ++ks) {
+            const int slot = ks % kStages;
+            if (ks + 1 < k_steps) nxt.load(p, row, (k_first + ks + 1) * BK, half);
+            float v[32];
+            cur.decode((k_first + ks) * BK, half, v);
+            if (ks >= kStages && !dead && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 11); dead = true; }
+            uint8_t* a_hi = smem + (size_t)slot * kStageBytes;
+            uint8_t* a_lo = a_hi + kTileBytes;
 #pragma unroll
-        for (int u = 0; u < kPrefetch; ++u)
-            if (u < k_steps) ring[u].load(p, row, (k_first + u) * BK, half);
-        for (int ks0 = 0; ks0 < k_steps; ks0 += kPrefetch) {
-#pragma unroll
-            for (int u = 0; u < kPrefetch; ++u) {
-                const int ks = ks0 + u;
-                if (ks < k_steps) {
-                    const int slot = ks % kStages;
-                    uint32_t h2[16];
-                    float f[2];
-                    ring[u].unpack((k_first + ks) * BK, half, h2, f);
-                    if (ks + kPrefetch < k_steps) ring[u].load(p, row, (k_first + ks + kPrefetch) * BK, half);
-                    if (ks >= kStages && !dead && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 11); dead = true; }
-                    uint8_t* a_tile = smem + (size_t)slot * kStageBytes;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) *(uint4*)(a_tile + swizzled(r, 4 * half + c)) = make_uint4(h2[4 * c], h2[4 * c + 1], h2[4 * c + 2], h2[4 * c + 3]);
-                    ((float2*)(a_tile + kFactorOffset))[2 * r + half] = make_float2(f[0], f[1]);  // [row][half]
-                    // the tensor core reads shared memory through the async proxy
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_arrive(&full_bar[slot]);
-                }
+            for (int c = 0; c < 4; ++c) {
+                uint4 h, l;
+                split8(v + 8 * c, kWeightScale, h, l);
+                const int off = swizzled(r, 4 * half + c);
+                *(uint4*)(a_hi + off) = h;
+                *(uint4*)(a_lo + off) = l;
             }
+            // the tensor core reads shared memory through the async proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&full_bar[slot]);
+            cur = nxt;
         }
     } else if (warp < kMmaWarp) {
         // ------------------------------------------------------------ drain warps: tensor memory -> fp32 registers -> Y
@@ -375,62 +363,44 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
         const int dw = warp - kStageWarps, quarter = warp & 3, chalf = dw >> 2;
         const int cols_here = bn >> 1, col0 = chalf * cols_here;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const int r = quarter * 32 + lane;  // this thread's row of the tile
         float acc[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
         bool dead = false;
-        int drain = 0;  // drains so far: accumulator drain % kAccs, round drain / kAccs
         for (int ks = 0; ks < k_steps; ++ks) {
-            const int slot = ks % kStages;
-            const uint8_t* stage = smem + (size_t)slot * kStageBytes;
-#pragma unroll
-            for (int bi = 0; bi < NBLK; ++bi, ++drain) {
-                const int b = drain % kAccs;
-                if (!dead && !mbar_wait(&acc_full[b], (drain / kAccs) & 1)) { atomicExch(p.error_flag, 14); dead = true; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                // this row's factor(s) for the block: written by the staging warps before the slice was declared full
-                const float2 fac = ((const float2*)(stage + kFactorOffset))[2 * r + (bi * BLK) / 32];
-                const float scale = TYPE == RQ_Q6_K ? ((bi & 1) ? fac.y : fac.x) : fac.x;
-                const float* xsum = (const float*)(stage + kTileBytes + (size_t)bn * 256) + ((bi * BLK) / 32) * bn + col0;  // sums of x over the block's 32 inputs, per token
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    if (16 * c < cols_here) {
-                        uint32_t t[16];
-                        tmem_ld16(tmem_base + lane_base + (uint32_t)(b * bn + col0 + 16 * c), t);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) acc[16 * c + j] = fmaf(scale, __uint_as_float(t[j]), acc[16 * c + j]);
-                        if (TYPE == RQ_Q4_K) {
-#pragma unroll
-                            for (int j4 = 0; j4 < 4; ++j4) {
-                                const float4 xs4 = *(const float4*)(xsum + 16 * c + 4 * j4);
-                                acc[16 * c + 4 * j4 + 0] = fmaf(-fac.y, xs4.x, acc[16 * c + 4 * j4 + 0]);
-                                acc[16 * c + 4 * j4 + 1] = fmaf(-fac.y, xs4.y, acc[16 * c + 4 * j4 + 1]);
-                                acc[16 * c + 4 * j4 + 2] = fmaf(-fac.y, xs4.z, acc[16 * c + 4 * j4 + 2]);
-                                acc[16 * c + 4 * j4 + 3] = fmaf(-fac.y, xs4.w, acc[16 * c + 4 * j4 + 3]);
-                            }
-                        }
-                    }
-                }
-                // this warp has read the accumulator: the tensor core may overwrite it
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[b]);
-            }
-            // and the slice's factors and sums: the stage may be refilled
-            if (lane == 0) mbar_arrive(&empty_bar[slot]);
-        }
-        const int64_t out_row = m0 + r;
-        if (out_row < p.rows && !dead) {
+            const int b = ks & 1;
+            if (!dead && !mbar_wait(&acc_full[b], (ks >> 1) & 1)) { atomicExch(p.error_flag, 14); dead = true; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 if (16 * c < cols_here) {
+                    uint32_t t[16];
+                    tmem_ld16(tmem_base + lane_base + (uint32_t)(b * bn + col0 + 16 * c), t);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[16 * c + j] += __uint_as_float(t[j]);
+                }
+            }
+            // this warp has read the accumulator: the tensor core may overwrite it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);
+        }
+        if (!dead && !mbar_wait(&done_bar, 0)) { atomicExch(p.error_flag, 12); dead = true; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int64_t out_row = m0 + quarter * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (16 * c < cols_here) {
+                uint32_t t[16];
+                tmem_ld16(tmem_base + lane_base + (uint32_t)(2 * bn + col0 + 16 * c), t);  // the cross terms
+                if (out_row < p.rows && !dead) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int token = n0 + col0 + 16 * c + j;
+                        const float out = (acc[16 * c + j] + __uint_as_float(t[j])) * kWeightUnscale;
                         if (token < p.tokens) {
-                            if (gridDim.z == 1) p.y[out_row * p.yn + (int64_t)token * p.yt] = acc[16 * c + j];
-                            else p.partial[((size_t)blockIdx.z * p.tokens + token) * p.rows + out_row] = acc[16 * c + j];
+                            if (gridDim.z == 1) p.y[out_row * p.yn + (int64_t)token * p.yt] = out;
+                            else p.partial[((size_t)blockIdx.z * p.tokens + token) * p.rows + out_row] = out;
                         }
                     }
                 }
@@ -440,45 +410,41 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
         // ------------------------------------------------------------ MMA warp (lane 0 issues)
         bool dead = false;
         const uint32_t idesc = instr_desc(bn);
-        int drain = 0;
         for (int ks = 0; ks < k_steps; ++ks) {
-            const int slot = ks % kStages;
+            const int slot = ks % kStages, b = ks & 1;
             if (!dead && !mbar_wait(&full_bar[slot], (ks / kStages) & 1)) { atomicExch(p.error_flag, 13); dead = true; }
-            const uint32_t base = smem_u32(smem + (size_t)slot * kStageBytes);
-            const uint64_t a_codes = smem_desc(base), b_hi = smem_desc(base + kTileBytes), b_lo = smem_desc(base + kTileBytes + bn * 128);
+            if (ks >= 2 && !dead && !mbar_wait(&acc_empty[b], ((ks >> 1) - 1) & 1)) { atomicExch(p.error_flag, 15); dead = true; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0 && !dead) {
+                const uint32_t base = smem_u32(smem + (size_t)slot * kStageBytes);
+                const uint64_t a_hi = smem_desc(base), a_lo = smem_desc(base + kTileBytes);
+                const uint64_t b_hi = smem_desc(base + 2 * kTileBytes), b_lo = smem_desc(base + 2 * kTileBytes + bn * 128);
+                const uint32_t acc_main = tmem_base + (uint32_t)(b * bn), acc_cross = tmem_base + (uint32_t)(2 * bn);
 #pragma unroll
-            for (int bi = 0; bi < NBLK; ++bi, ++drain) {
-                const int b = drain % kAccs;
-                // a fresh sum for every block of BLK inputs: wait until the drain warps have read the accumulator's last one
-                if (drain >= kAccs && !dead && !mbar_wait(&acc_empty[b], ((drain / kAccs) - 1) & 1)) { atomicExch(p.error_flag, 15); dead = true; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (lane == 0 && !dead) {
-                    const uint32_t acc = tmem_base + (uint32_t)(b * bn);
-#pragma unroll
-                    for (int kk = 0; kk < BLK / 16; ++kk) {
-                        const uint64_t adv = (uint64_t)((bi * (BLK / 16) + kk) * 2);  // 32 bytes along K per 16 inputs, in 16-byte units
-                        mma_f16(acc, a_codes + adv, b_hi + adv, idesc, kk ? 1u : 0u);
-                        mma_f16(acc, a_codes + adv, b_lo + adv, idesc, 1u);
-                    }
-                    mma_commit(&acc_full[b]);
+                for (int kk = 0; kk < BK / 16; ++kk) {
+                    const uint64_t adv = (uint64_t)(kk * 2);  // 32 bytes along K, in 16-byte units of the start address
+                    mma_f16(acc_main, a_hi + adv, b_hi + adv, idesc, kk ? 1u : 0u);       // a fresh sum for every slice
+                    mma_f16(acc_cross, a_hi + adv, b_lo + adv, idesc, (ks | kk) ? 1u : 0u);
+                    mma_f16(acc_cross, a_lo + adv, b_hi + adv, idesc, 1u);
                 }
-                __syncwarp();
+                mma_commit(&empty_bar[slot]);  // the stage is free once these have read it
+                mma_commit(&acc_full[b]);      // and the slice's sum is complete
+                if (ks == k_steps - 1) mma_commit(&done_bar);
             }
-            if (lane == 0 && !dead) mma_commit(&empty_bar[slot]);  // the tiles are free once these have read them
             __syncwarp();
         }
     } else {
-        // ------------------------------------------------------------ copy warp (lane 0): the split X tiles and sums
+        // ------------------------------------------------------------ copy warp (lane 0): the split X tiles
         if (lane == 0) {
-            // written by the kernel before this one
+            // the activation tiles were written by the kernel before this one
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            const uint32_t bytes = (uint32_t)x_image_bytes(bn);
+            const uint32_t bytes = 2u * (uint32_t)bn * 128u;
             const uint8_t* src = p.xs + ((size_t)nt * k_total + k_first) * bytes;
             for (int ks = 0; ks < k_steps; ++ks) {
                 const int slot = ks % kStages;
                 if (ks >= kStages && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 16); break; }
                 mbar_expect_tx(&full_bar[slot], bytes);
-                bulk_g2s(smem + (size_t)slot * kStageBytes + kTileBytes, src + (size_t)ks * bytes, bytes, &full_bar[slot]);
+                bulk_g2s(smem + (size_t)slot * kStageBytes + 2 * kTileBytes, src + (size_t)ks * bytes, bytes, &full_bar[slot]);
             }
         }
     }
@@ -523,7 +489,7 @@ int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk
     p.tokens = tokens; p.y = y; p.yn = yn; p.yt = yt; p.error_flag = ctx->error_flag;
     // the split activations live in the context's scratch (whatever int8 records it held are gone)
     const int n_tiles = (tokens + p.bn - 1) / p.bn, k_steps = p.cols / BK;
-    const size_t bytes = (size_t)n_tiles * k_steps * ((size_t)p.bn * 256 + (size_t)p.bn * 8);
+    const size_t bytes = (size_t)n_tiles * k_steps * 2 * p.bn * 128;
     // Few tiles and a long K: several CTAs share a tile's K (at least sixteen slices each) so that the whole GPU
     // dequantises, and a second kernel adds their sums.
     const int64_t tiles = ((w->rows + BM - 1) / BM) * n_tiles;
