@@ -33,8 +33,8 @@ if str(ROOT) not in sys.path:
 
 import numpy as np  # noqa: E402
 
-Q4_K, Q6_K = 12, 14
-GEOM = {Q4_K: (256, 144), Q6_K: (256, 210)}
+Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+GEOM = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
 # name, type, rows, cols, shares the activation column of the previous projection
 LAYER = [
     ("q", Q4_K, 4096, 4096, False),
@@ -321,6 +321,7 @@ def run_ours(args):
         for w in ws:
             w.free()
     sharded_out = run_sharded_configs(ctx, rq, torch, dist, rank, world, device, args.steps) if args.sharded else None
+    other_out = run_other_configs(ctx, rq, torch, device) if (args.sharded and rank == 0) else None
 
     # max over ranks
     if dist is not None:
@@ -358,6 +359,8 @@ def run_ours(args):
     }
     if sharded_out is not None:
         line["sharded"] = sharded_out
+    if other_out is not None:
+        line["other_configs"] = other_out
     if args.cpu_baseline:
         from tests import oracle_lib as ol
 
@@ -569,6 +572,71 @@ def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
                                                   "launch": "cuda graph" if timed.graphed else "eager"}
     ctx.check()
     bank.free()
+    return out
+
+
+def run_other_configs(ctx, rq, torch, device):
+    """BASELINE's remaining single-GPU configs, device-timed on rank 0 (not the headline: recorded beside it):
+    the Q8_0 4096 x 4096 matvec (int8, one token) and the batched tensor-core product at 16 / 64 / 512 tokens."""
+    out = {}
+    gen = torch.Generator(device=device)
+    gen.manual_seed(5)
+    stream = torch.cuda.current_stream()
+
+    def quantised(t, rows, cols, copies):
+        ws = []
+        for _ in range(copies):
+            w32 = torch.randn(rows * cols, generator=gen, device=device) * 0.02
+            ws.append(ctx.weight_from_device(t, ctx.quantize(t, w32), rows, cols))
+            del w32
+        return ws
+
+    def graph_time(fn, reps):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(reps):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return 1e3 * e0.elapsed_time(e1) / reps
+
+    # cfg 1: Q8_0 4096 x 4096, eight copies in rotation (143 MB: larger than L2)
+    ws = quantised(Q8_0, 4096, 4096, 8)
+    x = torch.randn(4096, generator=gen, device=device)
+    y = torch.empty(4096, device=device)
+    us = graph_time(lambda i: ctx.matvec(ws[i % 8], x, y, act_mode=rq.ACT_INT8, step=32), 64)
+    nbytes = algo_bytes(Q8_0, 4096, 4096)
+    out["q8_0_4096x4096_int8_batch1"] = {"us": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes": nbytes}
+    for w in ws:
+        w.free()
+    # cfg 5: the batched product, fp32 activations, tensor cores
+    for name, t, rows, cols in (("q4k_14336x4096", Q4_K, 14336, 4096), ("q6k_4096x14336", Q6_K, 4096, 14336)):
+        ws = quantised(t, rows, cols, 4)
+        for tokens in (16, 64, 512):
+            xb = torch.randn(tokens, cols, generator=gen, device=device)
+            yb = torch.empty(tokens, rows, device=device)
+            for i in range(2):
+                ctx.matmul(ws[i], xb, yb)  # grows the scratch before timing
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(8):
+                ctx.matmul(ws[i % 4], xb, yb)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            us = 1e3 * e0.elapsed_time(e1) / 8
+            out[f"matmul_{name}_tokens{tokens}"] = {"us": us, "TFLOPs_useful": 2.0 * rows * cols * tokens / us / 1e6}
+        for w in ws:
+            w.free()
+    ctx.check()
     return out
 
 

@@ -19,7 +19,6 @@
 // error code in the context's flag word and stops waiting (it keeps walking its loop, so the
 // CTA's barriers still balance); the CTA drains the copies it issued before it exits. A set
 // flag makes the next rq_check() fail.
-#include <stdlib.h>
 #include <string.h>
 
 #include "rq_internal.cuh"
@@ -1457,12 +1456,7 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     if (p.act_regs) p.act_vectors = p.fuse_step ? 1 : 0;        // fused: one token's records are made in shared memory; else nothing is staged
     if (p.act_bytes * p.act_vectors > 64 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
-#ifdef RQ_PROBE_CTAS
-    static const int probe_ctas = getenv("RQ_CTAS_PER_SM") ? atoi(getenv("RQ_CTAS_PER_SM")) : kCtasPerSm;
-    int ctas = sm_count * probe_ctas;
-#else
     int ctas = sm_count * kCtasPerSm;
-#endif
     if (p.plan_count > 1) { ctas /= p.plan_count; if (ctas < 1) ctas = 1; }  // the batch's grid rows share the GPU
     const int64_t rows_per_cta = (p.rows + ctas - 1) / ctas;
     const int ipr = 2 * p.units * p.subs;  // items per virtual row
@@ -1506,9 +1500,6 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
         const int64_t piece_bytes = (int64_t)p.piece_rows * row_bytes * p.subs;
         p.window = (int)((32 * 1024 + piece_bytes - 1) / piece_bytes);
         if (p.window < 2) p.window = 2;
-#ifdef RQ_PROBE_CTAS
-        if (getenv("RQ_WINDOW_KB")) { p.window = (int)((atoi(getenv("RQ_WINDOW_KB")) * 1024 + piece_bytes - 1) / piece_bytes); if (p.window < 1) p.window = 1; }
-#endif
     }
     p.sub_main_bytes = ((size_t)stage_rows * row_bytes + 127) & ~(size_t)127;
     p.sub_scale_bytes = p.scales_per_unit ? (((size_t)stage_rows * p.units * p.scales_per_unit * 2 + 32 + 127) & ~(size_t)127) : 0;
