@@ -153,7 +153,7 @@ struct Item {
                 }
             }
         } else if (TYPE == RQ_Q8_0) {
-            uint4 q = ldg128(p.main + row * cols + 16 * (int64_t)item);
+            uint4 q = ldg128(p.main + row * cols + 16 * (rq_plane_permuted(TYPE, cols) ? rq_plane_chunk(TYPE, item) : (int64_t)item));
             const float d = rq_h2f(__ldg(p.scale + row * (cols >> 5) + (item >> 1)));
             const int k0 = 16 * item;
             uint32_t w[4] = {q.x, q.y, q.z, q.w};
@@ -178,7 +178,7 @@ struct Item {
                 }
             }
         } else {  // Q4_0
-            uint4 q = ldg128(p.main + row * (cols >> 1) + 16 * (int64_t)item);
+            uint4 q = ldg128(p.main + row * (cols >> 1) + 16 * (rq_plane_permuted(TYPE, cols) ? rq_plane_chunk(TYPE, item) : (int64_t)item));
             const float d = rq_h2f(__ldg(p.scale + row * (cols >> 5) + item));
             const int k_lo = 32 * item, k_hi = k_lo + 16;
             uint32_t w[4] = {q.x, q.y, q.z, q.w}, lo[4], hi[4];

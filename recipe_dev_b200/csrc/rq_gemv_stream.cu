@@ -210,7 +210,7 @@ struct ActHalf {
 // `w` = the unit in shared memory, `sc` = its fp16 d values in shared memory (not Q4_K).
 // ------------------------------------------------------------------------------------------
 template <int TYPE, int MODE>
-__device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const uint16_t* __restrict__ sc, const uint8_t* __restrict__ ar, const ActHalf& ah8, const int h) {
+__device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const uint16_t* __restrict__ sc, const uint8_t* __restrict__ ar, const ActHalf& ah8, const int h, const int u) {
     const float* xf = (const float*)ar + 128 * h;      // FLOAT: the half's 128 inputs
     const float* xsum = (const float*)ar + 256 + 8 * h;  // and its eight slice sums
     if (TYPE == RQ_Q4_K) {
@@ -326,8 +326,8 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
-            const uint8_t* qp = w + 128 * h + 32 * b;
-            const uint4 q0 = *(const uint4*)qp, q1 = *(const uint4*)(qp + 16);
+            // chunks 8h + 2b and 8h + 2b + 1 of the unit, at their permuted places (rq_plane_chunk)
+            const uint4 q0 = *(const uint4*)(w + 16 * ((8 * h + 2 * b) ^ (u & 7))), q1 = *(const uint4*)(w + 16 * ((8 * h + 2 * b + 1) ^ (u & 7)));
             if (MODE == RQ_ACT_INT8) {
                 const uint32_t* a0 = ah8.c + 8 * b;
                 const uint32_t* a1 = a0 + 4;
@@ -354,7 +354,7 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
-            const uint4 q = *(const uint4*)(w + 64 * h + 16 * b);
+            const uint4 q = *(const uint4*)(w + 16 * ((4 * h + b) ^ (u & 7)));  // chunk 4h + b of the unit, at its permuted place
             const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
             if (MODE == RQ_ACT_INT8) {
                 const uint32_t* alw = ah8.c + 8 * b;
@@ -388,7 +388,7 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
 template <int TYPE> struct ItemRegs;
 template <> struct ItemRegs<RQ_Q4_K> {
     uint4 hdr, q[4];
-    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t*, int h) {
+    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t*, int h, int) {
         hdr = *(const uint4*)w;
         const uint4* qp = (const uint4*)(w + 16 + 64 * h);
         q[0] = qp[0]; q[1] = qp[1]; q[2] = qp[2]; q[3] = qp[3];
@@ -398,7 +398,7 @@ template <> struct ItemRegs<RQ_Q6_K> {
     uint4 ql[4], qh[2];  // ql[2 * gl + wh], qh[wh]
     uint2 sc;
     uint32_t d16;
-    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h) {
+    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h, int) {
         const uint4* lp = (const uint4*)(w + 64 * h);
         ql[0] = lp[0]; ql[1] = lp[1]; ql[2] = lp[2]; ql[3] = lp[3];
         const uint4* hp = (const uint4*)(w + 128 + 32 * h);
@@ -410,19 +410,18 @@ template <> struct ItemRegs<RQ_Q6_K> {
 template <> struct ItemRegs<RQ_Q8_0> {
     uint4 q[8];
     uint2 dd;
-    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h) {
-        const uint4* qp = (const uint4*)(w + 128 * h);
+    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h, int u) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = qp[i];
+        for (int i = 0; i < 8; ++i) q[i] = *(const uint4*)(w + 16 * ((8 * h + i) ^ (u & 7)));  // logical order in registers
         dd = *(const uint2*)(scp + 4 * h);
     }
 };
 template <> struct ItemRegs<RQ_Q4_0> {
     uint4 q[4];
     uint2 dd;
-    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h) {
-        const uint4* qp = (const uint4*)(w + 64 * h);
-        q[0] = qp[0]; q[1] = qp[1]; q[2] = qp[2]; q[3] = qp[3];
+    __device__ __forceinline__ void load(const uint8_t* w, const uint16_t* scp, int h, int u) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = *(const uint4*)(w + 16 * ((4 * h + i) ^ (u & 7)));  // logical order in registers
         dd = *(const uint2*)(scp + 4 * h);
     }
 };
@@ -1227,7 +1226,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                     if (have[k]) {
                         const uint16_t* sc = nullptr;
                         if (TYPE != RQ_Q4_K) sc = (const uint16_t*)(stage + p.sub_main_bytes + info.w) + ((size_t)lr * p.units + my_u) * p.scales_per_unit;
-                        wr[k].load(stage + my_off + k * pass_bytes, sc, my_h);
+                        wr[k].load(stage + my_off + k * pass_bytes, sc, my_h, my_u);
                     }
                 }
                 // the warp holds its weights in registers: the producer may refill the slot
@@ -1321,7 +1320,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                                 const uintptr_t first = (uintptr_t)sg.scale[my_s] + (uintptr_t)(lr0 * row_scales * 2);
                                 sc = (const uint16_t*)(stage + (size_t)p.subs * p.sub_main_bytes + (size_t)my_s * p.sub_scale_bytes + (first & 15)) + (size_t)my_su * p.scales_per_unit;
                             }
-                            wr[k].load(w, sc, my_h);
+                            wr[k].load(w, sc, my_h, my_u);
                         }
                         // the warp holds its weights in registers: the producer may refill the slot
                         __syncwarp();
@@ -1370,7 +1369,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                     for (int t = 0; t < T; ++t) {
                         const uint8_t* ar = a0 + t * p.act_bytes;
                         if (MODE == RQ_ACT_INT8) areg.load(ar, my_h);
-                        part[t * stage_items + tid] = item_dot<TYPE, MODE>(w, sc, ar, areg, my_h);
+                        part[t * stage_items + tid] = item_dot<TYPE, MODE>(w, sc, ar, areg, my_h, my_u);
                     }
                 }
                 // this warp is done with the stage's weights: the producer may refill the slot

@@ -132,6 +132,14 @@ int rq_launch_gemv_stream(rq_ctx* ctx, const rq_weight* w, const float* x, int64
 #ifdef __CUDACC__
 __device__ __forceinline__ float rq_h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
+// Q8_0 / Q4_0 main planes of rows made of whole 256-value units keep each row's 16-byte chunks PERMUTED: logical chunk L
+// of a row (a unit is 16 chunks of Q8_0, 8 of Q4_0) sits at L with its low three bits xor-ed with the low three bits of
+// its unit index. In shared memory a thread's unit starts at a multiple of 128 bytes, so eight threads on adjacent
+// units reading the same logical chunk would otherwise all hit one 16-byte bank group; permuted, they hit eight.
+// The map is its own inverse. Rows that are not whole units (the tiled kernel's) are stored as they come.
+__host__ __device__ __forceinline__ bool rq_plane_permuted(int type, int64_t cols) { return (type == RQ_Q8_0 || type == RQ_Q4_0) && cols % 256 == 0; }
+__host__ __device__ __forceinline__ int64_t rq_plane_chunk(int type, int64_t logical) { return logical ^ ((logical >> (type == RQ_Q8_0 ? 4 : 3)) & 7); }
+
 // Six-bit scale and minimum of sub-block j from the twelve scale bytes held as three words
 // (little-endian bytes 0..11).
 __device__ __forceinline__ void rq_q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, int& sc, int& mn) {

@@ -5,7 +5,7 @@
 // mode 0: GGUF -> planes, mode 1: planes -> GGUF.
 template <int TYPE>
 __global__ void rq_plane_kernel(uint16_t* __restrict__ gguf, uint16_t* __restrict__ main_plane, uint16_t* __restrict__ scale_plane,
-                                int64_t blocks, int to_gguf) {
+                                int64_t blocks, int to_gguf, int64_t cols) {
     constexpr int WORDS = TYPE == RQ_Q6_K ? 105 : (TYPE == RQ_Q8_0 ? 17 : 9);
     constexpr int BODY = WORDS - 1;                       // 16-bit words of the block that are not d
     constexpr int D_AT = TYPE == RQ_Q6_K ? 104 : 0;       // where d sits in the GGUF block
@@ -15,8 +15,17 @@ __global__ void rq_plane_kernel(uint16_t* __restrict__ gguf, uint16_t* __restric
         int wd = (int)(i - b * WORDS);
         uint16_t* g = gguf + i;
         uint16_t* p;
-        if (wd == D_AT) p = scale_plane + b;
-        else p = main_plane + b * BODY + (TYPE == RQ_Q6_K ? wd : wd - 1);
+        if (wd == D_AT) {
+            p = scale_plane + b;
+        } else if (rq_plane_permuted(TYPE, cols)) {
+            // byte offset of this word in its row's plane, with the row's chunk permutation applied
+            const int64_t per_row = cols >> 5, row = b / per_row, in_row = b - row * per_row;
+            const int64_t off = in_row * (2 * BODY) + 2 * (wd - 1);
+            const int64_t phys = (rq_plane_chunk(TYPE, off >> 4) << 4) | (off & 15);
+            p = main_plane + (row * per_row * (2 * BODY) + phys) / 2;
+        } else {
+            p = main_plane + b * BODY + (TYPE == RQ_Q6_K ? wd : wd - 1);
+        }
         if (to_gguf) *g = *p; else *p = *g;
     }
 }
@@ -35,9 +44,9 @@ static int plane_launch(const rq_weight* w, uint8_t* blocks, int to_gguf, cudaSt
     uint16_t* g = (uint16_t*)blocks;
     uint16_t* m = (uint16_t*)w->main;
     switch (w->type) {
-        case RQ_Q6_K: rq_plane_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf); break;
-        case RQ_Q8_0: rq_plane_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf); break;
-        case RQ_Q4_0: rq_plane_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf); break;
+        case RQ_Q6_K: rq_plane_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf, w->cols); break;
+        case RQ_Q8_0: rq_plane_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf, w->cols); break;
+        case RQ_Q4_0: rq_plane_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(g, m, w->scale, nblocks, to_gguf, w->cols); break;
         default: return rq_fail(RQ_ERR_INVALID, "layout: type %d", w->type);
     }
     RQ_CUDA(cudaGetLastError());
@@ -54,7 +63,7 @@ int rq_launch_export(const rq_weight* w, uint8_t* dev_blocks, cudaStream_t s) { 
 // the one inexact step, the final subtract, rounds the same exact difference.
 // ---------------------------------------------------------------------------------------
 template <int TYPE>
-__global__ void rq_dequant_kernel(const uint8_t* __restrict__ main_plane, const uint16_t* __restrict__ scale_plane, float* __restrict__ out, int64_t count) {
+__global__ void rq_dequant_kernel(const uint8_t* __restrict__ main_plane, const uint16_t* __restrict__ scale_plane, float* __restrict__ out, int64_t count, int64_t cols) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
         float value;
         if (TYPE == RQ_Q4_K) {
@@ -80,11 +89,21 @@ __global__ void rq_dequant_kernel(const uint8_t* __restrict__ main_plane, const 
             float scaled = __fmul_rn(rq_h2f(scale_plane[b]), (float)scale);
             value = __fmul_rn(scaled, (float)code);
         } else if (TYPE == RQ_Q8_0) {
-            value = __fmul_rn((float)(int8_t)main_plane[i], rq_h2f(scale_plane[i >> 5]));
+            int64_t at = i;
+            if (rq_plane_permuted(TYPE, cols)) {
+                const int64_t row = i / cols, off = i - row * cols;  // one byte per value
+                at = row * cols + ((rq_plane_chunk(TYPE, off >> 4) << 4) | (off & 15));
+            }
+            value = __fmul_rn((float)(int8_t)main_plane[at], rq_h2f(scale_plane[i >> 5]));
         } else {
             int64_t b = i >> 5;
             int v = (int)(i & 31);
-            int code = ((main_plane[b * 16 + (v & 15)] >> ((v >> 4) * 4)) & 15) - 8;
+            int64_t at = b * 16 + (v & 15);
+            if (rq_plane_permuted(TYPE, cols)) {
+                const int64_t row_bytes = cols >> 1, row = at / row_bytes, off = at - row * row_bytes;
+                at = row * row_bytes + ((rq_plane_chunk(TYPE, off >> 4) << 4) | (off & 15));
+            }
+            int code = ((main_plane[at] >> ((v >> 4) * 4)) & 15) - 8;
             value = __fmul_rn((float)code, rq_h2f(scale_plane[b]));
         }
         out[i] = value;
@@ -97,10 +116,10 @@ int rq_launch_dequant(const rq_weight* w, float* out, cudaStream_t s) {
     int64_t want = (count + threads - 1) / threads;
     int grid = (int)(want < 148 * 32 ? want : 148 * 32);
     switch (w->type) {
-        case RQ_Q4_K: rq_dequant_kernel<RQ_Q4_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count); break;
-        case RQ_Q6_K: rq_dequant_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count); break;
-        case RQ_Q8_0: rq_dequant_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count); break;
-        case RQ_Q4_0: rq_dequant_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count); break;
+        case RQ_Q4_K: rq_dequant_kernel<RQ_Q4_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        case RQ_Q6_K: rq_dequant_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        case RQ_Q8_0: rq_dequant_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        case RQ_Q4_0: rq_dequant_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
         default: return rq_fail(RQ_ERR_INVALID, "dequant: type %d", w->type);
     }
     RQ_CUDA(cudaGetLastError());

@@ -213,9 +213,10 @@ template <> struct RawHalf<RQ_Q8_0> {
     uint4 a, c;
     uint32_t d16;
     __device__ __forceinline__ void load(const MatmulParams& p, int64_t row, int k0, int half) {
-        const int64_t at = row * p.cols + k0 + 32 * half;
-        a = __ldg((const uint4*)(p.main + at));
-        c = __ldg((const uint4*)(p.main + at + 16));
+        const int64_t chunk = (k0 + 32 * half) >> 4;  // two 16-byte chunks of the row
+        const bool perm = rq_plane_permuted(RQ_Q8_0, p.cols);
+        a = __ldg((const uint4*)(p.main + row * p.cols + 16 * (perm ? rq_plane_chunk(RQ_Q8_0, chunk) : chunk)));
+        c = __ldg((const uint4*)(p.main + row * p.cols + 16 * (perm ? rq_plane_chunk(RQ_Q8_0, chunk + 1) : chunk + 1)));
         d16 = __ldg(p.scale + row * (p.cols >> 5) + (k0 >> 5) + half);
     }
     __device__ __forceinline__ void decode(int, int, float* v) const {
@@ -231,7 +232,8 @@ template <> struct RawHalf<RQ_Q4_0> {
     uint4 a;
     uint32_t d16;
     __device__ __forceinline__ void load(const MatmulParams& p, int64_t row, int k0, int half) {
-        a = __ldg((const uint4*)(p.main + row * (p.cols >> 1) + ((k0 >> 5) + half) * 16));
+        const int64_t chunk = (k0 >> 5) + half;  // one 16-byte chunk per block of 32 values
+        a = __ldg((const uint4*)(p.main + row * (p.cols >> 1) + 16 * (rq_plane_permuted(RQ_Q4_0, p.cols) ? rq_plane_chunk(RQ_Q4_0, chunk) : chunk)));
         d16 = __ldg(p.scale + row * (p.cols >> 5) + (k0 >> 5) + half);
     }
     __device__ __forceinline__ void decode(int, int, float* v) const {
