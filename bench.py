@@ -349,8 +349,8 @@ def run_ours(args):
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": dom_us, "algorithmic_bytes_per_launch": dom_bytes,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the same kernel over one of the two
-                     # row sets (14336 x 4096: 33.10 MB read, nothing written), scaled to the launch's two row sets
-                     "traffic": 2 * 33_101_300, "traffic_source": "profiles/rq_gemv_stream_q4k_14336x4096_int8.md, x2 row sets"},
+                     # row sets (14336 x 4096: 33.11 MB read, nothing written), scaled to the launch's two row sets
+                     "traffic": 2 * 33_106_400, "traffic_source": "profiles/rq_gemv_stream_q4k_14336x4096_int8.md, x2 row sets"},
         "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": sum(4 * c for _, _, _, c, _ in LAYER), "d2h_bytes_per_step": sum(4 * r for _, _, r, _, _ in LAYER),
                 "ms_per_step": 1e3 * e2e_s / args.steps, "call": "rq_matvec_multi_host x 4 per step (q/k/v, o, gate/up, down: host x in, host y out)"},

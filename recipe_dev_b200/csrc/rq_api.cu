@@ -270,6 +270,20 @@ extern "C" int rq_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_
     return rq_launch_gemv(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, step, (cudaStream_t)stream);
 }
 
+// Host planes <-> the token-major pinned staging buffer: one memcpy per token when the plane's elements are adjacent.
+static void gather_plane(float* dst, const float* src, int64_t n, int tokens, int64_t sn, int64_t st) {
+    for (int t = 0; t < tokens; ++t) {
+        if (sn == 1) memcpy(dst + (size_t)t * n, src + (int64_t)t * st, (size_t)n * 4);
+        else for (int64_t k = 0; k < n; ++k) dst[(size_t)t * n + k] = src[k * sn + t * st];
+    }
+}
+static void scatter_plane(float* dst, const float* src, int64_t n, int64_t src_token_stride, int tokens, int64_t sn, int64_t st) {
+    for (int t = 0; t < tokens; ++t) {
+        if (sn == 1) memcpy(dst + (int64_t)t * st, src + (size_t)t * src_token_stride, (size_t)n * 4);
+        else for (int64_t k = 0; k < n; ++k) dst[k * sn + t * st] = src[(size_t)t * src_token_stride + k];
+    }
+}
+
 static int ensure_buffer(float** dev, size_t* dev_bytes, float** pin, size_t* pin_bytes, size_t need) {
     if (need > *dev_bytes) {
         if (*dev) cudaFree(*dev);
@@ -298,8 +312,7 @@ extern "C" int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host
     if (rc) return rc;
     rc = ensure_buffer(&ctx->stage_y, &ctx->stage_y_bytes, &ctx->pin_y, &ctx->pin_y_bytes, yb);
     if (rc) return rc;
-    for (int t = 0; t < tokens; ++t)
-        for (int64_t k = 0; k < w->cols; ++k) ctx->pin_x[(size_t)t * w->cols + k] = host_x[k * sk + t * st];
+    gather_plane(ctx->pin_x, host_x, w->cols, tokens, sk, st);
     RQ_CUDA(cudaMemcpyAsync(ctx->stage_x, ctx->pin_x, xb, cudaMemcpyHostToDevice, ctx->stream));
     rc = rq_launch_gemv(ctx, w, ctx->stage_x, 1, w->cols, tokens, ctx->stage_y, 1, w->rows, act_mode, step, ctx->stream);
     if (rc) return rc;
@@ -307,8 +320,7 @@ extern "C" int rq_matvec_host(rq_ctx* ctx, const rq_weight* w, const float* host
     RQ_CUDA(cudaMemcpyAsync(ctx->pin_flag, ctx->error_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     RQ_CUDA(cudaStreamSynchronize(ctx->stream));
     if (*ctx->pin_flag) return rq_check(ctx);
-    for (int t = 0; t < tokens; ++t)
-        for (int64_t n = 0; n < w->rows; ++n) host_y[n * yn + t * yt] = ctx->pin_y[(size_t)t * w->rows + n];
+    scatter_plane(host_y, ctx->pin_y, w->rows, w->rows, tokens, yn, yt);
     return RQ_OK;
 }
 
@@ -333,8 +345,7 @@ extern "C" int rq_matvec_multi_host(rq_ctx* ctx, int n, const rq_weight* const* 
     if (rc) return rc;
     rc = ensure_buffer(&ctx->stage_y, &ctx->stage_y_bytes, &ctx->pin_y, &ctx->pin_y_bytes, yb);
     if (rc) return rc;
-    for (int t = 0; t < tokens; ++t)
-        for (int64_t k = 0; k < cols; ++k) ctx->pin_x[(size_t)t * cols + k] = host_x[k * sk + t * st];
+    gather_plane(ctx->pin_x, host_x, cols, tokens, sk, st);
     RQ_CUDA(cudaMemcpyAsync(ctx->stage_x, ctx->pin_x, xb, cudaMemcpyHostToDevice, ctx->stream));
     float* dev_ys[16];
     int64_t at = 0;
@@ -347,8 +358,7 @@ extern "C" int rq_matvec_multi_host(rq_ctx* ctx, int n, const rq_weight* const* 
     if (*ctx->pin_flag) return rq_check(ctx);
     at = 0;
     for (int i = 0; i < n; ++i) {
-        for (int t = 0; t < tokens; ++t)
-            for (int64_t r = 0; r < ws[i]->rows; ++r) host_ys[i][r * yn + t * yt] = ctx->pin_y[(size_t)t * total_rows + at + r];
+        scatter_plane(host_ys[i], ctx->pin_y + at, ws[i]->rows, total_rows, tokens, yn, yt);
         at += ws[i]->rows;
     }
     return RQ_OK;
