@@ -558,7 +558,7 @@ def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
 
         def moe_step():
             routing = ctx.moe_route(scores, top)
-            ctx.moe_forward(bank, xm, routing[ef:ef + ec], top, include_shared=(rank == 0), y=y)
+            ctx.moe_forward(bank, xm, routing, top, include_shared=(rank == 0), y=y)  # the whole routing plane: a rank reads its experts' rows
             if dist is not None:
                 dist.all_reduce(y)
             return y

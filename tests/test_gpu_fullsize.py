@@ -91,3 +91,44 @@ def test_full_size_batched_product_matches_matvec(rq_ctx, t, rows, cols, tokens)
     assert rel_err(both[0].cpu().numpy(), (y[0] + y[1]).cpu().numpy()) <= TOL
     rq_ctx.check()
     w.free()
+
+
+def test_full_size_expert_bank_split_adds_up(rq_ctx, oracle):
+    """BASELINE's expert bank (256 experts, top-8, hidden 2048, ffn 512, gated shared expert) at 16 tokens: the outputs of
+    eight expert-parallel shares (shared expert on share 0) add up to the whole bank's, and the token the oracle is run
+    on agrees with it."""
+    import torch
+
+    t, experts, top, hidden, ffn, tokens = ol.Q4_K, 256, 8, 2048, 512, 16
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(77)
+
+    def host_blocks(n_rows, n_cols):
+        w32 = torch.randn(n_rows * n_cols, generator=gen, device="cuda") * 0.02
+        b = rq_ctx.quantize(t, w32).cpu().numpy()
+        del w32
+        return b
+
+    gate, up, down = host_blocks(experts * ffn, hidden), host_blocks(experts * ffn, hidden), host_blocks(experts * hidden, ffn)
+    shared = (host_blocks(ffn, hidden), host_blocks(ffn, hidden), host_blocks(hidden, ffn), (torch.randn(hidden, generator=gen, device="cuda") * 0.02).cpu().numpy())
+    scores = torch.randn(experts, tokens, generator=gen, device="cuda")
+    x = torch.randn(hidden, tokens, generator=gen, device="cuda")
+    routing = rq_ctx.moe_route(scores, top)
+    assert np.array_equal(routing.cpu().numpy().view(np.uint32), oracle.topk(scores.cpu().numpy(), top, 0, True).view(np.uint32))
+    whole = rq_ctx.moe_prepare(t, gate, up, down, experts, hidden, ffn, shared=shared)
+    want = rq_ctx.moe_forward(whole, x, routing, top).double()
+    whole.free()
+    total = torch.zeros_like(want)
+    shares = 8
+    for r in range(shares):
+        first, count = r * experts // shares, experts // shares
+        bank = rq_ctx.moe_prepare(t, gate, up, down, experts, hidden, ffn, expert_first=first, expert_count=count, shared=shared if r == 0 else None)
+        total += rq_ctx.moe_forward(bank, x, routing, top, include_shared=(r == 0)).double()  # the whole plane: a share reads its experts' rows
+        bank.free()
+    rq_ctx.check()
+    assert rel_err(total.cpu().numpy(), want.cpu().numpy()) <= TOL
+    # one token through the CPU oracle
+    xo = x[:, :1].contiguous().cpu().numpy()
+    ro = routing[:, :1].contiguous().cpu().numpy()
+    ref = oracle.moe_forward(t, gate, up, down, experts, top, hidden, ffn, xo, ro, shared=shared)
+    assert rel_err(want[:, :1].cpu().numpy(), ref) <= TOL
