@@ -165,7 +165,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 x q4/q6 -> i32, fp32 accumulate" if args.act == "int8" else "fp32",
-        "data": "synthetic", "config": workload_config(args, 1),
+        "data": "synthetic", "config": workload_config(args, 1, cpu=True),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"{args.steps} decode layers (7 matvecs, {LAYER_BYTES} algorithmic bytes each) after {max(args.warmup, 1)} warm-up"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -173,11 +173,15 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, layers):
+def workload_config(args, layers, cpu=False):
+    l2 = "inputs larger than L2: each step reads a different layer of a stack larger than 1 GB"
+    timing = "the K timed steps are one CUDA graph, replayed once untimed (its first launch uploads it) after the W warm-up steps, then timed with CUDA events"
+    if cpu:
+        l2 = "one layer (138 MB of blocks) re-read every step: larger than the host's last-level cache"
+        timing = "host wall clock around the K steps, after the W warm-up steps; all host threads"
     return {"workload": "llama-8B-shaped decode layer, batch 1: q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096 Q4_K; down 4096x14336 Q6_K",
             "activation_mode": "int8 records, step 32 (recipe default profile)" if args.act == "int8" else "fp32 activations as they are",
-            "layers_in_rotation": layers, "l2": "inputs larger than L2: each step reads a different layer of a stack larger than 1 GB",
-            "timing": "the K timed steps are one CUDA graph, replayed once untimed (its first launch uploads it) after the W warm-up steps, then timed with CUDA events",
+            "layers_in_rotation": layers, "l2": l2, "timing": timing,
             "algorithmic_bytes_per_step": LAYER_BYTES, "multi_gpu": "replicas only (the decode layer is unsharded)"}
 
 
