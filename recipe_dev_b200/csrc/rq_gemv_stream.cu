@@ -381,6 +381,164 @@ __device__ __forceinline__ float item_dot(const uint8_t* __restrict__ w, const u
 }
 
 // ------------------------------------------------------------------------------------------
+// Four tokens against one item (INT8). The tokens' records of a unit are interleaved in shared memory
+// (kRecord4 bytes per unit), so that one 128-bit load brings the same word of all four tokens:
+//   word k of the codes (k < 64) of token t  at 16 k + 4 t
+//   step of group g (g < 8)                  at 1024 + 16 g + 4 t
+//   sum of slice s (s < 16), int16           at 1152 + 8 s + 2 t
+//   sum of group g, int16                    at 1280 + 8 g + 2 t
+// 1360 bytes = 85 sixteen-byte lines, an odd count: the loads of eight threads on adjacent units fall
+// in eight different bank groups. A weight word is masked once and dotted with four tokens; every
+// token's float operations are those of item_dot, in its order, so the sums are bit for bit the same.
+// ------------------------------------------------------------------------------------------
+constexpr int kRecord4 = 1360;
+__device__ __forceinline__ uint32_t lane_of(const uint4& v, int t) { return t == 0 ? v.x : (t == 1 ? v.y : (t == 2 ? v.z : v.w)); }
+__device__ __forceinline__ float lane_of(const float4& v, int t) { return t == 0 ? v.x : (t == 1 ? v.y : (t == 2 ? v.z : v.w)); }
+__device__ __forceinline__ int short_of(const uint2& v, int t) { return (int)(int16_t)((t < 2 ? v.x : v.y) >> (16 * (t & 1))); }
+
+template <int TYPE>
+__device__ __forceinline__ void item_dot_tok4(const uint8_t* __restrict__ w, const uint16_t* __restrict__ sc, const uint8_t* __restrict__ rec, const int h, const int u, float (&out)[4]) {
+    const uint4* codes = (const uint4*)rec + 32 * h;              // the half's 32 code words, four tokens each
+    const float4* steps = (const float4*)(rec + 1024) + 4 * h;    // its four group steps
+    const uint2* sum16 = (const uint2*)(rec + 1152) + 8 * h;      // its eight slice sums
+    const uint2* sum32 = (const uint2*)(rec + 1280) + 4 * h;      // its four group sums
+    if (TYPE == RQ_Q4_K) {
+        const uint4 hdr = *(const uint4*)w;
+        const float d = rq_h2f((uint16_t)(hdr.x & 0xffff)), dmin = rq_h2f((uint16_t)(hdr.x >> 16));
+        const uint32_t scw = h == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u));
+        const uint32_t mnw = h == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u));
+        float acc_s[4] = {0.f, 0.f, 0.f, 0.f}, acc_m[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {
+            const uint8_t* qp = w + 16 + 64 * h + 32 * pp;
+            const uint4 q0 = *(const uint4*)qp, q1 = *(const uint4*)(qp + 16);
+            const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            const int sc_lo = (scw >> (16 * pp)) & 0xff, sc_hi = (scw >> (16 * pp + 8)) & 0xff;
+            const int mn_lo = (mnw >> (16 * pp)) & 0xff, mn_hi = (mnw >> (16 * pp + 8)) & 0xff;
+            int dl[4] = {0, 0, 0, 0}, dh[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t lo = qw[j] & 0x0F0F0F0Fu, hi = qw[j] & 0xF0F0F0F0u;
+                const uint4 al = codes[16 * pp + j], ah = codes[16 * pp + 8 + j];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    dl[t] = dp4a_us(lo, lane_of(al, t), dl[t]);
+                    dh[t] = dp4a_us(hi, lane_of(ah, t), dh[t]);  // sixteen times the high-nibble dot
+                }
+            }
+            const float4 d_lo = steps[2 * pp], d_hi = steps[2 * pp + 1];
+            const uint2 g_lo = sum32[2 * pp], g_hi = sum32[2 * pp + 1];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                acc_s[t] = fmaf(lane_of(d_lo, t), (float)(sc_lo * dl[t]), acc_s[t]);
+                acc_s[t] = fmaf(lane_of(d_hi, t), (float)(sc_hi * (dh[t] >> 4)), acc_s[t]);
+                acc_m[t] = fmaf(__fmul_rn(lane_of(d_lo, t), (float)short_of(g_lo, t)), (float)mn_lo, acc_m[t]);
+                acc_m[t] = fmaf(__fmul_rn(lane_of(d_hi, t), (float)short_of(g_hi, t)), (float)mn_hi, acc_m[t]);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) out[t] = diff_of_products(d, acc_s[t], dmin, acc_m[t]);
+    } else if (TYPE == RQ_Q6_K) {
+        const float d = rq_h2f(sc[0]);
+        const uint2 s2 = *(const uint2*)(w + 192 + 8 * h);
+        const uint32_t scales[2] = {s2.x, s2.y};
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int wh = 0; wh < 2; ++wh) {
+            const uint4 qh4 = *(const uint4*)(w + 128 + 32 * h + 16 * wh);
+            const uint32_t qh[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
+#pragma unroll
+            for (int gl = 0; gl < 2; ++gl) {
+                const uint4 ql4 = *(const uint4*)(w + 64 * h + 32 * gl + 16 * wh);
+                const uint32_t ql[4] = {ql4.x, ql4.y, ql4.z, ql4.w};
+                const int s_lo = 2 * gl + wh, s_hi = s_lo + 4;
+                const int sc_lo = (int)(int8_t)(scales[s_lo >> 2] >> (8 * (s_lo & 3)));
+                const int sc_hi = (int)(int8_t)(scales[s_hi >> 2] >> (8 * (s_hi & 3)));
+                const int k_lo = 32 * gl + 16 * wh, k_hi = k_lo + 64;
+                constexpr uint32_t kPairLo = 0x03030303u, kPairHi = 0x30303030u;
+                int nl[4] = {0, 0, 0, 0}, nh[4] = {0, 0, 0, 0}, pl[4] = {0, 0, 0, 0}, ph[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t m_nl = ql[j] & 0x0F0F0F0Fu, m_nh = ql[j] & 0xF0F0F0F0u;
+                    const uint32_t m_pl = qh[j] & (kPairLo << (2 * gl)), m_ph = qh[j] & (kPairHi << (2 * gl));
+                    const uint4 al = codes[(k_lo >> 2) + j], ah = codes[(k_hi >> 2) + j];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        nl[t] = dp4a_us(m_nl, lane_of(al, t), nl[t]);
+                        nh[t] = dp4a_us(m_nh, lane_of(ah, t), nh[t]);
+                        pl[t] = dp4a_us(m_pl, lane_of(al, t), pl[t]);
+                        ph[t] = dp4a_us(m_ph, lane_of(ah, t), ph[t]);
+                    }
+                }
+                const float4 d_lo = steps[k_lo >> 5], d_hi = steps[k_hi >> 5];
+                const uint2 a_lo = sum16[k_lo >> 4], a_hi = sum16[k_hi >> 4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int dl = nl[t] + ((pl[t] >> (2 * gl)) << 4) - 32 * short_of(a_lo, t);
+                    const int dh = (nh[t] >> 4) + (ph[t] >> (2 * gl)) - 32 * short_of(a_hi, t);
+                    acc[t] = fmaf(lane_of(d_lo, t), (float)(sc_lo * dl), acc[t]);
+                    acc[t] = fmaf(lane_of(d_hi, t), (float)(sc_hi * dh), acc[t]);
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) out[t] = d * acc[t];
+    } else if (TYPE == RQ_Q8_0) {
+        const uint2 dd = *(const uint2*)(sc + 4 * h);
+        const uint32_t dw[2] = {dd.x, dd.y};
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
+            const uint4 q0 = *(const uint4*)(w + 16 * ((8 * h + 2 * b) ^ (u & 7))), q1 = *(const uint4*)(w + 16 * ((8 * h + 2 * b + 1) ^ (u & 7)));
+            const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            int dot[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint4 a = codes[8 * b + j];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) dot[t] = dp4a_ss(qw[j], lane_of(a, t), dot[t]);
+            }
+            const float4 d8 = steps[b];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) acc[t] = fmaf(__fmul_rn(lane_of(d8, t), d), (float)dot[t], acc[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) out[t] = acc[t];
+    } else {  // Q4_0
+        const uint2 dd = *(const uint2*)(sc + 4 * h);
+        const uint32_t dw[2] = {dd.x, dd.y};
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float d = rq_h2f((uint16_t)(dw[b >> 1] >> (16 * (b & 1))));
+            const uint4 q = *(const uint4*)(w + 16 * ((4 * h + b) ^ (u & 7)));
+            const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+            int dl[4] = {0, 0, 0, 0}, dh[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t lo = qw[j] & 0x0F0F0F0Fu, hi = qw[j] & 0xF0F0F0F0u;
+                const uint4 al = codes[8 * b + j], ah = codes[8 * b + 4 + j];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    dl[t] = dp4a_us(lo, lane_of(al, t), dl[t]);
+                    dh[t] = dp4a_us(hi, lane_of(ah, t), dh[t]);
+                }
+            }
+            const float4 d8 = steps[b];
+            const uint2 g = sum32[b];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int dot = dl[t] + (dh[t] >> 4) - 8 * short_of(g, t);
+                acc[t] = fmaf(__fmul_rn(lane_of(d8, t), d), (float)dot, acc[t]);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) out[t] = acc[t];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // Register-resident items (single-token INT8 launches): a thread copies its item's weights out
 // of the stage into registers and releases the stage at once, so the ring slot is busy only while
 // the bytes are in flight, and works on two items at a time for instruction-level parallelism.
@@ -1105,6 +1263,45 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 }
             }
             consumer_sync<kConsumers>();
+        } else if (MODE == RQ_ACT_INT8 && T == 4) {
+            // four tokens' records, interleaved unit by unit (the layout item_dot_tok4 reads); a token past
+            // the end of the batch is staged as zeros
+            const int per_vec = p.units * (kRecord / 16), total = 4 * per_vec;
+            for (int base_i = tid; base_i < total; base_i += 4 * kConsumers) {  // four 16-byte loads in flight per thread
+                uint4 got[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = base_i + j * kConsumers;
+                    got[j] = make_uint4(0, 0, 0, 0);
+                    if (i < total) {
+                        const int v = i / per_vec, e = i - v * per_vec;
+                        if (tok0 + v < p.tokens) got[j] = __ldg((const uint4*)(p.act + (size_t)(tok0 + v) * per_vec * 16) + e);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = base_i + j * kConsumers;
+                    if (i < total) {
+                        const int v = i / per_vec, e = i - v * per_vec;
+                        const int unit = e / (kRecord / 16), line = e - unit * (kRecord / 16);  // 16-byte line of the token's record
+                        uint8_t* rec = act_smem + (size_t)unit * kRecord4;
+                        const uint32_t wv[4] = {got[j].x, got[j].y, got[j].z, got[j].w};
+                        if (line < 18) {
+                            // code words (lines 0..15) and steps (16, 17, which follow the 64 code words at
+                            // the same pitch): word by word, sixteen bytes apart
+                            uint32_t* dst = (uint32_t*)rec + 16 * line + v;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) dst[4 * q] = wv[q];
+                        } else {
+                            // slice sums (lines 18, 19) and group sums (20): int16 by int16, eight bytes apart
+                            uint16_t* dst = (uint16_t*)(rec + (line < 20 ? 1152 + 64 * (line - 18) : 1280)) + v;
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) dst[4 * q] = (uint16_t)(wv[q >> 1] >> (16 * (q & 1)));
+                        }
+                    }
+                }
+            }
+            consumer_sync<kConsumers>();
         } else {
             const size_t src_bytes = (size_t)p.units * kRecord;
             const int per_vec = (int)(src_bytes / 16), total = p.act_vectors * per_vec;
@@ -1364,12 +1561,19 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                         const uintptr_t first = (uintptr_t)sg.scale[my_s] + (uintptr_t)(lr0 * row_scales * 2);
                         sc = (const uint16_t*)(stage + (size_t)p.subs * p.sub_main_bytes + (size_t)my_s * p.sub_scale_bytes + (first & 15)) + (size_t)my_su * p.scales_per_unit;
                     }
-                    const uint8_t* a0 = act_smem + (size_t)sg.act[my_s] * p.act_bytes + (size_t)my_u * kRecord;
+                    if constexpr (MODE == RQ_ACT_INT8 && T == 4) {
+                        float v4[4];
+                        item_dot_tok4<TYPE>(w, sc, act_smem + (size_t)my_u * kRecord4, my_h, my_u, v4);
 #pragma unroll
-                    for (int t = 0; t < T; ++t) {
-                        const uint8_t* ar = a0 + t * p.act_bytes;
-                        if (MODE == RQ_ACT_INT8) areg.load(ar, my_h);
-                        part[t * stage_items + tid] = item_dot<TYPE, MODE>(w, sc, ar, areg, my_h, my_u);
+                        for (int t = 0; t < 4; ++t) part[t * stage_items + tid] = v4[t];
+                    } else {
+                        const uint8_t* a0 = act_smem + (size_t)sg.act[my_s] * p.act_bytes + (size_t)my_u * kRecord;
+#pragma unroll
+                        for (int t = 0; t < T; ++t) {
+                            const uint8_t* ar = a0 + t * p.act_bytes;
+                            if (MODE == RQ_ACT_INT8) areg.load(ar, my_h);
+                            part[t * stage_items + tid] = item_dot<TYPE, MODE>(w, sc, ar, areg, my_h, my_u);
+                        }
                     }
                 }
                 // this warp is done with the stage's weights: the producer may refill the slot
@@ -1448,6 +1652,8 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     } else {
         t = (p.tokens >= 2 && 4 * p.act_bytes <= 40 * 1024) ? 4 : 1;
         p.act_vectors = t;
+        // four int8 tokens are staged interleaved, kRecord4 bytes per unit: a quarter of that per vector
+        if (MODE == RQ_ACT_INT8 && t == 4) p.act_bytes = ((size_t)p.units * (kRecord4 / 4) + 127) & ~(size_t)127;
     }
     // single-token INT8 launches whose sub-rows all read vector 0 keep the activations in registers
     p.act_regs = (MODE == RQ_ACT_INT8 && t == 1 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr) ? 1 : 0;
