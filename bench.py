@@ -170,7 +170,7 @@ def run_reference(args):
                          "sample": f"{args.steps} decode layers (7 matvecs, {LAYER_BYTES} algorithmic bytes each) after {max(args.warmup, 1)} warm-up"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(args, layers, cpu=False):
@@ -380,7 +380,7 @@ def run_ours(args):
         line["cpu_baseline"] = {"value": LAYER_BYTES / cpu_s / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
                                 "ms_per_step": 1e3 * cpu_s,
                                 "sample": f"{reps} passes of one decode layer (layer 0 of the stack, same blocks and activations) through oracle/rq_oracle.c"}
-    print(json.dumps(line), flush=True)
+    emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -424,8 +424,8 @@ def run_case(args):
         torch.cuda.synchronize()
         us = 1e3 * e0.elapsed_time(e1) / args.steps
         flops = 2.0 * rows * cols * tokens
-        print(json.dumps({"case": args.case, "entry": "rq_matmul", "us_per_call": us, "TFLOPs_useful": flops / us / 1e6, "TFLOPs_issued_fp16": 3 * flops / us / 1e6,
-                          "calls": args.steps, "weight_copies": args.layers}), flush=True)
+        emit({"case": args.case, "entry": "rq_matmul", "us_per_call": us, "TFLOPs_useful": flops / us / 1e6, "TFLOPs_issued_fp16": 3 * flops / us / 1e6,
+                          "calls": args.steps, "weight_copies": args.layers})
         ctx.check()
         return
     ctx.matvec(ws[0], x, y, act_mode=mode, step=32, stream=stream)
@@ -454,8 +454,8 @@ def run_case(args):
     per, stride = {rq.Q4_K: (256, 144), rq.Q6_K: (256, 210), rq.Q8_0: (32, 34), rq.Q4_0: (32, 18)}[t]
     nbytes = rows * (cols // per) * stride + 4 * cols * tokens + 4 * rows * tokens
     peak, kind = measured_peak_gbs()
-    print(json.dumps({"case": args.case, "us_per_launch": us, "GBps": nbytes / us / 1e3, "frac_of_hbm": nbytes / us / 1e3 / peak,
-                      "peak": f"{peak} ({kind})", "algorithmic_bytes": nbytes, "launches": args.steps, "weight_copies": args.layers, "graph": bool(args.graph)}), flush=True)
+    emit({"case": args.case, "us_per_launch": us, "GBps": nbytes / us / 1e3, "frac_of_hbm": nbytes / us / 1e3 / peak,
+                      "peak": f"{peak} ({kind})", "algorithmic_bytes": nbytes, "launches": args.steps, "weight_copies": args.layers, "graph": bool(args.graph)})
 
 
 def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
@@ -644,7 +644,23 @@ def run_other_configs(ctx, rq, torch, device):
     return out
 
 
+RESULT_OUT = None
+
+
+def emit(line):
+    """The run's one JSON line, on the process's original standard output."""
+    out = RESULT_OUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main():
+    # Standard output carries the JSON line and nothing else: libraries that write to file descriptor 1 on their
+    # own (NCCL prints its version there) are sent to standard error for the whole run.
+    global RESULT_OUT
+    sys.stdout.flush()
+    RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default=None, help="profile one matvec shape, e.g. q4k:14336x4096:int8")
     ap.add_argument("--gpus", type=int, default=1)
