@@ -75,6 +75,14 @@ int rq_weight_prepare_device(rq_ctx* ctx, int ggml_type, const void* dev_blocks,
                              rq_weight** out, void* stream);
 /* Writes the weight back as GGUF blocks into host memory (round-trip check of the layout). */
 int rq_weight_export(rq_ctx* ctx, const rq_weight* w, void* host_blocks);
+/* The load-time re-encode of a bound tensor: decodes `src` with its own decoder and encodes it as
+ * `target_type` (RQ_Q8_0) with the load kernel's encoder, byte-exact with what the reference's
+ * recipe_model_load writes (requantize_bound recipe.rs:22373-22431, emit_requantize :8016-8127).
+ * This is what `.int(8)` does to a tensor bound in a format it does not keep. `src` stays valid. */
+int rq_weight_requantize(rq_ctx* ctx, const rq_weight* src, int target_type, rq_weight** out, void* stream);
+/* 1 when `.int(8)` dots a lone tensor of this type as stored (Q8_0, Q4_K), 0 when the reference
+ * re-encodes it to Q8_0 at load first (Q6_K, Q4_0): finish_int_sums, recipe.rs:22345-22369. */
+int rq_int8_keeps(int ggml_type);
 void rq_weight_free(rq_ctx* ctx, rq_weight* w);
 int64_t rq_weight_rows(const rq_weight* w);
 int64_t rq_weight_cols(const rq_weight* w);
@@ -98,6 +106,10 @@ int rq_quantize(rq_ctx* ctx, int ggml_type, const float* dev_values, int64_t cou
  * (amd-nv-cpu.ll:2242-2300 -> :1231-2241) and packed_rows_body mode 0 (amd-nv-cpu.ll:3136-3508).
  * The reference's channel-major planes are x_k_stride = tokens, x_t_stride = 1.
  * act_mode RQ_ACT_INT8 takes step 32 or 256 (recipe.model.int.step); FLOAT ignores step.
+ * RQ_ACT_INT8 dots the blocks of `w` as they are stored. The reference does that for Q8_0 and Q4_K
+ * only; a lone Q6_K or Q4_0 tensor under `.int(8)` is first re-encoded to Q8_0 (rq_int8_keeps,
+ * rq_weight_requantize): pass the re-encoded weight to reproduce recipe's `.int(8)`, the stored one
+ * for the direct dot over the file's own blocks (fewer bytes, a different rounding of the weights).
  * Enqueues on `stream` (a cudaStream_t, may be NULL) and returns without synchronising. */
 int rq_matvec(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
               float* y, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);

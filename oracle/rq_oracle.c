@@ -430,6 +430,56 @@ int rqo_quantize(int type, const float* values, int64_t count, uint8_t* blocks, 
     return 0;
 }
 
+/* -------------------------------------------- load-time re-encode of a bound tensor (a20) */
+
+/* One 32-value block through the load kernel's encoder, emit_requantize recipe.rs:8016-8127.
+ * The extreme is the FIRST value of strictly largest magnitude, found from a running value
+ * that starts at zero (:8066-8081); Q8_0 (:8141-8155): scale = |extreme| / 127, inverse =
+ * 1 / scale (0 when the scale is 0), code = fptosi(q + 0.5) or fptosi(q - 0.5) by the sign
+ * of q = v * inverse (half away from zero by truncation, NOT f32::round), clamped to
+ * [-128, 127]; the scale is stored with fptrunc (round to nearest even). */
+static void requant_block_q8_0(const float* v, uint8_t* out) {
+    float e = 0.0f;
+    for (int i = 0; i < 32; ++i) if (fabsf(v[i]) > fabsf(e)) e = v[i];
+    float ext = fabsf(e);
+    float scale = ext / 127.0f;
+    float inverse = scale == 0.0f ? 0.0f : 1.0f / scale;
+    put_half(out, scale);
+    for (int i = 0; i < 32; ++i) {
+        float q = v[i] * inverse;
+        float r = q >= 0.0f ? q + 0.5f : q + -0.5f;
+        int32_t code = (int32_t)r; /* fptosi: toward zero */
+        if (code < -128) code = -128;
+        if (code > 127) code = 127;
+        out[2 + i] = (uint8_t)(int8_t)code;
+    }
+}
+
+typedef struct { int type; const uint8_t* blocks; int64_t count; uint8_t* out; } requant_ctx;
+static void requant_span(void* p, int64_t first, int64_t last, int worker, int workers) {
+    (void)worker; (void)workers;
+    requant_ctx* c = (requant_ctx*)p;
+    int per = rqo_block_values(c->type), bytes = rqo_block_bytes(c->type);
+    float v[32];
+    for (int64_t blk = first; blk < last; ++blk) {
+        for (int i = 0; i < 32; ++i) {
+            /* a tail past the weight's end contributes zero (recipe.rs:8049-8063) */
+            int64_t at = blk * 32 + i;
+            v[i] = at < c->count ? block_value(c->type, c->blocks + (at / per) * bytes, (int)(at % per)) : 0.0f;
+        }
+        requant_block_q8_0(v, c->out + blk * 34);
+    }
+}
+/* finish_int_sums + requantize_bound (recipe.rs:22345-22431): a tensor bound in a format that
+ * `.int(8)` does not keep (anything but Q8_0, Q4_K and the Q4_K + Q6_K mix) is decoded by its
+ * source decoder and encoded again as Q8_0 by the load kernel, once, before any matvec. */
+int rqo_requantize_q8_0(int type, const uint8_t* blocks, int64_t count, uint8_t* out, int threads) {
+    if (!rqo_block_values(type) || count < 0) return -1;
+    requant_ctx c = {type, blocks, count, out};
+    run_spans((count + 31) / 32, threads, requant_span, &c);
+    return 0;
+}
+
 /* ----------------------------------------------------- int8 activation records (a10) */
 
 #define RQO_RECORD 36 /* fp32 step + 32 int8 codes: build.rs:332-337 */

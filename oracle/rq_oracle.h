@@ -47,6 +47,11 @@ int rqo_dequantize(int type, const uint8_t* blocks, int64_t count, float* out, i
 /* Quantise `count` fp32 values (padded with zeros to whole blocks) into blocks. */
 int rqo_quantize(int type, const float* values, int64_t count, uint8_t* blocks, int threads);
 
+/* The load-time re-encode `.int(8)` applies to a tensor bound in a format it does not keep
+ * (a lone Q6_K or Q4_0 tensor): decode with the source decoder, encode as Q8_0 with the load
+ * kernel's encoder (recipe.rs:22345-22431, :8016-8127). out: ceil(count / 32) * 34 bytes. */
+int rqo_requantize_q8_0(int type, const uint8_t* blocks, int64_t count, uint8_t* out, int threads);
+
 /* int8 activation records (36 bytes each: fp32 d, 32 codes) for one column of `terms`
  * inputs read at x[k * x_stride]; `step` is 32 or 256. ll:1381-1517, CPU wave width 1. */
 int rqo_quantize_activations(const float* x, int64_t x_stride, int64_t terms, int step, uint8_t* records);

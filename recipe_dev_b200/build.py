@@ -20,7 +20,6 @@ OBJ = PKG / "build"
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", f"-I{ROOT / 'include'}", f"-I{CSRC}"]
-COMMON += os.environ.get("RQ_NVCC_FLAGS", "").split()  # e.g. -DRQ_TRACE for a development build
 # per-file extras: the weight quantisers must not contract a*b+c into one rounding
 EXTRA = {"rq_quantize.cu": ["--fmad=false"]}
 

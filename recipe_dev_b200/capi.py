@@ -43,6 +43,8 @@ def _declare(lib) -> None:
         "rq_weight_prepare": (i32, [p, i32, p, i64, i64, i64, i64, C.POINTER(p)]),
         "rq_weight_prepare_device": (i32, [p, i32, p, i64, i64, C.POINTER(p), p]),
         "rq_weight_export": (i32, [p, p, p]),
+        "rq_weight_requantize": (i32, [p, p, i32, C.POINTER(p), p]),
+        "rq_int8_keeps": (i32, [i32]),
         "rq_weight_free": (None, [p, p]),
         "rq_weight_rows": (i64, [p]),
         "rq_weight_cols": (i64, [p]),
@@ -208,6 +210,16 @@ class Context:
         out = C.c_void_p()
         _check(self.lib.rq_weight_prepare_device(self.handle, ggml_type, _ptr(dev_blocks), rows, cols, C.byref(out), _stream(stream)))
         return Weight(self, out.value)
+
+    def requantize(self, w: Weight, target_type: int = Q8_0, stream=None) -> Weight:
+        """The load-time re-encode `.int(8)` applies to a tensor it does not keep (a lone Q6_K / Q4_0 one)."""
+        out = C.c_void_p()
+        _check(self.lib.rq_weight_requantize(self.handle, w.handle, target_type, C.byref(out), _stream(stream)))
+        return Weight(self, out.value)
+
+    def int8_weight(self, w: Weight, stream=None) -> Weight:
+        """The weight recipe's `.int(8)` dots: `w` itself when the format is kept, else its Q8_0 re-encode."""
+        return w if self.lib.rq_int8_keeps(w.type) else self.requantize(w, Q8_0, stream)
 
     def export(self, w: Weight) -> np.ndarray:
         n = w.rows * (w.cols // block_values(w.type)) * block_bytes(w.type)

@@ -1,0 +1,54 @@
+// Per-value decode of a stored weight from its device planes, shared by the dequantiser and the
+// load-time re-encoder. Every fp32 step is a separate rounded operation (__fmul_rn / __fsub_rn never
+// contract), which makes the result bit-equal to the reference's f64 unpacking rounded to fp32
+// (dequant_scalar / dequant_q45k / dequant_q6k, recipe.rs:3687-3833): d*sc, dmin*m and step*q are
+// exact in fp32, and the one inexact step, the final subtract, rounds the same exact difference.
+#pragma once
+#include "rq_internal.cuh"
+
+// Value i (row-major over rows x cols) of a weight whose planes are main_plane / scale_plane.
+template <int TYPE>
+__device__ __forceinline__ float rq_decode_value(const uint8_t* __restrict__ main_plane, const uint16_t* __restrict__ scale_plane, int64_t i, int64_t cols) {
+    float value;
+    if (TYPE == RQ_Q4_K) {
+        int64_t b = i >> 8;
+        int v = (int)(i & 255), sub = v >> 5, within = v & 31;
+        const uint8_t* blk = main_plane + b * 144;
+        const uint32_t* hdr = (const uint32_t*)blk;
+        uint32_t dd = hdr[0];
+        int sc, mn;
+        rq_q4k_scale_min(hdr[1], hdr[2], hdr[3], sub, sc, mn);
+        int q = (blk[16 + (sub >> 1) * 32 + within] >> ((sub & 1) * 4)) & 15;
+        float step = __fmul_rn(rq_h2f((uint16_t)(dd & 0xffff)), (float)sc);
+        float base = __fmul_rn(rq_h2f((uint16_t)(dd >> 16)), (float)mn);
+        value = __fsub_rn(__fmul_rn(step, (float)q), base);
+    } else if (TYPE == RQ_Q6_K) {
+        int64_t b = i >> 8;
+        int v = (int)(i & 255), chunk = v >> 7, local = v & 127, group = local >> 5, within = local & 31;
+        const uint8_t* body = main_plane + b * 208;
+        int lo = (body[64 * chunk + 32 * (group & 1) + within] >> (4 * (group >> 1))) & 15;
+        int hi = (body[128 + 32 * chunk + within] >> (2 * group)) & 3;
+        int code = (lo | (hi << 4)) - 32;
+        int scale = (int8_t)body[192 + 8 * chunk + 2 * group + (within >> 4)];
+        float scaled = __fmul_rn(rq_h2f(scale_plane[b]), (float)scale);
+        value = __fmul_rn(scaled, (float)code);
+    } else if (TYPE == RQ_Q8_0) {
+        int64_t at = i;
+        if (rq_plane_permuted(TYPE, cols)) {
+            const int64_t row = i / cols, off = i - row * cols;  // one byte per value
+            at = row * cols + ((rq_plane_chunk(TYPE, off >> 4) << 4) | (off & 15));
+        }
+        value = __fmul_rn((float)(int8_t)main_plane[at], rq_h2f(scale_plane[i >> 5]));
+    } else {
+        int64_t b = i >> 5;
+        int v = (int)(i & 31);
+        int64_t at = b * 16 + (v & 15);
+        if (rq_plane_permuted(TYPE, cols)) {
+            const int64_t row_bytes = cols >> 1, row = at / row_bytes, off = at - row * row_bytes;
+            at = row * row_bytes + ((rq_plane_chunk(TYPE, off >> 4) << 4) | (off & 15));
+        }
+        int code = ((main_plane[at] >> ((v >> 4) * 4)) & 15) - 8;
+        value = __fmul_rn((float)code, rq_h2f(scale_plane[b]));
+    }
+    return value;
+}

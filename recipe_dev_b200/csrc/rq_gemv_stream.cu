@@ -23,9 +23,6 @@
 
 #include "rq_internal.cuh"
 
-#ifdef RQ_TRACE
-unsigned long long* rq_trace_buffer();
-#endif
 
 namespace {
 
@@ -82,15 +79,7 @@ struct StreamParams {
     int64_t yn, yt;
     int tokens;
     int* error_flag;
-#ifdef RQ_TRACE
-    unsigned long long* trace;  // [grid][64] time stamps of the consumer thread 0 (development builds only)
-#endif
 };
-#ifdef RQ_TRACE
-#define RQ_STAMP(i) do { if (tid == 0 && p.trace && (i) < 64) p.trace[(size_t)blockIdx.x * 64 + (i)] = global_ns(); } while (0)
-#else
-#define RQ_STAMP(i) do { } while (0)
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)); }
@@ -998,7 +987,6 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
     __shared__ float cross_sum[kMaxStages + 1][8][NW];
     __shared__ int cross_count[kMaxStages + 1];
 
-    RQ_STAMP(0);
     // Programmatic dependent launch: the next kernel in the stream may start its own prologue now.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int batch_row = p.plan_count > 1 ? (int)blockIdx.y : 0;
@@ -1088,9 +1076,6 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                         }
                     }
                     mbar_expect_tx(bar, total);
-#ifdef RQ_TRACE
-                    if (p.trace && st < 16 && k == 0) p.trace[(size_t)blockIdx.x * 64 + 48 + st] = global_ns();
-#endif
                     const int64_t piece_off = (int64_t)k * p.piece_rows * row_bytes;
                     for (int s = 0; s < subs; ++s) {
                         if (main_bytes) bulk_g2s(dst + (size_t)s * p.sub_main_bytes + piece_off, sg.main[s] + lr0 * row_bytes + piece_off, main_bytes, bar, policy);
@@ -1174,11 +1159,8 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             for (int i = tid; i < words; i += kConsumers) dst[i] = src[i];
         };
         if (direct) stage_table();
-        RQ_STAMP(41);
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        RQ_STAMP(44);
         if (!direct) stage_table();
-        RQ_STAMP(43);
         // A thread's item is the same (half, sub-row, row slot, unit) in every stage: thread t takes
         // item t of the stage's grid [half][sub-row][row][unit]. Halves are outermost so that a warp
         // works on one half of adjacent units: no divergence, no bank conflicts.
@@ -1204,11 +1186,8 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             // launches) from records this CTA makes of x right here, while its first weights fly.
             if (p.fuse_step) {
                 quantise_to_smem<kThreads>(p.x, p.sk, p.cols, p.fuse_step, act_smem, tid);
-                RQ_STAMP(45);
                 __syncthreads();  // with the producer warp: records complete, barriers initialised
-                RQ_STAMP(46);
                 if (act_owner) areg.load(act_smem + (size_t)my_u * kRecord, my_h);
-                RQ_STAMP(47);
                 if (blockIdx.x == 0 && p.act_out) {
                     const uint4* src = (const uint4*)act_smem;
                     uint4* dst = (uint4*)p.act_out;
@@ -1247,9 +1226,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 }
                 v0 = v; k0 = k;
             }
-            RQ_STAMP(45);
             consumer_sync<kConsumers>();
-            RQ_STAMP(46);
             {
                 // the sums of every 16-input slice of every vector, dealt flat over the threads
                 const int per_vec = p.cols >> 4, slices = p.act_vectors * per_vec;
@@ -1330,7 +1307,6 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             consumer_sync<kConsumers>();
         }
         if (!fused) __syncthreads();  // the producer has initialised the barriers; table and plan counts are in place
-        RQ_STAMP(1);
         // counts: from the launch, or (planned launches) from the device-side plan, never above the launch's
         if (p.plan) { n_segments = min(plan_counts[0], p.n_segments); subs = min(plan_counts[1], p.subs); }
         split_rows(p.plan ? min((int64_t)plan_counts[2], p.rows) : p.rows);
@@ -1400,15 +1376,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             const size_t my_off = (size_t)row_in_pass * row_bytes + (size_t)my_u * p.unit_bytes;
             const size_t pass_bytes = (size_t)rows_per_pass * row_bytes;
             const bool writer = (lane & (group - 1)) == 0;
-#ifdef RQ_TRACE
-            int trace_st = 0;
-#endif
             while (true) {
                 if (!mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
                 if (dead) break;
-#ifdef RQ_TRACE
-                RQ_STAMP(2 + 2 * trace_st);
-#endif
                 const int4 info = stage_info[slot];  // rows, segment, first local row, offset of the first d
                 if (info.x == 0) break;               // the producer has no more rows for this CTA
                 const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
@@ -1478,10 +1448,6 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                     }
                     if (++cross_buf > kMaxStages) cross_buf = 0;
                 }
-#ifdef RQ_TRACE
-                RQ_STAMP(3 + 2 * trace_st);
-                ++trace_st;
-#endif
             }
         } else if (R == 2) {
             // two-row instantiations serve the warp scheme only
@@ -1550,7 +1516,6 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 const int nr = (int)(stop - r);
                 const int64_t lr0 = r - sg.row_begin;
                 if (!dead && !mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
-                RQ_STAMP(2 + 3 * st);
                 const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
                 float* part = partial + (size_t)(st & 1) * T * stage_items;
                 if (tid < items_cap && my_lr < nr && my_s < subs) {
@@ -1580,9 +1545,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[slot]);
                 if (++slot == p.stages) { slot = 0; phase ^= 1; }
-                RQ_STAMP(3 + 3 * st);
                 consumer_sync<kConsumers>();
-                RQ_STAMP(4 + 3 * st);
                 reduce_rows(part, sg, nr, lr0, tid >> 3, kSweep);
                 r = stop;
             }
@@ -1750,22 +1713,6 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
 
 }  // namespace
 
-#ifdef RQ_TRACE
-// development builds: a device buffer of time stamps, read back with rq_trace_read()
-static unsigned long long* g_trace = nullptr;
-static int g_trace_launch = 0;
-// sixteen regions of 512 CTAs x 64 stamps: consecutive launches write consecutive regions
-unsigned long long* rq_trace_buffer() {
-    if (!g_trace) { cudaMalloc(&g_trace, 16 * 512 * 64 * 8); cudaMemset(g_trace, 0, 16 * 512 * 64 * 8); }
-    return g_trace + (size_t)((g_trace_launch++) % 16) * 512 * 64;
-}
-extern "C" int rq_trace_reset() { g_trace_launch = 0; rq_trace_buffer(); g_trace_launch = 0; return (int)cudaMemset(g_trace, 0, 16 * 512 * 64 * 8); }
-extern "C" int rq_trace_read(unsigned long long* host, int ctas) {
-    cudaDeviceSynchronize();
-    if (!g_trace) return -1;
-    return (int)cudaMemcpy(host, g_trace, (size_t)ctas * 64 * 8, cudaMemcpyDeviceToHost);
-}
-#endif
 
 // Launches the streaming kernel over a segment table. `table` is device memory, or null with the
 // segments in `inline_seg` (at most RQ_INLINE_SEGMENTS, one sub-row each).
@@ -1785,9 +1732,6 @@ int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table
     p.x = x; p.sk = sk; p.st = st; p.act = act; p.yn = yn; p.yt = yt; p.tokens = tokens;
     p.fuse_step = act_mode == RQ_ACT_INT8 ? fuse_step : 0; p.act_out = act_out;
     p.error_flag = ctx->error_flag;
-#ifdef RQ_TRACE
-    p.trace = rq_trace_buffer();
-#endif
     switch (type) {
         case RQ_Q4_K: p.unit_bytes = 144; p.scales_per_unit = 0; break;
         case RQ_Q6_K: p.unit_bytes = 208; p.scales_per_unit = 1; break;
@@ -1819,9 +1763,6 @@ int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* pla
     p.rows = max_rows; p.cols = (int)cols; p.units = (int)(cols / 256);
     p.x = x; p.sk = sk; p.st = st; p.yn = yn; p.yt = yt; p.tokens = 1;
     p.error_flag = ctx->error_flag;
-#ifdef RQ_TRACE
-    p.trace = rq_trace_buffer();
-#endif
     switch (type) {
         case RQ_Q4_K: p.unit_bytes = 144; p.scales_per_unit = 0; break;
         case RQ_Q6_K: p.unit_bytes = 208; p.scales_per_unit = 1; break;

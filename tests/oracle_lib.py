@@ -37,6 +37,7 @@ class Oracle:
         lib.rqo_qround.argtypes = [C.c_float]
         lib.rqo_dequantize.argtypes = [i32, p, i64, p, i32]
         lib.rqo_quantize.argtypes = [i32, p, i64, p, i32]
+        lib.rqo_requantize_q8_0.argtypes = [i32, p, i64, p, i32]
         lib.rqo_quantize_activations.argtypes = [p, i64, i64, i32, p]
         lib.rqo_matvec.argtypes = [i32, p, i64, i64, p, i64, i32, p, i64, i32, i32, i32]
         for name in ("rqo_exp", "rqo_tanh", "rqo_sigmoid", "rqo_silu"):
@@ -63,6 +64,19 @@ class Oracle:
         out = np.empty(count, dtype=np.float32)
         assert self.lib.rqo_dequantize(t, b.ctypes.data, count, out.ctypes.data, THREADS) == 0
         return out
+
+    def requantize_q8_0(self, t: int, blocks: np.ndarray) -> np.ndarray:
+        """The load kernel's Q8_0 re-encode of a tensor stored as type t (what `.int(8)` dots for Q6_K / Q4_0)."""
+        b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        per, stride = GEOMETRY[t]
+        count = b.size // stride * per
+        out = np.empty(count // 32 * 34, dtype=np.uint8)
+        assert self.lib.rqo_requantize_q8_0(t, b.ctypes.data, count, out.ctypes.data, THREADS) == 0
+        return out
+
+    def int8_blocks(self, t: int, blocks: np.ndarray):
+        """(type, blocks) that recipe's `.int(8)` dots for a lone tensor: kept for Q8_0 / Q4_K, re-encoded to Q8_0 otherwise."""
+        return (t, blocks) if t in (Q8_0, Q4_K) else (Q8_0, self.requantize_q8_0(t, blocks))
 
     def activation_records(self, x: np.ndarray, step: int) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=np.float32)
