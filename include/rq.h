@@ -5,6 +5,15 @@
  * quantised contraction nodes. Plain pointers and sizes only; every entry point returns
  * 0 on success or a negative rq_status, and rq_last_error() gives thread-local text.
  * The library owns prepared weights and its context; the caller owns every other buffer.
+ *
+ * Streams. The device-pointer entry points enqueue on the caller's stream and return without
+ * synchronising. A context keeps work areas (the int8 activation records, the batched product's
+ * activation image, an expert bank's plans) that successive calls reuse: calls on ONE stream are
+ * ordered by the stream; when a call arrives on a different stream than the previous call on the
+ * context, the library makes the new stream wait for the work enqueued on the previous one (an
+ * event), so the two never overlap on the work areas. Inside a stream capture no such event is
+ * recorded: calls captured into one graph must share one stream. A stream handed to a call must
+ * stay alive until the next call on the context. One host thread at a time per context.
  * No entry point aborts on bad arguments, none falls back to the CPU.
  *
  * Each declaration names the reference interface (nm-z/recipe-dev, file:line) it replaces.
@@ -27,7 +36,8 @@ enum rq_status {
     RQ_ERR_CUDA = -2,        /* a CUDA runtime call failed; text names it */
     RQ_ERR_ALLOC = -3,       /* device or host allocation failed */
     RQ_ERR_UNSUPPORTED = -4, /* valid request this build does not serve */
-    RQ_ERR_LIMIT = -5        /* size beyond a documented fixed maximum */
+    RQ_ERR_LIMIT = -5,       /* size beyond a documented fixed maximum */
+    RQ_ERR_WAIT = -6         /* rq_check: a kernel gave up one of its bounded waits; text names which */
 };
 
 /* GGML tensor types on this path (recipe.rs:9925-9962). */
@@ -56,6 +66,20 @@ void rq_destroy(rq_ctx* ctx);
  * bounded waits since the last check (the device code never traps and never spins unbounded;
  * the reference's hand PTX waits return a status the same way, barrier.ptx:1653-1748). */
 int rq_check(rq_ctx* ctx);
+/* How long a kernel of this context waits on a barrier (a copy that has not landed, a ring slot, a peer's
+ * flag) before it records a code, stops waiting and returns: 2 s unless set. 1 us .. 60 s. */
+int rq_set_wait_limit(rq_ctx* ctx, uint64_t nanoseconds);
+/* Runs the give-up path on purpose: one warp waits, with the context's limit (which must have been set to
+ * 100 ms or less), on a barrier nothing arrives on, gives up and returns; the next rq_check reports
+ * RQ_ERR_WAIT. No fault, no trap, no endless loop: the kernel ends by itself after the limit. */
+int rq_wait_selftest(rq_ctx* ctx, void* stream);
+/* Sizes the context's work areas ahead of time for weights of up to max_rows x max_cols and calls of up
+ * to max_tokens tokens. Growing a work area frees and allocates device memory, which synchronises the
+ * device: a call wider than anything seen or reserved so far does that on demand, inside the call, and
+ * cannot do it while its stream is being captured. After rq_reserve no matvec / matmul call within the
+ * reserved sizes allocates, frees or synchronises. (The reference sizes its arenas once, at place():
+ * recipe.rs:24795-24801.) */
+int rq_reserve(rq_ctx* ctx, int64_t max_rows, int64_t max_cols, int max_tokens);
 /* Thread-local text of the last failure on the calling thread (RecipeError, recipe.rs:13416-13433). */
 const char* rq_last_error(void);
 /* Block geometry of a type: values per block and bytes per block (QUANTIZATIONS, recipe.rs:15811-15822). 0 if unknown. */
@@ -144,8 +168,10 @@ int rq_matvec_multi_host(rq_ctx* ctx, int n, const rq_weight* const* ws, const f
 /* The INT8 product of one contiguous column (x[cols] -> y[rows]) for callers that cannot allocate.
  * No counterpart in the reference: there the host owns every arena and kernels never allocate, so
  * the question does not arise; here rq_matvec grows a scratch buffer with cudaMalloc on demand.
- * This entry point calls no allocating routine at all. Its activation scratch is a fixed array in
- * the library's device image, held by every GPU that loads the library until the process exits.
+ * After one warm-up call per device (which looks up the array's address and lets the runtime load
+ * the kernels), no call of this entry point allocates, frees or synchronises. Its activation scratch
+ * is a fixed array in the library's device image, held by every GPU that loads the library until
+ * the process exits; the context's own scratch is not touched.
  * Who needs it: a host that has given all device memory to its own pre-planned arenas, and a decode
  * loop that must never stall on the device-wide synchronisation an allocation or free brings.
  *  - at most RQ_STATIC_MAX_COLS inputs per row; wider weights are refused with RQ_ERR_LIMIT;

@@ -38,6 +38,9 @@ def _declare(lib) -> None:
         "rq_destroy": (None, [p]),
         "rq_last_error": (C.c_char_p, []),
         "rq_check": (i32, [p]),
+        "rq_reserve": (i32, [p, i64, i64, i32]),
+        "rq_set_wait_limit": (i32, [p, C.c_uint64]),
+        "rq_wait_selftest": (i32, [p, p]),
         "rq_block_values": (i32, [i32]),
         "rq_block_bytes": (i32, [i32]),
         "rq_weight_prepare": (i32, [p, i32, p, i64, i64, i64, i64, C.POINTER(p)]),
@@ -197,6 +200,16 @@ class Context:
     def check(self) -> None:
         """Synchronises and raises if a kernel gave up a bounded wait since the last check."""
         _check(self.lib.rq_check(self.handle))
+
+    def reserve(self, max_rows: int, max_cols: int, max_tokens: int) -> None:
+        """Sizes the work areas ahead of time, so that no later call within these sizes allocates or synchronises."""
+        _check(self.lib.rq_reserve(self.handle, max_rows, max_cols, max_tokens))
+
+    def set_wait_limit(self, nanoseconds: int) -> None:
+        _check(self.lib.rq_set_wait_limit(self.handle, nanoseconds))
+
+    def wait_selftest(self, stream=None) -> None:
+        _check(self.lib.rq_wait_selftest(self.handle, _stream(stream)))
 
     # ---- weights ----
     def weight_from_host(self, ggml_type: int, blocks: np.ndarray, rows: int, cols: int, row_first: int = 0, row_count: int | None = None) -> Weight:

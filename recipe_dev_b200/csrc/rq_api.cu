@@ -53,12 +53,14 @@ extern "C" int rq_init(int device, rq_ctx** out) {
     memset(ctx, 0, sizeof(*ctx));
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
+    ctx->wait_limit_ns = 2000000000ull;
     cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete ctx; return rq_fail(RQ_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
     e = cudaMalloc(&ctx->error_flag, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->error_flag, 0, sizeof(int));
     if (e == cudaSuccess) e = cudaMallocHost(&ctx->pin_flag, sizeof(int));
     if (e == cudaSuccess) *ctx->pin_flag = 0;
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->work_event, cudaEventDisableTiming);
     if (e != cudaSuccess) { cudaStreamDestroy(ctx->stream); delete ctx; return rq_fail(RQ_ERR_CUDA, "error flag: %s", cudaGetErrorString(e)); }
     *out = ctx;
     return RQ_OK;
@@ -74,14 +76,32 @@ extern "C" void rq_destroy(rq_ctx* ctx) {
     if (ctx->stage_y) cudaFree(ctx->stage_y);
     if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
     if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
+    if (ctx->work_event) cudaEventDestroy(ctx->work_event);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
 
-int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes) {
-    if (bytes <= ctx->act_scratch_bytes) return RQ_OK;
-    // grow geometrically; the old buffer may still be read by kernels in flight
-    size_t want = bytes + bytes / 2 + 4096;
+int rq_order_work_areas(rq_ctx* ctx, cudaStream_t s) {
+    if (ctx->work_stream_set && ctx->work_stream != s) {
+        // The previous call's kernels may still read or write the work areas on their stream: this call's stream waits
+        // for everything enqueued there so far. Inside a stream capture nothing is recorded or waited for (an event
+        // cannot cross a capture's boundary): calls captured into one graph must share a stream.
+        cudaStreamCaptureStatus before = cudaStreamCaptureStatusNone, now = cudaStreamCaptureStatusNone;
+        const bool known = cudaStreamIsCapturing(ctx->work_stream, &before) == cudaSuccess && cudaStreamIsCapturing(s, &now) == cudaSuccess;
+        if (known && before == cudaStreamCaptureStatusNone && now == cudaStreamCaptureStatusNone) {
+            RQ_CUDA(cudaEventRecord(ctx->work_event, ctx->work_stream));
+            RQ_CUDA(cudaStreamWaitEvent(s, ctx->work_event, 0));
+        } else if (!known) {
+            cudaGetLastError();  // the earlier stream no longer exists: its work was finished or abandoned with it
+        }
+    }
+    ctx->work_stream = s;
+    ctx->work_stream_set = true;
+    return RQ_OK;
+}
+
+static int grow_act_scratch(rq_ctx* ctx, size_t want) {
+    // the old buffer may still be read by kernels in flight
     RQ_CUDA(cudaDeviceSynchronize());
     if (ctx->act_scratch) RQ_CUDA(cudaFree(ctx->act_scratch));
     ctx->act_scratch = nullptr;
@@ -93,6 +113,48 @@ int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes) {
     return RQ_OK;
 }
 
+int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes, cudaStream_t s) {
+    if (bytes > ctx->act_scratch_bytes) {
+        // grow geometrically, so that a run of slightly wider calls does not allocate every time
+        int rc = grow_act_scratch(ctx, bytes + bytes / 2 + 4096);
+        if (rc) return rc;
+    }
+    return rq_order_work_areas(ctx, s);
+}
+
+extern "C" int rq_reserve(rq_ctx* ctx, int64_t max_rows, int64_t max_cols, int max_tokens) {
+    if (!ctx) return rq_fail(RQ_ERR_INVALID, "rq_reserve: null context");
+    if (max_rows <= 0 || max_cols <= 0 || max_tokens <= 0 || max_cols > (int64_t)1 << 24 || max_rows > (int64_t)1 << 31 || max_tokens > 1 << 20)
+        return rq_fail(RQ_ERR_INVALID, "rq_reserve: max_rows=%lld max_cols=%lld max_tokens=%d out of range", (long long)max_rows, (long long)max_cols, max_tokens);
+    DeviceGuard guard(ctx->device);
+    // the int8 records of every token, or the batched product's activation image and split-K sums, whichever is larger
+    const int64_t cols32 = (max_cols + 255) / 256 * 256;
+    size_t want = rq_act_token_bytes(cols32) * (size_t)max_tokens;
+    const size_t mm = rq_matmul_scratch_bytes(ctx, max_rows, cols32, max_tokens);
+    if (mm > want) want = mm;
+    if (want <= ctx->act_scratch_bytes) return RQ_OK;
+    return grow_act_scratch(ctx, want);
+}
+
+static const char* wait_code_text(int code) {
+    switch (code) {
+        case 1: return "matvec producer: a ring slot never came free";
+        case 2: return "matvec producer: a copy it issued never landed";
+        case 3: return "matvec consumer: a stage never arrived";
+        case 4: return "matvec producer: an earlier copy of its window never landed";
+        case 11: return "batched product, staging warps: a stage never came free";
+        case 12: return "batched product, drain warps: the last product never finished";
+        case 13: return "batched product, issuing warp: a stage was never filled";
+        case 14: return "batched product, drain warps: an accumulator never filled";
+        case 15: return "batched product, issuing warp: an accumulator never came free";
+        case 16: return "batched product, copy warp: a stage never came free";
+        case 17: return "batched product: the activation sums never arrived";
+        case 21: return "wait self-test: the barrier nothing arrives on";
+        case 31: return "exchange: a peer's arrival flag never came";
+        default: return "unknown wait";
+    }
+}
+
 extern "C" int rq_check(rq_ctx* ctx) {
     if (!ctx) return rq_fail(RQ_ERR_INVALID, "rq_check: null context");
     DeviceGuard guard(ctx->device);
@@ -101,8 +163,48 @@ extern "C" int rq_check(rq_ctx* ctx) {
     RQ_CUDA(cudaMemcpy(&flag, ctx->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag) {
         cudaMemset(ctx->error_flag, 0, sizeof(int));
-        return rq_fail(RQ_ERR_CUDA, "a kernel gave up a bounded wait (code %d: 1 producer/empty, 2 drain, 3 consumer/full); its outputs are not valid", flag);
+        return rq_fail(RQ_ERR_WAIT, "a kernel gave up a bounded wait (code %d: %s); its outputs are not valid", flag, wait_code_text(flag));
     }
+    return RQ_OK;
+}
+
+extern "C" int rq_set_wait_limit(rq_ctx* ctx, uint64_t nanoseconds) {
+    if (!ctx) return rq_fail(RQ_ERR_INVALID, "rq_set_wait_limit: null context");
+    if (nanoseconds < 1000 || nanoseconds > 60000000000ull) return rq_fail(RQ_ERR_INVALID, "rq_set_wait_limit: %llu ns is outside 1 us .. 60 s", (unsigned long long)nanoseconds);
+    ctx->wait_limit_ns = nanoseconds;
+    return RQ_OK;
+}
+
+// One warp waits, with the context's limit, on a barrier that nothing ever arrives on, gives up, records code 21 and
+// returns: the same wait, the same give-up path and the same error word as the matvec and batched kernels use.
+__global__ void rq_wait_selftest_kernel(int* error_flag, unsigned long long limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&bar);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(1u));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long t0, now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+        bool done = false;
+        while (!done) {
+            uint32_t ok;
+            asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(addr), "r"(0u) : "memory");
+            if (ok) break;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (now - t0 > limit_ns) { atomicExch(error_flag, 21); done = true; }
+        }
+    }
+}
+
+extern "C" int rq_wait_selftest(rq_ctx* ctx, void* stream) {
+    if (!ctx) return rq_fail(RQ_ERR_INVALID, "rq_wait_selftest: null context");
+    if (ctx->wait_limit_ns > 100000000ull) return rq_fail(RQ_ERR_INVALID, "rq_wait_selftest: set a wait limit of at most 100 ms first (rq_set_wait_limit); it is %llu ns", (unsigned long long)ctx->wait_limit_ns);
+    DeviceGuard guard(ctx->device);
+    rq_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->error_flag, ctx->wait_limit_ns);
+    RQ_CUDA(cudaGetLastError());
     return RQ_OK;
 }
 
@@ -388,7 +490,7 @@ extern "C" int rq_quantize_activations(rq_ctx* ctx, const float* x, int64_t sk, 
     if (step != 32 && step != 256) return rq_fail(RQ_ERR_INVALID, "rq_quantize_activations: step=%d must be 32 or 256", step);
     if (tokens <= 0 || sk <= 0) return rq_fail(RQ_ERR_INVALID, "rq_quantize_activations: tokens and strides must be positive");
     DeviceGuard guard(ctx->device);
-    int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols) * (size_t)tokens);
+    int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols) * (size_t)tokens, (cudaStream_t)stream);
     if (rc) return rc;
     rc = rq_launch_act_quant(x, sk, st, cols, tokens, step, ctx->act_scratch, (uint8_t*)dev_records, (cudaStream_t)stream);
     if (rc) return rc;

@@ -371,12 +371,14 @@ int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, in
 static int int8_records(rq_ctx* ctx, const char* who, const float* x, int64_t sk, int64_t st, int64_t cols, int tokens, int step, int act_mode,
                         cudaStream_t s) {
     if (act_mode == RQ_ACT_INT8) {
-        int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols) * (size_t)tokens);
+        int rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols) * (size_t)tokens, s);
         if (rc) return rc;
         rc = rq_launch_act_quant(x, sk, st, cols, tokens, step, ctx->act_scratch, nullptr, s);
         if (rc) return rc;
         ctx->act_cols = cols; ctx->act_tokens = tokens; ctx->act_step = step;
     } else if (act_mode == RQ_ACT_INT8_CACHED) {
+        int rc = rq_order_work_areas(ctx, s);  // the records may have been written on another stream
+        if (rc) return rc;
         if (ctx->act_cols != cols || ctx->act_tokens != tokens || ctx->act_step != step)
             return rq_fail(RQ_ERR_INVALID, "%s: no cached int8 records for %lld inputs x %d tokens at step %d (held: %lld x %d at %d)", who,
                            (long long)cols, tokens, step, (long long)ctx->act_cols, ctx->act_tokens, ctx->act_step);
@@ -387,12 +389,12 @@ static int int8_records(rq_ctx* ctx, const char* who, const float* x, int64_t sk
 // A single-token INT8 call over whole 256-value units can quantise inside the matvec launch. True when
 // that is to be tried (the scratch is then large enough for the records the launch leaves behind);
 // *rc carries an allocation failure.
-static bool fused_int8(rq_ctx* ctx, int act_mode, int tokens, int64_t cols, int* rc) {
+static bool fused_int8(rq_ctx* ctx, int act_mode, int tokens, int64_t cols, int* rc, cudaStream_t s) {
     *rc = RQ_OK;
     // Every CTA of a fused launch reads all of x: beyond 8192 inputs that traffic (some 300 CTAs x 4 bytes x inputs)
     // costs more than the quantiser launch it saves.
     if (act_mode != RQ_ACT_INT8 || tokens != 1 || cols % 256 || cols > 8192) return false;
-    *rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols));
+    *rc = rq_ensure_act_scratch(ctx, rq_act_token_bytes(cols), s);
     return *rc == RQ_OK;
 }
 
@@ -412,7 +414,7 @@ int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const f
             seg[i].main[0] = ws[i]->main; seg[i].scale[0] = ws[i]->scale; seg[i].act[0] = 0; seg[i].coef[0] = 1.0f;
             total += ws[i]->rows;
         }
-        if (fused_int8(ctx, act_mode, tokens, w0->cols, &rc)) {
+        if (fused_int8(ctx, act_mode, tokens, w0->cols, &rc, s)) {
             // one launch: the matvec quantises x in its prologue
             rc = rq_launch_stream(ctx, w0->type, w0->cols, nullptr, seg, n, 1, RQ_EPI_PLAIN, total, x, sk, st, tokens, 0, yn, yt, mode, ctx->act_scratch, step,
                                   ctx->act_scratch, s);
@@ -439,7 +441,7 @@ int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, 
                    float* y, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s) {
     const int mode = act_mode == RQ_ACT_FLOAT ? RQ_ACT_FLOAT : RQ_ACT_INT8;
     int rc;
-    if (fused_int8(ctx, act_mode, tokens, w->cols, &rc)) {
+    if (fused_int8(ctx, act_mode, tokens, w->cols, &rc, s)) {
         // one launch: the matvec quantises x in its prologue
         rc = rq_launch_gemv_stream(ctx, w, x, sk, st, tokens, y, yn, yt, mode, ctx->act_scratch, step, ctx->act_scratch, s);
         if (rc == RQ_OK) { ctx->act_cols = w->cols; ctx->act_tokens = tokens; ctx->act_step = step; }

@@ -27,7 +27,6 @@
 namespace {
 
 constexpr int kMaxStages = 12;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait on an mbarrier gives up after two seconds
 
 // What a launch computes is described by a table of SEGMENTS of virtual output rows. A virtual
 // row is made of `subs` sub-rows, each a row of some stored matrix dotted with one activation
@@ -79,6 +78,7 @@ struct StreamParams {
     int64_t yn, yt;
     int tokens;
     int* error_flag;
+    unsigned long long wait_ns;  // a wait on an mbarrier gives up after this long (the context's limit, two seconds unless set)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -98,11 +98,11 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 // Bounded wait: false when the time limit ran out (the caller records the error and stops waiting).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     while (!mbar_try_wait(bar, parity))
-        if (global_ns() - t0 > kWaitLimitNs) return false;
+        if (global_ns() - t0 > limit_ns) return false;
     return true;
 }
 // Weights are read once per launch: the copies carry an evict-first L2 policy, so the stream does not push
@@ -1048,7 +1048,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                     r = stop;
                 }
                 const RqSegment& sg = segs[seg];
-                if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase)) { atomicExch(p.error_flag, 1); failed = true; break; }
+                if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase, p.wait_ns)) { atomicExch(p.error_flag, 1); failed = true; break; }
                 uint8_t* dst = ring + (size_t)slot * p.stage_bytes;
                 stage_info[slot] = make_int4(nr, seg, (int)lr0,
                                              TYPE != RQ_Q4_K ? (int)(((uintptr_t)sg.scale[0] + (uintptr_t)(lr0 * row_scales * 2)) & 15) : 0);
@@ -1056,7 +1056,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                     // at most `window` pieces in flight: wait for the one issued `window` pieces ago
                     if (n_pieces >= p.window) {
                         const int old_piece = n_pieces - p.window, old_st = old_piece / p.pieces;
-                        if (!mbar_wait(&full_bar[2 * (old_st % p.stages) + (old_piece - old_st * p.pieces)], (old_st / p.stages) & 1)) { atomicExch(p.error_flag, 4); failed = true; break; }
+                        if (!mbar_wait(&full_bar[2 * (old_st % p.stages) + (old_piece - old_st * p.pieces)], (old_st / p.stages) & 1, p.wait_ns)) { atomicExch(p.error_flag, 4); failed = true; break; }
                     }
                     ++n_pieces;
                     uint64_t* bar = &full_bar[2 * slot + k];
@@ -1132,7 +1132,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             issue(0x7fffffff);
             if (p.warp_rows && !failed) {
                 // the warp scheme's consumers read what each slot holds from stage_info: a stage of no rows ends their loop
-                if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase)) { atomicExch(p.error_flag, 1); failed = true; }
+                if (st >= p.stages && !mbar_wait(&empty_bar[slot], phase, p.wait_ns)) { atomicExch(p.error_flag, 1); failed = true; }
                 else {
                     stage_info[slot] = make_int4(0, 0, 0, 0);
                     for (int k = 0; k < p.pieces; ++k) mbar_expect_tx(&full_bar[2 * slot + k], 0);
@@ -1142,7 +1142,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             // leave only after every copy this CTA issued has landed (bounded)
             for (int w = (issued > p.stages ? issued - p.stages : 0); w < issued; ++w)
                 for (int k = 0; k < p.pieces; ++k)
-                    if (!mbar_wait(&full_bar[2 * (w % p.stages) + k], (w / p.stages) & 1)) { atomicExch(p.error_flag, 2); break; }
+                    if (!mbar_wait(&full_bar[2 * (w % p.stages) + k], (w / p.stages) & 1, p.wait_ns)) { atomicExch(p.error_flag, 2); break; }
         }
     } else {
         // ---------------------------------------------------------------- consumers
@@ -1377,7 +1377,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             const size_t pass_bytes = (size_t)rows_per_pass * row_bytes;
             const bool writer = (lane & (group - 1)) == 0;
             while (true) {
-                if (!mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                if (!mbar_wait(&full_bar[2 * slot], phase, p.wait_ns)) { atomicExch(p.error_flag, 3); dead = true; }
                 if (dead) break;
                 const int4 info = stage_info[slot];  // rows, segment, first local row, offset of the first d
                 if (info.x == 0) break;               // the producer has no more rows for this CTA
@@ -1388,7 +1388,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 for (int k = 0; k < R; ++k) {
                     const int lr = row_in_pass + k * rows_per_pass;
                     // the second pass's rows are the stage's second piece
-                    if (k == 1 && p.pieces == 2 && !dead && !mbar_wait(&full_bar[2 * slot + 1], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                    if (k == 1 && p.pieces == 2 && !dead && !mbar_wait(&full_bar[2 * slot + 1], phase, p.wait_ns)) { atomicExch(p.error_flag, 3); dead = true; }
                     have[k] = lr < info.x && act_owner;
                     if (have[k]) {
                         const uint16_t* sc = nullptr;
@@ -1473,7 +1473,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                         const int nr = (int)(stop - r);
                         const int64_t lr0 = r - sg.row_begin;
                         st_seg[k] = seg; st_nr[k] = nr; st_lr0[k] = lr0;
-                        if (!dead && !mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                        if (!dead && !mbar_wait(&full_bar[2 * slot], phase, p.wait_ns)) { atomicExch(p.error_flag, 3); dead = true; }
                         const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
                         have[k] = tid < items_cap && my_lr < nr && my_s < subs;
                         if (have[k]) {
@@ -1515,7 +1515,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 if (stop > row_end) stop = row_end;
                 const int nr = (int)(stop - r);
                 const int64_t lr0 = r - sg.row_begin;
-                if (!dead && !mbar_wait(&full_bar[2 * slot], phase)) { atomicExch(p.error_flag, 3); dead = true; }
+                if (!dead && !mbar_wait(&full_bar[2 * slot], phase, p.wait_ns)) { atomicExch(p.error_flag, 3); dead = true; }
                 const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
                 float* part = partial + (size_t)(st & 1) * T * stage_items;
                 if (tid < items_cap && my_lr < nr && my_s < subs) {
@@ -1731,7 +1731,7 @@ int rq_launch_stream(rq_ctx* ctx, int type, int64_t cols, const RqSegment* table
     p.rows = total_rows; p.cols = (int)cols; p.units = (int)(cols / 256);
     p.x = x; p.sk = sk; p.st = st; p.act = act; p.yn = yn; p.yt = yt; p.tokens = tokens;
     p.fuse_step = act_mode == RQ_ACT_INT8 ? fuse_step : 0; p.act_out = act_out;
-    p.error_flag = ctx->error_flag;
+    p.error_flag = ctx->error_flag; p.wait_ns = ctx->wait_limit_ns;
     switch (type) {
         case RQ_Q4_K: p.unit_bytes = 144; p.scales_per_unit = 0; break;
         case RQ_Q6_K: p.unit_bytes = 208; p.scales_per_unit = 1; break;
@@ -1762,7 +1762,7 @@ int rq_launch_stream_plan(rq_ctx* ctx, int type, int64_t cols, const RqPlan* pla
     p.n_segments = max_segments; p.subs = max_subs; p.epilogue = epilogue;
     p.rows = max_rows; p.cols = (int)cols; p.units = (int)(cols / 256);
     p.x = x; p.sk = sk; p.st = st; p.yn = yn; p.yt = yt; p.tokens = 1;
-    p.error_flag = ctx->error_flag;
+    p.error_flag = ctx->error_flag; p.wait_ns = ctx->wait_limit_ns;
     switch (type) {
         case RQ_Q4_K: p.unit_bytes = 144; p.scales_per_unit = 0; break;
         case RQ_Q6_K: p.unit_bytes = 208; p.scales_per_unit = 1; break;

@@ -37,11 +37,15 @@ struct rq_ctx {
     size_t act_scratch_bytes;
     int64_t act_cols; int act_tokens; int act_step;  // what the scratch holds (0 = nothing)
     int* error_flag;  // device word a kernel sets when a bounded wait ran out
+    unsigned long long wait_limit_ns;  // how long a kernel of this context waits on a barrier before it gives up
     int* pin_flag;    // pinned host copy, refreshed by the host-buffer entry points
     // pinned + device staging for the host-buffer entry points
     float* stage_x; float* stage_y; size_t stage_x_bytes, stage_y_bytes;
     float* pin_x; float* pin_y; size_t pin_x_bytes, pin_y_bytes;
     cudaStream_t stream; // used by the host-buffer entry points
+    // the stream of the last call that used the context's work areas (the activation scratch, a bank's plans), and the event
+    // a call on another stream waits for before it touches them
+    cudaStream_t work_stream; bool work_stream_set; cudaEvent_t work_event;
 };
 
 int rq_fail(int status, const char* fmt, ...);
@@ -75,7 +79,11 @@ __host__ __device__ inline size_t rq_act_token_bytes(int64_t cols) {
                                     : (size_t)cols + (size_t)(cols / 32) * 4 + (size_t)(cols / 16) * 2;
 }
 
-int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes);
+// Orders this call's use of the context's work areas after the previous call's when the two were given different streams.
+int rq_order_work_areas(rq_ctx* ctx, cudaStream_t s);
+// Makes the activation scratch at least `bytes` large (growing it synchronises the device: rq_reserve does that ahead of
+// time) and orders its use on `s` after the previous call's.
+int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes, cudaStream_t s);
 
 // launchers (defined in the .cu files)
 int rq_launch_repack(const rq_weight* w, const uint8_t* dev_blocks, cudaStream_t s);
@@ -91,6 +99,8 @@ int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const f
 int rq_launch_gemv_tiled_int8(rq_ctx* ctx, const rq_weight* w, int tokens, float* y, int64_t yn, int64_t yt, const uint8_t* act, cudaStream_t s);
 // RQ_ERR_UNSUPPORTED (no error text) = width not served by the tensor-core kernel
 int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s);
+// scratch bytes rq_launch_matmul takes for a weight of this shape and this many tokens (its activation image and split-K sums)
+size_t rq_matmul_scratch_bytes(const rq_ctx* ctx, int64_t rows, int64_t cols, int tokens);
 int rq_launch_quantize(int type, const float* values, int64_t count, uint8_t* blocks, cudaStream_t s);
 // A run of virtual output rows of the streaming kernel (see rq_gemv_stream.cu).
 #define RQ_MAX_SUB 16

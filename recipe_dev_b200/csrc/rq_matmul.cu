@@ -35,7 +35,6 @@ constexpr int kMmaWarp = kStageWarps + kDrainWarps, kCopyWarp = kMmaWarp + 1;
 constexpr int kThreadsMM = (kCopyWarp + 1) * 32;
 constexpr int kTileBytes = BM * BK * 2;            // one fp16 tile of 128 rows: 16 KB
 constexpr int kStageBytes = 4 * kTileBytes;        // A_hi | A_lo | B_hi | B_lo (B tiles of BN rows, at most 128)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct MatmulParams {
     const uint8_t* main;
@@ -49,6 +48,7 @@ struct MatmulParams {
     int ks_per_split;   // 64-wide slices per CTA along K (gridDim.z CTAs share a tile's K)
     float* partial;     // gridDim.z > 1: [split][token][row] sums, added in split order by rq_sum_splits_kernel
     int* error_flag;
+    unsigned long long wait_ns;  // bounded waits give up after this long
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -72,11 +72,11 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
                  : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     while (!mbar_try_wait_parked(bar, parity, 2000u))  // parked waits do not eat the staging warps' issue slots
-        if (global_ns() - t0 > kWaitLimitNs) return false;
+        if (global_ns() - t0 > limit_ns) return false;
     return true;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
             if (ks + 1 < k_steps) nxt.load(p, row, (k_first + ks + 1) * BK, half);
             float v[32];
             cur.decode((k_first + ks) * BK, half, v);
-            if (ks >= kStages && !dead && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 11); dead = true; }
+            if (ks >= kStages && !dead && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 11); dead = true; }
             uint8_t* a_hi = smem + (size_t)slot * kStageBytes;
             uint8_t* a_lo = a_hi + kTileBytes;
 #pragma unroll
@@ -371,7 +371,7 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
         bool dead = false;
         for (int ks = 0; ks < k_steps; ++ks) {
             const int b = ks & 1;
-            if (!dead && !mbar_wait(&acc_full[b], (ks >> 1) & 1)) { atomicExch(p.error_flag, 14); dead = true; }
+            if (!dead && !mbar_wait(&acc_full[b], (ks >> 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 14); dead = true; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -387,7 +387,7 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[b]);
         }
-        if (!dead && !mbar_wait(&done_bar, 0)) { atomicExch(p.error_flag, 12); dead = true; }
+        if (!dead && !mbar_wait(&done_bar, 0, p.wait_ns)) { atomicExch(p.error_flag, 12); dead = true; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int64_t out_row = m0 + quarter * 32 + lane;
 #pragma unroll
@@ -414,8 +414,8 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
         const uint32_t idesc = instr_desc(bn);
         for (int ks = 0; ks < k_steps; ++ks) {
             const int slot = ks % kStages, b = ks & 1;
-            if (!dead && !mbar_wait(&full_bar[slot], (ks / kStages) & 1)) { atomicExch(p.error_flag, 13); dead = true; }
-            if (ks >= 2 && !dead && !mbar_wait(&acc_empty[b], ((ks >> 1) - 1) & 1)) { atomicExch(p.error_flag, 15); dead = true; }
+            if (!dead && !mbar_wait(&full_bar[slot], (ks / kStages) & 1, p.wait_ns)) { atomicExch(p.error_flag, 13); dead = true; }
+            if (ks >= 2 && !dead && !mbar_wait(&acc_empty[b], ((ks >> 1) - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 15); dead = true; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0 && !dead) {
                 const uint32_t base = smem_u32(smem + (size_t)slot * kStageBytes);
@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(kThreadsMM, 1) rq_matmul_kernel(const __grid_c
             const uint8_t* src = p.xs + ((size_t)nt * k_total + k_first) * bytes;
             for (int ks = 0; ks < k_steps; ++ks) {
                 const int slot = ks % kStages;
-                if (ks >= kStages && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1)) { atomicExch(p.error_flag, 16); break; }
+                if (ks >= kStages && !mbar_wait(&empty_bar[slot], ((ks / kStages) - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 16); break; }
                 mbar_expect_tx(&full_bar[slot], bytes);
                 bulk_g2s(smem + (size_t)slot * kStageBytes + 2 * kTileBytes, src + (size_t)ks * bytes, bytes, &full_bar[slot]);
             }
@@ -483,28 +483,44 @@ int launch_mm(const MatmulParams& p, cudaStream_t s) {
 
 }  // namespace
 
+// How a call is cut: tokens per tile, K slices per CTA, CTAs along K, and the scratch it takes.
+struct MatmulCut { int bn, n_tiles, k_steps, ks_per_split, splits; size_t xs_bytes, partial_bytes; };
+static MatmulCut matmul_cut(int sm_count, int64_t rows, int64_t cols, int tokens) {
+    MatmulCut c;
+    c.bn = tokens <= 32 ? 32 : (tokens <= 64 ? 64 : 128);
+    c.n_tiles = (tokens + c.bn - 1) / c.bn; c.k_steps = (int)(cols / BK);
+    c.xs_bytes = (size_t)c.n_tiles * c.k_steps * 2 * c.bn * 128;
+    // Few tiles and a long K: several CTAs share a tile's K (at least sixteen slices each) so that the whole GPU
+    // dequantises, and a second kernel adds their sums.
+    const int64_t tiles = ((rows + BM - 1) / BM) * c.n_tiles;
+    int splits = 1;
+    if (tiles < sm_count) {
+        splits = (int)(sm_count / tiles);
+        if (splits > c.k_steps / 16) splits = c.k_steps / 16;
+        if (splits < 1) splits = 1;
+    }
+    c.ks_per_split = (c.k_steps + splits - 1) / splits;
+    c.splits = (c.k_steps + c.ks_per_split - 1) / c.ks_per_split;
+    c.partial_bytes = c.splits > 1 ? (size_t)c.splits * tokens * rows * 4 : 0;
+    return c;
+}
+size_t rq_matmul_scratch_bytes(const rq_ctx* ctx, int64_t rows, int64_t cols, int tokens) {
+    const MatmulCut c = matmul_cut(ctx->sm_count, rows, cols, tokens);
+    return c.xs_bytes + c.partial_bytes;
+}
+
 int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s) {
     if (w->cols % BK) return RQ_ERR_UNSUPPORTED;
     MatmulParams p;
     p.main = w->main; p.scale = w->scale; p.rows = w->rows; p.cols = (int)w->cols;
-    p.bn = tokens <= 32 ? 32 : (tokens <= 64 ? 64 : 128);
-    p.tokens = tokens; p.y = y; p.yn = yn; p.yt = yt; p.error_flag = ctx->error_flag;
+    const MatmulCut cut = matmul_cut(ctx->sm_count, w->rows, w->cols, tokens);
+    p.bn = cut.bn;
+    p.tokens = tokens; p.y = y; p.yn = yn; p.yt = yt; p.error_flag = ctx->error_flag; p.wait_ns = ctx->wait_limit_ns;
     // the split activations live in the context's scratch (whatever int8 records it held are gone)
-    const int n_tiles = (tokens + p.bn - 1) / p.bn, k_steps = p.cols / BK;
-    const size_t bytes = (size_t)n_tiles * k_steps * 2 * p.bn * 128;
-    // Few tiles and a long K: several CTAs share a tile's K (at least sixteen slices each) so that the whole GPU
-    // dequantises, and a second kernel adds their sums.
-    const int64_t tiles = ((w->rows + BM - 1) / BM) * n_tiles;
-    int splits = 1;
-    if (tiles < ctx->sm_count) {
-        splits = (int)(ctx->sm_count / tiles);
-        if (splits > k_steps / 16) splits = k_steps / 16;
-        if (splits < 1) splits = 1;
-    }
-    p.ks_per_split = (k_steps + splits - 1) / splits;
-    splits = (k_steps + p.ks_per_split - 1) / p.ks_per_split;
-    const size_t partial_bytes = splits > 1 ? (size_t)splits * tokens * w->rows * 4 : 0;
-    int rc = rq_ensure_act_scratch(ctx, bytes + partial_bytes);
+    const int n_tiles = cut.n_tiles, k_steps = cut.k_steps, splits = cut.splits;
+    const size_t bytes = cut.xs_bytes, partial_bytes = cut.partial_bytes;
+    p.ks_per_split = cut.ks_per_split;
+    int rc = rq_ensure_act_scratch(ctx, bytes + partial_bytes, s);
     if (rc) return rc;
     ctx->act_cols = 0;
     p.xs = ctx->act_scratch;

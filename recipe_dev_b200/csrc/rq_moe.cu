@@ -482,13 +482,15 @@ extern "C" int rq_moe_forward(rq_ctx* ctx, rq_moe* m, const float* x, int64_t x_
     if (x_k_stride <= 0 || y_n_stride <= 0) return rq_fail(RQ_ERR_INVALID, "rq_moe_forward: strides must be positive");
     DeviceGuard guard(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
+    int rc = rq_order_work_areas(ctx, s);  // the bank's plans and hidden activations are shared by every call on it
+    if (rc) return rc;
     const int slots = top_k + 1;
     rq_moe_plan_kernel<<<tokens, 256, 0, s>>>(view_of(m), routing, routing_e_stride, routing_t_stride, x, x_k_stride, x_t_stride, top_k, include_shared,
                                               m->plans, m->h, y, y_n_stride, y_t_stride);
     RQ_CUDA(cudaGetLastError());
     // All tokens in two launches: grid row t of each reads token t's plan and activations.
     // expert gate and up rows against the token's x, h = silu(g) * u per slot
-    int rc = rq_launch_stream_plan(ctx, m->type, m->hidden, m->plans, tokens, 2, slots, 2, RQ_EPI_GLU, (int64_t)slots * m->ffn, x, x_t_stride, x_k_stride, 0,
+    rc = rq_launch_stream_plan(ctx, m->type, m->hidden, m->plans, tokens, 2, slots, 2, RQ_EPI_GLU, (int64_t)slots * m->ffn, x, x_t_stride, x_k_stride, 0,
                                    1, 1, 0, s);
     if (rc == RQ_ERR_UNSUPPORTED) return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: hidden=%d is beyond what the streaming kernel holds", m->hidden);
     if (rc) return rc;

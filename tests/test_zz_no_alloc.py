@@ -64,3 +64,36 @@ def test_static_scratch_refuses_columns_beyond_its_size(rq_ctx, oracle):
     got = rq_ctx.matvec_int8_static(w, cuda(xh)).cpu().numpy()
     assert rel_err(got, oracle.matvec(ol.Q8_0, blocks, 2, cols, xh, ol.INT8, 32)) <= TOL
     assert rq_ctx.lib.rq_matvec_int8_static(rq_ctx.handle, w.handle, None, y.data_ptr(), 32, None) == -1
+
+
+def test_static_call_allocates_nothing_and_leaves_the_context_scratch_alone(oracle):
+    """The property the entry point exists for: on a fresh context, at a width the context has never
+    seen, the second static call leaves free device memory unchanged, and the context holds no int8
+    records afterwards (an INT8_CACHED call of that width still fails)."""
+    import torch
+
+    import recipe_dev_b200 as rq
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    ctx = rq.Context(0)
+    try:
+        rows, cols = 48, 5 * 256
+        blocks = oracle.quantize(ol.Q4_K, oracle.normal(23, 0, rows * cols, 0.02))
+        w = ctx.weight_from_host(ol.Q4_K, blocks, rows, cols)
+        xh = oracle.normal(23, 1, cols, 1.0)
+        x, y = cuda(xh), cuda(np.zeros(rows, np.float32))
+        ctx.matvec_int8_static(w, x, y)  # the warm-up call: symbol address, module load
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        ctx.matvec_int8_static(w, x, y)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, (free_before, free_after)
+        assert rel_err(y.cpu().numpy(), oracle.matvec(ol.Q4_K, blocks, rows, cols, xh, ol.INT8, 32)) <= TOL
+        # the context's scratch was never written: nothing is cached for this width
+        rc = ctx.matvec_raw(w, x.data_ptr(), 1, cols, 1, y.data_ptr(), 1, rows, 2, 32)
+        assert rc == -1 and b"no cached int8 records" in ctx.lib.rq_last_error()
+        ctx.check()
+    finally:
+        ctx.close()
