@@ -124,6 +124,35 @@ def dist_env():
     return rank, world, local
 
 
+# --------------------------------------------------------------------------- shared inputs
+
+
+def oracle_normal(oracle, seed: int, stream: int, count: int, sigma: float) -> np.ndarray:
+    """`count` values of the oracle's counter-based generator (value i depends on (seed, stream, i) only), drawn in
+    parallel chunks: the same numbers as one call, in a fraction of the time."""
+    import concurrent.futures
+
+    out = np.empty(count, dtype=np.float32)
+    chunk = 1 << 22
+    spans = [(first, min(chunk, count - first)) for first in range(0, count, chunk)]
+
+    def fill(span):
+        first, n = span
+        out[first:first + n] = oracle.normal(seed, stream, n, sigma, first=first)
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as pool:
+        list(pool.map(fill, spans))
+    return out
+
+
+LAYER_SEED = 1  # BASELINE: the decode layer's weights are seed 1, one sub-stream per tensor in the order q, k, v, o, gate, up, down
+
+
+def layer_inputs(oracle):
+    """The activations both arms read: fp32 N(0, 1), seed 1, sub-streams 100 (4096 inputs) and 101 (14336 inputs)."""
+    return {4096: oracle.normal(LAYER_SEED, 100, 4096, 1.0), 14336: oracle.normal(LAYER_SEED, 101, 14336, 1.0)}
+
+
 # --------------------------------------------------------------------------- CPU arm
 
 
@@ -135,11 +164,11 @@ def cpu_layer_sample(oracle, ol, blocks, xs, mode, step, threads):
     return time.perf_counter() - t0
 
 
-def host_layer_blocks(oracle, ol, seed=1):
+def host_layer_blocks(oracle, ol, seed=LAYER_SEED):
     """The layer's weights from the oracle's counter-based generator and quantisers (host only)."""
     out = []
     for i, (name, t, rows, cols, _) in enumerate(LAYER):
-        out.append(oracle.quantize(t, oracle.normal(seed, i, rows * cols, 0.02)))
+        out.append(oracle.quantize(t, oracle_normal(oracle, seed, i, rows * cols, 0.02)))
     return out
 
 
@@ -155,7 +184,7 @@ def run_reference(args):
     threads = os.cpu_count() or 1
     mode, step = (ol.INT8, 32) if args.act == "int8" else (ol.FLOAT_RUN, 32)
     blocks = host_layer_blocks(oracle, ol)
-    xs = {4096: oracle.normal(1, 100, 4096, 1.0), 14336: oracle.normal(1, 101, 14336, 1.0)}
+    xs = layer_inputs(oracle)
     for _ in range(max(args.warmup, 1)):
         cpu_layer_sample(oracle, ol, blocks, xs, mode, step, threads)
     times = [cpu_layer_sample(oracle, ol, blocks, xs, mode, step, threads) for _ in range(args.steps)]
@@ -175,12 +204,14 @@ def run_reference(args):
 
 def workload_config(args, layers, cpu=False):
     l2 = "inputs larger than L2: each step reads a different layer of a stack larger than 1 GB"
-    timing = "the K timed steps are one CUDA graph, replayed once untimed (its first launch uploads it) after the W warm-up steps, then timed with CUDA events"
+    timing = ("the K timed steps are one CUDA graph, replayed once untimed (its first launch uploads it) after the W warm-up steps, then timed with "
+              "CUDA events; the graph is then replayed 20 more times for the spread (repeat_ms)")
     if cpu:
         l2 = "one layer (138 MB of blocks) re-read every step: larger than the host's last-level cache"
         timing = "host wall clock around the K steps, after the W warm-up steps; all host threads"
     return {"workload": "llama-8B-shaped decode layer, batch 1: q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096 Q4_K; down 4096x14336 Q6_K",
             "activation_mode": "int8 records, step 32 (recipe default profile)" if args.act == "int8" else "fp32 activations as they are",
+            "seeds": "weights seed 1, one sub-stream per tensor (q, k, v, o, gate, up, down); activations seed 1, sub-streams 100 / 101; the oracle's counter-based generator",
             "layers_in_rotation": layers, "l2": l2, "timing": timing,
             "algorithmic_bytes_per_step": LAYER_BYTES, "multi_gpu": "replicas only (the decode layer is unsharded)"}
 
@@ -188,15 +219,27 @@ def workload_config(args, layers, cpu=False):
 # --------------------------------------------------------------------------- GPU arm
 
 
-def build_layers(ctx, rq, torch, n_layers, seed, device):
-    """n_layers decode layers: fp32 N(0, 0.02) on the device, quantised by the library."""
+def rel_err(y, ref) -> float:
+    """max_i |y_i - ref_i| / max(|ref_i|, 1e-3 max|ref|): the error measure of the parity tests."""
+    y, ref = np.asarray(y, np.float64), np.asarray(ref, np.float64)
+    floor = 1e-3 * np.max(np.abs(ref))
+    return float(np.max(np.abs(y - ref) / np.maximum(np.abs(ref), floor)))
+
+
+def build_layers(ctx, rq, torch, oracle, n_layers, rank, device):
+    """n_layers decode layers on the device. Layer 0 is BASELINE's: fp32 N(0, 0.02) from the oracle's generator at seed 1
+    (the CPU arm's weights), quantised on the device (byte-exact with the oracle's quantisers); the other layers of the
+    rotation exist only so that a step's weights are cold, and come from the device's own generator."""
     gen = torch.Generator(device=device)
-    gen.manual_seed(seed)
+    gen.manual_seed(1000 + rank)
     layers, first_blocks = [], []
     for li in range(n_layers):
         ws = []
-        for (name, t, rows, cols, _) in LAYER:
-            w32 = torch.randn(rows * cols, generator=gen, device=device, dtype=torch.float32) * 0.02
+        for i, (name, t, rows, cols, _) in enumerate(LAYER):
+            if li == 0:
+                w32 = torch.from_numpy(oracle_normal(oracle, LAYER_SEED, i, rows * cols, 0.02)).to(device)
+            else:
+                w32 = torch.randn(rows * cols, generator=gen, device=device, dtype=torch.float32) * 0.02
             blocks = ctx.quantize(t, w32)
             ws.append(ctx.weight_from_device(t, blocks, rows, cols))
             if li == 0:
@@ -207,10 +250,23 @@ def build_layers(ctx, rq, torch, n_layers, seed, device):
     return layers, first_blocks
 
 
+def profile_traffic(name: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch from a committed ncu summary (its `dram_bytes_per_launch:` line)."""
+    path = ROOT / "profiles" / name
+    try:
+        for line in path.read_text().splitlines():
+            if line.startswith("dram_bytes_per_launch:"):
+                return int(line.split(":")[1].split()[0].replace(",", ""))
+    except OSError:
+        pass
+    return None
+
+
 def run_ours(args):
     import torch
 
     import recipe_dev_b200 as rq
+    from tests import oracle_lib as ol
 
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
@@ -222,24 +278,29 @@ def run_ours(args):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=device)
+    oracle = ol.load()  # the checker and the source of BASELINE's seeded inputs; nothing timed on the GPU runs through it
     ctx = rq.Context(local)
     mode = rq.ACT_INT8 if args.act == "int8" else rq.ACT_FLOAT
-    cached = 2 if mode == rq.ACT_INT8 else rq.ACT_FLOAT
     step = 32
     n_layers = args.layers
-    layers, first_blocks = build_layers(ctx, rq, torch, n_layers, 1 + rank, device)
-    gen = torch.Generator(device=device)
-    gen.manual_seed(100 + rank)
-    xs = {4096: torch.randn(4096, generator=gen, device=device), 14336: torch.randn(14336, generator=gen, device=device)}
+    layers, first_blocks = build_layers(ctx, rq, torch, oracle, n_layers, rank, device)
+    hx = layer_inputs(oracle)
+    xs = {4096: torch.from_numpy(hx[4096]).to(device)}
     ys = {name: torch.empty(rows, device=device) for name, _, rows, _, _ in LAYER}
     # q/k/v read one activation column, gate/up another: one call (and one launch) per group
     GROUPS = [[0, 1, 2], [3], [4, 5], [6]]
+    ctx.reserve(14336, 14336, 1)  # no call below grows a work area: nothing allocates or synchronises inside a timed region
 
-    def layer_pass(li):
+    # The layer's launches are chained: o reads q's output plane (attention itself is not on this path), gate / up read
+    # o's, down reads gate's; the planes between the launches never leave the device.
+    SOURCE = {0: None, 3: "q", 4: "o", 6: "gate"}
+
+    def layer_pass(li, stream=None):
         ws = layers[li % n_layers]
         for g in GROUPS:
-            cols = LAYER[g[0]][3]
-            ctx.matvec_multi([ws[j] for j in g], xs[cols], [ys[LAYER[j][0]] for j in g], act_mode=mode, step=step)
+            src = SOURCE[g[0]]
+            x_in = xs[4096] if src is None else ys[src]
+            ctx.matvec_multi([ws[j] for j in g], x_in, [ys[LAYER[j][0]] for j in g], act_mode=mode, step=step, stream=stream)
 
     # kernels of the library per step: one streaming matvec per group; an int8 group wider than 8192 inputs
     # also launches the activation quantiser (narrower ones quantise inside the matvec launch)
@@ -250,11 +311,10 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # one CUDA graph per layer of the stack: a step is one graph launch, so the host's launch rate
-    # does not bound the 5-20 us kernels
     for i in range(3):
-        layer_pass(i)  # grows the library's scratch before capture
+        layer_pass(i)  # module load before capture
     torch.cuda.synchronize()
+
     # the W warm-up steps and the K timed steps are one CUDA graph each (as a decoder captures its whole
     # stack of layers): step i runs layer i of the rotation
     def capture(first, count):
@@ -283,13 +343,37 @@ def run_ours(args):
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
+    # the spread: the same K steps twenty more times, each timed on its own
+    repeats = []
+    for _ in range(20):
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record(stream)
+        timed_graph.replay()
+        r1.record(stream)
+        torch.cuda.synchronize()
+        repeats.append(r0.elapsed_time(r1))
     ctx.check()
+
+    # ---- what the timed kernels computed, against the oracle: layer 0 (BASELINE's seeded layer), a sample of rows of each projection
+    layer_pass(0)
+    torch.cuda.synchronize()
+    omode = ol.INT8 if mode == rq.ACT_INT8 else ol.FLOAT_RUN
+    worst = 0.0
+    rng = np.random.default_rng(7)
+    host_planes = {name: ys[name].cpu().numpy() for name in ys}
+    reads = {"q": None, "k": None, "v": None, "o": "q", "gate": "o", "up": "o", "down": "gate"}
+    for (name, t, rows, cols, _), blocks in zip(LAYER, first_blocks):
+        pick = np.sort(rng.choice(rows, size=32, replace=False))
+        row_bytes = cols // GEOM[t][0] * GEOM[t][1]
+        sub = blocks.reshape(rows, row_bytes)[pick].reshape(-1)
+        x_in = hx[4096] if reads[name] is None else host_planes[reads[name]]  # each projection against the input it really read
+        ref = oracle.matvec(t, sub, pick.size, cols, x_in, omode, step)
+        worst = max(worst, rel_err(host_planes[name][pick], ref))
+    if worst > 1e-3:
+        raise SystemExit(f"bench.py: the timed kernels' outputs differ from the CPU oracle by {worst:.3e} (bar 1e-3)")
 
     # ---- dominant kernel alone: the streaming Q4_K matvec over gate+up (28672 x 4096), launches back to back
     n_dom = max(args.steps, 20)
-    if mode == rq.ACT_INT8:
-        ctx.matvec(layers[0][4], xs[4096], ys["gate"], act_mode=mode, step=step)  # leaves the records the cached launches read
-    torch.cuda.synchronize()
     dom_graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(dom_graph):
         for i in range(n_dom):
@@ -304,34 +388,37 @@ def run_ours(args):
     torch.cuda.synchronize()
     dom_us = 1e3 * d0.elapsed_time(d1) / n_dom
 
-    # ---- end to end: host buffers through rq_matvec_host, copies inside the timed region ----
-    hx = {c: np.ascontiguousarray(v.cpu().numpy()) for c, v in xs.items()}
-    def layer_pass_host(li):
-        ws = layers[li % n_layers]
-        out = None
-        for g in GROUPS:  # one host call per group of projections that read the same x
-            out = ctx.matvec_multi_host([ws[j] for j in g], hx[LAYER[g[0]][3]], act_mode=mode, step=step)
-        return out
-    for i in range(min(args.warmup, 3)):
-        layer_pass_host(i)
+    # ---- end to end: one boundary crossing per step. Each layer of the rotation is a recorded sequence of its four calls;
+    # a step copies x in from host memory, replays the sequence, copies the step's result (down's output) back, synchronises.
+    sequences = []
+    for li in range(n_layers):
+        s = ctx.sequence_begin()
+        layer_pass(li, stream=s)
+        sequences.append(ctx.sequence_end())
+    host_out = np.empty(4096, np.float32)
+    for i in range(max(args.warmup, 3)):
+        sequences[i % n_layers].run_host(hx[4096], xs[4096], ys["down"], host_out)
     barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        layer_pass_host(args.warmup + i)
+        sequences[(args.warmup + i) % n_layers].run_host(hx[4096], xs[4096], ys["down"], host_out)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    e2e_err = rel_err(host_out, ys["down"].cpu().numpy())
     clocks = sampler.stop() if rank == 0 else None
+    for sq in sequences:
+        sq.free()
     for ws in layers:
         for w in ws:
             w.free()
     sharded_out = run_sharded_configs(ctx, rq, torch, dist, rank, world, device, args.steps) if args.sharded else None
-    other_out = run_other_configs(ctx, rq, torch, device) if (args.sharded and rank == 0) else None
+    other_out = run_other_configs(ctx, rq, torch, oracle, ol, device) if (args.sharded and rank == 0) else None
 
     # max over ranks
     if dist is not None:
-        t = torch.tensor([ms, e2e_s], device=device, dtype=torch.float64)
+        t = torch.tensor([ms, e2e_s, worst], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(t[0]), float(t[1])
+        ms, e2e_s, worst = float(t[0]), float(t[1]), float(t[2])
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -342,22 +429,29 @@ def run_ours(args):
     peak, peak_kind = measured_peak_gbs()
     dom_bytes = 2 * algo_bytes(Q4_K, 14336, 4096) - 4 * 4096  # two row sets, one activation column
     achieved = dom_bytes / (dom_us * 1e-6) / 1e9
+    one_set = profile_traffic("rq_gemv_stream_q4k_14336x4096_int8.md")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 x q4/q6 -> i32, fp32 accumulate" if mode == rq.ACT_INT8 else "fp32",
         "data": "synthetic", "config": workload_config(args, n_layers),
         "us_per_decode_layer": 1e3 * ms / args.steps,
+        "repeat_ms": {"n": len(repeats), "median": statistics.median(repeats), "p99": sorted(repeats)[-1], "min": min(repeats)},
+        "max_rel_err_vs_oracle": worst,
         "frac_of_hbm_measured": value / world / peak, "frac_of_hbm_nominal_8TBs": value / world / 8000.0,
         "roofline": {"bound": "hbm", "kernel": "rq_gemv_stream_kernel<Q4_K> over gate+up (2 x 14336 x 4096), one launch", "achieved": achieved, "peak": peak,
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": dom_us, "algorithmic_bytes_per_launch": dom_bytes,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the same kernel over one of the two
-                     # row sets (14336 x 4096: 33.11 MB read, nothing written), scaled to the launch's two row sets
-                     "traffic": 2 * 33_106_400, "traffic_source": "profiles/rq_gemv_stream_q4k_14336x4096_int8.md, x2 row sets"},
+                     # an ncu capture of the same kernel over one of the two row sets (14336 x 4096), scaled to the launch's two:
+                     # traffic grows with the rows read
+                     "traffic": None if one_set is None else 2 * one_set,
+                     "traffic_source": "profiles/rq_gemv_stream_q4k_14336x4096_int8.md (dram_bytes_per_launch), x2 row sets"},
         "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": UNIT,
-                "h2d_bytes_per_step": sum(4 * c for _, _, _, c, _ in LAYER), "d2h_bytes_per_step": sum(4 * r for _, _, r, _, _ in LAYER),
-                "ms_per_step": 1e3 * e2e_s / args.steps, "call": "rq_matvec_multi_host x 4 per step (q/k/v, o, gate/up, down: host x in, host y out)"},
+                "h2d_bytes_per_step": 4 * 4096, "d2h_bytes_per_step": 4 * 4096,
+                "ms_per_step": 1e3 * e2e_s / args.steps, "result_equals_device_plane": e2e_err == 0.0,
+                "call": "rq_sequence_run_host: x copied in from host memory, the layer's four recorded calls replayed as one submission "
+                        "(o reads q's plane, gate/up read o's, down reads gate's: the planes between stay on the device), down's output copied "
+                        "back, one synchronisation"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
@@ -366,20 +460,16 @@ def run_ours(args):
     if other_out is not None:
         line["other_configs"] = other_out
     if args.cpu_baseline:
-        from tests import oracle_lib as ol
-
-        oracle = ol.load()
         threads = os.cpu_count() or 1
-        omode = ol.INT8 if mode == rq.ACT_INT8 else ol.FLOAT_RUN
         t0 = time.perf_counter()
         reps = 0
         while reps < 1 or (time.perf_counter() - t0 < 10.0 and reps < 50):
-            cpu_layer_sample(oracle, ol, first_blocks, hx, omode, step, threads)
+            cpu_layer_sample(oracle, ol, first_blocks, hx, omode, step, threads)  # the CPU arm's fixed inputs: the same bytes and flops
             reps += 1
         cpu_s = (time.perf_counter() - t0) / reps
         line["cpu_baseline"] = {"value": LAYER_BYTES / cpu_s / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
                                 "ms_per_step": 1e3 * cpu_s,
-                                "sample": f"{reps} passes of one decode layer (layer 0 of the stack, same blocks and activations) through oracle/rq_oracle.c"}
+                                "sample": f"{reps} passes of one decode layer (BASELINE's seeded layer: the same blocks and activations the GPU arm timed as layer 0) through oracle/rq_oracle.c"}
     emit(line)
     if dist is not None:
         dist.destroy_process_group()
@@ -417,10 +507,21 @@ def run_case(args):
             ctx.matmul(ws[i % len(ws)], x, y, act_mode=mode, step=32, stream=stream)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(args.steps):
-            ctx.matmul(ws[(args.warmup + i) % len(ws)], x, y, act_mode=mode, step=32, stream=stream)
-        e1.record(stream)
+        if args.graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(args.steps):
+                    ctx.matmul(ws[(args.warmup + i) % len(ws)], x, y, act_mode=mode, step=32)
+            g.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            g.replay()
+            e1.record()
+        else:
+            e0.record(stream)
+            for i in range(args.steps):
+                ctx.matmul(ws[(args.warmup + i) % len(ws)], x, y, act_mode=mode, step=32, stream=stream)
+            e1.record(stream)
         torch.cuda.synchronize()
         us = 1e3 * e0.elapsed_time(e1) / args.steps
         flops = 2.0 * rows * cols * tokens
@@ -459,18 +560,28 @@ def run_case(args):
 
 
 def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
-    """The two configs that shard across GPUs, timed on the device (max over ranks):
-    the row-split Q6_K LM head (262144 x 2560, logits all-gathered) at batch 1 and 4, and the
-    expert-parallel Q4_K MoE bank (256 experts, top-8, hidden 2048, ffn 512, gated shared expert on
-    rank 0, outputs all-reduced) at batch 1 and 16. Returns a dict for the JSON line."""
+    """The two configs that shard across GPUs, timed on the device (max over ranks), each through the C ABI end to end:
+    the row-split Q6_K LM head (262144 x 2560; the ranks' logit slices gathered) at batch 1 and 4, and the expert-parallel
+    Q4_K MoE bank (256 experts, top-8, hidden 2048, ffn 512, gated shared expert on rank 0; the ranks' outputs summed in
+    rank order) at batch 1 and 16. The exchange is the library's own kernel over NVLink peer memory (rq_exchange_*); the
+    same step through NCCL (rq_allgather_rows / rq_allreduce_sum) is timed beside it. After timing, outside every timed
+    region, rank 0 recomputes the whole config on its one GPU and the exchanged result is compared with it."""
     from recipe_dev_b200 import sharded
 
     out = {}
     stream = torch.cuda.current_stream()
+    gloo = dist.new_group(backend="gloo") if dist is not None else None  # the host-side channel for handles and ids
+
+    def share(obj):
+        if dist is None:
+            return [obj]
+        got = [None] * world
+        dist.all_gather_object(got, obj, group=gloo)
+        return got
 
     def timed(fn, reps):
-        """Mean device time of fn, max over ranks. The reps are captured into one CUDA graph (kernels and the NCCL
-        collective alike), so the host's launch rate is not what is measured; if capture is refused the reps run eagerly."""
+        """Mean device time of fn, max over ranks. The reps are captured into one CUDA graph (the library's kernels and, in
+        the NCCL variant, the collective alike), so the host's launch rate is not what is measured."""
         for _ in range(3):
             fn()
         if dist is not None:
@@ -506,86 +617,174 @@ def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
         timed.graphed = graph is not None
         return float(us[0])
 
-    # ---- LM head: rows [first, first + count) of 262144 x 2560 Q6_K on this rank
+    nccl = None
+    if world > 1:
+        ids = share(rq.NcclComm.unique_id() if rank == 0 else None)
+        nccl = rq.NcclComm.create(ctx, ids[0], world, rank)
+    reps = max(10, steps // 10)
+
+    # ---- LM head: rows [first, first + count) of 262144 x 2560 Q6_K on this rank. Rank r's share is drawn from the
+    # device generator at seed 2000 + r, so rank 0 can draw every share again for the check.
     rows, cols = 262144, 2560
     first, count = sharded.shard_range(rows, world, rank)
-    gen = torch.Generator(device=device)
-    gen.manual_seed(2000 + rank)
-    copies = []
-    for _ in range(2 if count * cols // 256 * 210 < 200_000_000 else 1):  # small shares rotate two copies so L2 cannot hold them
-        w32 = torch.randn(count * cols, generator=gen, device=device) * 0.02
-        copies.append(ctx.weight_from_device(Q6_K, ctx.quantize(Q6_K, w32), count, cols))
+
+    def head_share(r, n_rows):
+        gen = torch.Generator(device=device)
+        gen.manual_seed(2000 + r)
+        w32 = torch.randn(n_rows * cols, generator=gen, device=device) * 0.02
+        w = ctx.weight_from_device(Q6_K, ctx.quantize(Q6_K, w32), n_rows, cols)
         del w32
-    mode = rq.ACT_INT8
+        return w
+
+    copies = [head_share(rank, count)]
+    if count * cols // 256 * 210 < 200_000_000:  # small shares rotate a second copy so L2 cannot hold them
+        copies.append(head_share(100 + rank, count))
+    xgen = torch.Generator(device=device)
+    xgen.manual_seed(2999)  # the hidden vectors are the same on every rank (x is replicated)
+    ctx.reserve(count, cols, 4)
     for tokens in (1, 4):
-        x = torch.randn(tokens, cols, generator=gen, device=device)
+        x = torch.randn(tokens, cols, generator=xgen, device=device)
         local = torch.empty(tokens, count, device=device)
+        gathered = torch.empty(world, tokens * count, device=device)
+        ex = rq.Exchange(ctx, rank, world, tokens * count * 4)
+        ex.connect(share(ex.ipc_handle()))
         it = [0]
 
-        def head_step():
-            ctx.matvec(copies[it[0] % len(copies)], x, local, act_mode=mode, step=32)
+        def compute():
+            ctx.matvec(copies[it[0] % len(copies)], x, local, act_mode=rq.ACT_INT8, step=32)
             it[0] += 1
-            return sharded.gather_rows(local, rows, dist, world, rank)
 
-        us = timed(head_step, max(10, steps // 10))
+        def head_step():
+            compute()
+            if world > 1:
+                ex.gather(local.reshape(-1), gathered)
+
+        def head_step_nccl():
+            compute()
+            nccl.allgather_rows(local.reshape(-1), gathered)
+
+        compute_us = timed(compute, reps)
+        us = timed(head_step, reps) if world > 1 else compute_us
+        graphed = timed.graphed
+        nccl_us = timed(head_step_nccl, reps) if world > 1 else None
+        # the check: the first copy's shares, gathered through the exchange, against rank 0's own product over every share
+        it[0] = 0
+        head_step()
+        torch.cuda.synchronize()
+        err = 0.0
+        if world > 1 and rank == 0:
+            got = gathered.view(world, tokens, count)
+            for r in range(world):
+                wr = copies[0] if r == 0 else head_share(r, sharded.shard_range(rows, world, r)[1])
+                want = ctx.matvec(wr, x, act_mode=rq.ACT_INT8, step=32)
+                err = max(err, rel_err(got[r].cpu().numpy(), want.cpu().numpy()))
+                if r:
+                    wr.free()
+            if err > 1e-3:
+                raise SystemExit(f"bench.py: gathered LM-head logits differ from a one-GPU product by {err:.3e}")
+        if dist is not None:
+            dist.barrier()
         nbytes = rows * (cols // 256) * 210 + 4 * cols * tokens + 4 * rows * tokens
-        out[f"lm_head_q6k_262144x2560_batch{tokens}"] = {"us": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes": nbytes,
-                                                         "rows_per_gpu": count, "collective": "all_gather fp32 logits" if world > 1 else "none",
-                                                         "launch": "cuda graph" if timed.graphed else "eager"}
+        out[f"lm_head_q6k_262144x2560_batch{tokens}"] = {
+            "us": us, "compute_us": compute_us, "exchange_us": us - compute_us, "nccl_variant_us": nccl_us, "GBps": nbytes / us / 1e3,
+            "algorithmic_bytes": nbytes, "rows_per_gpu": count, "max_rel_err": err,
+            "exchange": "rq_exchange_gather: peer stores over NVLink + one flag per peer, the library's own kernel" if world > 1 else "none",
+            "checked": "gathered logits against rank 0's own product over every share" if world > 1 else "single GPU: nothing to gather",
+            "launch": "cuda graph" if graphed else "eager"}
+        ex.free()
     for w in copies:
         w.free()
     del copies
-    # ---- MoE bank: experts [first, first + count) of 256 on this rank
+
+    # ---- MoE bank: experts [ef, ef + ec) of 256 on this rank. The whole bank is drawn from one seed on every rank (the
+    # tensors are the model's), so that the shares belong to one bank and rank 0 can hold it whole for the check.
     experts, top, hidden, ffn = 256, 8, 2048, 512
     ef, ec = sharded.shard_range(experts, world, rank)
-    gen.manual_seed(3000 + rank)
+    bgen = torch.Generator(device=device)
+    bgen.manual_seed(3000)
 
     def host_blocks(n_rows, n_cols):
-        w32 = torch.randn(n_rows * n_cols, generator=gen, device=device) * 0.02
-        b = ctx.quantize(Q4_K, w32).cpu().numpy()
-        del w32
-        return b
+        parts = []
+        chunk_rows = max(1, (1 << 26) // n_cols)
+        for r0 in range(0, n_rows, chunk_rows):
+            nr = min(chunk_rows, n_rows - r0)
+            w32 = torch.randn(nr * n_cols, generator=bgen, device=device) * 0.02
+            parts.append(ctx.quantize(Q4_K, w32).cpu().numpy())
+            del w32
+        return np.concatenate(parts)
 
-    gate, up, down = host_blocks(ec * ffn, hidden), host_blocks(ec * ffn, hidden), host_blocks(ec * hidden, ffn)
-    shared = None
-    if rank == 0:
-        shared = (host_blocks(ffn, hidden), host_blocks(ffn, hidden), host_blocks(hidden, ffn), (torch.randn(hidden, generator=gen, device=device) * 0.02).cpu().numpy())
-    bank = ctx.moe_prepare(Q4_K, gate, up, down, ec, hidden, ffn, shared=shared)
-    del gate, up, down
+    gate, up, down = host_blocks(experts * ffn, hidden), host_blocks(experts * ffn, hidden), host_blocks(experts * hidden, ffn)
+    shared = (host_blocks(ffn, hidden), host_blocks(ffn, hidden), host_blocks(hidden, ffn), (torch.randn(hidden, generator=bgen, device=device) * 0.02).cpu().numpy())
+    bank = ctx.moe_prepare(Q4_K, gate, up, down, experts, hidden, ffn, expert_first=ef, expert_count=ec, shared=shared if rank == 0 else None)
     rgen = torch.Generator(device=device)
     rgen.manual_seed(3999)  # the router scores are the same on every rank (the router is replicated)
     expert_bytes = 3 * ffn * (hidden // 256) * 144
     for tokens in (1, 16):
         scores = torch.randn(experts, tokens, generator=rgen, device=device)
         xm = torch.randn(hidden, tokens, generator=rgen, device=device)
+        part = torch.empty(hidden, tokens, device=device)
         y = torch.empty(hidden, tokens, device=device)
+        ex = rq.Exchange(ctx, rank, world, hidden * tokens * 4)
+        ex.connect(share(ex.ipc_handle()))
+
+        def compute():
+            routing = ctx.moe_route(scores, top)
+            ctx.moe_forward(bank, xm, routing, top, include_shared=(rank == 0), y=part)  # the whole routing plane: a rank reads its experts' rows
+            return routing
 
         def moe_step():
-            routing = ctx.moe_route(scores, top)
-            ctx.moe_forward(bank, xm, routing, top, include_shared=(rank == 0), y=y)  # the whole routing plane: a rank reads its experts' rows
-            if dist is not None:
-                dist.all_reduce(y)
-            return y
+            compute()
+            if world > 1:
+                ex.reduce(part.reshape(-1), y.reshape(-1))
 
-        us = timed(moe_step, max(10, steps // 10))
+        def moe_step_nccl():
+            compute()
+            nccl.allreduce_sum(part.reshape(-1), y.reshape(-1))
+
+        compute_us = timed(compute, reps)
+        us = timed(moe_step, reps) if world > 1 else compute_us
+        graphed = timed.graphed
+        nccl_us = timed(moe_step_nccl, reps) if world > 1 else None
+        moe_step()
+        torch.cuda.synchronize()
+        result = (y if world > 1 else part).cpu().numpy()
+        err = 0.0
+        if world > 1 and rank == 0:
+            whole = ctx.moe_prepare(Q4_K, gate, up, down, experts, hidden, ffn, shared=shared)
+            want = ctx.moe_forward(whole, xm, ctx.moe_route(scores, top), top).cpu().numpy()
+            whole.free()
+            err = rel_err(result, want)
+            if err > 1e-3:
+                raise SystemExit(f"bench.py: the summed MoE output differs from a one-GPU bank by {err:.3e}")
+        if dist is not None:
+            dist.barrier()
         nbytes = tokens * ((top + 1) * expert_bytes + (top + 1) * 3 * 4 * (hidden + ffn))
-        loads = sharded.routed_bytes_per_rank(ctx.moe_route(scores, top), experts, world, expert_bytes)
-        out[f"moe_q4k_256e_top8_batch{tokens}"] = {"us": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes": nbytes, "experts_per_gpu": ec,
-                                                  "routed_bytes_per_rank_min_max": [min(loads), max(loads)],
-                                                  "collective": "all_reduce fp32 [hidden, tokens]" if world > 1 else "none",
-                                                  "launch": "cuda graph" if timed.graphed else "eager"}
-    ctx.check()
+        per_rank = sharded.routed_bytes_per_rank(compute(), experts, world, expert_bytes)
+        torch.cuda.synchronize()
+        out[f"moe_q4k_256e_top8_batch{tokens}"] = {
+            "us": us, "compute_us": compute_us, "exchange_us": us - compute_us, "nccl_variant_us": nccl_us, "GBps": nbytes / us / 1e3,
+            "algorithmic_bytes": nbytes, "experts_per_gpu": ec, "routed_bytes_per_rank_min_max": [min(per_rank), max(per_rank)], "max_rel_err": err,
+            "exchange": "rq_exchange_reduce: peer stores over NVLink, slots added in rank order by the library's own kernel" if world > 1 else "none",
+            "checked": "summed output against the whole bank on rank 0's one GPU" if world > 1 else "single GPU: nothing to sum",
+            "launch": "cuda graph" if graphed else "eager"}
+        ex.free()
     bank.free()
+    if nccl is not None:
+        nccl.destroy()
+    ctx.check()
     return out
 
 
-def run_other_configs(ctx, rq, torch, device):
-    """BASELINE's remaining single-GPU configs, device-timed on rank 0 (not the headline: recorded beside it):
-    the Q8_0 4096 x 4096 matvec (int8, one token) and the batched tensor-core product at 16 / 64 / 512 tokens."""
+def run_other_configs(ctx, rq, torch, oracle, ol, device):
+    """BASELINE's remaining single-GPU configs, device-timed on rank 0 (not the headline: recorded beside it): the Q8_0
+    4096 x 4096 matvec, the decode layer with fp32 activations and in Q4_0 (under `.int(8)` both as recipe computes it, over
+    the Q8_0 re-encode, and as the direct dot over the stored nibbles), `down` and the LM head under recipe's `.int(8)`,
+    and the batched tensor-core product at 16 / 64 / 512 tokens with fp32 and int8 activations."""
     out = {}
     gen = torch.Generator(device=device)
     gen.manual_seed(5)
     stream = torch.cuda.current_stream()
+    peak, _ = measured_peak_gbs()
 
     def quantised(t, rows, cols, copies):
         ws = []
@@ -612,32 +811,46 @@ def run_other_configs(ctx, rq, torch, device):
         torch.cuda.synchronize()
         return 1e3 * e0.elapsed_time(e1) / reps
 
+    def matvec_line(t, rows, cols, mode, copies, label, weights=None):
+        ws = weights or quantised(t, rows, cols, copies)
+        x = torch.randn(cols, generator=gen, device=device)
+        y = torch.empty(rows, device=device)
+        ctx.reserve(rows, cols, 1)
+        us = graph_time(lambda i: ctx.matvec(ws[i % len(ws)], x, y, act_mode=mode, step=32), 8 * len(ws))
+        nbytes = algo_bytes(ws[0].type, rows, cols)
+        out[label] = {"us": us, "GBps": nbytes / us / 1e3, "frac_of_hbm_measured": nbytes / us / 1e3 / peak, "algorithmic_bytes": nbytes}
+        return ws
+
     # cfg 1: Q8_0 4096 x 4096, eight copies in rotation (143 MB: larger than L2)
-    ws = quantised(Q8_0, 4096, 4096, 8)
-    x = torch.randn(4096, generator=gen, device=device)
-    y = torch.empty(4096, device=device)
-    us = graph_time(lambda i: ctx.matvec(ws[i % 8], x, y, act_mode=rq.ACT_INT8, step=32), 64)
-    nbytes = algo_bytes(Q8_0, 4096, 4096)
-    out["q8_0_4096x4096_int8_batch1"] = {"us": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes": nbytes}
-    for w in ws:
+    for w in matvec_line(Q8_0, 4096, 4096, rq.ACT_INT8, 8, "q8_0_4096x4096_int8_batch1"):
         w.free()
-    # cfg 5: the batched product, fp32 activations, tensor cores
+    # fp32 activations (the `.fp` handling, and every expert bank's)
+    for w in matvec_line(Q4_K, 14336, 4096, rq.ACT_FLOAT, 4, "q4k_14336x4096_float_batch1"):
+        w.free()
+    for w in matvec_line(Q6_K, 4096, 14336, rq.ACT_FLOAT, 4, "q6k_4096x14336_float_batch1"):
+        w.free()
+    # the Q4_0 layer's widest projection, and `down`: `.int(8)` as recipe computes it (the Q8_0 re-encode made at load) and
+    # the direct dot over the stored blocks
+    for t, rows, cols, name in ((Q4_0, 14336, 4096, "q4_0_14336x4096"), (Q6_K, 4096, 14336, "q6k_4096x14336")):
+        stored = matvec_line(t, rows, cols, rq.ACT_INT8, 4, f"{name}_int8_direct_batch1")
+        reenc = [ctx.int8_weight(w) for w in stored]
+        for w in stored:
+            w.free()
+        matvec_line(Q8_0, rows, cols, rq.ACT_INT8, 4, f"{name}_int8_recipe_q8_0_reencode_batch1", weights=reenc)
+        for w in reenc:
+            w.free()
+    # cfg 5: the batched product on the tensor cores, fp32 and int8 activations, each call's launches captured in a graph
     for name, t, rows, cols in (("q4k_14336x4096", Q4_K, 14336, 4096), ("q6k_4096x14336", Q6_K, 4096, 14336)):
         ws = quantised(t, rows, cols, 4)
+        ctx.reserve(rows, cols, 512)
         for tokens in (16, 64, 512):
             xb = torch.randn(tokens, cols, generator=gen, device=device)
             yb = torch.empty(tokens, rows, device=device)
-            for i in range(2):
-                ctx.matmul(ws[i], xb, yb)  # grows the scratch before timing
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for i in range(8):
-                ctx.matmul(ws[i % 4], xb, yb)
-            e1.record(stream)
-            torch.cuda.synchronize()
-            us = 1e3 * e0.elapsed_time(e1) / 8
-            out[f"matmul_{name}_tokens{tokens}"] = {"us": us, "TFLOPs_useful": 2.0 * rows * cols * tokens / us / 1e6}
+            for mode, tag in ((rq.ACT_FLOAT, ""), (rq.ACT_INT8, "_int8")):
+                us = graph_time(lambda i: ctx.matmul(ws[i % 4], xb, yb, act_mode=mode, step=32), 8)
+                flops = 2.0 * rows * cols * tokens
+                hbm_us = algo_bytes(t, rows, cols, tokens) / peak / 1e3
+                out[f"matmul_{name}_tokens{tokens}{tag}"] = {"us": us, "TFLOPs_useful": flops / us / 1e6, "hbm_time_us": hbm_us}
         for w in ws:
             w.free()
     ctx.check()

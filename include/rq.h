@@ -224,6 +224,102 @@ int rq_moe_forward(rq_ctx* ctx, rq_moe* moe, const float* x, int64_t x_k_stride,
                    int64_t routing_e_stride, int64_t routing_t_stride, int top_k, int tokens, int include_shared, float* y,
                    int64_t y_n_stride, int64_t y_t_stride, void* stream);
 
+/* ---- recorded sequences: one boundary crossing per step ------------------------------------------ */
+
+/* The reference crosses its host / device boundary once per step: recipe_model_step is one launch that
+ * walks every node of the step, with the planes between nodes resident on the device
+ * (recipe.rs:8262-8276). The same here: between rq_sequence_begin and rq_sequence_end the
+ * device-pointer entry points (rq_matvec, rq_matvec_multi, rq_matmul, rq_moe_route, rq_moe_forward, ...)
+ * called with the stream that rq_sequence_begin returns are recorded instead of run; rq_sequence_run
+ * replays the whole list as one submission, rq_sequence_run_host adds one copy in (host_in -> dev_in),
+ * one copy out (dev_out -> host_out) and one synchronisation. The planes between the calls are device
+ * buffers of the caller (rq_device_alloc for a host that has no allocator of its own).
+ * A recording cannot allocate: call rq_reserve for the widest recorded call first. Pointers, shapes
+ * and modes are fixed at recording time; the data in the planes is not. */
+typedef struct rq_sequence rq_sequence;
+int rq_device_alloc(rq_ctx* ctx, int64_t bytes, void** out);
+void rq_device_free(rq_ctx* ctx, void* ptr);
+int rq_sequence_begin(rq_ctx* ctx, void** stream_out);
+int rq_sequence_end(rq_ctx* ctx, rq_sequence** out);
+int rq_sequence_run(rq_sequence* seq, void* stream);
+int rq_sequence_run_host(rq_sequence* seq, const float* host_in, float* dev_in, int64_t in_floats, const float* dev_out, float* host_out, int64_t out_floats);
+void rq_sequence_free(rq_sequence* seq);
+
+/* ---- GGUF files: reader and tensor binding --------------------------------------------------- */
+
+/* A GGUF v3 file (or the complete split model its first shard names), mapped read-only. Replaces
+ * Gguf::open and the descriptors it yields (recipe.rs:9786-10326): little-endian header, metadata of
+ * the thirteen value kinds, tensor descriptors, data section at general.alignment (default 32), every
+ * tensor checked to lie inside its file. Needs no GPU. */
+typedef struct rq_gguf rq_gguf;
+int rq_gguf_open(const char* path, rq_gguf** out);
+void rq_gguf_close(rq_gguf* gguf);
+/* Tensor descriptors in file order (GgufTensor, recipe.rs:9846-9853): name, GGML type id, shape
+ * (dims[0] = the row length k, as GGUF stores it), bytes, and the bytes themselves in the mapping. */
+int rq_gguf_tensor_count(const rq_gguf* gguf);
+int rq_gguf_find(const rq_gguf* gguf, const char* name); /* index, or -1 */
+const char* rq_gguf_tensor_name(const rq_gguf* gguf, int index);
+int rq_gguf_tensor_type(const rq_gguf* gguf, int index);
+int rq_gguf_tensor_dims(const rq_gguf* gguf, int index, int64_t* shape, int capacity); /* returns the number of dimensions */
+int64_t rq_gguf_tensor_bytes(const rq_gguf* gguf, int index);
+const void* rq_gguf_tensor_data(const rq_gguf* gguf, int index);
+/* First-shard metadata (Gguf::value / integer_at / float_at, recipe.rs:10127-10160). kind: the GGUF value
+ * kind 0..12, -1 when absent. Integers of any width (and bools) come back as u64, floats as f64. */
+int rq_gguf_meta_count(const rq_gguf* gguf);
+const char* rq_gguf_meta_key(const rq_gguf* gguf, int index);
+int rq_gguf_meta_kind(const rq_gguf* gguf, const char* key);
+int rq_gguf_meta_integer(const rq_gguf* gguf, const char* key, uint64_t* out);
+int rq_gguf_meta_float(const rq_gguf* gguf, const char* key, double* out);
+const char* rq_gguf_meta_text(const rq_gguf* gguf, const char* key);
+int64_t rq_gguf_meta_array_length(const rq_gguf* gguf, const char* key);
+const char* rq_gguf_meta_array_text(const rq_gguf* gguf, const char* key, int64_t index);
+/* Binds rows [row_first, row_first + row_count) of a stored [k, n] (or [k, n, experts]: every expert's rows,
+ * one after another) tensor as a resident weight; row_count <= 0 binds every row. Replaces Gguf::stored +
+ * the tape's weight upload (recipe.rs:10196-10203, :22200) and GgufTensor::rows (:9873-9880). */
+int rq_gguf_bind(rq_ctx* ctx, const rq_gguf* gguf, const char* name, int64_t row_first, int64_t row_count, rq_weight** out);
+/* Binds experts [expert_first, expert_first + expert_count) of a gguf_moe block from its three [k, n, experts]
+ * tensors (GgufTensor::expert, recipe.rs:9862-9869; MoeTensors, :14382-14420) and, when named, a gated shared
+ * expert (three [k, n] tensors of the bank's format and an F32 gate vector). expert_count <= 0: every expert. */
+int rq_gguf_bind_experts(rq_ctx* ctx, const rq_gguf* gguf, const char* gate, const char* up, const char* down, int expert_first, int expert_count,
+                         const char* shared_gate, const char* shared_up, const char* shared_down, const char* shared_gate_vector, rq_moe** out);
+
+/* ---- the exchange of the sharded configs ---------------------------------------------------- */
+
+/* The exchange through the host's own NCCL communicator (`nccl_comm` is its ncclComm_t): the ranks'
+ * slices of a row-split plane are gathered rank after rank (gathered: [nranks][count_per_rank]), or
+ * the ranks' planes are summed. Device pointers; enqueued on `stream`. Replaces Primitive::Exchange
+ * after a row split (gather, recipe.rs:5386-5394) and after a term split (die-order sum,
+ * recipe.rs:5395-5441; buffers :20412-20486). libnccl.so.2 is looked up at run time: RQ_ERR_UNSUPPORTED
+ * when the process has none. */
+int rq_allgather_rows(rq_ctx* ctx, void* nccl_comm, const float* local, float* gathered, int64_t count_per_rank, void* stream);
+int rq_allreduce_sum(rq_ctx* ctx, void* nccl_comm, const float* local, float* summed, int64_t count, void* stream);
+/* For a host without a communicator of its own: rank 0 makes an id (128 bytes, ncclUniqueId), hands it to
+ * the other ranks by whatever channel it has, and every rank creates its communicator from it. */
+int rq_nccl_unique_id(void* id128);
+int rq_nccl_comm_create(rq_ctx* ctx, const void* id128, int nranks, int rank, void** nccl_comm_out);
+void rq_nccl_comm_destroy(void* nccl_comm);
+
+/* The library's own exchange over NVLink peer memory: no collective library on the path, one kernel
+ * per exchange. Every rank owns a buffer of per-rank slots which its peers map; the kernel stores this
+ * rank's slice into its slot on every rank (plain peer stores), raises a flag on each peer, waits for
+ * the peers' flags (bounded: a peer that never arrives makes rq_check report RQ_ERR_WAIT) and then
+ * writes the result: the slots one after another (gather), or their sum in rank order (reduce: the same
+ * bits on every rank and every run, as the reference's die-order sum, recipe.rs:5395-5441).
+ * Set-up, once: every rank creates its exchange (slot_bytes = the largest slice it will ever send),
+ * exports a 64-byte handle (a CUDA IPC handle) to every other rank, and connects with all ranks' handles
+ * in rank order ([nranks][64]; its own entry is ignored). Ranks that share one process pass their
+ * buffers (rq_exchange_buffer) as `same_process_buffers` instead and `handles` null.
+ * Every rank must make the same sequence of gather / reduce calls with the same counts. Calls may be
+ * captured into a CUDA graph and replayed. At most 16 ranks. */
+typedef struct rq_exchange rq_exchange;
+int rq_exchange_create(rq_ctx* ctx, int rank, int nranks, int64_t slot_bytes, rq_exchange** out);
+int rq_exchange_handle(rq_exchange* ex, void* handle64);
+void* rq_exchange_buffer(rq_exchange* ex);
+int rq_exchange_connect(rq_exchange* ex, const void* handles, const void* const* same_process_buffers);
+int rq_exchange_gather(rq_exchange* ex, const float* local, int64_t count, float* gathered, void* stream);
+int rq_exchange_reduce(rq_exchange* ex, const float* local, int64_t count, float* summed, void* stream);
+void rq_exchange_free(rq_exchange* ex);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,6 +12,9 @@ from .capi import (  # noqa: F401
     Q6_K,
     Q8_0,
     Context,
+    Exchange,
+    Gguf,
+    NcclComm,
     RqError,
     Weight,
     block_bytes,
@@ -22,5 +25,5 @@ from .capi import (  # noqa: F401
 
 __all__ = [
     "ACT_FLOAT", "ACT_INT8", "Q4_0", "Q4_K", "Q6_K", "Q8_0",
-    "Context", "RqError", "Weight", "block_bytes", "block_values", "library_path", "load_library",
+    "Context", "Exchange", "Gguf", "NcclComm", "RqError", "Weight", "block_bytes", "block_values", "library_path", "load_library",
 ]

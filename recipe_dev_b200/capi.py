@@ -74,6 +74,44 @@ def _declare(lib) -> None:
         "rq_moe_free": (None, [p, p]),
         "rq_moe_bytes": (i64, [p]),
         "rq_moe_forward": (i32, [p, p, f32p, i64, i64, f32p, i64, i64, i32, i32, i32, f32p, i64, i64, p]),
+        "rq_device_alloc": (i32, [p, i64, C.POINTER(p)]),
+        "rq_device_free": (None, [p, p]),
+        "rq_sequence_begin": (i32, [p, C.POINTER(p)]),
+        "rq_sequence_end": (i32, [p, C.POINTER(p)]),
+        "rq_sequence_run": (i32, [p, p]),
+        "rq_sequence_run_host": (i32, [p, f32p, f32p, i64, f32p, f32p, i64]),
+        "rq_sequence_free": (None, [p]),
+        "rq_gguf_open": (i32, [C.c_char_p, C.POINTER(p)]),
+        "rq_gguf_close": (None, [p]),
+        "rq_gguf_tensor_count": (i32, [p]),
+        "rq_gguf_find": (i32, [p, C.c_char_p]),
+        "rq_gguf_tensor_name": (C.c_char_p, [p, i32]),
+        "rq_gguf_tensor_type": (i32, [p, i32]),
+        "rq_gguf_tensor_dims": (i32, [p, i32, C.POINTER(i64), i32]),
+        "rq_gguf_tensor_bytes": (i64, [p, i32]),
+        "rq_gguf_tensor_data": (p, [p, i32]),
+        "rq_gguf_meta_count": (i32, [p]),
+        "rq_gguf_meta_key": (C.c_char_p, [p, i32]),
+        "rq_gguf_meta_kind": (i32, [p, C.c_char_p]),
+        "rq_gguf_meta_integer": (i32, [p, C.c_char_p, C.POINTER(C.c_uint64)]),
+        "rq_gguf_meta_float": (i32, [p, C.c_char_p, C.POINTER(C.c_double)]),
+        "rq_gguf_meta_text": (C.c_char_p, [p, C.c_char_p]),
+        "rq_gguf_meta_array_length": (i64, [p, C.c_char_p]),
+        "rq_gguf_meta_array_text": (C.c_char_p, [p, C.c_char_p, i64]),
+        "rq_gguf_bind": (i32, [p, p, C.c_char_p, i64, i64, C.POINTER(p)]),
+        "rq_gguf_bind_experts": (i32, [p, p, C.c_char_p, C.c_char_p, C.c_char_p, i32, i32, C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.POINTER(p)]),
+        "rq_allgather_rows": (i32, [p, p, f32p, f32p, i64, p]),
+        "rq_allreduce_sum": (i32, [p, p, f32p, f32p, i64, p]),
+        "rq_nccl_unique_id": (i32, [p]),
+        "rq_nccl_comm_create": (i32, [p, p, i32, i32, C.POINTER(p)]),
+        "rq_nccl_comm_destroy": (None, [p]),
+        "rq_exchange_create": (i32, [p, i32, i32, i64, C.POINTER(p)]),
+        "rq_exchange_handle": (i32, [p, p]),
+        "rq_exchange_buffer": (p, [p]),
+        "rq_exchange_connect": (i32, [p, p, p]),
+        "rq_exchange_gather": (i32, [p, f32p, i64, f32p, p]),
+        "rq_exchange_reduce": (i32, [p, f32p, i64, f32p, p]),
+        "rq_exchange_free": (None, [p]),
     }
     for name, (res, args) in optional.items():
         if hasattr(lib, name):
@@ -210,6 +248,18 @@ class Context:
 
     def wait_selftest(self, stream=None) -> None:
         _check(self.lib.rq_wait_selftest(self.handle, _stream(stream)))
+
+    # ---- recorded sequences ----
+    def sequence_begin(self) -> int:
+        """Starts recording; returns the stream (an int) to pass to the calls that are to be recorded."""
+        out = C.c_void_p()
+        _check(self.lib.rq_sequence_begin(self.handle, C.byref(out)))
+        return out.value
+
+    def sequence_end(self) -> "Sequence":
+        out = C.c_void_p()
+        _check(self.lib.rq_sequence_end(self.handle, C.byref(out)))
+        return Sequence(self, out.value)
 
     # ---- weights ----
     def weight_from_host(self, ggml_type: int, blocks: np.ndarray, rows: int, cols: int, row_first: int = 0, row_count: int | None = None) -> Weight:
@@ -386,3 +436,170 @@ class Context:
         out = torch.empty((tokens, cols // 32, 36), dtype=torch.uint8, device=x.device)
         _check(self.lib.rq_quantize_activations(self.handle, _ptr(x2), x2.stride(1), x2.stride(0), cols, tokens, step, _ptr(out), _stream(stream)))
         return out
+
+
+class NcclComm:
+    """An NCCL communicator made through the library (rq_nccl_comm_create) for hosts that have none of their own."""
+
+    def __init__(self, ctx: "Context", handle: int, rank: int, nranks: int):
+        self.ctx, self.handle, self.rank, self.nranks = ctx, handle, rank, nranks
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        _check(load_library().rq_nccl_unique_id(buf))
+        return buf.raw
+
+    @classmethod
+    def create(cls, ctx: "Context", unique_id: bytes, nranks: int, rank: int) -> "NcclComm":
+        out = C.c_void_p()
+        _check(ctx.lib.rq_nccl_comm_create(ctx.handle, unique_id, nranks, rank, C.byref(out)))
+        return cls(ctx, out.value, rank, nranks)
+
+    def allgather_rows(self, local, gathered, stream=None):
+        """local: CUDA fp32 [count]; gathered: [nranks, count]."""
+        _check(self.ctx.lib.rq_allgather_rows(self.ctx.handle, self.handle, _ptr(local), _ptr(gathered), local.numel(), _stream(stream)))
+        return gathered
+
+    def allreduce_sum(self, local, summed, stream=None):
+        _check(self.ctx.lib.rq_allreduce_sum(self.ctx.handle, self.handle, _ptr(local), _ptr(summed), local.numel(), _stream(stream)))
+        return summed
+
+    def destroy(self) -> None:
+        if self.handle:
+            self.ctx.lib.rq_nccl_comm_destroy(self.handle)
+            self.handle = 0
+
+
+class Exchange:
+    """The library's own exchange over peer memory (rq_exchange): gather and rank-order sum, one kernel each."""
+
+    def __init__(self, ctx: "Context", rank: int, nranks: int, slot_bytes: int):
+        self.ctx, self.rank, self.nranks = ctx, rank, nranks
+        out = C.c_void_p()
+        _check(ctx.lib.rq_exchange_create(ctx.handle, rank, nranks, slot_bytes, C.byref(out)))
+        self.handle = out.value
+
+    def ipc_handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        _check(self.ctx.lib.rq_exchange_handle(self.handle, buf))
+        return buf.raw
+
+    def connect(self, handles: list[bytes]) -> None:
+        """handles: every rank's 64-byte handle, in rank order."""
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.nranks
+        _check(self.ctx.lib.rq_exchange_connect(self.handle, blob, None))
+
+    def connect_same_process(self, exchanges: list["Exchange"]) -> None:
+        ptrs = (C.c_void_p * self.nranks)(*[e.ctx.lib.rq_exchange_buffer(e.handle) for e in exchanges])
+        _check(self.ctx.lib.rq_exchange_connect(self.handle, None, ptrs))
+
+    def gather(self, local, gathered, stream=None):
+        """local: CUDA fp32 [count] (contiguous); gathered: [nranks, count]."""
+        _check(self.ctx.lib.rq_exchange_gather(self.handle, _ptr(local), local.numel(), _ptr(gathered), _stream(stream)))
+        return gathered
+
+    def reduce(self, local, summed, stream=None):
+        _check(self.ctx.lib.rq_exchange_reduce(self.handle, _ptr(local), local.numel(), _ptr(summed), _stream(stream)))
+        return summed
+
+    def free(self) -> None:
+        if self.handle:
+            self.ctx.lib.rq_exchange_free(self.handle)
+            self.handle = 0
+
+
+class Gguf:
+    """A GGUF v3 file (or split model) mapped read-only: tensor descriptors, metadata, binding to resident weights."""
+
+    def __init__(self, path):
+        self.lib = load_library()
+        out = C.c_void_p()
+        _check(self.lib.rq_gguf_open(str(path).encode(), C.byref(out)))
+        self.handle = out.value
+
+    def close(self) -> None:
+        if getattr(self, "handle", 0):
+            self.lib.rq_gguf_close(self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def tensors(self) -> list[dict]:
+        out = []
+        for i in range(self.lib.rq_gguf_tensor_count(self.handle)):
+            dims = (C.c_int64 * 8)()
+            n = self.lib.rq_gguf_tensor_dims(self.handle, i, dims, 8)
+            out.append({"name": self.lib.rq_gguf_tensor_name(self.handle, i).decode(), "type": self.lib.rq_gguf_tensor_type(self.handle, i),
+                        "shape": [int(dims[d]) for d in range(n)], "bytes": int(self.lib.rq_gguf_tensor_bytes(self.handle, i))})
+        return out
+
+    def data(self, name: str) -> np.ndarray:
+        """The tensor's bytes as the file holds them (a copy of the mapped view)."""
+        i = self.lib.rq_gguf_find(self.handle, name.encode())
+        if i < 0:
+            raise KeyError(name)
+        n = int(self.lib.rq_gguf_tensor_bytes(self.handle, i))
+        return np.ctypeslib.as_array((C.c_uint8 * n).from_address(self.lib.rq_gguf_tensor_data(self.handle, i))).copy()
+
+    def keys(self) -> list[str]:
+        return [self.lib.rq_gguf_meta_key(self.handle, i).decode() for i in range(self.lib.rq_gguf_meta_count(self.handle))]
+
+    def integer(self, key: str) -> int:
+        v = C.c_uint64()
+        _check(self.lib.rq_gguf_meta_integer(self.handle, key.encode(), C.byref(v)))
+        return int(v.value)
+
+    def float(self, key: str) -> float:
+        v = C.c_double()
+        _check(self.lib.rq_gguf_meta_float(self.handle, key.encode(), C.byref(v)))
+        return float(v.value)
+
+    def text(self, key: str):
+        v = self.lib.rq_gguf_meta_text(self.handle, key.encode())
+        return None if v is None else v.decode()
+
+    def array_text(self, key: str) -> list[str]:
+        n = self.lib.rq_gguf_meta_array_length(self.handle, key.encode())
+        if n < 0:
+            raise KeyError(key)
+        return [self.lib.rq_gguf_meta_array_text(self.handle, key.encode(), i).decode() for i in range(n)]
+
+    def bind(self, ctx: "Context", name: str, row_first: int = 0, row_count: int = 0) -> Weight:
+        out = C.c_void_p()
+        _check(self.lib.rq_gguf_bind(ctx.handle, self.handle, name.encode(), row_first, row_count, C.byref(out)))
+        return Weight(ctx, out.value)
+
+    def bind_experts(self, ctx: "Context", gate: str, up: str, down: str, expert_first: int = 0, expert_count: int = 0, shared=None) -> MoeBank:
+        """shared = (gate, up, down, gate_vector) tensor names or None."""
+        sh = [None] * 4 if shared is None else [s.encode() for s in shared]
+        out = C.c_void_p()
+        _check(self.lib.rq_gguf_bind_experts(ctx.handle, self.handle, gate.encode(), up.encode(), down.encode(), expert_first, expert_count, *sh, C.byref(out)))
+        dims = (C.c_int64 * 8)()
+        self.lib.rq_gguf_tensor_dims(self.handle, self.lib.rq_gguf_find(self.handle, gate.encode()), dims, 8)
+        return MoeBank(ctx, out.value, int(dims[0]), int(dims[1]))
+
+
+class Sequence:
+    """A recorded list of calls (rq_sequence): replayed as one submission."""
+
+    def __init__(self, ctx: "Context", handle: int):
+        self.ctx, self.handle = ctx, handle
+
+    def run(self, stream=None) -> None:
+        _check(self.ctx.lib.rq_sequence_run(self.handle, _stream(stream)))
+
+    def run_host(self, host_in: np.ndarray, dev_in, dev_out, host_out: np.ndarray) -> np.ndarray:
+        """One copy in (host_in -> dev_in), the recorded calls, one copy out (dev_out -> host_out), one synchronisation."""
+        _check(self.ctx.lib.rq_sequence_run_host(self.handle, host_in.ctypes.data, _ptr(dev_in), host_in.size, _ptr(dev_out), host_out.ctypes.data, host_out.size))
+        return host_out
+
+    def free(self) -> None:
+        if self.handle:
+            self.ctx.lib.rq_sequence_free(self.handle)
+            self.handle = 0

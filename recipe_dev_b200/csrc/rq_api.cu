@@ -101,6 +101,9 @@ int rq_order_work_areas(rq_ctx* ctx, cudaStream_t s) {
 }
 
 static int grow_act_scratch(rq_ctx* ctx, size_t want) {
+    if (ctx->recording)
+        return rq_fail(RQ_ERR_INVALID, "a recorded call needs %zu bytes of work area and the context holds %zu: call rq_reserve for the widest call before rq_sequence_begin",
+                       want, ctx->act_scratch_bytes);
     // the old buffer may still be read by kernels in flight
     RQ_CUDA(cudaDeviceSynchronize());
     if (ctx->act_scratch) RQ_CUDA(cudaFree(ctx->act_scratch));
@@ -381,11 +384,17 @@ extern "C" int rq_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_
     if (rc) return rc;
     if (sk <= 0 || yn <= 0 || (tokens > 1 && (st <= 0 || yt <= 0))) return rq_fail(RQ_ERR_INVALID, "rq_matmul: strides must be positive");
     DeviceGuard guard(ctx->device);
+    // K-quant weights: the integer-operand tensor-core kernel, for fp32 activations and for int8 windows of four and more
+    // positions (fewer go four to a pass through the matvec kernel's exact integer dots)
+    if (act_mode == RQ_ACT_FLOAT || (act_mode == RQ_ACT_INT8 && tokens >= 4)) {
+        rc = rq_launch_matmul_kq(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, step, (cudaStream_t)stream);
+        if (rc != RQ_ERR_UNSUPPORTED) return rc;
+    }
     if (act_mode == RQ_ACT_FLOAT) {
         rc = rq_launch_matmul(ctx, w, x, sk, st, tokens, y, yn, yt, (cudaStream_t)stream);
         if (rc != RQ_ERR_UNSUPPORTED) return rc;
     }
-    // int8 activations (exact integer dots) and odd widths go through the matvec kernels, four tokens a pass
+    // int8 activations over the 32-value formats and odd widths go through the matvec kernels, four tokens a pass
     return rq_launch_gemv(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, step, (cudaStream_t)stream);
 }
 
@@ -495,5 +504,102 @@ extern "C" int rq_quantize_activations(rq_ctx* ctx, const float* x, int64_t sk, 
     rc = rq_launch_act_quant(x, sk, st, cols, tokens, step, ctx->act_scratch, (uint8_t*)dev_records, (cudaStream_t)stream);
     if (rc) return rc;
     ctx->act_cols = cols; ctx->act_tokens = tokens; ctx->act_step = step;
+    return RQ_OK;
+}
+
+// ---- recorded sequences: one boundary crossing per step ----------------------------------------------
+
+struct rq_sequence {
+    rq_ctx* ctx;
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+};
+
+extern "C" int rq_device_alloc(rq_ctx* ctx, int64_t bytes, void** out) {
+    if (!ctx || !out || bytes <= 0) return rq_fail(RQ_ERR_INVALID, "rq_device_alloc: null argument or no bytes");
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaMalloc(out, (size_t)bytes);
+    if (e != cudaSuccess) { *out = nullptr; return rq_fail(RQ_ERR_ALLOC, "device buffer of %lld bytes: %s", (long long)bytes, cudaGetErrorString(e)); }
+    return RQ_OK;
+}
+extern "C" void rq_device_free(rq_ctx* ctx, void* ptr) {
+    if (!ctx || !ptr) return;
+    DeviceGuard guard(ctx->device);
+    cudaFree(ptr);
+}
+
+extern "C" int rq_sequence_begin(rq_ctx* ctx, void** stream_out) {
+    if (!ctx || !stream_out) return rq_fail(RQ_ERR_INVALID, "rq_sequence_begin: null argument");
+    if (ctx->recording) return rq_fail(RQ_ERR_INVALID, "rq_sequence_begin: the context is already recording");
+    DeviceGuard guard(ctx->device);
+    RQ_CUDA(cudaStreamSynchronize(ctx->stream));
+    RQ_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->recording = true;
+    ctx->work_stream = ctx->stream;  // the recorded calls share this stream: no event is needed between them
+    ctx->work_stream_set = true;
+    *stream_out = ctx->stream;
+    return RQ_OK;
+}
+
+extern "C" int rq_sequence_end(rq_ctx* ctx, rq_sequence** out) {
+    if (!ctx || !out) return rq_fail(RQ_ERR_INVALID, "rq_sequence_end: null argument");
+    *out = nullptr;
+    if (!ctx->recording) return rq_fail(RQ_ERR_INVALID, "rq_sequence_end: the context is not recording");
+    DeviceGuard guard(ctx->device);
+    ctx->recording = false;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (e != cudaSuccess || !graph) { cudaGetLastError(); return rq_fail(RQ_ERR_CUDA, "the recording was invalidated (a recorded call failed or did something a recording cannot hold): %s", cudaGetErrorString(e)); }
+    rq_sequence* seq = new (std::nothrow) rq_sequence();
+    if (!seq) { cudaGraphDestroy(graph); return rq_fail(RQ_ERR_ALLOC, "out of host memory"); }
+    seq->ctx = ctx; seq->graph = graph; seq->exec = nullptr;
+    e = cudaGraphInstantiate(&seq->exec, graph, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(graph); delete seq; return rq_fail(RQ_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
+    e = cudaGraphUpload(seq->exec, ctx->stream);  // so that the first run is not the one that pays for the upload
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { cudaGraphExecDestroy(seq->exec); cudaGraphDestroy(graph); delete seq; return rq_fail(RQ_ERR_CUDA, "cudaGraphUpload: %s", cudaGetErrorString(e)); }
+    *out = seq;
+    return RQ_OK;
+}
+
+extern "C" void rq_sequence_free(rq_sequence* seq) {
+    if (!seq) return;
+    DeviceGuard guard(seq->ctx->device);
+    cudaStreamSynchronize(seq->ctx->stream);
+    if (seq->exec) cudaGraphExecDestroy(seq->exec);
+    if (seq->graph) cudaGraphDestroy(seq->graph);
+    delete seq;
+}
+
+extern "C" int rq_sequence_run(rq_sequence* seq, void* stream) {
+    if (!seq) return rq_fail(RQ_ERR_INVALID, "rq_sequence_run: null sequence");
+    DeviceGuard guard(seq->ctx->device);
+    int rc = rq_order_work_areas(seq->ctx, (cudaStream_t)stream);
+    if (rc) return rc;
+    RQ_CUDA(cudaGraphLaunch(seq->exec, (cudaStream_t)stream));
+    return RQ_OK;
+}
+
+extern "C" int rq_sequence_run_host(rq_sequence* seq, const float* host_in, float* dev_in, int64_t in_floats, const float* dev_out, float* host_out, int64_t out_floats) {
+    if (!seq || !host_in || !dev_in || !dev_out || !host_out) return rq_fail(RQ_ERR_INVALID, "rq_sequence_run_host: null argument");
+    if (in_floats <= 0 || out_floats <= 0) return rq_fail(RQ_ERR_INVALID, "rq_sequence_run_host: in_floats and out_floats must be positive");
+    rq_ctx* ctx = seq->ctx;
+    DeviceGuard guard(ctx->device);
+    // pinned staging on both sides, so that the two copies are asynchronous and the call synchronises once
+    float* unused = nullptr; size_t zero = 0;
+    const size_t ib = (size_t)in_floats * 4, ob = (size_t)out_floats * 4;
+    if (ib > ctx->pin_x_bytes) { if (ctx->pin_x) cudaFreeHost(ctx->pin_x); ctx->pin_x = nullptr; ctx->pin_x_bytes = 0; RQ_CUDA(cudaMallocHost(&ctx->pin_x, ib)); ctx->pin_x_bytes = ib; }
+    if (ob > ctx->pin_y_bytes) { if (ctx->pin_y) cudaFreeHost(ctx->pin_y); ctx->pin_y = nullptr; ctx->pin_y_bytes = 0; RQ_CUDA(cudaMallocHost(&ctx->pin_y, ob)); ctx->pin_y_bytes = ob; }
+    (void)unused; (void)zero;
+    memcpy(ctx->pin_x, host_in, ib);
+    int rc = rq_order_work_areas(ctx, ctx->stream);
+    if (rc) return rc;
+    RQ_CUDA(cudaMemcpyAsync(dev_in, ctx->pin_x, ib, cudaMemcpyHostToDevice, ctx->stream));
+    RQ_CUDA(cudaGraphLaunch(seq->exec, ctx->stream));
+    RQ_CUDA(cudaMemcpyAsync(ctx->pin_y, dev_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    RQ_CUDA(cudaMemcpyAsync(ctx->pin_flag, ctx->error_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    RQ_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (*ctx->pin_flag) return rq_check(ctx);
+    memcpy(host_out, ctx->pin_y, ob);
     return RQ_OK;
 }

@@ -97,12 +97,20 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: false when the time limit ran out (the caller records the error and stops waiting).
+// Bounded wait: false when the time limit ran out (the caller records the error and stops waiting). Reading
+// %globaltimer costs about a microsecond, so the clock is looked at only every 256th unsuccessful try (a try itself
+// suspends the thread for a short, system-chosen time).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    while (!mbar_try_wait(bar, parity))
-        if (global_ns() - t0 > limit_ns) return false;
+    unsigned long long t0 = 0;
+    uint32_t tries = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++tries & 255u) == 0) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_ns) return false;
+        }
+    }
     return true;
 }
 // Weights are read once per launch: the copies carry an evict-first L2 policy, so the stream does not push

@@ -46,6 +46,7 @@ struct rq_ctx {
     // the stream of the last call that used the context's work areas (the activation scratch, a bank's plans), and the event
     // a call on another stream waits for before it touches them
     cudaStream_t work_stream; bool work_stream_set; cudaEvent_t work_event;
+    bool recording;  // between rq_sequence_begin and rq_sequence_end: the context's stream is capturing, nothing may allocate
 };
 
 int rq_fail(int status, const char* fmt, ...);
@@ -99,6 +100,13 @@ int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const f
 int rq_launch_gemv_tiled_int8(rq_ctx* ctx, const rq_weight* w, int tokens, float* y, int64_t yn, int64_t yt, const uint8_t* act, cudaStream_t s);
 // RQ_ERR_UNSUPPORTED (no error text) = width not served by the tensor-core kernel
 int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s);
+// The K-quant batched product with integer weight operands (rq_matmul_kq.cu): FLOAT or INT8 activations.
+// RQ_ERR_UNSUPPORTED (no error text) = not a Q4_K / Q6_K weight.
+int rq_launch_matmul_kq(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, int act_mode,
+                        int step, cudaStream_t s);
+size_t rq_matmul_kq_scratch_bytes(const rq_ctx* ctx, int type, int64_t rows, int64_t cols, int tokens);
+// y[row][token] = the splits' partial sums ([split][token][row]) added in split order
+int rq_launch_sum_splits(const float* partial, int splits, int64_t rows, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s);
 // scratch bytes rq_launch_matmul takes for a weight of this shape and this many tokens (its activation image and split-K sums)
 size_t rq_matmul_scratch_bytes(const rq_ctx* ctx, int64_t rows, int64_t cols, int tokens);
 int rq_launch_quantize(int type, const float* values, int64_t count, uint8_t* blocks, cudaStream_t s);

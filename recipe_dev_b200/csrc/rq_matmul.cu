@@ -25,10 +25,13 @@
 // Every wait is bounded in time; a wait that runs out records a code in the context's error word,
 // the thread stops waiting and the CTA still frees its tensor memory before it exits.
 #include "rq_internal.cuh"
+#include "rq_mma.cuh"
+
+using namespace rqmma;
 
 namespace {
 
-constexpr int BM = 128, BK = 64, kStages = 3;
+constexpr int kStages = 3;
 constexpr int kStageWarps = 8, kDrainWarps = 8;
 constexpr int kStagers = kStageWarps * 32;
 constexpr int kMmaWarp = kStageWarps + kDrainWarps, kCopyWarp = kMmaWarp + 1;
@@ -51,73 +54,6 @@ struct MatmulParams {
     unsigned long long wait_ns;  // bounded waits give up after this long
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)); }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory"); }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// a try_wait that lets the hardware park the thread for up to `ns` (it wakes when the phase completes)
-__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok)
-                 : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
-                 : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    while (!mbar_try_wait_parked(bar, parity, 2000u))  // parked waits do not eat the staging warps' issue slots
-        if (global_ns() - t0 > limit_ns) return false;
-    return true;
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes),
-                 "r"(smem_u32(bar))
-                 : "memory");
-}
-
-// K-major, 128-byte-swizzled operand tile of 128-byte rows: rows 128 bytes apart, groups of eight
-// rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type SWIZZLE_128B.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    uint64_t d = (uint64_t)((addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
-    d |= (uint64_t)1 << 46;                 // descriptor version
-    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
-    return d;
-}
-// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = bn
-__device__ __forceinline__ uint32_t instr_desc(int bn) { return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24); }
-
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// sixteen fp32 columns of this warp's 32 accumulator rows
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
-          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 // Weights are scaled by 2^8 before the split and the accumulator by 2^-8 after: a weight of 0.02
 // leaves a residual near 1e-5, which fp16 could only hold as a subnormal with a few bits; scaled, the
 // residual keeps its eleven. (Weights of magnitude 255 and more would overflow fp16; GGUF model
@@ -139,8 +75,6 @@ __device__ __forceinline__ void split8(const float* v, float scale, uint4& hi, u
     hi = make_uint4(hw[0], hw[1], hw[2], hw[3]);
     lo = make_uint4(lw[0], lw[1], lw[2], lw[3]);
 }
-// Swizzle<3,4,3>: the 16-byte chunk index of a 128-byte row, xor the row within its group of eight
-__device__ __forceinline__ int swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
 // ------------------------------------------------------------------------------------------
 // The raw bytes behind 32 consecutive values of one row (`half` 0 or 1 of a 64-wide slice at k0),
@@ -506,7 +440,14 @@ static MatmulCut matmul_cut(int sm_count, int64_t rows, int64_t cols, int tokens
 }
 size_t rq_matmul_scratch_bytes(const rq_ctx* ctx, int64_t rows, int64_t cols, int tokens) {
     const MatmulCut c = matmul_cut(ctx->sm_count, rows, cols, tokens);
-    return c.xs_bytes + c.partial_bytes;
+    size_t want = c.xs_bytes + c.partial_bytes;
+    if (cols % 256 == 0) {
+        // the K-quant kernel's images (int8 records included), for either K-quant format
+        const size_t a = rq_matmul_kq_scratch_bytes(ctx, RQ_Q4_K, rows, cols, tokens), b = rq_matmul_kq_scratch_bytes(ctx, RQ_Q6_K, rows, cols, tokens);
+        if (a > want) want = a;
+        if (b > want) want = b;
+    }
+    return want;
 }
 
 int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s) {
@@ -545,8 +486,12 @@ int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk
         default: return RQ_ERR_UNSUPPORTED;
     }
     if (rc || splits == 1) return rc;
+    return rq_launch_sum_splits(p.partial, splits, w->rows, tokens, y, yn, yt, s);
+}
+
+int rq_launch_sum_splits(const float* partial, int splits, int64_t rows, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
-    const int64_t total = w->rows * tokens;
+    const int64_t total = rows * tokens;
     cfg.gridDim = dim3((unsigned)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184));
     cfg.blockDim = dim3(256);
     cfg.stream = s;
@@ -555,6 +500,6 @@ int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_sum_splits_kernel, (const float*)p.partial, splits, (int64_t)w->rows, tokens, y, yn, yt));
+    RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_sum_splits_kernel, partial, splits, rows, tokens, y, yn, yt));
     return RQ_OK;
 }

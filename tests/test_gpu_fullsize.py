@@ -6,7 +6,9 @@ sample of rows only. Beside that sample:
   * scaling x by two scales an int8 result by two, bit for bit (the codes do not change, the steps double exactly);
   * a row range uploaded on its own (a die's share of a row split) gives the bits the whole matrix gives for those rows;
   * the dequantised matrix is the oracle's on the sampled rows, bit for bit;
-  * the batched product equals the matvec within the fp32 noise of either, at every token count of the batched config.
+  * the batched product, the Q8_0 and Q4_0 configs, the LM head at four tokens and every token of the expert bank meet
+    the oracle on sampled rows as well; `.int(8)` over a lone Q6_K / Q4_0 tensor is checked both as recipe computes it
+    (Q8_0 re-encode at load) and as the direct dot over the stored blocks.
 """
 import numpy as np
 import pytest
@@ -74,21 +76,126 @@ def test_full_size_matvec_properties(rq_ctx, oracle, t, rows, cols):
     w.free()
 
 
+def sampled_rows(rq_ctx, w, t, rows, cols, count, seed):
+    """`count` rows of a device weight as host GGUF blocks (through rq_weight_export), with their indices."""
+    per, stride = ol.GEOMETRY[t]
+    row_bytes = cols // per * stride
+    host_blocks = rq_ctx.export(w)
+    sample = np.sort(np.random.default_rng(seed).choice(rows, size=min(count, rows), replace=False))
+    return sample, np.concatenate([host_blocks[r * row_bytes:(r + 1) * row_bytes] for r in sample]), host_blocks
+
+
 @pytest.mark.parametrize("t,rows,cols", SHAPES[:2])
 @pytest.mark.parametrize("tokens", [16, 64, 512])
-def test_full_size_batched_product_matches_matvec(rq_ctx, t, rows, cols, tokens):
+def test_full_size_batched_product_against_oracle(rq_ctx, oracle, t, rows, cols, tokens):
+    """BASELINE's batched config (Q4_K 14336 x 4096, Q6_K 4096 x 14336 at 16 / 64 / 512 tokens): every token of a sample
+    of rows against the CPU oracle, fp32 activations and int8 activations (the tensor-core kernel serves both)."""
     import torch
 
     w, gen = device_weight(rq_ctx, t, rows, cols, 2000 + rows)
     x = torch.randn(tokens, cols, generator=gen, device="cuda")
+    sample, sample_blocks, _ = sampled_rows(rq_ctx, w, t, rows, cols, 24, rows + tokens)
+    xh = x.cpu().numpy()
+    pick = torch.from_numpy(sample).cuda()
     y = rq_ctx.matmul(w, x)
-    # the fp32 matvec of a few positions; both are within a few 1e-7 of the exact product
-    for pos in (0, tokens // 2, tokens - 1):
-        one = rq_ctx.matvec(w, x[pos], act_mode=0)
-        assert rel_err(y[pos].cpu().numpy(), one.cpu().numpy()) <= TOL
+    ref = oracle.matvec(t, sample_blocks, len(sample), cols, xh, ol.FLOAT_RUN)
+    assert rel_err(y[:, pick].cpu().numpy(), ref) <= TOL
+    y8 = rq_ctx.matmul(w, x, act_mode=1, step=32)
+    ref8 = oracle.matvec(t, sample_blocks, len(sample), cols, xh, ol.INT8, 32)
+    assert rel_err(y8[:, pick].cpu().numpy(), ref8) <= TOL
     # linearity in the tokens: the product of a sum of two positions is the sum of their products (fp32 noise)
     both = rq_ctx.matmul(w, (x[0] + x[1]).unsqueeze(0).contiguous())
     assert rel_err(both[0].cpu().numpy(), (y[0] + y[1]).cpu().numpy()) <= TOL
+    rq_ctx.check()
+    w.free()
+
+
+def test_full_size_q8_0_first_config(rq_ctx, oracle):
+    """BASELINE's first config: Q8_0 4096 x 4096, batch 1, both activation modes, against the oracle on sampled rows."""
+    import torch
+
+    t, rows, cols = ol.Q8_0, 4096, 4096
+    w, gen = device_weight(rq_ctx, t, rows, cols, 3000)
+    x = torch.randn(cols, generator=gen, device="cuda")
+    sample, sample_blocks, _ = sampled_rows(rq_ctx, w, t, rows, cols, 96, 3000)
+    xh = x.cpu().numpy()
+    for mode, omode, step in ((1, ol.INT8, 32), (1, ol.INT8, 256), (0, ol.FLOAT_RUN, 32)):
+        y = rq_ctx.matvec(w, x, act_mode=mode, step=step).cpu().numpy()
+        assert rel_err(y[sample], oracle.matvec(t, sample_blocks, len(sample), cols, xh, omode, step)) <= TOL, (mode, step)
+    rq_ctx.check()
+    w.free()
+
+
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+def test_full_size_q4_0_layer_both_int8_readings(rq_ctx, oracle, rows, cols):
+    """The Q4_0 variant of the decode layer (q/o, k/v, gate/up, down shapes). Under `.int(8)` recipe re-encodes a lone
+    Q4_0 tensor to Q8_0 at load and dots that ("recipe's .int(8)"); the direct dot over the stored nibbles is this
+    library's opt-in. Each is checked against the oracle doing the same thing."""
+    import torch
+
+    import recipe_dev_b200 as rq
+
+    t = ol.Q4_0
+    w, gen = device_weight(rq_ctx, t, rows, cols, 4000 + rows + cols)
+    x = torch.randn(cols, generator=gen, device="cuda")
+    sample, sample_blocks, _ = sampled_rows(rq_ctx, w, t, rows, cols, 48, rows + cols)
+    xh = x.cpu().numpy()
+    # recipe's .int(8): the Q8_0 re-encode, byte for byte on the sampled rows, then the int8 dot
+    w8 = rq_ctx.int8_weight(w)
+    assert w8.type == rq.Q8_0
+    t8, b8 = oracle.int8_blocks(t, sample_blocks)
+    got8 = rq_ctx.export(w8).reshape(rows, cols // 32 * 34)[sample].reshape(-1)
+    assert np.array_equal(got8, b8)
+    y = rq_ctx.matvec(w8, x, act_mode=1, step=32).cpu().numpy()
+    assert rel_err(y[sample], oracle.matvec(t8, b8, len(sample), cols, xh, ol.INT8, 32)) <= TOL
+    # the direct dot and the fp32 handling over the stored blocks
+    for mode, omode in ((1, ol.INT8), (0, ol.FLOAT_RUN)):
+        y = rq_ctx.matvec(w, x, act_mode=mode, step=32).cpu().numpy()
+        assert rel_err(y[sample], oracle.matvec(t, sample_blocks, len(sample), cols, xh, omode, 32)) <= TOL, mode
+    rq_ctx.check()
+    w8.free()
+    w.free()
+
+
+@pytest.mark.parametrize("rows,cols", [(4096, 14336), (262144, 2560)])
+def test_full_size_q6k_recipes_int8(rq_ctx, oracle, rows, cols):
+    """`down` and the LM head are lone Q6_K tensors: recipe's `.int(8)` dots their Q8_0 re-encode."""
+    import torch
+
+    import recipe_dev_b200 as rq
+
+    t = ol.Q6_K
+    w, gen = device_weight(rq_ctx, t, rows, cols, 5000 + rows)
+    x = torch.randn(cols, generator=gen, device="cuda")
+    sample, sample_blocks, _ = sampled_rows(rq_ctx, w, t, rows, cols, 48, rows)
+    w8 = rq_ctx.int8_weight(w)
+    t8, b8 = oracle.int8_blocks(t, sample_blocks)
+    y = rq_ctx.matvec(w8, x, act_mode=1, step=32).cpu().numpy()
+    assert rel_err(y[sample], oracle.matvec(t8, b8, len(sample), cols, x.cpu().numpy(), ol.INT8, 32)) <= TOL
+    rq_ctx.check()
+    w8.free()
+    w.free()
+
+
+def test_full_size_lm_head_four_tokens(rq_ctx, oracle):
+    """The LM head at batch 4: the four-token pass of the matvec kernel and the tensor-core route of rq_matmul, every
+    token of a sample of rows against the oracle's int8 answer, steps 32 and 256."""
+    import torch
+
+    t, rows, cols = ol.Q6_K, 262144, 2560
+    w, gen = device_weight(rq_ctx, t, rows, cols, 6000)
+    x = torch.randn(4, cols, generator=gen, device="cuda")
+    sample, sample_blocks, _ = sampled_rows(rq_ctx, w, t, rows, cols, 64, 6000)
+    pick = torch.from_numpy(sample).cuda()
+    xh = x.cpu().numpy()
+    for step in (32, 256):
+        ref = oracle.matvec(t, sample_blocks, len(sample), cols, xh, ol.INT8, step)
+        y = rq_ctx.matvec(w, x, act_mode=1, step=step)
+        assert rel_err(y[:, pick].cpu().numpy(), ref) <= TOL, step
+        y = rq_ctx.matmul(w, x, act_mode=1, step=step)
+        assert rel_err(y[:, pick].cpu().numpy(), ref) <= TOL, step
+    yf = rq_ctx.matmul(w, x, act_mode=0)
+    assert rel_err(yf[:, pick].cpu().numpy(), oracle.matvec(t, sample_blocks, len(sample), cols, xh, ol.FLOAT_RUN)) <= TOL
     rq_ctx.check()
     w.free()
 
@@ -127,8 +234,6 @@ def test_full_size_expert_bank_split_adds_up(rq_ctx, oracle):
         bank.free()
     rq_ctx.check()
     assert rel_err(total.cpu().numpy(), want.cpu().numpy()) <= TOL
-    # one token through the CPU oracle
-    xo = x[:, :1].contiguous().cpu().numpy()
-    ro = routing[:, :1].contiguous().cpu().numpy()
-    ref = oracle.moe_forward(t, gate, up, down, experts, top, hidden, ffn, xo, ro, shared=shared)
-    assert rel_err(want[:, :1].cpu().numpy(), ref) <= TOL
+    # every token through the CPU oracle
+    ref = oracle.moe_forward(t, gate, up, down, experts, top, hidden, ffn, x.cpu().numpy(), routing.cpu().numpy(), shared=shared)
+    assert rel_err(want.cpu().numpy(), ref) <= TOL

@@ -55,7 +55,57 @@ def test_matmul_channel_major_planes_and_int8(rq_ctx, oracle):
     rc = rq_ctx.lib.rq_matmul(rq_ctx.handle, w.handle, xc.data_ptr(), tokens, 1, tokens, yc.data_ptr(), tokens, 1, 0, 32, torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     assert np.array_equal(yc.cpu().numpy().T, y)
-    # int8 activations: the exact integer dots, same bits as the matvec entry point
+    # int8 activations: the tensor-core kernel over code * step; the integer dots' answer to fp32 summation noise
     y8 = rq_ctx.matmul(w, cuda(x), act_mode=1, step=32).cpu().numpy()
-    assert rel_err(y8, oracle.matvec(t, blocks, rows, cols, x, ol.INT8, 32)) <= 2e-4
+    assert rel_err(y8, oracle.matvec(t, blocks, rows, cols, x, ol.INT8, 32)) <= TOL
     rq_ctx.check()
+
+
+# K-quant shapes that exercise the cut of the integer-operand kernel: one to fifty-six superblocks per row (windows of
+# eight for the Q4_K minimum term, whole and partial, CTAs that start in the middle of a window), rows that are no
+# multiple of 128, every token tile width and ragged last tiles.
+KQ_SHAPES = [(ol.Q4_K, 128, 256, 4), (ol.Q4_K, 130, 768, 17), (ol.Q4_K, 300, 2304, 20), (ol.Q4_K, 257, 2048, 33), (ol.Q4_K, 140, 4352, 65),
+             (ol.Q4_K, 129, 2560, 129), (ol.Q4_K, 64, 14336, 7), (ol.Q4_K, 4100, 1024, 300), (ol.Q6_K, 128, 256, 4), (ol.Q6_K, 300, 2304, 20),
+             (ol.Q6_K, 200, 2560, 130), (ol.Q6_K, 70, 14336, 16), (ol.Q6_K, 4100, 768, 260),
+             # a row tile per SM: no CTAs along K, so one CTA walks several windows of eight superblocks with narrow token tiles
+             (ol.Q4_K, 18944, 4608, 8), (ol.Q4_K, 18944, 4608, 24), (ol.Q4_K, 18944, 2304, 70), (ol.Q6_K, 18944, 2560, 8)]
+
+
+@pytest.mark.parametrize("t,rows,cols,tokens", KQ_SHAPES)
+@pytest.mark.parametrize("mode", ["float", "int8_32", "int8_256"])
+def test_kquant_matmul_parity(rq_ctx, oracle, t, rows, cols, tokens, mode):
+    blocks = oracle.quantize(t, oracle.normal(63, t + rows, rows * cols, 0.02))
+    x = oracle.normal(63, 70 + t + tokens, tokens * cols, 1.0).reshape(tokens, cols)
+    w = rq_ctx.weight_from_host(t, blocks, rows, cols)
+    # the oracle on a sample of rows keeps the CPU side to seconds
+    pick = np.unique(np.concatenate([np.arange(0, rows, max(1, rows // 40)), [rows - 1, min(rows - 1, 127), min(rows - 1, 128)]]))
+    per, stride = ol.GEOMETRY[t]
+    sub = blocks.reshape(rows, cols // per * stride)[pick].reshape(-1)
+    if mode == "float":
+        y = rq_ctx.matmul(w, cuda(x)).cpu().numpy()
+        ref = oracle.matvec(t, sub, pick.size, cols, x, ol.FLOAT_RUN)
+        exact = x.astype(np.float64) @ oracle.dequantize(t, sub).astype(np.float64).reshape(pick.size, cols).T
+        assert np.max(np.abs(y[:, pick] - exact)) <= 3e-6 * np.max(np.abs(exact))
+    else:
+        step = int(mode.split("_")[1])
+        y = rq_ctx.matmul(w, cuda(x), act_mode=1, step=step).cpu().numpy()
+        ref = oracle.matvec(t, sub, pick.size, cols, x, ol.INT8, step)
+    rq_ctx.check()
+    assert rel_err(y[:, pick], ref) <= TOL
+
+
+def test_kquant_matmul_extreme_blocks(rq_ctx, oracle):
+    """Arbitrary block bytes: every six-bit scale and minimum, every int8 scale, codes at both ends of their range."""
+    rng = np.random.default_rng(5)
+    for t in (ol.Q4_K, ol.Q6_K):
+        per, stride = ol.GEOMETRY[t]
+        rows, cols, tokens = 256, 1024, 24
+        raw = rng.integers(0, 256, size=(rows * cols // per, stride), dtype=np.uint8)
+        for off in ([0, 2] if t == ol.Q4_K else [208]):
+            raw[:, off + 1] = (raw[:, off + 1] & 0x83) | 0x10  # |d| in [2^-11, 2^-7): sums stay well inside fp32
+        x = oracle.normal(64, t, tokens * cols, 1.0).reshape(tokens, cols)
+        w = rq_ctx.weight_from_host(t, raw.reshape(-1), rows, cols)
+        y = rq_ctx.matmul(w, cuda(x)).cpu().numpy()
+        exact = x.astype(np.float64) @ oracle.dequantize(t, raw.reshape(-1)).astype(np.float64).reshape(rows, cols).T
+        assert np.max(np.abs(y - exact)) <= 3e-6 * np.max(np.abs(exact)), t
+        rq_ctx.check()

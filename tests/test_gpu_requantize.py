@@ -55,10 +55,11 @@ def test_int8_over_reencoded_weight_is_recipes_int8(rq_ctx, oracle, t, step):
     y = rq_ctx.matvec(w8, torch_cuda(x), act_mode=rq.ACT_INT8, step=step).cpu().numpy()
     t8, b8 = oracle.int8_blocks(t, blocks)
     ref = oracle.matvec(t8, b8, rows, cols, x, ol.INT8, step)
-    assert rel_err(y, ref) <= 5e-5
+    assert rel_err(y, ref) <= (5e-5 if step == 32 else 2e-4)  # the integer parts are exact; fp32 summation order differs
     # the direct dot over the stored blocks is a different rounding of the weights: close, not the same path
     direct = rq_ctx.matvec(w, torch_cuda(x), act_mode=rq.ACT_INT8, step=step).cpu().numpy()
-    assert rel_err(direct, ref) <= 5e-2
+    gap = float(np.max(np.abs(direct - ref)) / np.max(np.abs(ref)))
+    assert 0.0 < gap <= 2e-2, gap
     rq_ctx.check()
 
 
