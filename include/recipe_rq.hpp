@@ -2,8 +2,8 @@
 //
 // The reference's host is Rust; where no Rust toolchain exists this header gives the same
 // surface for the quantised matvec path: the names, argument meaning and error behaviour of
-// recipe's `Block::fp/int`, `Model::layer`, `Model::gguf_moe`, `Placed::infer/clear/
-// resident_bytes/moved_bytes` (recipe.rs:14027-14054, :14671, :14722, :21314-21490). As in
+// recipe's `Block::fp/int`, `Model::layer`, `Model::gguf_moe`, `Placed::infer/prefill/step/decode/
+// clear/resident_bytes/moved_bytes` (recipe.rs:14027-14054, :14671, :14722, :21314-21490). As in
 // recipe, host numbers are f64 at the API and become the model type (fp32) on upload
 // (encode_floats, recipe.rs:2072-2075); internals report errors as RecipeError (recipe.rs:13416-13433)
 // and the public methods throw it with the library's text (recipe panics with the same text).
@@ -31,9 +31,10 @@ inline void require(int status) {
 enum class Scoring { Softmax = RQ_SCORE_SOFTMAX, Sigmoid = RQ_SCORE_SIGMOID };  // recipe.rs:13955
 enum class Activation { Silu };                                                   // the expert activation this path serves
 struct SharedExpert {                                                             // recipe.rs:13855-13862
-    enum Kind { None, Gated } kind = None;
-    int count = 1;
+    enum Kind { None, Ungated, Gated } kind = None;
+    int count = 1;  // how many experts it merges: its feed-forward is count times the routed expert width
     static SharedExpert none() { return {}; }
+    static SharedExpert ungated(int count) { return {Ungated, count}; }
     static SharedExpert gated(int count) { return {Gated, count}; }
 };
 
@@ -54,7 +55,7 @@ struct MoeTensors {  // recipe.rs:14382-14420
 // records (step from the profile: 32 for `recipe`, 256 for `llamacpp`).
 class Block {
   public:
-    enum Kind { Layer, Moe } kind = Layer;
+    enum Kind { Layer, Moe, Embed } kind = Layer;
     Tensor tensor{};
     MoeTensors moe{};
     int experts = 0, top_k = 0, hidden = 0, ffn = 0;
@@ -100,6 +101,17 @@ class Model {
         m.blocks.push_back(b);
         return m;
     }
+    // A lookup of token ids in a stored table ([vocab][hidden] blocks): the first block of a model whose input is a sequence
+    // of ids (Model::embed / Primitive::Gather over a bound table, recipe.rs:4632-4651).
+    Model embed(const Tensor& table) const {
+        if (!blocks.empty()) throw RecipeError("an embedding is the first block of its model");
+        Model m = *this;
+        Block b;
+        b.kind = Block::Embed;
+        b.tensor = table;
+        m.blocks.push_back(b);
+        return m;
+    }
     // Applies a precision to the block just added, as `recipe.model().layer(n).int(8)` reads.
     Model fp(uint8_t bits) const { Model m = *this; if (m.blocks.empty()) throw RecipeError("no block to set a precision on"); m.blocks.back() = m.blocks.back().fp(bits); return m; }
     Model int_(uint8_t bits) const { Model m = *this; if (m.blocks.empty()) throw RecipeError("no block to set a precision on"); m.blocks.back() = m.blocks.back().int_(bits); return m; }
@@ -130,19 +142,34 @@ class Placed {
         require(rq_init(device, &ctx_));
         try {
             for (const Block& b : model_.blocks) {
-                if (b.kind == Block::Layer) {
+                if (b.kind == Block::Layer || b.kind == Block::Embed) {
                     rq_weight* w = nullptr;
                     require(rq_weight_prepare(ctx_, b.tensor.ggml_type, b.tensor.blocks, b.tensor.rows, b.tensor.cols, 0, b.tensor.rows, &w));
+                    if (b.kind == Block::Layer && b.act_mode == RQ_ACT_INT8 && !rq_int8_keeps(b.tensor.ggml_type)) {
+                        // finish_int_sums (recipe.rs:22345-22369): `.int(8)` keeps Q8_0 and Q4_K; any other bound tensor is
+                        // re-encoded to Q8_0 once, at load, and the int8 dot runs over that
+                        rq_weight* q8 = nullptr;
+                        const int rc = rq_weight_requantize(ctx_, w, RQ_Q8_0, &q8, nullptr);
+                        if (rc == RQ_OK) cudaDeviceSynchronize();
+                        rq_weight_free(ctx_, w);
+                        require(rc);
+                        w = q8;
+                    }
                     weights_.push_back(w);
                     banks_.push_back(nullptr);
                     resident_ += (size_t)rq_weight_bytes(w);
                 } else {
                     rq_moe* m = nullptr;
-                    const bool sh = b.shared.kind == SharedExpert::Gated;
-                    require(rq_moe_prepare(ctx_, b.moe.ggml_type, b.moe.gate, b.moe.up, b.moe.down, b.experts, 0, b.experts, b.hidden, b.ffn, sh ? b.moe.shared_gate : nullptr,
-                                           sh ? b.moe.shared_up : nullptr, sh ? b.moe.shared_down : nullptr, sh ? b.moe.shared_gate_vector : nullptr, &m));
+                    require(rq_moe_prepare(ctx_, b.moe.ggml_type, b.moe.gate, b.moe.up, b.moe.down, b.experts, 0, b.experts, b.hidden, b.ffn, nullptr, nullptr, nullptr,
+                                           nullptr, &m));
                     weights_.push_back(nullptr);
                     banks_.push_back(m);
+                    if (b.shared.kind != SharedExpert::None) {
+                        if (b.shared.count == 0) throw RecipeError("shared expert count must be positive");
+                        require(rq_moe_attach_shared(ctx_, m, b.shared.kind == SharedExpert::Gated ? 1 : 0, b.shared.count, b.moe.shared_gate, b.moe.shared_up,
+                                                     b.moe.shared_down, b.moe.shared_gate_vector));
+                    }
+                    require(rq_moe_set_routed_scale(m, (float)b.scale));
                     resident_ += (size_t)rq_moe_bytes(m);
                 }
             }
@@ -160,15 +187,81 @@ class Placed {
     std::vector<double> infer(const std::vector<double>& input) { return run(input, nullptr); }
     // The same with the router scores of the (single) gguf_moe block of the chain.
     std::vector<double> infer(const std::vector<double>& input, const std::vector<double>& router_scores) { return run(input, &router_scores); }
-    void clear() {}                                              // no carried state on this path
+    // The sequence calls (Placed::prefill / step / decode, recipe.rs:21314-21325, :21468): the model's first block is an
+    // embedding, its input a sequence of token ids, its output the last block's values (logits) at the last position.
+    // prefill fills exactly the supplied prefix; step extends the completed prefix by one id. No block on this path carries
+    // state from one position to the next, so a step runs one position and gives the bits the same position gets in a prefill.
+    std::vector<double> prefill(const std::vector<uint32_t>& ids) {
+        ids_.clear();
+        if (ids.empty()) throw RecipeError("token window is outside the placement capacity");
+        std::vector<double> logits = run_ids(ids);
+        ids_ = ids;
+        return logits;
+    }
+    std::vector<double> step(uint32_t id) {
+        if (ids_.empty()) throw RecipeError("step requires a completed prefill");
+        std::vector<double> logits = run_ids({id});
+        ids_.push_back(id);
+        return logits;
+    }
+    // Greedy autoregressive decode: the prompt is prefilled, then the id of the largest logit (the lowest index on a tie) is
+    // appended and stepped, until a `stop` id, `budget` ids, or the end. Returns the generated ids.
+    std::vector<uint32_t> decode(const std::vector<uint32_t>& prompt, const std::vector<uint32_t>& stop, size_t budget) {
+        std::vector<uint32_t> out;
+        std::vector<double> logits = prefill(prompt);
+        while (out.size() < budget) {
+            uint32_t best = 0;
+            for (size_t i = 1; i < logits.size(); ++i) if (logits[i] > logits[best]) best = (uint32_t)i;
+            out.push_back(best);
+            bool stopped = false;
+            for (uint32_t s : stop) stopped = stopped || s == best;
+            if (stopped || out.size() == budget) break;
+            logits = step(best);
+        }
+        return out;
+    }
+    const std::vector<uint32_t>& ids() const { return ids_; }
+    void clear() { ids_.clear(); }                               // forgets the sequence; weights stay resident (recipe.rs:21458)
     std::vector<size_t> resident_bytes() const { return {resident_}; }
     size_t moved_bytes() const { return moved_; }
 
   private:
+    // A window of positions through embedding + layers with the planes on the device; returns the last position's output.
+    std::vector<double> run_ids(const std::vector<uint32_t>& ids) {
+        if (model_.blocks.empty() || model_.blocks[0].kind != Block::Embed) throw RecipeError("the sequence calls take a model whose first block is an embedding");
+        const int tokens = (int)ids.size();
+        const Block& e = model_.blocks[0];
+        std::vector<int32_t> host_ids(ids.size());
+        for (size_t i = 0; i < ids.size(); ++i) {
+            if ((int64_t)ids[i] >= e.tensor.rows) throw RecipeError("token id " + std::to_string(ids[i]) + " is outside the table's " + std::to_string(e.tensor.rows) + " rows");
+            host_ids[i] = (int32_t)ids[i];
+        }
+        DeviceBuffer dids(ids.size() * 4);
+        cuda(cudaMemcpy(dids.p, host_ids.data(), ids.size() * 4, cudaMemcpyHostToDevice));
+        int64_t width = e.tensor.cols;
+        std::unique_ptr<DeviceBuffer> cur(new DeviceBuffer((size_t)tokens * width * 4));
+        require(rq_gather_rows(ctx_, weights_[0], (const int32_t*)dids.p, tokens, (float*)cur->p, 1, width, nullptr));
+        for (size_t i = 1; i < model_.blocks.size(); ++i) {
+            const Block& b = model_.blocks[i];
+            if (b.kind != Block::Layer) throw RecipeError("the sequence calls serve chains of layers");
+            if (width != b.tensor.cols) throw RecipeError("input width " + std::to_string(width) + " does not match the layer's " + std::to_string(b.tensor.cols));
+            std::unique_ptr<DeviceBuffer> out(new DeviceBuffer((size_t)tokens * b.tensor.rows * 4));
+            // token-major planes; a window goes through the matvec entry point, whose positions get the bits a single step gets
+            require(rq_matvec(ctx_, weights_[i], (const float*)cur->p, 1, width, tokens, (float*)out->p, 1, b.tensor.rows, b.act_mode, b.step, nullptr));
+            cur.swap(out);
+            width = b.tensor.rows;
+        }
+        require(rq_check(ctx_));
+        std::vector<float> last((size_t)width);
+        cuda(cudaMemcpy(last.data(), (const float*)cur->p + (size_t)(tokens - 1) * width, last.size() * 4, cudaMemcpyDeviceToHost));
+        moved_ += 4 * (ids.size() + last.size());
+        return std::vector<double>(last.begin(), last.end());
+    }
     std::vector<double> run(const std::vector<double>& input, const std::vector<double>* scores) {
         std::vector<float> cur(input.begin(), input.end());
         for (size_t i = 0; i < model_.blocks.size(); ++i) {
             const Block& b = model_.blocks[i];
+            if (b.kind == Block::Embed) throw RecipeError("a model that begins with an embedding takes ids: use prefill / step / decode");
             if (b.kind == Block::Layer) {
                 if ((int64_t)cur.size() != b.tensor.cols) throw RecipeError("input width " + std::to_string(cur.size()) + " does not match the layer's " + std::to_string(b.tensor.cols));
                 std::vector<float> out((size_t)b.tensor.rows);
@@ -186,7 +279,6 @@ class Placed {
                 require(rq_moe_forward(ctx_, banks_[i], (const float*)dx.p, 1, 1, (const float*)dw.p, 1, 1, b.top_k, 1, 1, (float*)dy.p, 1, 1, nullptr));
                 require(rq_check(ctx_));
                 cuda(cudaMemcpy(out.data(), dy.p, out.size() * 4, cudaMemcpyDeviceToHost));
-                if (b.scale != 1.0) throw RecipeError("a routed scale other than 1 is not served");
                 moved_ += 4 * (cur.size() + sc.size() + out.size());
                 cur.swap(out);
             }
@@ -211,6 +303,7 @@ class Placed {
     std::vector<rq_weight*> weights_;
     std::vector<rq_moe*> banks_;
     size_t resident_ = 0, moved_ = 0;
+    std::vector<uint32_t> ids_;  // the completed prefix (DecodeState.ids, recipe.rs:21316)
 };
 
 inline Placed Model::place(int device) const { return Placed(*this, device); }  // guaranteed elision: Placed is neither copied nor moved

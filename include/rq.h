@@ -118,6 +118,11 @@ int64_t rq_weight_bytes(const rq_weight* w);
  * (dequant_scalar / dequant_q45k / dequant_q6k, recipe.rs:3687-3833). dev_out: rows*cols floats. */
 int rq_dequant(rq_ctx* ctx, const rq_weight* w, float* dev_out, void* stream);
 
+/* Embedding-row gather from a packed table: y[k * y_k_stride + t * y_t_stride] = value k of row dev_ids[t] of `table`,
+ * decoded with rq_dequant's arithmetic (the same bits). dev_ids: `tokens` int32 in device memory; an id outside the table
+ * is clamped into it. Replaces Primitive::Gather over a stored table (recipe.rs:4632-4651). */
+int rq_gather_rows(rq_ctx* ctx, const rq_weight* table, const int32_t* dev_ids, int tokens, float* y, int64_t y_k_stride, int64_t y_t_stride, void* stream);
+
 /* Quantises `count` fp32 device values into GGUF blocks in device memory, byte-exact with
  * Integer::compress (recipe.rs:16191-16242 Q8_0/Q4_0, :16325-16375 Q4_K, :16376-16414 Q6_K).
  * count must be a whole number of blocks. */
@@ -210,6 +215,15 @@ int rq_moe_route(rq_ctx* ctx, const float* scores, int64_t score_e_stride, int64
 int rq_moe_prepare(rq_ctx* ctx, int ggml_type, const void* gate, const void* up, const void* down, int experts, int expert_first,
                    int expert_count, int hidden, int ffn, const void* shared_gate, const void* shared_up, const void* shared_down,
                    const float* shared_gate_vector, rq_moe** out);
+/* The block's routed scale: the routing weights are multiplied by it before the experts add up (gguf_moe's `scale`,
+ * lower_scale after the top-k, recipe.rs:23426-23428). 1 unless set. */
+int rq_moe_set_routed_scale(rq_moe* moe, float scale);
+/* Attaches the block's shared expert to a bank made without one (SharedExpert, recipe.rs:13855-13862, :23430-23457):
+ * `count` merged experts, so its banks are gate / up [count * ffn][hidden] and down [hidden][count * ffn], host GGUF blocks
+ * of the bank's format; gated != 0: weight sigmoid(gate_vector . x) (Gated), else weight one at every position (Ungated,
+ * gate_vector ignored). top_k + count may not exceed 16. */
+int rq_moe_attach_shared(rq_ctx* ctx, rq_moe* moe, int gated, int count, const void* shared_gate, const void* shared_up, const void* shared_down,
+                         const float* shared_gate_vector);
 void rq_moe_free(rq_ctx* ctx, rq_moe* moe);
 int64_t rq_moe_bytes(const rq_moe* moe);
 
@@ -219,7 +233,9 @@ int64_t rq_moe_bytes(const rq_moe* moe);
  * reference, recipe.rs:24284-24294). Tokens nothing here is routed to get zeros, so the outputs of
  * the ranks of an expert-parallel split add up to the block's output.
  * Replaces lower_experts over the packed bodies, modes 1 and 2 (recipe.rs:23386-23459,
- * amd-nv-cpu.ll:2304-2365, :3136-3508). At most 64 tokens per call, top_k <= 15. */
+ * amd-nv-cpu.ll:2304-2365, :3136-3508). At most 64 tokens per call; top_k plus the shared expert's count at most 16.
+ * A bank's plans and hidden activations are work areas shared by every call on it: calls on one stream are ordered, a call
+ * on another stream waits for the previous one (see "Streams" at the top). */
 int rq_moe_forward(rq_ctx* ctx, rq_moe* moe, const float* x, int64_t x_k_stride, int64_t x_t_stride, const float* routing,
                    int64_t routing_e_stride, int64_t routing_t_stride, int top_k, int tokens, int include_shared, float* y,
                    int64_t y_n_stride, int64_t y_t_stride, void* stream);

@@ -1010,29 +1010,51 @@ static void moe_span(void* p, int64_t first, int64_t last, int worker, int worke
     free(hbuf); free(xcol);
 }
 
+/* lower_gguf_moe, recipe.rs:23415-23459. The routed weights are multiplied by `routed_scale` first when it is not 1
+ * (lower_scale after the top-k, :23426-23428). The shared expert is one more expert of width shared_count * ffn that every
+ * position takes: at weight one (SharedExpert::Ungated, :23447) or at sigmoid(gate_vector . x) (Gated, :23448-23454). */
+int rqo_moe_forward_ex(int type, const uint8_t* gate, const uint8_t* up, const uint8_t* down,
+                       int experts, int top, int hidden, int ffn,
+                       const float* x, const float* routing, int tokens, float routed_scale,
+                       int shared_kind, int shared_count,
+                       const uint8_t* sh_gate, const uint8_t* sh_up, const uint8_t* sh_down,
+                       const float* shared_gate_w, float* y, int threads) {
+    int per = rqo_block_values(type);
+    if (!per || hidden % per || ffn % per || top > 64 || top < 1) return -1;
+    if (shared_kind < 0 || shared_kind > 2 || (shared_kind && shared_count < 1) || (shared_kind == 2 && !shared_gate_w)) return -1;
+    float* scaled = NULL;
+    if (routed_scale != 1.0f) {
+        scaled = (float*)malloc(sizeof(float) * (size_t)experts * (size_t)tokens);
+        for (int64_t i = 0; i < (int64_t)experts * tokens; ++i) scaled[i] = routing[i] * routed_scale;
+        routing = scaled;
+    }
+    moe_ctx routed = {type, gate, up, down, experts, top, hidden, ffn, tokens, x, routing, y, 0};
+    run_spans(tokens, threads, moe_span, &routed);
+    free(scaled);
+    if (shared_kind) {
+        float* weight = (float*)malloc(sizeof(float) * (size_t)tokens);
+        for (int p = 0; p < tokens; ++p) {
+            if (shared_kind == 1) { weight[p] = 1.0f; continue; }
+            /* recipe.rs:23450-23453: a one-row bias-free contraction (dense sum loop, ll:2094-2123:
+             * product then add, unfused), the gate activation, then one expert at that weight. */
+            float sum = 0.0f;
+            for (int k = 0; k < hidden; ++k) { float product = shared_gate_w[k] * x[(int64_t)k * tokens + p]; sum = sum + product; }
+            weight[p] = rqo_sigmoid(sum);
+        }
+        moe_ctx shared = {type, sh_gate, sh_up, sh_down, 1, 1, hidden, ffn * shared_count, tokens, x, weight, y, 1};
+        run_spans(tokens, threads, moe_span, &shared);
+        free(weight);
+    }
+    return 0;
+}
+
 int rqo_moe_forward(int type, const uint8_t* gate, const uint8_t* up, const uint8_t* down,
                     int experts, int top, int hidden, int ffn,
                     const float* x, const float* routing, int tokens,
                     const uint8_t* sh_gate, const uint8_t* sh_up, const uint8_t* sh_down,
                     const float* shared_gate_w, float* y, int threads) {
-    int per = rqo_block_values(type);
-    if (!per || hidden % per || ffn % per || top > 64 || top < 1) return -1;
-    moe_ctx routed = {type, gate, up, down, experts, top, hidden, ffn, tokens, x, routing, y, 0};
-    run_spans(tokens, threads, moe_span, &routed);
-    if (shared_gate_w) {
-        /* recipe.rs:23450-23453: a one-row bias-free contraction (dense sum loop, ll:2094-2123:
-         * product then add, unfused), the gate activation, then one expert at that weight. */
-        float* weight = (float*)malloc(sizeof(float) * (size_t)tokens);
-        for (int p = 0; p < tokens; ++p) {
-            float sum = 0.0f;
-            for (int k = 0; k < hidden; ++k) { float product = shared_gate_w[k] * x[(int64_t)k * tokens + p]; sum = sum + product; }
-            weight[p] = rqo_sigmoid(sum);
-        }
-        moe_ctx shared = {type, sh_gate, sh_up, sh_down, 1, 1, hidden, ffn, tokens, x, weight, y, 1};
-        run_spans(tokens, threads, moe_span, &shared);
-        free(weight);
-    }
-    return 0;
+    return rqo_moe_forward_ex(type, gate, up, down, experts, top, hidden, ffn, x, routing, tokens, 1.0f, shared_gate_w ? 2 : 0, 1, sh_gate, sh_up, sh_down,
+                              shared_gate_w, y, threads);
 }
 
 /* ------------------------------------------------------------------ synthetic inputs */

@@ -86,6 +86,16 @@ int rqo_moe_forward(int type, const uint8_t* gate, const uint8_t* up, const uint
                     const uint8_t* sh_gate, const uint8_t* sh_up, const uint8_t* sh_down,
                     const float* shared_gate_w, float* y, int threads);
 
+/* The same with the rest of gguf_moe's arguments: routed weights times `routed_scale`; shared_kind 0 none, 1 ungated
+ * (weight one), 2 gated; the shared expert is shared_count * ffn wide (its banks: gate/up [count*ffn][hidden], down
+ * [hidden][count*ffn]). recipe.rs:23415-23459, SharedExpert :13855-13862. */
+int rqo_moe_forward_ex(int type, const uint8_t* gate, const uint8_t* up, const uint8_t* down,
+                       int experts, int top, int hidden, int ffn,
+                       const float* x, const float* routing, int tokens, float routed_scale,
+                       int shared_kind, int shared_count,
+                       const uint8_t* sh_gate, const uint8_t* sh_up, const uint8_t* sh_down,
+                       const float* shared_gate_w, float* y, int threads);
+
 /* Counter-based synthetic inputs: splitmix64 -> Box-Muller (f64) -> scale -> f32.
  * Value i of stream (seed, stream) depends only on (seed, stream, i). */
 void rqo_normal(uint64_t seed, uint64_t stream, int64_t first, int64_t count, double sigma, float* out);

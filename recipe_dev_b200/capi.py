@@ -55,6 +55,7 @@ def _declare(lib) -> None:
         "rq_weight_bytes": (i64, [p]),
         "rq_dequant": (i32, [p, p, f32p, p]),
         "rq_quantize": (i32, [p, i32, f32p, i64, p, p]),
+        "rq_gather_rows": (i32, [p, p, p, i32, f32p, i64, i64, p]),
         "rq_matvec": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
         "rq_matmul": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
         "rq_matvec_multi": (i32, [p, i32, p, f32p, i64, i64, i32, p, i64, i64, i32, i32, p]),
@@ -72,6 +73,8 @@ def _declare(lib) -> None:
         "rq_moe_route": (i32, [p, f32p, i64, i64, i32, i32, i32, i32, f32p, i32, f32p, i64, i64, p]),
         "rq_moe_prepare": (i32, [p, i32, p, p, p, i32, i32, i32, i32, i32, p, p, p, f32p, C.POINTER(p)]),
         "rq_moe_free": (None, [p, p]),
+        "rq_moe_set_routed_scale": (i32, [p, C.c_float]),
+        "rq_moe_attach_shared": (i32, [p, p, i32, i32, p, p, p, f32p]),
         "rq_moe_bytes": (i64, [p]),
         "rq_moe_forward": (i32, [p, p, f32p, i64, i64, f32p, i64, i64, i32, i32, i32, f32p, i64, i64, p]),
         "rq_device_alloc": (i32, [p, i64, C.POINTER(p)]),
@@ -202,6 +205,16 @@ class MoeBank:
     def nbytes(self) -> int:
         return self.ctx.lib.rq_moe_bytes(self.handle)
 
+    def set_routed_scale(self, scale: float) -> None:
+        _check(self.ctx.lib.rq_moe_set_routed_scale(self.handle, scale))
+
+    def attach_shared(self, gate, up, down, count: int = 1, gate_vector=None) -> None:
+        """A shared expert of count * ffn width: gated by sigmoid(gate_vector . x) when a vector is given, else at weight one."""
+        g, u, d = (np.ascontiguousarray(a, dtype=np.uint8) for a in (gate, up, down))
+        v = None if gate_vector is None else np.ascontiguousarray(gate_vector, dtype=np.float32)
+        _check(self.ctx.lib.rq_moe_attach_shared(self.ctx.handle, self.handle, int(v is not None), count, g.ctypes.data, u.ctypes.data, d.ctypes.data,
+                                                 None if v is None else v.ctypes.data))
+
     def free(self) -> None:
         if self.handle:
             self.ctx.lib.rq_moe_free(self.ctx.handle, self.handle)
@@ -297,6 +310,17 @@ class Context:
             out = torch.empty((w.rows, w.cols), dtype=torch.float32, device=f"cuda:{self.device}")
         _check(self.lib.rq_dequant(self.handle, w.handle, _ptr(out), _stream(stream)))
         return out
+
+    def gather_rows(self, table: Weight, ids, y=None, stream=None):
+        """ids: CUDA int32 [tokens] -> y [tokens, cols]: the table's rows ids[t], decoded (embedding lookup)."""
+        import torch
+
+        assert ids.is_cuda and ids.dtype == torch.int32 and ids.is_contiguous()
+        tokens = ids.numel()
+        if y is None:
+            y = torch.empty((tokens, table.cols), dtype=torch.float32, device=ids.device)
+        _check(self.lib.rq_gather_rows(self.handle, table.handle, _ptr(ids), tokens, _ptr(y), y.stride(1), y.stride(0), _stream(stream)))
+        return y
 
     def quantize(self, ggml_type: int, values, stream=None):
         """fp32 CUDA tensor -> uint8 CUDA tensor of GGUF blocks."""

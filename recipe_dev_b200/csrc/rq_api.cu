@@ -333,6 +333,14 @@ extern "C" int rq_dequant(rq_ctx* ctx, const rq_weight* w, float* dev_out, void*
     return rq_launch_dequant(w, dev_out, (cudaStream_t)stream);
 }
 
+extern "C" int rq_gather_rows(rq_ctx* ctx, const rq_weight* table, const int32_t* dev_ids, int tokens, float* y, int64_t y_k_stride, int64_t y_t_stride, void* stream) {
+    if (!ctx || !table || !dev_ids || !y) return rq_fail(RQ_ERR_INVALID, "rq_gather_rows: null argument");
+    if (table->device != ctx->device) return rq_fail(RQ_ERR_INVALID, "rq_gather_rows: table lives on device %d, context on %d", table->device, ctx->device);
+    if (tokens <= 0 || y_k_stride <= 0 || (tokens > 1 && y_t_stride <= 0)) return rq_fail(RQ_ERR_INVALID, "rq_gather_rows: tokens and strides must be positive");
+    DeviceGuard guard(ctx->device);
+    return rq_launch_gather(table, dev_ids, tokens, y, y_k_stride, y_t_stride, (cudaStream_t)stream);
+}
+
 extern "C" int rq_quantize(rq_ctx* ctx, int type, const float* dev_values, int64_t count, void* dev_blocks, void* stream) {
     if (!ctx || !dev_values || !dev_blocks) return rq_fail(RQ_ERR_INVALID, "rq_quantize: null argument");
     int per = rq_block_values(type);
@@ -384,9 +392,9 @@ extern "C" int rq_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_
     if (rc) return rc;
     if (sk <= 0 || yn <= 0 || (tokens > 1 && (st <= 0 || yt <= 0))) return rq_fail(RQ_ERR_INVALID, "rq_matmul: strides must be positive");
     DeviceGuard guard(ctx->device);
-    // K-quant weights: the integer-operand tensor-core kernel, for fp32 activations and for int8 windows of four and more
-    // positions (fewer go four to a pass through the matvec kernel's exact integer dots)
-    if (act_mode == RQ_ACT_FLOAT || (act_mode == RQ_ACT_INT8 && tokens >= 4)) {
+    // K-quant weights: the integer-operand tensor-core kernel, for fp32 activations and for int8 windows of twelve and more
+    // positions (measured: below that the matvec kernel's exact integer dots, four tokens a pass, are faster)
+    if (act_mode == RQ_ACT_FLOAT || (act_mode == RQ_ACT_INT8 && tokens >= 12)) {
         rc = rq_launch_matmul_kq(ctx, w, x, sk, st, tokens, y, yn, yt, act_mode, step, (cudaStream_t)stream);
         if (rc != RQ_ERR_UNSUPPORTED) return rc;
     }

@@ -90,6 +90,7 @@ int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes, cudaStream_t s);
 int rq_launch_repack(const rq_weight* w, const uint8_t* dev_blocks, cudaStream_t s);
 int rq_launch_export(const rq_weight* w, uint8_t* dev_blocks, cudaStream_t s);
 int rq_launch_dequant(const rq_weight* w, float* out, cudaStream_t s);
+int rq_launch_gather(const rq_weight* w, const int32_t* ids, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s);
 int rq_launch_requant_q8_0(const rq_weight* src, rq_weight* dst, cudaStream_t s);
 int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, int tokens, int step,
                         uint8_t* scratch, uint8_t* records36, cudaStream_t s);

@@ -84,3 +84,36 @@ int rq_launch_dequant(const rq_weight* w, float* out, cudaStream_t s) {
     RQ_CUDA(cudaGetLastError());
     return RQ_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Embedding-row gather from a packed table (Primitive::Gather, recipe.rs:4632-4651): position t takes row ids[t] of the
+// stored table, decoded value by value with the dequantiser's arithmetic (the same bits), into y[channel * yn + t * yt].
+// Ids live in device memory, so they cannot be checked before the launch: an id outside the table is clamped into it.
+// ---------------------------------------------------------------------------------------
+template <int TYPE>
+__global__ void rq_gather_kernel(const uint8_t* __restrict__ main_plane, const uint16_t* __restrict__ scale_plane, int64_t rows, int64_t cols,
+                                 const int32_t* __restrict__ ids, int tokens, float* __restrict__ y, int64_t yn, int64_t yt) {
+    const int64_t total = (int64_t)tokens * cols;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / cols, k = i - t * cols;
+        int64_t row = ids[t];
+        row = row < 0 ? 0 : (row >= rows ? rows - 1 : row);
+        y[k * yn + t * yt] = rq_decode_value<TYPE>(main_plane, scale_plane, row * cols + k, cols);
+    }
+}
+
+int rq_launch_gather(const rq_weight* w, const int32_t* ids, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s) {
+    const int64_t total = (int64_t)tokens * w->cols;
+    const int threads = 256;
+    int64_t want = (total + threads - 1) / threads;
+    const int grid = (int)(want < 148 * 16 ? (want < 1 ? 1 : want) : 148 * 16);
+    switch (w->type) {
+        case RQ_Q4_K: rq_gather_kernel<RQ_Q4_K><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        case RQ_Q6_K: rq_gather_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        case RQ_Q8_0: rq_gather_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        case RQ_Q4_0: rq_gather_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        default: return rq_fail(RQ_ERR_INVALID, "gather: type %d", w->type);
+    }
+    RQ_CUDA(cudaGetLastError());
+    return RQ_OK;
+}

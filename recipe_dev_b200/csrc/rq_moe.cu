@@ -15,6 +15,7 @@
 //             (amd-nv-cpu.ll:2359-2362)
 // and the streaming matvec kernel walks them. The gated shared expert is one more slot whose
 // weight is sigmoid(gate_vector . x) (recipe.rs:23450-23453).
+#include <stdlib.h>
 #include <string.h>
 
 #include <new>
@@ -27,7 +28,11 @@ struct rq_moe {
     uint8_t *gate, *up, *down;          // main planes of the local experts' banks
     uint16_t *gate_sc, *up_sc, *down_sc;
     bool has_shared;
-    uint8_t *sh_gate, *sh_up, *sh_down;
+    int sh_count;                       // the shared expert is sh_count * ffn wide: sh_count slots of the routed experts' shape
+    bool sh_gated;                      // weight sigmoid(gate_vector . x); else weight one
+    float routed_scale;                 // the routed weights are multiplied by this (gguf_moe's `scale`)
+    uint8_t* sh_base;                   // a shared expert attached after the bank was made: its own allocation
+    uint8_t *sh_gate, *sh_up, *sh_down; // gate / up: [sh_count * ffn][hidden]; down: sh_count matrices [hidden][ffn], one per column block
     uint16_t *sh_gate_sc, *sh_up_sc, *sh_down_sc;
     float* sh_vector;                   // [hidden] fp32 gate vector of the shared expert
     // per-token work areas (sized for RQ_MOE_MAX_TOKENS tokens at once)
@@ -253,7 +258,8 @@ struct BankView {
     int type, experts, expert_first, expert_count, hidden, ffn;
     const uint8_t *gate, *up, *down;
     const uint16_t *gate_sc, *up_sc, *down_sc;
-    int has_shared;
+    int has_shared, sh_count, sh_gated;
+    float routed_scale;
     const uint8_t *sh_gate, *sh_up, *sh_down;
     const uint16_t *sh_gate_sc, *sh_up_sc, *sh_down_sc;
     const float* sh_vector;
@@ -270,7 +276,7 @@ __global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const floa
     const int64_t in_row_main = (int64_t)(b.hidden / per) * main_unit, in_row_sc = b.hidden / per;   // gate / up rows (hidden inputs)
     const int64_t dn_row_main = (int64_t)(b.ffn / per) * main_unit, dn_row_sc = b.ffn / per;         // down rows (ffn inputs)
     // the shared expert's weight: sigmoid of a one-row bias-free contraction (partials in a fixed tree)
-    if (b.has_shared && include_shared) {
+    if (b.has_shared && include_shared && b.sh_gated) {
         float acc = 0.0f;
         for (int k = tid; k < b.hidden; k += 256) acc = __fadd_rn(acc, __fmul_rn(b.sh_vector[k], x[k * sk + t * st]));
         red[tid] = acc;
@@ -281,7 +287,7 @@ __global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const floa
     }
     RqPlan* pa = plans + 2 * t;
     RqPlan* pb = pa + 1;
-    const int slots_max = top + 1;
+    const int slots_max = top + (b.has_shared ? b.sh_count : 1);
     float* ht = h + (size_t)t * slots_max * b.ffn;
     // Routed experts that live here take slots in ascending expert index. Every thread looks at one expert
     // per sweep; a selected expert's slot is the number of selected experts before it (ballots and counts).
@@ -311,7 +317,7 @@ __global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const floa
             RqSegment& sb = pb->seg[0];
             sb.main[n] = b.down + (size_t)le * b.hidden * dn_row_main;
             sb.scale[n] = b.down_sc ? b.down_sc + (size_t)le * b.hidden * dn_row_sc : nullptr;
-            sb.act[n] = n; sb.coef[n] = w;
+            sb.act[n] = n; sb.coef[n] = b.routed_scale == 1.0f ? w : __fmul_rn(w, b.routed_scale);
         }
         __syncthreads();
         if (tid == 0) { int total = 0; for (int w2 = 0; w2 < 8; ++w2) total += s_warp_count[w2]; s_base += total; }
@@ -320,13 +326,21 @@ __global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const floa
     if (tid == 0) {
         int n = s_base < top ? s_base : top;
         if (b.has_shared && include_shared) {
-            RqSegment& sa = pa->seg[n];
-            sa.row_begin = n * b.ffn; sa.rows = b.ffn; sa.y = ht + (size_t)n * b.ffn;
-            sa.main[0] = b.sh_gate; sa.main[1] = b.sh_up; sa.scale[0] = b.sh_gate_sc; sa.scale[1] = b.sh_up_sc;
-            sa.act[0] = 0; sa.act[1] = 0; sa.coef[0] = 1.0f; sa.coef[1] = 1.0f;
-            RqSegment& sb = pb->seg[0];
-            sb.main[n] = b.sh_down; sb.scale[n] = b.sh_down_sc; sb.act[n] = n; sb.coef[n] = s_gate;
-            ++n;
+            // the shared expert: sh_count slots of the routed experts' shape (rows j * ffn .. of its gate / up banks, column
+            // block j of its down bank), every one at the shared weight
+            const float weight = b.sh_gated ? s_gate : 1.0f;
+            for (int j = 0; j < b.sh_count; ++j, ++n) {
+                RqSegment& sa = pa->seg[n];
+                sa.row_begin = n * b.ffn; sa.rows = b.ffn; sa.y = ht + (size_t)n * b.ffn;
+                sa.main[0] = b.sh_gate + (size_t)j * b.ffn * in_row_main; sa.main[1] = b.sh_up + (size_t)j * b.ffn * in_row_main;
+                sa.scale[0] = b.sh_gate_sc ? b.sh_gate_sc + (size_t)j * b.ffn * in_row_sc : nullptr;
+                sa.scale[1] = b.sh_up_sc ? b.sh_up_sc + (size_t)j * b.ffn * in_row_sc : nullptr;
+                sa.act[0] = 0; sa.act[1] = 0; sa.coef[0] = 1.0f; sa.coef[1] = 1.0f;
+                RqSegment& sb = pb->seg[0];
+                sb.main[n] = b.sh_down + (size_t)j * b.hidden * dn_row_main;
+                sb.scale[n] = b.sh_down_sc ? b.sh_down_sc + (size_t)j * b.hidden * dn_row_sc : nullptr;
+                sb.act[n] = n; sb.coef[n] = weight;
+            }
         }
         pa->n_segments = n; pa->subs = 2; pa->total_rows = n * b.ffn; pa->pad = 0;
         RqSegment& sb = pb->seg[0];
@@ -343,7 +357,7 @@ static BankView view_of(const rq_moe* m) {
     BankView b;
     b.type = m->type; b.experts = m->experts; b.expert_first = m->expert_first; b.expert_count = m->expert_count; b.hidden = m->hidden; b.ffn = m->ffn;
     b.gate = m->gate; b.up = m->up; b.down = m->down; b.gate_sc = m->gate_sc; b.up_sc = m->up_sc; b.down_sc = m->down_sc;
-    b.has_shared = m->has_shared ? 1 : 0;
+    b.has_shared = m->has_shared ? 1 : 0; b.sh_count = m->sh_count; b.sh_gated = m->sh_gated ? 1 : 0; b.routed_scale = m->routed_scale;
     b.sh_gate = m->sh_gate; b.sh_up = m->sh_up; b.sh_down = m->sh_down; b.sh_gate_sc = m->sh_gate_sc; b.sh_up_sc = m->sh_up_sc; b.sh_down_sc = m->sh_down_sc;
     b.sh_vector = m->sh_vector;
     return b;
@@ -393,6 +407,7 @@ extern "C" void rq_moe_free(rq_ctx* ctx, rq_moe* m) {
     if (!m) return;
     DeviceGuard guard(ctx ? ctx->device : m->device);
     if (m->base) cudaFree(m->base);
+    if (m->sh_base) cudaFree(m->sh_base);
     delete m;
 }
 
@@ -413,7 +428,7 @@ extern "C" int rq_moe_prepare(rq_ctx* ctx, int type, const void* gate, const voi
     if (!m) return rq_fail(RQ_ERR_ALLOC, "out of host memory");
     memset(m, 0, sizeof(*m));
     m->type = type; m->experts = experts; m->expert_first = expert_first; m->expert_count = expert_count; m->hidden = hidden; m->ffn = ffn;
-    m->device = ctx->device; m->has_shared = shared;
+    m->device = ctx->device; m->has_shared = shared; m->sh_count = 1; m->sh_gated = true; m->routed_scale = 1.0f;
     const int64_t in_rows = (int64_t)expert_count * ffn, dn_rows = (int64_t)expert_count * hidden;
     const int64_t in_main = pad256(main_bytes_of(type, in_rows, hidden)), in_sc = pad256(scale_bytes_of(type, in_rows, hidden) + 64);
     const int64_t dn_main = pad256(main_bytes_of(type, dn_rows, ffn)), dn_sc = pad256(scale_bytes_of(type, dn_rows, ffn) + 64);
@@ -457,6 +472,58 @@ extern "C" int rq_moe_prepare(rq_ctx* ctx, int type, const void* gate, const voi
 
 extern "C" int64_t rq_moe_bytes(const rq_moe* m) { return m ? m->bytes : 0; }
 
+extern "C" int rq_moe_set_routed_scale(rq_moe* m, float scale) {
+    if (!m) return rq_fail(RQ_ERR_INVALID, "rq_moe_set_routed_scale: null bank");
+    if (!(scale == scale) || scale > 3.0e38f || scale < -3.0e38f) return rq_fail(RQ_ERR_INVALID, "moe routed scale must be finite");
+    m->routed_scale = scale;
+    return RQ_OK;
+}
+
+extern "C" int rq_moe_attach_shared(rq_ctx* ctx, rq_moe* m, int gated, int count, const void* sh_gate, const void* sh_up, const void* sh_down, const float* gate_vector) {
+    if (!ctx || !m || !sh_gate || !sh_up || !sh_down) return rq_fail(RQ_ERR_INVALID, "rq_moe_attach_shared: null argument");
+    if (m->has_shared) return rq_fail(RQ_ERR_INVALID, "rq_moe_attach_shared: the bank already has a shared expert");
+    if (count <= 0) return rq_fail(RQ_ERR_INVALID, "shared expert count must be positive");
+    if (count >= RQ_MAX_SUB) return rq_fail(RQ_ERR_LIMIT, "rq_moe_attach_shared: count=%d, at most %d", count, RQ_MAX_SUB - 1);
+    if (gated && !gate_vector) return rq_fail(RQ_ERR_INVALID, "rq_moe_attach_shared: a gated shared expert needs its gate vector");
+    DeviceGuard guard(ctx->device);
+    const int type = m->type, hidden = m->hidden, ffn = m->ffn, per = rq_block_values(type), stride = rq_block_bytes(type);
+    const int64_t width = (int64_t)count * ffn;
+    const int64_t in_main = pad256(main_bytes_of(type, width, hidden)), in_sc = pad256(scale_bytes_of(type, width, hidden) + 64);
+    const int64_t dn_main = pad256(main_bytes_of(type, (int64_t)count * hidden, ffn)), dn_sc = pad256(scale_bytes_of(type, (int64_t)count * hidden, ffn) + 64);
+    const int64_t vec = pad256((int64_t)hidden * 4);
+    const int64_t total = 2 * (in_main + in_sc) + dn_main + dn_sc + vec + 256;
+    cudaError_t e = cudaMalloc(&m->sh_base, (size_t)total);
+    if (e != cudaSuccess) return rq_fail(RQ_ERR_ALLOC, "shared expert of %lld bytes: %s", (long long)total, cudaGetErrorString(e));
+    uint8_t* at = m->sh_base;
+    auto take = [&](int64_t n) { uint8_t* p = at; at += n; return p; };
+    const bool planes = type != RQ_Q4_K;
+    m->sh_gate = take(in_main); m->sh_gate_sc = planes ? (uint16_t*)take(in_sc) : nullptr;
+    m->sh_up = take(in_main); m->sh_up_sc = planes ? (uint16_t*)take(in_sc) : nullptr;
+    m->sh_down = take(dn_main); m->sh_down_sc = planes ? (uint16_t*)take(dn_sc) : nullptr;
+    m->sh_vector = (float*)take(vec);
+    int rc = upload_bank(ctx, type, sh_gate, width, hidden, m->sh_gate, m->sh_gate_sc);
+    if (!rc) rc = upload_bank(ctx, type, sh_up, width, hidden, m->sh_up, m->sh_up_sc);
+    if (!rc) {
+        // down is [hidden][count * ffn]: column block j of every row becomes matrix j, [hidden][ffn] (a block of ffn inputs is
+        // whole GGUF blocks, so the split moves bytes, nothing is re-encoded)
+        const int64_t block_row = (int64_t)ffn / per * stride, full_row = block_row * count;
+        uint8_t* split = (uint8_t*)malloc((size_t)(full_row * hidden));
+        if (!split) rc = rq_fail(RQ_ERR_ALLOC, "out of host memory");
+        else {
+            for (int j = 0; j < count; ++j)
+                for (int64_t r = 0; r < hidden; ++r)
+                    memcpy(split + ((int64_t)j * hidden + r) * block_row, (const uint8_t*)sh_down + r * full_row + (int64_t)j * block_row, (size_t)block_row);
+            rc = upload_bank(ctx, type, split, (int64_t)count * hidden, ffn, m->sh_down, m->sh_down_sc);
+            free(split);
+        }
+    }
+    if (!rc && gated && cudaMemcpy(m->sh_vector, gate_vector, (size_t)hidden * 4, cudaMemcpyHostToDevice) != cudaSuccess) rc = rq_fail(RQ_ERR_CUDA, "shared gate vector upload failed");
+    if (rc) { cudaFree(m->sh_base); m->sh_base = nullptr; return rc; }
+    m->has_shared = true; m->sh_count = count; m->sh_gated = gated != 0;
+    m->bytes += total;
+    return RQ_OK;
+}
+
 extern "C" int rq_moe_route(rq_ctx* ctx, const float* scores, int64_t score_e_stride, int64_t score_t_stride, int experts, int top_k, int scoring,
                             int renormalize, const float* selection_bias, int tokens, float* weights, int64_t weight_e_stride,
                             int64_t weight_t_stride, void* stream) {
@@ -465,6 +532,15 @@ extern "C" int rq_moe_route(rq_ctx* ctx, const float* scores, int64_t score_e_st
     if (experts > 8192) return rq_fail(RQ_ERR_LIMIT, "rq_moe_route: %d experts, at most 8192", experts);
     if (scoring != RQ_SCORE_SOFTMAX && scoring != RQ_SCORE_SIGMOID) return rq_fail(RQ_ERR_INVALID, "rq_moe_route: scoring=%d", scoring);
     DeviceGuard guard(ctx->device);
+    if ((size_t)experts * 16 > 40 * 1024) {
+        // beyond the default dynamic shared memory of a block: opt in once per device (8192 experts take 128 KB)
+        static bool configured[64] = {};
+        int dev = ctx->device;
+        if (dev < 0 || dev >= 64 || !configured[dev]) {
+            RQ_CUDA(cudaFuncSetAttribute(rq_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8192 * 16));
+            if (dev >= 0 && dev < 64) configured[dev] = true;
+        }
+    }
     rq_route_kernel<<<tokens, kRouteThreads, (size_t)experts * 16, (cudaStream_t)stream>>>(scores, score_e_stride, score_t_stride, experts, top_k, scoring,
                                                                                         renormalize, selection_bias, weights, weight_e_stride,
                                                                                         weight_t_stride);
@@ -478,13 +554,15 @@ extern "C" int rq_moe_forward(rq_ctx* ctx, rq_moe* m, const float* x, int64_t x_
     if (!ctx || !m || !x || !routing || !y) return rq_fail(RQ_ERR_INVALID, "rq_moe_forward: null argument");
     if (m->device != ctx->device) return rq_fail(RQ_ERR_INVALID, "rq_moe_forward: bank lives on device %d, context on %d", m->device, ctx->device);
     if (tokens <= 0 || tokens > kMaxTokens) return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: tokens=%d, between 1 and %d per call", tokens, kMaxTokens);
-    if (top_k <= 0 || top_k + 1 > RQ_MAX_SUB) return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: top_k=%d, at most %d", top_k, RQ_MAX_SUB - 1);
+    const int shared_slots = m->has_shared ? m->sh_count : 1;
+    if (top_k <= 0 || top_k + shared_slots > RQ_MAX_SUB)
+        return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: top_k=%d with a shared expert of %d x the expert width: at most %d slots together", top_k, shared_slots, RQ_MAX_SUB);
     if (x_k_stride <= 0 || y_n_stride <= 0) return rq_fail(RQ_ERR_INVALID, "rq_moe_forward: strides must be positive");
     DeviceGuard guard(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
     int rc = rq_order_work_areas(ctx, s);  // the bank's plans and hidden activations are shared by every call on it
     if (rc) return rc;
-    const int slots = top_k + 1;
+    const int slots = top_k + shared_slots;
     rq_moe_plan_kernel<<<tokens, 256, 0, s>>>(view_of(m), routing, routing_e_stride, routing_t_stride, x, x_k_stride, x_t_stride, top_k, include_shared,
                                               m->plans, m->h, y, y_n_stride, y_t_stride);
     RQ_CUDA(cudaGetLastError());

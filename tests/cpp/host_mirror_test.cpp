@@ -59,6 +59,58 @@ int main() {
     rqo_moe_forward(RQO_Q4_K, bg.data(), bu.data(), bd.data(), experts, top, mh, ffn, xm.data(), routing.data(), 1, bsg.data(), bsu.data(), bsd.data(), sv.data(), yref.data(), 4);
     const double e2 = rel_err(ym, yref);
     if (!(e2 <= 1e-3)) { std::printf("moe relative error %g\n", e2); return 1; }
+    // .int(8) over a lone Q6_K tensor: recipe re-encodes it to Q8_0 at load (finish_int_sums, recipe.rs:22345-22369), and so does place()
+    {
+        std::vector<uint8_t> b8((size_t)hidden * mid / 32 * 34);
+        rqo_requantize_q8_0(RQO_Q6_K, b2.data(), (int64_t)hidden * mid, b8.data(), 4);
+        std::vector<float> xin2(mid), ref8(hidden);
+        rqo_normal(73, 0, 0, mid, 1.0, xin2.data());
+        rqo_matvec(RQO_Q8_0, b8.data(), hidden, mid, xin2.data(), 1, 1, ref8.data(), 1, RQO_ACT_INT8, 32, 4);
+        auto lone = Model().layer({RQ_Q6_K, hidden, mid, b2.data()}).int_(8).place(0);
+        std::vector<double> y8 = lone.infer(std::vector<double>(xin2.begin(), xin2.end()));
+        const double e3 = rel_err(y8, ref8);
+        if (!(e3 <= 5e-5)) { std::printf("lone Q6_K under int(8): relative error %g against the Q8_0 re-encode\n", e3); return 1; }
+        if (lone.resident_bytes()[0] != b8.size()) { std::printf("re-encoded weight holds %zu bytes, expected %zu\n", lone.resident_bytes()[0], b8.size()); return 1; }
+    }
+    // ids -> embedding -> two layers: prefill, step and greedy decode; a step gives the bits its position gets in a prefill
+    {
+        const int vocab = 96;
+        std::vector<float> emb((size_t)vocab * hidden), head((size_t)vocab * hidden);
+        rqo_normal(74, 0, 0, (int64_t)emb.size(), 1.0, emb.data());
+        rqo_normal(74, 1, 0, (int64_t)head.size(), 0.02, head.data());
+        std::vector<uint8_t> be(emb.size() / 32 * 34), bh(head.size() / 256 * 144);
+        rqo_quantize(RQO_Q8_0, emb.data(), (int64_t)emb.size(), be.data(), 4);
+        rqo_quantize(RQO_Q4_K, head.data(), (int64_t)head.size(), bh.data(), 4);
+        auto lm = Model().embed({RQ_Q8_0, vocab, hidden, be.data()}).layer({RQ_Q4_K, mid, hidden, b1.data()}).int_(8).layer({RQ_Q6_K, hidden, mid, b2.data()}).fp(32)
+                      .layer({RQ_Q4_K, vocab, hidden, bh.data()}).fp(32).place(0);
+        const std::vector<uint32_t> prompt = {5, 17, 3, 90, 41};
+        std::vector<double> whole = lm.prefill(prompt);
+        std::vector<double> part = lm.prefill({5, 17, 3, 90});
+        std::vector<double> stepped = lm.step(41);
+        if (whole != stepped) { std::printf("a step differs from the same position of a prefill\n"); return 1; }
+        if (lm.ids() != prompt) { std::printf("the retained prefix is wrong\n"); return 1; }
+        // the last position against the oracle: embedding row, then the three layers
+        std::vector<float> row(hidden), h1(mid), h2(hidden), lg(vocab);
+        std::vector<float> table((size_t)vocab * hidden);
+        rqo_dequantize(RQO_Q8_0, be.data(), (int64_t)table.size(), table.data(), 4);
+        for (int k = 0; k < hidden; ++k) row[k] = table[(size_t)41 * hidden + k];
+        rqo_matvec(RQO_Q4_K, b1.data(), mid, hidden, row.data(), 1, 1, h1.data(), 1, RQO_ACT_INT8, 32, 4);
+        rqo_matvec(RQO_Q6_K, b2.data(), hidden, mid, h1.data(), 1, 1, h2.data(), 1, RQO_ACT_FLOAT_RUN, 32, 4);
+        rqo_matvec(RQO_Q4_K, bh.data(), vocab, hidden, h2.data(), 1, 1, lg.data(), 1, RQO_ACT_FLOAT_RUN, 32, 4);
+        const double e4 = rel_err(whole, lg);
+        if (!(e4 <= 1e-3)) { std::printf("prefill logits relative error %g\n", e4); return 1; }
+        std::vector<uint32_t> gen = lm.decode(prompt, {7}, 4);
+        if (gen.empty() || gen.size() > 4) { std::printf("decode produced %zu ids\n", gen.size()); return 1; }
+        uint32_t best = 0;
+        for (int i = 1; i < vocab; ++i) if (lg[i] > lg[best]) best = (uint32_t)i;
+        if (gen[0] != best) { std::printf("greedy decode picked %u, the oracle's largest logit is %u\n", gen[0], best); return 1; }
+        try { lm.infer(std::vector<double>(hidden, 0.0)); std::printf("infer accepted a model of ids\n"); return 1; } catch (const RecipeError&) {}
+        try { lm.prefill({1000}); std::printf("an id outside the table was accepted\n"); return 1; } catch (const RecipeError&) {}
+        lm.clear();
+        try { lm.step(1); std::printf("step without a prefill was accepted\n"); return 1; } catch (const RecipeError& e) {
+            if (std::string(e.what()) != "step requires a completed prefill") { std::printf("wrong text: %s\n", e.what()); return 1; }
+        }
+    }
     std::printf("ok %g %g\n", e1, e2);
     return 0;
 }

@@ -45,6 +45,7 @@ class Oracle:
             getattr(lib, name).argtypes = [C.c_float]
         lib.rqo_topk.argtypes = [p, i32, i32, i32, i32, i32, p, p]
         lib.rqo_moe_forward.argtypes = [i32, p, p, p, i32, i32, i32, i32, p, p, i32, p, p, p, p, p, i32]
+        lib.rqo_moe_forward_ex.argtypes = [i32, p, p, p, i32, i32, i32, i32, p, p, i32, C.c_float, i32, i32, p, p, p, p, p, i32]
         lib.rqo_normal.argtypes = [C.c_uint64, C.c_uint64, i64, i64, C.c_double, p]
         lib.rqo_normal.restype = None
 
@@ -126,6 +127,27 @@ class Oracle:
             ptrs = (sg.ctypes.data, su.ctypes.data, sd.ctypes.data, sw.ctypes.data)
         rc = self.lib.rqo_moe_forward(t, g.ctypes.data, u.ctypes.data, d.ctypes.data, experts, top, hidden, ffn,
                                       x.ctypes.data, routing.ctypes.data, tokens, *ptrs, y.ctypes.data, threads or THREADS)
+        assert rc == 0, rc
+        return y
+
+    def moe_forward_ex(self, t, gate, up, down, experts, top, hidden, ffn, x, routing, routed_scale=1.0, shared_kind=0, shared_count=1, shared=None, threads=None):
+        """gguf_moe with a routed scale and an ungated (1) / gated (2) shared expert of shared_count * ffn width."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        routing = np.ascontiguousarray(routing, dtype=np.float32)
+        tokens = x.shape[1]
+        y = np.zeros((hidden, tokens), dtype=np.float32)
+        g, u, d = (np.ascontiguousarray(a, dtype=np.uint8) for a in (gate, up, down))
+        ptrs, keep = (None, None, None, None), []
+        if shared_kind:
+            sg, su, sd = (np.ascontiguousarray(a, dtype=np.uint8) for a in shared[:3])
+            keep = [sg, su, sd]
+            sw = None
+            if shared_kind == 2:
+                sw = np.ascontiguousarray(shared[3], dtype=np.float32)
+                keep.append(sw)
+            ptrs = (sg.ctypes.data, su.ctypes.data, sd.ctypes.data, None if sw is None else sw.ctypes.data)
+        rc = self.lib.rqo_moe_forward_ex(t, g.ctypes.data, u.ctypes.data, d.ctypes.data, experts, top, hidden, ffn, x.ctypes.data, routing.ctypes.data, tokens,
+                                         routed_scale, shared_kind, shared_count, *ptrs, y.ctypes.data, threads or THREADS)
         assert rc == 0, rc
         return y
 

@@ -105,3 +105,41 @@ def test_moe_argument_validation(rq_ctx, oracle):
     assert lib.rq_moe_route(rq_ctx.handle, None, 1, 1, 8, 2, 0, 1, None, 1, None, 1, 1, None) == -1
     s = cuda(np.zeros((8, 1), np.float32))
     assert lib.rq_moe_route(rq_ctx.handle, s.data_ptr(), 1, 1, 8, 9, 0, 1, None, 1, s.data_ptr(), 1, 1, None) == -1
+
+
+@pytest.mark.parametrize("kind,count,scale", [("ungated", 1, 1.0), ("ungated", 2, 2.5), ("gated", 3, 0.5), ("none", 1, 1.75)])
+def test_moe_routed_scale_and_shared_expert_variants(rq_ctx, oracle, kind, count, scale):
+    """The rest of gguf_moe's arguments (recipe.rs:23415-23459): a routed scale other than one, an ungated shared expert,
+    a shared expert that merges `count` experts (count times the expert width)."""
+    t, experts, top, hidden, ffn, tokens = ol.Q4_K, 16, 4, 512, 256, 3
+    gate, up, down, _ = make_bank(oracle, t, experts, hidden, ffn, 45)
+    width = count * ffn
+    sh = (oracle.quantize(t, oracle.normal(45, 4, width * hidden, 0.05)), oracle.quantize(t, oracle.normal(45, 5, width * hidden, 0.05)),
+          oracle.quantize(t, oracle.normal(45, 6, hidden * width, 0.05)), oracle.normal(45, 7, hidden, 0.05))
+    x = oracle.normal(45, 8, hidden * tokens, 1.0).reshape(hidden, tokens)
+    scores = oracle.normal(45, 9, experts * tokens, 1.0).reshape(experts, tokens)
+    routing = oracle.topk(scores, top, 0, True)
+    shared_kind = {"none": 0, "ungated": 1, "gated": 2}[kind]
+    want = oracle.moe_forward_ex(t, gate, up, down, experts, top, hidden, ffn, x, routing, routed_scale=scale, shared_kind=shared_kind, shared_count=count, shared=sh)
+    bank = rq_ctx.moe_prepare(t, gate, up, down, experts, hidden, ffn)
+    bank.set_routed_scale(scale)
+    if shared_kind:
+        bank.attach_shared(sh[0], sh[1], sh[2], count=count, gate_vector=sh[3] if shared_kind == 2 else None)
+    got = rq_ctx.moe_forward(bank, cuda(x), rq_ctx.moe_route(cuda(scores), top), top).cpu().numpy()
+    rq_ctx.check()
+    assert rel_err(got, want) <= TOL
+    # a second shared expert is refused, so is a non-finite scale, so is a count that leaves no room for the routed slots
+    import ctypes
+
+    if shared_kind:
+        assert rq_ctx.lib.rq_moe_attach_shared(rq_ctx.handle, bank.handle, 0, 1, sh[0].ctypes.data, sh[1].ctypes.data, sh[2].ctypes.data, None) == -1
+    assert rq_ctx.lib.rq_moe_set_routed_scale(bank.handle, ctypes.c_float(float("inf"))) == -1
+
+
+def test_route_many_experts(rq_ctx, oracle):
+    """4096 experts: beyond the default dynamic shared memory of a block."""
+    experts, tokens, top = 4096, 2, 6
+    scores = oracle.normal(46, 0, experts * tokens, 1.0).reshape(experts, tokens)
+    got = rq_ctx.moe_route(cuda(scores), top).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), oracle.topk(scores, top, 0, True).view(np.uint32))
+    rq_ctx.check()
