@@ -150,6 +150,23 @@ int rq_matvec(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t x_k_strid
 int rq_matvec_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
                     float* const* ys, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);
 
+/* The dense gated feed-forward's first half in one launch: y[n] = silu(gate[n] . x) * (up[n] . x), both matrices streamed
+ * as one virtual row set, the activation and the product applied as the launch's epilogue (lower_gated,
+ * recipe.rs:23279-23286; silu with recipe's portable transcendentals). gate and up: one format, one shape, rows of whole
+ * 256-value units. Arguments as rq_matvec. */
+int rq_matvec_glu(rq_ctx* ctx, const rq_weight* gate, const rq_weight* up, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens, float* y,
+                  int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);
+
+/* The steps either side of a projection in a decode layer, device pointers, enqueued on `stream`:
+ * RMS normalisation of `tokens` positions of n values, y = (x / sqrt(mean(x^2) + epsilon)) * gain (gain may be null),
+ *   emit_normalize_stats in Rms mode, recipe.rs:6836-7120;
+ * the residual add y = a + b over n values;
+ * the logit soft-cap y = cap * tanh(x / cap) with recipe's portable tanh (scale, tanh, scale: rnj-1.rs:47-51). */
+int rq_rmsnorm(rq_ctx* ctx, const float* x, int64_t x_k_stride, int64_t x_t_stride, int64_t n, int tokens, const float* gain, float epsilon, float* y,
+               int64_t y_k_stride, int64_t y_t_stride, void* stream);
+int rq_add(rq_ctx* ctx, const float* a, const float* b, int64_t n, float* y, void* stream);
+int rq_softcap(rq_ctx* ctx, const float* x, int64_t n, double cap, float* y, void* stream);
+
 /* The batched product (prefill, multi-sequence decode): the same contraction as rq_matvec for many
  * tokens. With RQ_ACT_FLOAT the weights are dequantised a tile at a time into shared memory and
  * multiplied on the tensor cores (tcgen05.mma, fp16 hi + lo operand pairs, fp32 accumulation in

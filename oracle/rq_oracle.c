@@ -1057,6 +1057,35 @@ int rqo_moe_forward(int type, const uint8_t* gate, const uint8_t* up, const uint
                               shared_gate_w, y, threads);
 }
 
+/* ------------------------------------------------- the steps either side of a projection */
+
+/* RMS normalisation of one position (emit_normalize_stats, recipe.rs:6836-7120, NormalizeMode::Rms, fp32 state, CPU wave
+ * width 1): the squares are added in index order (square, then add: two operations), variance = sum / n,
+ * scale = 1 / sqrt(variance + epsilon), y = (x * scale) * gain. gain may be NULL (no per-channel gain). */
+void rqo_rmsnorm(const float* x, int64_t x_stride, int64_t n, const float* gain, float epsilon, float* y, int64_t y_stride) {
+    float sum = 0.0f;
+    for (int64_t k = 0; k < n; ++k) { float v = x[k * x_stride]; float square = v * v; sum = sum + square; }
+    float variance = sum / (float)n;
+    float adjusted = variance + epsilon;
+    float deviation = sqrtf(adjusted);
+    float scale = 1.0f / deviation;
+    for (int64_t k = 0; k < n; ++k) {
+        float v = x[k * x_stride] * scale;
+        y[k * y_stride] = gain ? v * gain[k] : v;
+    }
+}
+
+/* Logit soft-cap as the model scripts spell it (rnj-1.rs:47-51): scale(1 / cap), tanh, scale(cap), with the portable tanh. */
+void rqo_softcap(const float* x, int64_t n, double cap, float* y) {
+    float down = (float)(1.0 / cap), up = (float)cap;
+    for (int64_t k = 0; k < n; ++k) y[k] = rqo_tanh(x[k] * down) * up;
+}
+
+/* lower_gated (recipe.rs:23279-23286): act(gate) * up, elementwise, silu with the portable transcendentals. */
+void rqo_glu(const float* gate, const float* up, int64_t n, float* y) {
+    for (int64_t k = 0; k < n; ++k) y[k] = rqo_silu(gate[k]) * up[k];
+}
+
 /* ------------------------------------------------------------------ synthetic inputs */
 
 static inline uint64_t splitmix64(uint64_t z) {

@@ -96,6 +96,12 @@ int rqo_moe_forward_ex(int type, const uint8_t* gate, const uint8_t* up, const u
                        const uint8_t* sh_gate, const uint8_t* sh_up, const uint8_t* sh_down,
                        const float* shared_gate_w, float* y, int threads);
 
+/* The steps either side of a projection in a decode layer: RMS norm (recipe.rs:6836-7120, Rms mode), the logit soft-cap
+ * (scale, tanh, scale: rnj-1.rs:47-51) and the gated product silu(gate) * up (lower_gated, recipe.rs:23279-23286). */
+void rqo_rmsnorm(const float* x, int64_t x_stride, int64_t n, const float* gain, float epsilon, float* y, int64_t y_stride);
+void rqo_softcap(const float* x, int64_t n, double cap, float* y);
+void rqo_glu(const float* gate, const float* up, int64_t n, float* y);
+
 /* Counter-based synthetic inputs: splitmix64 -> Box-Muller (f64) -> scale -> f32.
  * Value i of stream (seed, stream) depends only on (seed, stream, i). */
 void rqo_normal(uint64_t seed, uint64_t stream, int64_t first, int64_t count, double sigma, float* out);

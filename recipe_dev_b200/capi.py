@@ -58,6 +58,10 @@ def _declare(lib) -> None:
         "rq_gather_rows": (i32, [p, p, p, i32, f32p, i64, i64, p]),
         "rq_matvec": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
         "rq_matmul": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
+        "rq_matvec_glu": (i32, [p, p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32, p]),
+        "rq_rmsnorm": (i32, [p, f32p, i64, i64, i64, i32, f32p, C.c_float, f32p, i64, i64, p]),
+        "rq_add": (i32, [p, f32p, f32p, i64, f32p, p]),
+        "rq_softcap": (i32, [p, f32p, i64, C.c_double, f32p, p]),
         "rq_matvec_multi": (i32, [p, i32, p, f32p, i64, i64, i32, p, i64, i64, i32, i32, p]),
         "rq_matvec_host": (i32, [p, p, f32p, i64, i64, i32, f32p, i64, i64, i32, i32]),
         "rq_matvec_multi_host": (i32, [p, i32, p, f32p, i64, i64, i32, p, i64, i64, i32, i32]),
@@ -347,6 +351,48 @@ class Context:
         _check(self.lib.rq_matvec(self.handle, w.handle, _ptr(x2), x2.stride(1), x2.stride(0), tokens,
                                   _ptr(y2), y2.stride(1), y2.stride(0), act_mode, step, _stream(stream)))
         return y2[0] if single else y2
+
+    def matvec_glu(self, gate: Weight, up: Weight, x, y=None, act_mode: int = ACT_FLOAT, step: int = 32, stream=None):
+        """silu(gate x) * (up x) in one launch; x [cols] or [tokens, cols] -> y [rows] or [tokens, rows]."""
+        import torch
+
+        single = x.dim() == 1
+        x2 = x.unsqueeze(0) if single else x
+        tokens = x2.shape[0]
+        if y is None:
+            y = torch.empty((tokens, gate.rows), dtype=torch.float32, device=x.device)
+        y2 = y.unsqueeze(0) if y.dim() == 1 else y
+        _check(self.lib.rq_matvec_glu(self.handle, gate.handle, up.handle, _ptr(x2), x2.stride(1), x2.stride(0), tokens, _ptr(y2), y2.stride(1), y2.stride(0),
+                                      act_mode, step, _stream(stream)))
+        return y2[0] if single else y2
+
+    def rmsnorm(self, x, gain=None, epsilon: float = 1e-6, y=None, stream=None):
+        """x [n] or [tokens, n] (token-major) -> RMS-normalised, times gain [n] when given."""
+        import torch
+
+        x2 = x.unsqueeze(0) if x.dim() == 1 else x
+        tokens, n = x2.shape
+        if y is None:
+            y = torch.empty_like(x2)
+        y2 = y.unsqueeze(0) if y.dim() == 1 else y
+        _check(self.lib.rq_rmsnorm(self.handle, _ptr(x2), x2.stride(1), x2.stride(0), n, tokens, _ptr(gain), epsilon, _ptr(y2), y2.stride(1), y2.stride(0), _stream(stream)))
+        return y2[0] if x.dim() == 1 else y2
+
+    def add(self, a, b, y=None, stream=None):
+        import torch
+
+        if y is None:
+            y = torch.empty_like(a)
+        _check(self.lib.rq_add(self.handle, _ptr(a), _ptr(b), a.numel(), _ptr(y), _stream(stream)))
+        return y
+
+    def softcap(self, x, cap: float, y=None, stream=None):
+        import torch
+
+        if y is None:
+            y = torch.empty_like(x)
+        _check(self.lib.rq_softcap(self.handle, _ptr(x), x.numel(), cap, _ptr(y), _stream(stream)))
+        return y
 
     def matmul(self, w: Weight, x, y=None, act_mode: int = ACT_FLOAT, step: int = 32, stream=None):
         """x: CUDA fp32 [tokens, cols] -> y [tokens, rows]; the tensor-core path for RQ_ACT_FLOAT."""

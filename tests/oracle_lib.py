@@ -46,6 +46,12 @@ class Oracle:
         lib.rqo_topk.argtypes = [p, i32, i32, i32, i32, i32, p, p]
         lib.rqo_moe_forward.argtypes = [i32, p, p, p, i32, i32, i32, i32, p, p, i32, p, p, p, p, p, i32]
         lib.rqo_moe_forward_ex.argtypes = [i32, p, p, p, i32, i32, i32, i32, p, p, i32, C.c_float, i32, i32, p, p, p, p, p, i32]
+        lib.rqo_rmsnorm.argtypes = [p, i64, i64, p, C.c_float, p, i64]
+        lib.rqo_rmsnorm.restype = None
+        lib.rqo_softcap.argtypes = [p, i64, C.c_double, p]
+        lib.rqo_softcap.restype = None
+        lib.rqo_glu.argtypes = [p, p, i64, p]
+        lib.rqo_glu.restype = None
         lib.rqo_normal.argtypes = [C.c_uint64, C.c_uint64, i64, i64, C.c_double, p]
         lib.rqo_normal.restype = None
 
@@ -149,6 +155,28 @@ class Oracle:
         rc = self.lib.rqo_moe_forward_ex(t, g.ctypes.data, u.ctypes.data, d.ctypes.data, experts, top, hidden, ffn, x.ctypes.data, routing.ctypes.data, tokens,
                                          routed_scale, shared_kind, shared_count, *ptrs, y.ctypes.data, threads or THREADS)
         assert rc == 0, rc
+        return y
+
+    def rmsnorm(self, x: np.ndarray, gain, epsilon: float) -> np.ndarray:
+        """x [n] or [tokens, n] -> the RMS-normalised positions."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        x2 = x[None, :] if x.ndim == 1 else x
+        y = np.empty_like(x2)
+        g = None if gain is None else np.ascontiguousarray(gain, dtype=np.float32)
+        for t in range(x2.shape[0]):
+            self.lib.rqo_rmsnorm(x2[t].ctypes.data, 1, x2.shape[1], None if g is None else g.ctypes.data, epsilon, y[t].ctypes.data, 1)
+        return y[0] if x.ndim == 1 else y
+
+    def softcap(self, x: np.ndarray, cap: float) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty_like(x)
+        self.lib.rqo_softcap(x.ctypes.data, x.size, cap, y.ctypes.data)
+        return y
+
+    def glu(self, gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+        g, u = np.ascontiguousarray(gate, dtype=np.float32), np.ascontiguousarray(up, dtype=np.float32)
+        y = np.empty_like(g)
+        self.lib.rqo_glu(g.ctypes.data, u.ctypes.data, g.size, y.ctypes.data)
         return y
 
     def normal(self, seed: int, stream: int, count: int, sigma: float = 1.0, first: int = 0) -> np.ndarray:

@@ -34,11 +34,13 @@ def test_recorded_layer_matches_direct_calls(oracle):
             ctx.matvec_multi([w["gate"], w["up"]], o, [gu[:ffn], gu[ffn:]], act_mode=rq.ACT_INT8, stream=stream)
             ctx.matvec(w["down"], gu[:ffn], y, act_mode=rq.ACT_INT8, stream=stream)
 
-        # a recording cannot allocate: without a reservation the first recorded call is refused and the recording ends invalid
+        # a recording cannot allocate: without a reservation a recorded call that needs a larger work area is refused
+        # (before it touches the stream, so the recording itself stays valid and simply holds nothing)
         s = ctx.sequence_begin()
         with pytest.raises(rq.RqError, match="rq_reserve"):
             ctx.matvec(w["down"], gu[:ffn], y, act_mode=rq.ACT_INT8, stream=s)
-        with pytest.raises(rq.RqError):
+        ctx.sequence_end().free()
+        with pytest.raises(rq.RqError, match="not recording"):
             ctx.sequence_end()
         ctx.reserve(ffn, ffn, 1)
         xs = [oracle.normal(95, 10 + i, hidden, 1.0) for i in range(3)]
