@@ -1,7 +1,7 @@
 """Independent NumPy restatement of the reference unpacking -- TEST INFRASTRUCTURE ONLY.
 
-A second, vectorised statement of recipe.rs:3687-3833 (dequant_q45k, dequant_q6k,
-dequant_scalar) evaluated as HostQuantOps does (recipe.rs:3973-4057): every product and the
+A second, vectorised statement of recipe.rs:3687-3833 and :3919-3958 (dequant_q45k, dequant_q6k,
+dequant_scalar, dequant_iq4) evaluated as HostQuantOps does (recipe.rs:3973-4057): every product and the
 final subtract in float64, the result rounded once to float32. It shares no code with
 rq_oracle.c, so agreement between the two pins the layout reading of each. Only tests import it.
 """
@@ -10,7 +10,15 @@ from __future__ import annotations
 import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
-GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL = 3, 6, 7, 13, 20
+GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
+            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176), IQ4_NL: (32, 18)}
+IQ4_LEVELS = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float64)  # recipe.rs:15211
+
+
+def _fifth_bits(qh: np.ndarray) -> np.ndarray:
+    """Four bytes per block -> 32 bits, value i = bit i % 8 of byte i // 8 (dequant_scalar, man 5)."""
+    return np.unpackbits(qh, axis=1, bitorder="little").astype(np.int64)
 
 
 def _half(raw: np.ndarray) -> np.ndarray:
@@ -58,6 +66,41 @@ def dequantize(ggml_type: int, blocks: np.ndarray) -> np.ndarray:
             scale = np.repeat(sc[:, :, g, :], 16, axis=2)
             out[:, :, g, :] = (d[:, None, None] * scale) * code
         out = out.reshape(n, 256)
+    elif ggml_type == Q4_1:
+        d, m = _half(b[:, 0:2]), _half(b[:, 2:4])
+        qs = b[:, 4:20]
+        q = np.concatenate([qs & 15, qs >> 4], axis=1).astype(np.float64)
+        out = q * d[:, None] + m[:, None]
+    elif ggml_type in (Q5_0, Q5_1):
+        header = 4 if ggml_type == Q5_1 else 2
+        d = _half(b[:, 0:2])
+        qs = b[:, header + 4:header + 20]
+        low = np.concatenate([qs & 15, qs >> 4], axis=1).astype(np.int64)
+        code = low | (_fifth_bits(b[:, header:header + 4]) << 4)
+        if ggml_type == Q5_0:
+            out = (code - 16).astype(np.float64) * d[:, None]
+        else:
+            out = code.astype(np.float64) * d[:, None] + _half(b[:, 2:4])[:, None]
+    elif ggml_type == Q5_K:
+        d, dmin = _half(b[:, 0:2]), _half(b[:, 2:4])
+        s = b[:, 4:16].astype(np.int64)
+        sc = np.empty((n, 8), np.int64)
+        mn = np.empty((n, 8), np.int64)
+        sc[:, :4] = s[:, 0:4] & 63
+        mn[:, :4] = s[:, 4:8] & 63
+        sc[:, 4:] = (s[:, 8:12] & 15) | ((s[:, 0:4] >> 6) << 4)
+        mn[:, 4:] = (s[:, 8:12] >> 4) | ((s[:, 4:8] >> 6) << 4)
+        qh = b[:, 16:48].astype(np.int64)                     # bit `sub` of byte w is the fifth bit of value w of sub-block `sub`
+        qs = b[:, 48:176].reshape(n, 4, 32)
+        low = np.stack([qs & 15, qs >> 4], axis=2).reshape(n, 8, 32).astype(np.int64)
+        high = np.stack([(qh >> sub) & 1 for sub in range(8)], axis=1)
+        q = (low | (high << 4)).astype(np.float64)
+        out = ((d[:, None] * sc)[:, :, None] * q - (dmin[:, None] * mn)[:, :, None]).reshape(n, 256)
+    elif ggml_type == IQ4_NL:
+        d = _half(b[:, 0:2])
+        qs = b[:, 2:18]
+        code = np.concatenate([qs & 15, qs >> 4], axis=1)
+        out = (d[:, None] * 1.0) * IQ4_LEVELS[code]
     else:
         raise ValueError(f"type {ggml_type}")
     return out.astype(np.float32).reshape(-1)

@@ -18,8 +18,8 @@
 /* recipe.rs:15811-15822: block / stride of the four formats on the path. */
 int rqo_block_values(int type) {
     switch (type) {
-        case RQO_Q4_0: case RQO_Q8_0: return 32;
-        case RQO_Q4_K: case RQO_Q6_K: return 256;
+        case RQO_Q4_0: case RQO_Q8_0: case RQO_Q4_1: case RQO_Q5_0: case RQO_Q5_1: case RQO_IQ4_NL: return 32;
+        case RQO_Q4_K: case RQO_Q6_K: case RQO_Q5_K: return 256;
         default: return 0;
     }
 }
@@ -29,6 +29,11 @@ int rqo_block_bytes(int type) {
         case RQO_Q8_0: return 34;
         case RQO_Q4_K: return 144;
         case RQO_Q6_K: return 210;
+        case RQO_Q4_1: return 20;
+        case RQO_Q5_0: return 22;
+        case RQO_Q5_1: return 24;
+        case RQO_Q5_K: return 176;
+        case RQO_IQ4_NL: return 18;
         default: return 0;
     }
 }
@@ -153,14 +158,61 @@ static inline int q40_code(const uint8_t* b, int i) { return ((b[2 + i % 16] >> 
 static inline float q80_value(const uint8_t* b, int i) { return (float)q80_code(b, i) * half_at(b); }
 static inline float q40_value(const uint8_t* b, int i) { return (float)q40_code(b, i) * half_at(b); }
 
+/* recipe.rs:3782-3833, variant 1 (a block minimum after the step: header d, m) and man 5 (the
+ * fifth bit of value i is bit i % 8 of byte header + i / 8; the nibbles follow those four bytes). */
+static inline float q41_value(const uint8_t* b, int i) {
+    int code = (b[4 + i % 16] >> ((i / 16) * 4)) & 15;
+    float product = (float)code * half_at(b);
+    return product + half_at(b + 2);
+}
+static inline float q50_value(const uint8_t* b, int i) {
+    int low = (b[6 + i % 16] >> ((i / 16) * 4)) & 15;
+    int high = (b[2 + i / 8] >> (i % 8)) & 1;
+    return (float)((low | (high << 4)) - 16) * half_at(b);
+}
+static inline float q51_value(const uint8_t* b, int i) {
+    int low = (b[8 + i % 16] >> ((i / 16) * 4)) & 15;
+    int high = (b[4 + i / 8] >> (i % 8)) & 1;
+    float product = (float)(low | (high << 4)) * half_at(b);
+    return product + half_at(b + 2);
+}
+/* recipe.rs:3687-3741 with man = 5: the nibbles start at byte 48, the fifth bit of value i of
+ * sub-block `sub` is bit `sub` of byte 16 + i % 32; scales and minima as Q4_K. */
+static inline float q5k_value(const uint8_t* b, int i) {
+    int sub = i / 32, within = i % 32;
+    int low = (b[48 + (sub / 2) * 32 + within] >> ((sub % 2) * 4)) & 15;
+    int high = (b[16 + within] >> sub) & 1;
+    int sc, mn;
+    q4k_scale_min(b + 4, sub, &sc, &mn);
+    float step = half_at(b) * (float)sc;
+    float base = half_at(b + 2) * (float)mn;
+    float product = step * (float)(low | (high << 4));
+    return product - base;
+}
+/* recipe.rs:3919-3958 without the per-sub-block exponent (xs = false): (d * 1) * IQ4[nibble];
+ * levels recipe.rs:15211. */
+static const int8_t IQ4_LEVELS[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+static inline float iq4nl_value(const uint8_t* b, int i) {
+    int code = (b[2 + i % 16] >> (i < 16 ? 0 : 4)) & 15;
+    float scaled = half_at(b) * 1.0f;
+    return scaled * (float)IQ4_LEVELS[code];
+}
+
 static inline float block_value(int type, const uint8_t* b, int i) {
     switch (type) {
         case RQO_Q4_0: return q40_value(b, i);
         case RQO_Q8_0: return q80_value(b, i);
         case RQO_Q4_K: return q4k_value(b, i);
+        case RQO_Q4_1: return q41_value(b, i);
+        case RQO_Q5_0: return q50_value(b, i);
+        case RQO_Q5_1: return q51_value(b, i);
+        case RQO_Q5_K: return q5k_value(b, i);
+        case RQO_IQ4_NL: return iq4nl_value(b, i);
         default: return q6k_value(b, i);
     }
 }
+/* the four formats with their own int8 slice helpers, exact-slice helpers and quantisers here */
+static inline int type_has_slices(int type) { return type == RQO_Q4_0 || type == RQO_Q8_0 || type == RQO_Q4_K || type == RQO_Q6_K; }
 
 /* ----------------------------------------------------------------------- threading */
 
@@ -424,7 +476,7 @@ static void quant_span(void* p, int64_t first, int64_t last, int worker, int wor
 }
 int rqo_quantize(int type, const float* values, int64_t count, uint8_t* blocks, int threads) {
     int per = rqo_block_values(type);
-    if (!per || count < 0) return -1;
+    if (!per || count < 0 || !type_has_slices(type)) return -1; /* encoders exist for the four formats of the path */
     quant_ctx c = {type, values, count, blocks};
     run_spans((count + per - 1) / per, threads, quant_span, &c);
     return 0;
@@ -779,6 +831,8 @@ int rqo_matvec(int type, const uint8_t* blocks, int64_t rows, int64_t cols,
     if (!per || rows < 0 || cols <= 0 || cols % per || tokens < 0) return -1;
     if (act_mode < 0 || act_mode > 2) return -1;
     if (act_mode == RQO_ACT_INT8 && step != 32 && step != 256) return -1;
+    /* the other stored formats are dotted by the run decoders only; `.int(8)` re-encodes them first */
+    if (act_mode != RQO_ACT_FLOAT_RUN && !type_has_slices(type)) return -1;
     matvec_ctx c = {type, blocks, rows, cols, x, x_stride, tokens, y, y_stride, act_mode, step, NULL};
     uint8_t* records = NULL;
     if (act_mode == RQO_ACT_INT8) {

@@ -29,6 +29,13 @@ extern "C" {
 #define RQO_Q8_0 8
 #define RQO_Q4_K 12
 #define RQO_Q6_K 14
+/* stored formats the same bodies serve beside the four above (recipe.rs:15812-15821, IQ4_NL :15823):
+ * decoded per value, dotted by the run decoders, re-encoded to Q8_0 under `.int(8)` */
+#define RQO_Q4_1 3
+#define RQO_Q5_0 6
+#define RQO_Q5_1 7
+#define RQO_Q5_K 13
+#define RQO_IQ4_NL 20
 
 /* activation handling, as a layer gets it from its precision (recipe.rs:22326-22369) */
 #define RQO_ACT_FLOAT_RUN 0   /* packed bodies + run decoders: recipe.rs:7826-7917, ll:3136-3508 */
@@ -36,7 +43,7 @@ extern "C" {
 #define RQO_ACT_INT8 2        /* int8 records: ll:1381-1517 and the slice/block dots */
 
 int rqo_block_values(int type);  /* 32 or 256, 0 if unknown */
-int rqo_block_bytes(int type);   /* 18, 34, 144, 210 */
+int rqo_block_bytes(int type);   /* 18, 34, 144, 210; 20, 22, 24, 176, 18 */
 
 uint16_t rqo_fp16(float value);      /* recipe.rs:15098-15112 */
 float rqo_unfp16(uint16_t value);    /* recipe.rs:15114-15126 */

@@ -22,8 +22,8 @@ extern "C" const char* rq_last_error(void) { return g_error; }
 
 extern "C" int rq_block_values(int t) {
     switch (t) {
-        case RQ_Q4_0: case RQ_Q8_0: return 32;
-        case RQ_Q4_K: case RQ_Q6_K: return 256;
+        case RQ_Q4_0: case RQ_Q8_0: case RQ_Q4_1: case RQ_Q5_0: case RQ_Q5_1: case RQ_IQ4_NL: return 32;
+        case RQ_Q4_K: case RQ_Q6_K: case RQ_Q5_K: return 256;
         default: return 0;
     }
 }
@@ -33,6 +33,11 @@ extern "C" int rq_block_bytes(int t) {
         case RQ_Q8_0: return 34;
         case RQ_Q4_K: return 144;
         case RQ_Q6_K: return 210;
+        case RQ_Q4_1: return 20;
+        case RQ_Q5_0: return 22;
+        case RQ_Q5_1: return 24;
+        case RQ_Q5_K: return 176;
+        case RQ_IQ4_NL: return 18;
         default: return 0;
     }
 }
@@ -215,7 +220,7 @@ extern "C" int rq_wait_selftest(rq_ctx* ctx, void* stream) {
 
 static int check_shape(const char* who, int type, int64_t rows, int64_t cols) {
     int per = rq_block_values(type);
-    if (!per) return rq_fail(RQ_ERR_INVALID, "%s: GGML type %d is not one of Q4_0(2) Q8_0(8) Q4_K(12) Q6_K(14)", who, type);
+    if (!per) return rq_fail(RQ_ERR_INVALID, "%s: GGML type %d is not one of Q4_0(2) Q4_1(3) Q5_0(6) Q5_1(7) Q8_0(8) Q4_K(12) Q5_K(13) Q6_K(14) IQ4_NL(20)", who, type);
     if (rows <= 0 || cols <= 0) return rq_fail(RQ_ERR_INVALID, "%s: rows=%lld cols=%lld must be positive", who, (long long)rows, (long long)cols);
     if (cols % per) return rq_fail(RQ_ERR_INVALID, "%s: cols=%lld is not a multiple of the %d-value block", who, (long long)cols, per);
     if (cols > (int64_t)1 << 24 || rows > (int64_t)1 << 31) return rq_fail(RQ_ERR_LIMIT, "%s: shape %lld x %lld beyond the supported range", who, (long long)rows, (long long)cols);
@@ -229,8 +234,9 @@ static int alloc_weight(rq_ctx* ctx, int type, int64_t rows, int64_t cols, rq_we
     w->type = type; w->rows = rows; w->cols = cols; w->device = ctx->device;
     int per = rq_block_values(type), bytes = rq_block_bytes(type);
     int64_t blocks = rows * (cols / per);
-    int64_t main_bytes = type == RQ_Q4_K ? blocks * 144 : blocks * (bytes - 2);
-    int64_t scale_bytes = type == RQ_Q4_K ? 0 : blocks * 2;
+    // formats kept as their GGUF blocks have one plane; the others a body plane and an fp16 scale plane
+    int64_t main_bytes = rq_type_keeps_blocks(type) ? blocks * bytes : blocks * (bytes - 2);
+    int64_t scale_bytes = rq_type_keeps_blocks(type) ? 0 : blocks * 2;
     w->bytes = main_bytes + scale_bytes;
     // one allocation, scale plane after the main plane at a 256-byte boundary
     int64_t main_padded = (main_bytes + 255) / 256 * 256;
@@ -240,6 +246,31 @@ static int alloc_weight(rq_ctx* ctx, int type, int64_t rows, int64_t cols, rq_we
     w->main = base;
     w->scale = scale_bytes ? (uint16_t*)(base + main_padded) : nullptr;
     *out = w;
+    return RQ_OK;
+}
+
+int rq_make_tile_map(rq_weight* w) {
+    w->has_tile_map = 0;
+    if ((w->type != RQ_Q4_K && w->type != RQ_Q6_K) || w->cols % 256) return RQ_OK;
+    typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeTiled encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess || found != cudaDriverEntryPointSuccess || !fn)
+            return rq_fail(RQ_ERR_CUDA, "the driver does not export cuTensorMapEncodeTiled");
+        encode = (EncodeTiled)fn;
+    }
+    const cuuint64_t unit = w->type == RQ_Q4_K ? 144 : 208, row_bytes = (cuuint64_t)(w->cols / 256) * unit;
+    const cuuint64_t dims[2] = {row_bytes, (cuuint64_t)w->rows};
+    const cuuint64_t strides[1] = {row_bytes};          // bytes between rows: a multiple of 16 (144 = 9 x 16, 208 = 13 x 16)
+    const cuuint32_t box[2] = {(cuuint32_t)unit, 128};  // one superblock of 128 rows; rows past the end arrive as zeros
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&w->tile_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->main, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return rq_fail(RQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d for a %lld x %lld weight", (int)rc, (long long)w->rows, (long long)w->cols);
+    w->has_tile_map = 1;
     return RQ_OK;
 }
 
@@ -260,6 +291,7 @@ extern "C" int rq_weight_prepare_device(rq_ctx* ctx, int type, const void* dev_b
     rc = alloc_weight(ctx, type, rows, cols, &w);
     if (rc) return rc;
     rc = rq_launch_repack(w, (const uint8_t*)dev_blocks, (cudaStream_t)stream);
+    if (!rc) rc = rq_make_tile_map(w);
     if (rc) { rq_weight_free(ctx, w); return rc; }
     *out = w;
     return RQ_OK;
@@ -517,10 +549,24 @@ extern "C" int rq_quantize_activations(rq_ctx* ctx, const float* x, int64_t sk, 
 
 // ---- recorded sequences: one boundary crossing per step ----------------------------------------------
 
+// Host <-> device planes of a recorded sequence, moved by a kernel rather than by the copy engines: the host buffer is pinned
+// and mapped, one CTA reads (or writes) it across the bus, and the move is one more kernel of the same submission.
+__global__ void __launch_bounds__(256) rq_plane_move_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t n, const int* flag_src, int* flag_dst) {
+    const int64_t n4 = (((uintptr_t)src | (uintptr_t)dst) & 15) == 0 ? n >> 2 : 0;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) ((float4*)dst)[i] = ((const float4*)src)[i];
+    for (int64_t i = 4 * n4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
+    if (flag_src && blockIdx.x == 0 && threadIdx.x == 0) *flag_dst = *flag_src;
+}
+
 struct rq_sequence {
     rq_ctx* ctx;
     cudaGraph_t graph;
     cudaGraphExec_t exec;
+    // rq_sequence_run_host: the copy in, the recorded calls, the copy out and the error word as ONE graph over the sequence's
+    // own pinned buffers, built at the first call and rebuilt when the call's pointers or sizes change
+    cudaGraphExec_t host_exec;
+    float* pin_in; float* pin_out; size_t pin_in_bytes, pin_out_bytes;
+    float* host_dev_in; const float* host_dev_out; int64_t host_in_floats, host_out_floats;
 };
 
 extern "C" int rq_device_alloc(rq_ctx* ctx, int64_t bytes, void** out) {
@@ -560,6 +606,7 @@ extern "C" int rq_sequence_end(rq_ctx* ctx, rq_sequence** out) {
     if (e != cudaSuccess || !graph) { cudaGetLastError(); return rq_fail(RQ_ERR_CUDA, "the recording was invalidated (a recorded call failed or did something a recording cannot hold): %s", cudaGetErrorString(e)); }
     rq_sequence* seq = new (std::nothrow) rq_sequence();
     if (!seq) { cudaGraphDestroy(graph); return rq_fail(RQ_ERR_ALLOC, "out of host memory"); }
+    memset(seq, 0, sizeof(*seq));
     seq->ctx = ctx; seq->graph = graph; seq->exec = nullptr;
     e = cudaGraphInstantiate(&seq->exec, graph, 0);
     if (e != cudaSuccess) { cudaGraphDestroy(graph); delete seq; return rq_fail(RQ_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
@@ -574,8 +621,11 @@ extern "C" void rq_sequence_free(rq_sequence* seq) {
     if (!seq) return;
     DeviceGuard guard(seq->ctx->device);
     cudaStreamSynchronize(seq->ctx->stream);
+    if (seq->host_exec) cudaGraphExecDestroy(seq->host_exec);
     if (seq->exec) cudaGraphExecDestroy(seq->exec);
     if (seq->graph) cudaGraphDestroy(seq->graph);
+    if (seq->pin_in) cudaFreeHost(seq->pin_in);
+    if (seq->pin_out) cudaFreeHost(seq->pin_out);
     delete seq;
 }
 
@@ -593,21 +643,53 @@ extern "C" int rq_sequence_run_host(rq_sequence* seq, const float* host_in, floa
     if (in_floats <= 0 || out_floats <= 0) return rq_fail(RQ_ERR_INVALID, "rq_sequence_run_host: in_floats and out_floats must be positive");
     rq_ctx* ctx = seq->ctx;
     DeviceGuard guard(ctx->device);
-    // pinned staging on both sides, so that the two copies are asynchronous and the call synchronises once
-    float* unused = nullptr; size_t zero = 0;
     const size_t ib = (size_t)in_floats * 4, ob = (size_t)out_floats * 4;
-    if (ib > ctx->pin_x_bytes) { if (ctx->pin_x) cudaFreeHost(ctx->pin_x); ctx->pin_x = nullptr; ctx->pin_x_bytes = 0; RQ_CUDA(cudaMallocHost(&ctx->pin_x, ib)); ctx->pin_x_bytes = ib; }
-    if (ob > ctx->pin_y_bytes) { if (ctx->pin_y) cudaFreeHost(ctx->pin_y); ctx->pin_y = nullptr; ctx->pin_y_bytes = 0; RQ_CUDA(cudaMallocHost(&ctx->pin_y, ob)); ctx->pin_y_bytes = ob; }
-    (void)unused; (void)zero;
-    memcpy(ctx->pin_x, host_in, ib);
+    if (!seq->host_exec || seq->host_dev_in != dev_in || seq->host_dev_out != dev_out || seq->host_in_floats != in_floats || seq->host_out_floats != out_floats) {
+        // (re)build the one-submission graph: pinned x -> dev_in, the recorded calls, dev_out -> pinned y and the error word
+        RQ_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (seq->host_exec) { cudaGraphExecDestroy(seq->host_exec); seq->host_exec = nullptr; }
+        if (ib > seq->pin_in_bytes) { if (seq->pin_in) cudaFreeHost(seq->pin_in); seq->pin_in = nullptr; seq->pin_in_bytes = 0; RQ_CUDA(cudaMallocHost(&seq->pin_in, ib)); seq->pin_in_bytes = ib; }
+        if (ob > seq->pin_out_bytes) { if (seq->pin_out) cudaFreeHost(seq->pin_out); seq->pin_out = nullptr; seq->pin_out_bytes = 0; RQ_CUDA(cudaMallocHost(&seq->pin_out, ob)); seq->pin_out_bytes = ob; }
+        RQ_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        const unsigned in_ctas = (unsigned)((in_floats + 4095) / 4096 < 8 ? (in_floats + 4095) / 4096 : 8), out_ctas = (unsigned)((out_floats + 4095) / 4096 < 8 ? (out_floats + 4095) / 4096 : 8);
+        rq_plane_move_kernel<<<in_ctas, 256, 0, ctx->stream>>>(seq->pin_in, dev_in, in_floats, nullptr, nullptr);
+        cudaError_t e = cudaGetLastError();
+        cudaGraphNode_t child = nullptr;
+        if (e == cudaSuccess) {
+            // the recorded calls as a child graph, after whatever the capture holds so far
+            cudaStreamCaptureStatus status;
+            cudaGraph_t capturing = nullptr;
+            const cudaGraphNode_t* deps = nullptr;
+            size_t n_deps = 0;
+            e = cudaStreamGetCaptureInfo(ctx->stream, &status, nullptr, &capturing, &deps, &n_deps);
+            if (e == cudaSuccess) e = cudaGraphAddChildGraphNode(&child, capturing, deps, n_deps, seq->graph);
+            if (e == cudaSuccess) e = cudaStreamUpdateCaptureDependencies(ctx->stream, &child, 1, cudaStreamSetCaptureDependencies);
+        }
+        if (e == cudaSuccess) {
+            rq_plane_move_kernel<<<out_ctas, 256, 0, ctx->stream>>>(dev_out, seq->pin_out, out_floats, ctx->error_flag, ctx->pin_flag);
+            e = cudaGetLastError();
+        }
+        cudaGraph_t whole = nullptr;
+        const cudaError_t e_end = cudaStreamEndCapture(ctx->stream, &whole);
+        if (e != cudaSuccess || e_end != cudaSuccess || !whole) {
+            cudaGetLastError();
+            if (whole) cudaGraphDestroy(whole);
+            return rq_fail(RQ_ERR_CUDA, "building the one-submission graph: %s", cudaGetErrorString(e != cudaSuccess ? e : e_end));
+        }
+        e = cudaGraphInstantiate(&seq->host_exec, whole, 0);
+        cudaGraphDestroy(whole);
+        if (e != cudaSuccess) { seq->host_exec = nullptr; return rq_fail(RQ_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
+        e = cudaGraphUpload(seq->host_exec, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) return rq_fail(RQ_ERR_CUDA, "cudaGraphUpload: %s", cudaGetErrorString(e));
+        seq->host_dev_in = dev_in; seq->host_dev_out = dev_out; seq->host_in_floats = in_floats; seq->host_out_floats = out_floats;
+    }
+    memcpy(seq->pin_in, host_in, ib);
     int rc = rq_order_work_areas(ctx, ctx->stream);
     if (rc) return rc;
-    RQ_CUDA(cudaMemcpyAsync(dev_in, ctx->pin_x, ib, cudaMemcpyHostToDevice, ctx->stream));
-    RQ_CUDA(cudaGraphLaunch(seq->exec, ctx->stream));
-    RQ_CUDA(cudaMemcpyAsync(ctx->pin_y, dev_out, ob, cudaMemcpyDeviceToHost, ctx->stream));
-    RQ_CUDA(cudaMemcpyAsync(ctx->pin_flag, ctx->error_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    RQ_CUDA(cudaGraphLaunch(seq->host_exec, ctx->stream));
     RQ_CUDA(cudaStreamSynchronize(ctx->stream));
     if (*ctx->pin_flag) return rq_check(ctx);
-    memcpy(host_out, ctx->pin_y, ob);
+    memcpy(host_out, seq->pin_out, ob);
     return RQ_OK;
 }

@@ -1,7 +1,7 @@
 // Per-value decode of a stored weight from its device planes, shared by the dequantiser and the
 // load-time re-encoder. Every fp32 step is a separate rounded operation (__fmul_rn / __fsub_rn never
 // contract), which makes the result bit-equal to the reference's f64 unpacking rounded to fp32
-// (dequant_scalar / dequant_q45k / dequant_q6k, recipe.rs:3687-3833): d*sc, dmin*m and step*q are
+// (dequant_scalar / dequant_q45k / dequant_q6k / dequant_iq4, recipe.rs:3687-3833, :3919-3958): d*sc, dmin*m and step*q are
 // exact in fp32, and the one inexact step, the final subtract, rounds the same exact difference.
 #pragma once
 #include "rq_internal.cuh"
@@ -39,6 +39,43 @@ __device__ __forceinline__ float rq_decode_value(const uint8_t* __restrict__ mai
             at = row * cols + ((rq_plane_chunk(TYPE, off >> 4) << 4) | (off & 15));
         }
         value = __fmul_rn((float)(int8_t)main_plane[at], rq_h2f(scale_plane[i >> 5]));
+    } else if (TYPE == RQ_Q4_1 || TYPE == RQ_Q5_0 || TYPE == RQ_Q5_1 || TYPE == RQ_IQ4_NL) {
+        // GGUF blocks as stored (dequant_scalar variants and dequant_iq4, recipe.rs:3782-3833, :3919-3958). Strides are even
+        // and the plane is 256-byte aligned, so the fp16 header fields are aligned 16-bit loads.
+        constexpr int kStride = TYPE == RQ_Q4_1 ? 20 : (TYPE == RQ_Q5_0 ? 22 : (TYPE == RQ_Q5_1 ? 24 : 18));
+        constexpr int kHeader = (TYPE == RQ_Q4_1 || TYPE == RQ_Q5_1) ? 4 : 2;
+        const uint8_t* blk = main_plane + (i >> 5) * kStride;
+        const int v = (int)(i & 31);
+        const float d = rq_h2f(*(const uint16_t*)blk);
+        if (TYPE == RQ_Q4_1) {
+            const int code = (blk[kHeader + (v & 15)] >> ((v >> 4) * 4)) & 15;
+            value = __fadd_rn(__fmul_rn((float)code, d), rq_h2f(*(const uint16_t*)(blk + 2)));
+        } else if (TYPE == RQ_IQ4_NL) {
+            const int code = (blk[kHeader + (v & 15)] >> ((v >> 4) * 4)) & 15;
+            // the sixteen levels (recipe.rs:15211), two eight-byte words indexed by shifts: no table in memory
+            const unsigned long long lo = 0xF6EADDCFBFAD9881ull, hi = 0x7159453526190D01ull;
+            const int level = (int)(int8_t)(((code < 8 ? lo : hi) >> (8 * (code & 7))) & 0xff);
+            value = __fmul_rn(__fmul_rn(d, 1.0f), (float)level);
+        } else {
+            const int low = (blk[kHeader + 4 + (v & 15)] >> ((v >> 4) * 4)) & 15;
+            const int high = (blk[kHeader + (v >> 3)] >> (v & 7)) & 1;
+            const int code = low | (high << 4);
+            if (TYPE == RQ_Q5_0) value = __fmul_rn((float)(code - 16), d);
+            else value = __fadd_rn(__fmul_rn((float)code, d), rq_h2f(*(const uint16_t*)(blk + 2)));
+        }
+    } else if (TYPE == RQ_Q5_K) {
+        // dequant_q45k with man = 5 (recipe.rs:3687-3741): nibbles from byte 48, fifth bits in bytes 16..47
+        const uint8_t* blk = main_plane + (i >> 8) * 176;
+        const int v = (int)(i & 255), sub = v >> 5, within = v & 31;
+        const uint32_t* hdr = (const uint32_t*)blk;
+        const uint32_t dd = hdr[0];
+        int sc, mn;
+        rq_q4k_scale_min(hdr[1], hdr[2], hdr[3], sub, sc, mn);
+        const int low = (blk[48 + (sub >> 1) * 32 + within] >> ((sub & 1) * 4)) & 15;
+        const int high = (blk[16 + within] >> sub) & 1;
+        const float step = __fmul_rn(rq_h2f((uint16_t)(dd & 0xffff)), (float)sc);
+        const float base = __fmul_rn(rq_h2f((uint16_t)(dd >> 16)), (float)mn);
+        value = __fsub_rn(__fmul_rn(step, (float)(low | (high << 4))), base);
     } else {
         int64_t b = i >> 5;
         int v = (int)(i & 31);

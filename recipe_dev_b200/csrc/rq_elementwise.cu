@@ -138,6 +138,7 @@ extern "C" int rq_matvec_glu(rq_ctx* ctx, const rq_weight* gate, const rq_weight
     if (tokens <= 0 || sk <= 0 || yn <= 0 || (tokens > 1 && (st <= 0 || yt <= 0))) return rq_fail(RQ_ERR_INVALID, "rq_matvec_glu: tokens and strides must be positive");
     if (act_mode != RQ_ACT_FLOAT && act_mode != RQ_ACT_INT8) return rq_fail(RQ_ERR_INVALID, "rq_matvec_glu: act_mode=%d is neither FLOAT(0) nor INT8(1)", act_mode);
     if (act_mode == RQ_ACT_INT8 && step != 32 && step != 256) return rq_fail(RQ_ERR_INVALID, "rq_matvec_glu: int8 step=%d must be 32 or 256", step);
+    if (!rq_type_has_fast_path(gate->type)) return rq_fail(RQ_ERR_UNSUPPORTED, "rq_matvec_glu: type %d has no fused form; run rq_matvec on gate and up", gate->type);
     if (gate->cols % 256) return rq_fail(RQ_ERR_UNSUPPORTED, "rq_matvec_glu: %lld inputs per row; the fused form serves rows of whole 256-value units", (long long)gate->cols);
     DeviceGuard guard(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;

@@ -12,7 +12,7 @@
 //     buffer of per-rank slots that its peers map (CUDA IPC); one kernel stores this rank's slice
 //     into its slot of every peer with plain peer stores, raises a flag on each peer, waits (bounded)
 //     for the peers' flags and, for a sum, adds the slots in rank order -- the same bits on every
-//     rank and on every run. No multicast loads, no library kernel ever sees peer memory.
+//     rank and on every run. Loads never leave the GPU, and no library kernel ever sees peer memory.
 //
 // The count of calls so far lives in device memory and the kernel advances it itself, so a CUDA graph that holds
 // exchange launches can be replayed: nothing about a call is baked into its launch parameters.
@@ -197,17 +197,21 @@ __global__ void __launch_bounds__(256) rq_exchange_kernel(const ExchangeParams p
             for (int r = 0; r < p.nranks; ++r) ((float*)(p.peer[r] + slot_off))[i] = v;
         }
     }
-    __threadfence_system();
+    // One system-scope fence per CTA, not per thread: the barrier orders the CTA's stores before thread 0's fence, and the
+    // fence is cumulative, so everything the CTA stored is ordered before what thread 0 does next.
     __syncthreads();
     __shared__ bool s_last;
     if (tid == 0) {
+        __threadfence_system();
         s_last = atomicAdd(arrivals, 1u) == gridDim.x - 1u;
-        if (s_last) *arrivals = 0;  // nobody adds again before the next call
+        if (s_last) {
+            *arrivals = 0;            // nobody adds again before the next call
+            __threadfence_system();   // the other CTAs' fenced stores, seen through their arrivals, go before the flags
+        }
     }
     __syncthreads();
     if (s_last && tid < p.nranks && tid != p.rank) {
-        // 2. every CTA's stores are out (each fenced before it counted itself): tell peer `tid` that this rank's slot is complete
-        __threadfence_system();
+        // 2. every CTA's stores are out: tell peer `tid` that this rank's slot is complete
         uint32_t* there = (uint32_t*)(p.peer[tid] + 2 * p.half_bytes) + p.rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(there), "r"(epoch + 1u) : "memory");
     }
@@ -218,7 +222,7 @@ __global__ void __launch_bounds__(256) rq_exchange_kernel(const ExchangeParams p
         while (true) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + tid) : "memory");
             if ((int32_t)(seen - (epoch + 1u)) >= 0) break;
-            if ((++tries & 63u) == 0) {  // the clock is slow to read: every 64th look at the flag
+            if ((++tries & 63u) == 0) {  // the clock is read at every 64th look at the flag
                 const unsigned long long now = ex_now();
                 if (t0 == 0) t0 = now;
                 else if (now - t0 > p.wait_ns) { atomicExch(p.error_flag, 31); break; }

@@ -405,6 +405,13 @@ int rq_launch_gemv_multi(rq_ctx* ctx, int n, const rq_weight* const* ws, const f
     const rq_weight* w0 = ws[0];
     const int mode = act_mode == RQ_ACT_FLOAT ? RQ_ACT_FLOAT : RQ_ACT_INT8;
     int rc;
+    if (!rq_type_has_fast_path(w0->type)) {
+        for (int i = 0; i < n; ++i) {
+            rc = rq_launch_gemv(ctx, ws[i], x, sk, st, tokens, ys[i], yn, yt, act_mode, step, s);
+            if (rc) return rc;
+        }
+        return RQ_OK;
+    }
     RqSegment seg[RQ_INLINE_SEGMENTS];
     int64_t total = 0;
     if (n <= RQ_INLINE_SEGMENTS) {
@@ -441,6 +448,12 @@ int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, 
                    float* y, int64_t yn, int64_t yt, int act_mode, int step, cudaStream_t s) {
     const int mode = act_mode == RQ_ACT_FLOAT ? RQ_ACT_FLOAT : RQ_ACT_INT8;
     int rc;
+    if (!rq_type_has_fast_path(w->type)) {
+        // the other stored formats: run decoders over fp32 activations; int sums never see them (recipe.rs:22345-22369)
+        if (mode != RQ_ACT_FLOAT)
+            return rq_fail(RQ_ERR_UNSUPPORTED, "matvec: int8 activations over a type-%d weight; `.int(8)` re-encodes such a tensor to Q8_0 at load: call rq_weight_requantize(.., RQ_Q8_0, ..) and use the result", w->type);
+        return rq_launch_gemv_generic(ctx, w, x, sk, st, tokens, y, yn, yt, s);
+    }
     if (fused_int8(ctx, act_mode, tokens, w->cols, &rc, s)) {
         // one launch: the matvec quantises x in its prologue
         rc = rq_launch_gemv_stream(ctx, w, x, sk, st, tokens, y, yn, yt, mode, ctx->act_scratch, step, ctx->act_scratch, s);

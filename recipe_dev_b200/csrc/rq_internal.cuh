@@ -1,6 +1,7 @@
 // Internal declarations shared by the translation units of librq_b200.so.
 // Device layouts of the four stored formats, the context, and small device helpers.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -27,6 +28,10 @@ struct rq_weight {
     uint16_t* scale; // fp16 d plane (null for Q4_K)
     int64_t bytes;   // total device bytes
     int device;
+    // K-quant weights of whole superblocks: a TMA descriptor of the main plane as a [rows][row bytes] byte matrix, fetched in
+    // tiles of 128 rows x one superblock (144 / 208 bytes) by the batched kernel
+    alignas(64) CUtensorMap tile_map;
+    int has_tile_map;
 };
 
 struct rq_ctx {
@@ -90,7 +95,10 @@ int rq_ensure_act_scratch(rq_ctx* ctx, size_t bytes, cudaStream_t s);
 int rq_launch_repack(const rq_weight* w, const uint8_t* dev_blocks, cudaStream_t s);
 int rq_launch_export(const rq_weight* w, uint8_t* dev_blocks, cudaStream_t s);
 int rq_launch_dequant(const rq_weight* w, float* out, cudaStream_t s);
+int rq_launch_gemv_generic(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s);
 int rq_launch_gather(const rq_weight* w, const int32_t* ids, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s);
+// fills w->tile_map for Q4_K / Q6_K weights (no-op for the others)
+int rq_make_tile_map(rq_weight* w);
 int rq_launch_requant_q8_0(const rq_weight* src, rq_weight* dst, cudaStream_t s);
 int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, int tokens, int step,
                         uint8_t* scratch, uint8_t* records36, cudaStream_t s);
@@ -157,6 +165,12 @@ __device__ __forceinline__ float rq_h2f(uint16_t h) { return __half2float(__usho
 // its unit index. In shared memory a thread's unit starts at a multiple of 128 bytes, so eight threads on adjacent
 // units reading the same logical chunk would otherwise all hit one 16-byte bank group; permuted, they hit eight.
 // The map is its own inverse. Rows that are not whole units (the tiled kernel's) are stored as they come.
+// Q4_K and the formats served by per-value decode alone stay in HBM as their GGUF blocks (one plane, no scale plane)
+__host__ __device__ __forceinline__ bool rq_type_keeps_blocks(int type) {
+    return type == RQ_Q4_K || type == RQ_Q4_1 || type == RQ_Q5_0 || type == RQ_Q5_1 || type == RQ_Q5_K || type == RQ_IQ4_NL;
+}
+// the formats with streaming / tensor-core kernels and int8 slice dots of their own; the rest go through rq_gemv_generic.cu
+__host__ __device__ __forceinline__ bool rq_type_has_fast_path(int type) { return type == RQ_Q4_0 || type == RQ_Q8_0 || type == RQ_Q4_K || type == RQ_Q6_K; }
 __host__ __device__ __forceinline__ bool rq_plane_permuted(int type, int64_t cols) { return (type == RQ_Q8_0 || type == RQ_Q4_0) && cols % 256 == 0; }
 __host__ __device__ __forceinline__ int64_t rq_plane_chunk(int type, int64_t logical) { return logical ^ ((logical >> (type == RQ_Q8_0 ? 4 : 3)) & 7); }
 

@@ -33,9 +33,10 @@ __global__ void rq_plane_kernel(uint16_t* __restrict__ gguf, uint16_t* __restric
 
 static int plane_launch(const rq_weight* w, uint8_t* blocks, int to_gguf, cudaStream_t s) {
     int64_t nblocks = w->rows * (w->cols / rq_block_values(w->type));
-    if (w->type == RQ_Q4_K) {
-        if (to_gguf) RQ_CUDA(cudaMemcpyAsync(blocks, w->main, (size_t)nblocks * 144, cudaMemcpyDeviceToDevice, s));
-        else RQ_CUDA(cudaMemcpyAsync(w->main, blocks, (size_t)nblocks * 144, cudaMemcpyDeviceToDevice, s));
+    if (rq_type_keeps_blocks(w->type)) {
+        const size_t bytes = (size_t)nblocks * (size_t)rq_block_bytes(w->type);
+        if (to_gguf) RQ_CUDA(cudaMemcpyAsync(blocks, w->main, bytes, cudaMemcpyDeviceToDevice, s));
+        else RQ_CUDA(cudaMemcpyAsync(w->main, blocks, bytes, cudaMemcpyDeviceToDevice, s));
         return RQ_OK;
     }
     int threads = 256;
@@ -79,6 +80,11 @@ int rq_launch_dequant(const rq_weight* w, float* out, cudaStream_t s) {
         case RQ_Q6_K: rq_dequant_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
         case RQ_Q8_0: rq_dequant_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
         case RQ_Q4_0: rq_dequant_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        case RQ_Q4_1: rq_dequant_kernel<RQ_Q4_1><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        case RQ_Q5_0: rq_dequant_kernel<RQ_Q5_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        case RQ_Q5_1: rq_dequant_kernel<RQ_Q5_1><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        case RQ_Q5_K: rq_dequant_kernel<RQ_Q5_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        case RQ_IQ4_NL: rq_dequant_kernel<RQ_IQ4_NL><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
         default: return rq_fail(RQ_ERR_INVALID, "dequant: type %d", w->type);
     }
     RQ_CUDA(cudaGetLastError());
@@ -112,6 +118,11 @@ int rq_launch_gather(const rq_weight* w, const int32_t* ids, int tokens, float* 
         case RQ_Q6_K: rq_gather_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
         case RQ_Q8_0: rq_gather_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
         case RQ_Q4_0: rq_gather_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        case RQ_Q4_1: rq_gather_kernel<RQ_Q4_1><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        case RQ_Q5_0: rq_gather_kernel<RQ_Q5_0><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        case RQ_Q5_1: rq_gather_kernel<RQ_Q5_1><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        case RQ_Q5_K: rq_gather_kernel<RQ_Q5_K><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        case RQ_IQ4_NL: rq_gather_kernel<RQ_IQ4_NL><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
         default: return rq_fail(RQ_ERR_INVALID, "gather: type %d", w->type);
     }
     RQ_CUDA(cudaGetLastError());

@@ -1,5 +1,5 @@
 // Batched product over Q4_K / Q6_K weights on the 5th-generation tensor cores, with EXACT INTEGER
-// weight operands.
+// weight operands that live in TENSOR MEMORY.
 //
 //   Y[t][n] = sum_k W[n][k] * X[t][k]
 //
@@ -9,25 +9,37 @@
 // fp16 holds every integer up to 2048 exactly, so the tensor core is fed the integers themselves
 // (Q4_K: one operand; Q6_K: the fp16 rounding of the integer plus its exact residual, -1 / 0 / 1)
 // and `d` is applied outside it, when a sum leaves tensor memory.
-// Unpacking is integer and half2 arithmetic only: a nibble pair becomes (1024 + q) by an OR with
-// 0x6400, one HFMA2 turns it into sc * q exactly. The activations are fp32 and go in as fp16 pairs
-// hi + lo (22 mantissa bits), prepared once per call by rq_kq_prep_kernel in the tensor core's
-// 128-byte-swizzled K-major image; the two middle inputs of every four swap places there, because
-// that is the order the nibble pairs come out of a 32-bit word.
 //
-// Per 16-wide slice: Q4_K issues A x B_hi and A x B_lo (two instructions where split weights need
-// three), Q6_K issues A_hi x B_hi, A_hi x B_lo, A_lo x B_hi. The tensor core adds into its fp32
-// accumulator by TRUNCATION, a bias that grows with the length of the chain (measured: 7e-7 relative
-// over 256 inputs, 1.2e-5 over 4096). So a sum stays in tensor memory for one 64-wide slice only, in
-// one of two accumulators in turn, the small cross terms issued first (while the accumulator is
-// still small, their truncation is nothing); eight drain warps multiply each finished slice by the
-// superblock's d and add it into fp32 registers with one round-to-nearest fma per value while the
-// tensor core fills the other accumulator.
+// Data path of one CTA (128 weight rows x bn tokens):
+//   * the stored bytes of 128 rows x one superblock arrive in shared memory by ONE TMA tensor copy
+//     (a [rows][row bytes] byte matrix, box 144 or 208 bytes x 128 rows), two superblocks ahead;
+//   * eight staging warps unpack a 64-wide slice at a time with integer and half2 arithmetic only
+//     (a nibble pair becomes 1024 + q by an OR with 0x6400, one HFMA2 turns it into sc * q exactly)
+//     and write the operand straight into tensor memory with tcgen05.st: the A operand of
+//     tcgen05.mma is read from there, so the weights never cross shared memory a second time and
+//     the tensor core's shared-memory reads are the activations' alone;
+//   * the activations are fp32 and go in as fp16 pairs hi + lo (22 mantissa bits), prepared once per
+//     call by rq_kq_prep_kernel in the tensor core's 128-byte-swizzled K-major image and fetched by
+//     bulk copies; the two middle inputs of every four swap places there, because that is the order
+//     the nibble pairs come out of a 32-bit word;
+//   * per 16-wide slice Q4_K issues A x B_lo and A x B_hi (two instructions where split weights need
+//     three), Q6_K issues A_hi x B_lo, A_lo x B_hi, A_hi x B_hi.
+//
+// The tensor core adds into its fp32 accumulator by TRUNCATION, a bias that grows with the length of
+// the chain (measured: 7e-7 relative over 256 inputs, 1.2e-5 over 4096). So a sum stays in tensor
+// memory for one 64-wide slice only, in one of a few accumulators in turn, the small cross terms
+// issued first (while the accumulator is still small, their truncation is nothing); eight drain
+// warps multiply each finished slice by the superblock's d and add it into fp32 registers with one
+// round-to-nearest fma per value while the tensor core fills the next accumulator.
+//
+// A tcgen05.commit costs its issuing thread some 200 cycles (measured), so a slice has exactly one:
+// its arrival says at once "the sum is complete" (drain warps), "the operand slot in tensor memory
+// is free" (staging warps) and "the activation slot is free" (copy warp).
 //
 // The Q4_K minimum term, sum_g (dmin * m_g) * (sum of x over group g), is a second, 32 times smaller
 // product. Its operands (dmin * m_g as fp16 hi + lo, scaled by 2^8; the group sums of x as hi + lo)
-// are collected for eight superblocks at a time in one more pair of swizzled tiles and multiplied
-// into a third accumulator that lives for the whole K.
+// are collected for eight superblocks at a time in one more pair of swizzled tiles in shared memory
+// and multiplied into an accumulator that lives for the whole K.
 //
 // INT8 activations take the same kernel: the int8 records are made by the standalone quantiser
 // (bit-exact with the reference's) and the prepared image holds code * step, which is what the
@@ -44,13 +56,16 @@ namespace {
 
 constexpr int kStageWarps = 8, kDrainWarps = 8;
 constexpr int kStagers = kStageWarps * 32;
-constexpr int kMmaWarp = kStageWarps + kDrainWarps, kCopyWarp = kMmaWarp + 1;
+constexpr int kMmaWarps = 2;  // issuing threads (lane 0 of each): thread i takes the slices ks = i (mod kMmaWarps)
+constexpr int kMmaWarp = kStageWarps + kDrainWarps, kCopyWarp = kMmaWarp + kMmaWarps;
 constexpr int kThreadsKq = (kCopyWarp + 1) * 32;
 constexpr int kTileBytes = BM * BK * 2;  // one fp16 tile of 128 rows x 64 inputs: 16 KB
-constexpr int kMaxStages = 6;
+constexpr int kMaxSlots = 8;   // ring depths (activation slots, operand slots in tensor memory, accumulators) and the ring of "slice done" barriers
+constexpr int kRawSlots = 2;   // superblocks of stored bytes in flight per CTA
 constexpr float kMinScale = 256.0f, kMinUnscale = 1.0f / 256.0f;  // the minimum term's weights are scaled so that their fp16 residuals are no subnormals
 
 struct KqParams {
+    CUtensorMap tile_map;  // the weight's main plane as a [rows][row bytes] byte matrix (TMA descriptor; first: 64-byte aligned)
     const uint8_t* main;
     const uint16_t* scale;
     int64_t rows;
@@ -61,8 +76,9 @@ struct KqParams {
     float* y; int64_t yn, yt;
     int sb_per_split;   // superblocks per CTA along K (gridDim.z CTAs share a tile's K)
     float* partial;     // gridDim.z > 1: [split][token][row] sums, added in split order afterwards
-    int stages;            // ring slots; each has its own accumulator of bn columns in tensor memory
-    int slices_per_stage;  // 64-wide slices per stage: 1, 2 or 4 (fewer, larger stages when the token tile is narrow)
+    int b_slots;        // activation slots in shared memory
+    int a_slots;        // operand slots in tensor memory (32 columns each for Q4_K, 64 for Q6_K)
+    int accs;           // accumulators in rotation (bn columns each)
     int* error_flag;
     unsigned long long wait_ns;
 };
@@ -71,19 +87,19 @@ __device__ __forceinline__ __half2 as_half2(uint32_t v) { return *reinterpret_ca
 __device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
 // ------------------------------------------------------------------------------------------
-// The raw bytes behind 32 consecutive inputs of one row (`half` 0 or 1 of the 64-wide slice
-// `kg`), and their integer operands as 32 fp16 values (four 16-byte chunks), inputs in the order
-// 0 2 1 3 within every four.
+// The stored bytes behind 32 consecutive inputs of one row (`half` 0 or 1 of the 64-wide slice
+// `kg`), read from the superblock tile in shared memory, and their integer operands as 32 fp16
+// values (sixteen 32-bit words, four 16-byte groups), inputs in the order 0 2 1 3 within every four.
 // ------------------------------------------------------------------------------------------
 template <int TYPE> struct RawKq;
 template <> struct RawKq<RQ_Q4_K> {
     uint4 hdr, q0, q1;
-    __device__ __forceinline__ void load(const KqParams& p, int64_t row, int kg, int) {
-        const uint8_t* blk = p.main + (row * (p.cols >> 8) + (kg >> 2)) * 144;
-        const int pr = kg & 3;
-        hdr = __ldg((const uint4*)blk);
-        q0 = __ldg((const uint4*)(blk + 16 + 32 * pr));
-        q1 = __ldg((const uint4*)(blk + 32 + 32 * pr));
+    // `tile`: 128 rows x 144 bytes of one superblock in shared memory; r: the row; pr: the 64-wide slice of the superblock
+    __device__ __forceinline__ void load(const uint8_t* tile, int r, int pr, int) {
+        const uint8_t* blk = tile + r * 144;
+        hdr = *(const uint4*)blk;
+        q0 = *(const uint4*)(blk + 16 + 32 * pr);
+        q1 = *(const uint4*)(blk + 32 + 32 * pr);
     }
     // sc * q of sub-block 2 pr + half (low nibbles hold sub-block 2 pr, high nibbles 2 pr + 1)
     __device__ __forceinline__ void decode(int kg, int half, uint4* hi, uint4*) const {
@@ -128,14 +144,15 @@ template <> struct RawKq<RQ_Q4_K> {
 template <> struct RawKq<RQ_Q6_K> {
     uint4 ql[2], qh[2];
     uint32_t scales;  // two int8 scales: inputs 0..15 and 16..31 of the group
-    __device__ __forceinline__ void load(const KqParams& p, int64_t row, int kg, int half) {
-        const int j64 = kg & 3, ch = j64 >> 1, sel = j64 & 1, g = 2 * sel + half;
-        const uint8_t* body = p.main + (row * (p.cols >> 8) + (kg >> 2)) * 208;
-        ql[0] = __ldg((const uint4*)(body + 64 * ch + 32 * half));
-        ql[1] = __ldg((const uint4*)(body + 64 * ch + 32 * half + 16));
-        qh[0] = __ldg((const uint4*)(body + 128 + 32 * ch));
-        qh[1] = __ldg((const uint4*)(body + 128 + 32 * ch + 16));
-        scales = __ldg((const uint16_t*)(body + 192 + 8 * ch + 2 * g));
+    // `tile`: 128 rows x 208 bytes (ql | qh | scales) of one superblock in shared memory
+    __device__ __forceinline__ void load(const uint8_t* tile, int r, int pr, int half) {
+        const int ch = pr >> 1, sel = pr & 1, g = 2 * sel + half;
+        const uint8_t* body = tile + r * 208;
+        ql[0] = *(const uint4*)(body + 64 * ch + 32 * half);
+        ql[1] = *(const uint4*)(body + 64 * ch + 32 * half + 16);
+        qh[0] = *(const uint4*)(body + 128 + 32 * ch);
+        qh[1] = *(const uint4*)(body + 128 + 32 * ch + 16);
+        scales = *(const uint16_t*)(body + 192 + 8 * ch + 2 * g);
     }
     // s * (q - 32) of group g = 2 sel + half of the slice's chunk: the fp16 rounding and the exact residual
     __device__ __forceinline__ void decode(int kg, int half, uint4* hi, uint4* lo) const {
@@ -242,14 +259,19 @@ __global__ void __launch_bounds__(128) rq_kq_prep_kernel(const float* __restrict
 template <int TYPE>
 __global__ void __launch_bounds__(kThreadsKq, 1) rq_matmul_kq_kernel(const __grid_constant__ KqParams p) {
     constexpr bool kQ4 = TYPE == RQ_Q4_K;
-    constexpr int kATiles = kQ4 ? 1 : 2;  // A | A_hi, A_lo
+    constexpr int kUnit = kQ4 ? 144 : 208;           // stored bytes of one row's superblock in the main plane
+    constexpr int kRawBytes = 128 * kUnit;           // one TMA tile: 128 rows x one superblock
+    constexpr int kACols = kQ4 ? 32 : 64;            // tensor-memory columns of one operand slot: 64 fp16 per row (and their residuals)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzled tiles want 1024-byte alignment
-    // One barrier says "stage filled" (the staging warps and the activation copy arrive), one says "stage done": the single
-    // tcgen05.commit of a stage arrives on it when the stage's products have finished, and both the drain warps (the sum
-    // is complete) and the staging and copy warps (the slot is free) wait on it. A commit costs the issuing thread some 200
-    // cycles, so a stage has exactly one. acc_empty: the drain warps have read the stage's accumulator.
-    __shared__ __align__(8) uint64_t full_bar[kMaxStages], stage_done[kMaxStages], acc_empty[kMaxStages], done_bar, min_full, min_free;
+    // Every barrier array is indexed by the slice, ks % kMaxSlots, not by the slot the slice uses: a parity wait is only sound
+    // while the waiter is less than one phase behind, and the issuing threads run up to kMmaWarps slices apart whatever the
+    // number of slots or accumulators (kMaxSlots >= slots + kMmaWarps keeps every waiter within a phase).
+    // done[]: the single tcgen05.commit of slice ks arrives on done[ks % kMaxSlots] when the slice's products have finished.
+    // The drain warps wait for it (the sum is complete), the staging warps wait for the slice that used their operand slot
+    // last, the copy warp for the slice that used its activation slot last.
+    __shared__ __align__(8) uint64_t b_full[kMaxSlots], a_full[kMaxSlots], done[kMaxSlots], acc_empty[kMaxSlots], raw_full[kRawSlots], raw_empty[kRawSlots], done_bar,
+        min_full, min_free;
     __shared__ uint32_t tmem_base_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t m0 = (int64_t)blockIdx.x * BM;
@@ -258,20 +280,21 @@ __global__ void __launch_bounds__(kThreadsKq, 1) rq_matmul_kq_kernel(const __gri
     const int sb_first = blockIdx.z * p.sb_per_split;            // this CTA's superblocks
     const int n_sb = min(p.sb_per_split, nb - sb_first);
     const int k_steps = 4 * n_sb, kg_first = 4 * sb_first;       // 64-wide slices
-    const int stages = p.stages;                                  // ring slots, each with its own accumulator
-    const int per = p.slices_per_stage;                           // 64-wide slices per stage: 1, 2 or 4
-    const int n_stages = k_steps / per;
-    const int a_bytes = kATiles * kTileBytes, b_bytes = 2 * bn * 128;  // one slice's weight tile(s), and its B_hi | B_lo
-    const int stage_bytes = per * (a_bytes + b_bytes);            // the slices' A tiles, then their B tiles
-    uint8_t* min_a = smem + (size_t)stages * stage_bytes;         // Q4_K: A' hi | A' lo (16 KB each), then B' hi | B' lo
+    const int b_slots = p.b_slots, a_slots = p.a_slots, accs = p.accs;
+    const int b_bytes = 2 * bn * 128;                             // one slice's B_hi | B_lo
+    uint8_t* raw = smem + (size_t)b_slots * b_bytes;              // kRawSlots tiles of stored bytes
+    uint8_t* min_a = raw + (size_t)kRawSlots * kRawBytes;         // Q4_K: A' hi | A' lo (16 KB each), then B' hi | B' lo
+    min_a = (uint8_t*)(((uintptr_t)min_a + 1023) & ~(uintptr_t)1023);
     uint8_t* min_b = min_a + 2 * kTileBytes;
-    // tensor memory: one accumulator per ring slot and, for Q4_K, one for the minimum term; a power of two of columns
-    const int want_cols = (stages + (kQ4 ? 1 : 0)) * bn;
+    // tensor memory: the accumulators, for Q4_K one for the minimum term, then the operand slots; a power of two of columns
+    const int acc_cols = (accs + (kQ4 ? 1 : 0)) * bn;
+    const int want_cols = acc_cols + a_slots * kACols;
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < want_cols) tmem_cols <<= 1;
 
     if (tid == 0) {
-        for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], kStageWarps + 1); mbar_init(&stage_done[s], 1); mbar_init(&acc_empty[s], kDrainWarps); }
+        for (int s = 0; s < kMaxSlots; ++s) { mbar_init(&b_full[s], 1); mbar_init(&a_full[s], kStageWarps); mbar_init(&done[s], 1); mbar_init(&acc_empty[s], kDrainWarps); }
+        for (int s = 0; s < kRawSlots; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kStageWarps); }
         mbar_init(&done_bar, 1);
         mbar_init(&min_full, 1);
         mbar_init(&min_free, 1);
@@ -291,61 +314,60 @@ __global__ void __launch_bounds__(kThreadsKq, 1) rq_matmul_kq_kernel(const __gri
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
-    const uint32_t acc_min = tmem_base + (uint32_t)(stages * bn);
+    const uint32_t acc_min = tmem_base + (uint32_t)(accs * bn);
+    const uint32_t a_ring = tmem_base + (uint32_t)acc_cols;
 
     if (warp < kStageWarps) {
-        // ------------------------------------------------------------ staging warps: W -> integer operand tiles
-        const int r = tid & 127, half = tid >> 7;  // a row of the tile, and which 32 of a slice's 64 inputs
-        const int64_t row = m0 + r < p.rows ? m0 + r : p.rows - 1;  // rows past the end are computed and dropped
+        // ------------------------------------------------------------ staging warps: stored bytes -> integer operands in tensor memory
+        // thread = (row r of the tile, half of the slice's 64 inputs); a warp may write the 32 tensor-memory lanes 32 (warp % 4) ..,
+        // so warps 0-3 take the rows' first halves and warps 4-7 their second halves
+        const int r = tid & 127, half = tid >> 7;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         bool dead = false;
-        // Three sets of raw bytes rotate by NAME (the loop is unrolled by three), never by copy: copying a set whose loads
-        // are still in flight would wait for them, and the point is to have two slices' bytes on their way while one is
-        // being unpacked.
-        RawKq<TYPE> raw0, raw1, raw2;
-        raw0.load(p, row, kg_first, half);
-        if (k_steps > 1) raw1.load(p, row, kg_first + 1, half);
-        auto slice_one = [&](int ks, const RawKq<TYPE>& cur, RawKq<TYPE>& ahead) {
-            const int st = ks / per, sub = ks - st * per, slot = st % stages, kg = kg_first + ks;
-            if (ks + 2 < k_steps) ahead.load(p, row, kg + 2, half);
-            uint4 hi[4], lo[4];
-            cur.decode(kg, half, hi, lo);
-            // the slot is free once the products of the stage that used it last have finished
-            if (sub == 0 && st >= stages && !dead && !mbar_wait(&stage_done[slot], ((st / stages) - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 11); dead = true; }
-            uint8_t* a_hi = smem + (size_t)slot * stage_bytes + (size_t)sub * a_bytes;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int off = swizzled(r, 4 * half + c);
-                *(uint4*)(a_hi + off) = hi[c];
-                if (!kQ4) *(uint4*)(a_hi + kTileBytes + off) = lo[c];
-            }
-            if (kQ4 && half == 0 && (kg & 3) == 3) {
-                // The superblock's minimum-term weights, one 16-byte chunk per row. The tiles are reused window after window
-                // (eight superblocks): the first chunk of a window waits until the previous window's products have read them.
-                const int sb_abs = kg >> 2, w_local = (sb_abs >> 3) - (sb_first >> 3);
-                if ((sb_abs & 7) == 0 && w_local >= 1 && !dead && !mbar_wait(&min_free, (w_local - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 11); dead = true; }
-                uint4 mh, ml;
-                cur.minimum_terms(mh, ml);
-                const int chunk = (kg >> 2) & 7;
-                *(uint4*)(min_a + swizzled(r, chunk)) = mh;
-                *(uint4*)(min_a + kTileBytes + swizzled(r, chunk)) = ml;
-                if (ks == k_steps - 1 && chunk < 7) {
-                    // the CTA's last superblock: the chunk after it shares a 16-wide slice with it when `chunk` is even
-                    *(uint4*)(min_a + swizzled(r, chunk + 1)) = make_uint4(0, 0, 0, 0);
-                    *(uint4*)(min_a + kTileBytes + swizzled(r, chunk + 1)) = make_uint4(0, 0, 0, 0);
+        for (int s = 0; s < n_sb; ++s) {
+            const int rslot = s % kRawSlots;
+            if (!dead && !mbar_wait_warp(&raw_full[rslot], (s / kRawSlots) & 1, p.wait_ns)) { atomicExch(p.error_flag, 18); dead = true; }
+            const uint8_t* tile = raw + (size_t)rslot * kRawBytes;
+#pragma unroll 1
+            for (int pr = 0; pr < 4; ++pr) {
+                const int ks = 4 * s + pr, kg = kg_first + ks, aslot = ks % a_slots;
+                RawKq<TYPE> cur;
+                cur.load(tile, r, pr, half);
+                uint4 hi[4], lo[4];
+                cur.decode(kg, half, hi, lo);
+                // the operand slot is free once the products of the slice that used it last have finished
+                if (ks >= a_slots && !dead && !mbar_wait_warp(&done[(ks - a_slots) % kMaxSlots], ((ks - a_slots) / kMaxSlots) & 1, p.wait_ns)) { atomicExch(p.error_flag, 11); dead = true; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t at = a_ring + lane_base + (uint32_t)(aslot * kACols + 16 * half);
+                tmem_st16(at, (const uint32_t*)hi);
+                if (!kQ4) tmem_st16(at + 32, (const uint32_t*)lo);
+                bool wrote_shared = false;
+                if (kQ4 && half == 0 && pr == 3) {
+                    // The superblock's minimum-term weights, one 16-byte chunk per row. The tiles are reused window after window
+                    // (eight superblocks): the first chunk of a window waits until the previous window's products have read them.
+                    const int sb_abs = kg >> 2, w_local = (sb_abs >> 3) - (sb_first >> 3);
+                    if ((sb_abs & 7) == 0 && w_local >= 1 && !dead && !mbar_wait_warp(&min_free, (w_local - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 11); dead = true; }
+                    uint4 mh, ml;
+                    cur.minimum_terms(mh, ml);
+                    const int chunk = sb_abs & 7;
+                    *(uint4*)(min_a + swizzled(r, chunk)) = mh;
+                    *(uint4*)(min_a + kTileBytes + swizzled(r, chunk)) = ml;
+                    if (ks == k_steps - 1 && chunk < 7) {
+                        // the CTA's last superblock: the chunk after it shares a 16-wide slice with it when `chunk` is even
+                        *(uint4*)(min_a + swizzled(r, chunk + 1)) = make_uint4(0, 0, 0, 0);
+                        *(uint4*)(min_a + kTileBytes + swizzled(r, chunk + 1)) = make_uint4(0, 0, 0, 0);
+                    }
+                    wrote_shared = true;
                 }
-            }
-            if (sub == per - 1) {
-                // the tensor core reads shared memory through the async proxy: every thread orders its own stores before it,
-                // then one lane per warp counts the warp in (an arrival is an atomic on the barrier: 8 per stage, not 256)
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tmem_st_wait();
+                if (wrote_shared) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads those tiles through the async proxy
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full_bar[slot]);
+                if (lane == 0) mbar_arrive(&a_full[ks % kMaxSlots]);  // one arrival per warp (an arrival is an atomic on the barrier)
             }
-        };
-        for (int ks = 0; ks < k_steps; ks += 3) {
-            slice_one(ks, raw0, raw2);
-            if (ks + 1 < k_steps) slice_one(ks + 1, raw1, raw0);
-            if (ks + 2 < k_steps) slice_one(ks + 2, raw2, raw1);
+            // this warp has read the superblock's stored bytes: the copy warp may fetch another into the slot
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_empty[rslot]);
         }
     } else if (warp < kMmaWarp) {
         // ------------------------------------------------------------ drain warps: tensor memory -> d * sum -> fp32 registers -> Y
@@ -365,21 +387,20 @@ __global__ void __launch_bounds__(kThreadsKq, 1) rq_matmul_kq_kernel(const __gri
             if (kQ4) return rq_h2f(__ldg((const uint16_t*)(p.main + (d_row * nb + sb) * 144)));
             return rq_h2f(__ldg(p.scale + d_row * nb + sb));
         };
-        const int stages_per_sb = 4 / per;
         float d = d_of(sb_first);
-        for (int st = 0; st < n_stages; ++st) {
-            const int slot = st % stages;
-            // the next superblock's d is on its way while this superblock's last stage is drained
+        for (int ks = 0; ks < k_steps; ++ks) {
+            const int a = ks % accs;
+            // the next superblock's d is on its way while this superblock's last slice is drained
             float d_next = d;
-            if ((st + 1) % stages_per_sb == 0 && st + 1 < n_stages) d_next = d_of(sb_first + (st + 1) / stages_per_sb);
-            if (!dead && !mbar_wait(&stage_done[slot], (st / stages) & 1, p.wait_ns)) { atomicExch(p.error_flag, 14); dead = true; }
+            if ((ks & 3) == 3 && ks + 1 < k_steps) d_next = d_of(sb_first + (ks >> 2) + 1);
+            if (!dead && !mbar_wait_warp(&done[ks % kMaxSlots], (ks / kMaxSlots) & 1, p.wait_ns)) { atomicExch(p.error_flag, 14); dead = true; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (active) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     if (16 * c < cols_here) {
                         uint32_t t[16];
-                        tmem_ld16(tmem_base + lane_base + (uint32_t)(slot * bn + col0 + 16 * c), t);
+                        tmem_ld16(tmem_base + lane_base + (uint32_t)(a * bn + col0 + 16 * c), t);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) acc[16 * c + j] = fmaf(d, __uint_as_float(t[j]), acc[16 * c + j]);
                     }
@@ -388,10 +409,10 @@ __global__ void __launch_bounds__(kThreadsKq, 1) rq_matmul_kq_kernel(const __gri
             // this warp has read the accumulator: the tensor core may overwrite it
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[slot]);
+            if (lane == 0) mbar_arrive(&acc_empty[ks % kMaxSlots]);
             d = d_next;
         }
-        if (!dead && !mbar_wait(&done_bar, 0, p.wait_ns)) { atomicExch(p.error_flag, 12); dead = true; }
+        if (!dead && !mbar_wait_warp(&done_bar, 0, p.wait_ns)) { atomicExch(p.error_flag, 12); dead = true; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (active) {
 #pragma unroll
@@ -413,53 +434,54 @@ __global__ void __launch_bounds__(kThreadsKq, 1) rq_matmul_kq_kernel(const __gri
                 }
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------ MMA warp (lane 0 issues)
+    } else if (warp < kCopyWarp) {
+        // ------------------------------------------------------------ MMA warps (lane 0 of each issues): warp i takes slices i, i + kMmaWarps, ..
+        // One thread's loop of waits, instruction issue and commit is a chain of slow operations (a look at a barrier, a
+        // tcgen05.mma, a commit each cost it on the order of a hundred cycles), some 2000 cycles a slice where the tensor core
+        // needs 500. Several threads on interleaved slices, each slice with its own accumulator, overlap those chains. A commit
+        // covers its own thread's products only, which is what a slice's barrier needs; the minimum term and the CTA's last
+        // slice (ks = 3 mod 4 both, kMmaWarps dividing 4) belong to the last of the threads.
+        static_assert(4 % kMmaWarps == 0, "window ends must all fall to one issuing thread");
+        const int first_slice = warp - kMmaWarp;
         bool dead = false;
         const uint32_t idesc = instr_desc(bn);
         bool min_started = false;
-        for (int st = 0; st < n_stages; ++st) {
-            const int slot = st % stages;
-            const int ks_last = st * per + per - 1;                     // the stage's last 64-wide slice
-            const int sb_abs = sb_first + (ks_last >> 2);
-            if (!dead && !mbar_wait(&full_bar[slot], (st / stages) & 1, p.wait_ns)) { atomicExch(p.error_flag, 13); dead = true; }
-            if (st >= stages && !dead && !mbar_wait(&acc_empty[slot], ((st / stages) - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 15); dead = true; }
+        // one thread waits, issues and commits: nothing here needs the other lanes, and a warp-wide look at a barrier costs
+        // thirty-two operations on its word
+        for (int ks = first_slice; lane == 0 && ks < k_steps; ks += kMmaWarps) {
+            const int aslot = ks % a_slots, bslot = ks % b_slots, a = ks % accs;
+            const int sb_abs = sb_first + (ks >> 2);
+            if (!dead && !mbar_wait(&a_full[ks % kMaxSlots], (ks / kMaxSlots) & 1, p.wait_ns)) { atomicExch(p.error_flag, 13); dead = true; }
+            if (!dead && !mbar_wait(&b_full[ks % kMaxSlots], (ks / kMaxSlots) & 1, p.wait_ns)) { atomicExch(p.error_flag, 13); dead = true; }
+            if (ks >= accs && !dead && !mbar_wait(&acc_empty[(ks - accs) % kMaxSlots], ((ks - accs) / kMaxSlots) & 1, p.wait_ns)) { atomicExch(p.error_flag, 15); dead = true; }
             // Q4_K: at the end of each window of eight superblocks (and at the CTA's last), the window's minimum-term product
-            const bool window_end = kQ4 && (ks_last & 3) == 3 && ((sb_abs & 7) == 7 || ks_last == k_steps - 1);
+            const bool window_end = kQ4 && (ks & 3) == 3 && ((sb_abs & 7) == 7 || ks == k_steps - 1);
             if (window_end && !dead) {
                 // windows are numbered from the CTA's first: the copy warp arms min_full once per window, in order
                 const int w_local = (sb_abs >> 3) - (sb_first >> 3);
                 if (!mbar_wait(&min_full, w_local & 1, p.wait_ns)) { atomicExch(p.error_flag, 17); dead = true; }
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (lane == 0 && !dead) {
-                const uint32_t base = smem_u32(smem + (size_t)slot * stage_bytes);
-                const uint32_t acc_main = tmem_base + (uint32_t)(slot * bn);
-                // a fresh sum for every stage; the cross terms (2^-11 of the sum) first, the main term last
-                for (int sub = 0; sub < per; ++sub) {
-                    const uint64_t a_hi = smem_desc(base + sub * a_bytes), a_lo = smem_desc(base + sub * a_bytes + kTileBytes);
-                    const uint64_t b_hi = smem_desc(base + per * a_bytes + sub * b_bytes), b_lo = smem_desc(base + per * a_bytes + sub * b_bytes + bn * 128);
+            if (!dead) {
+                const uint32_t bbase = smem_u32(smem + (size_t)bslot * b_bytes);
+                const uint64_t b_hi = smem_desc(bbase), b_lo = smem_desc(bbase + bn * 128);
+                const uint32_t a_hi = a_ring + (uint32_t)(aslot * kACols), a_lo = a_hi + 32;
+                const uint32_t acc_main = tmem_base + (uint32_t)(a * bn);
+                // a fresh sum for every slice; the cross terms (2^-11 of the sum) first, the main term last
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk) {
-                        const uint64_t adv = (uint64_t)(kk * 2);  // 32 bytes along K, in 16-byte units of the start address
-                        mma_f16(acc_main, a_hi + adv, b_lo + adv, idesc, (sub | kk) ? 1u : 0u);
-                        if (!kQ4) mma_f16(acc_main, a_lo + adv, b_hi + adv, idesc, 1u);
-                    }
+                for (int kk = 0; kk < BK / 16; ++kk) {
+                    const uint64_t adv = (uint64_t)(kk * 2);  // 32 bytes along K, in 16-byte units of the descriptor's start address
+                    mma_f16_ts(acc_main, a_hi + 8 * kk, b_lo + adv, idesc, kk ? 1u : 0u);
+                    if (!kQ4) mma_f16_ts(acc_main, a_lo + 8 * kk, b_hi + adv, idesc, 1u);
                 }
-                for (int sub = 0; sub < per; ++sub) {
-                    const uint64_t a_hi = smem_desc(base + sub * a_bytes), b_hi = smem_desc(base + per * a_bytes + sub * b_bytes);
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk) {
-                        const uint64_t adv = (uint64_t)(kk * 2);
-                        mma_f16(acc_main, a_hi + adv, b_hi + adv, idesc, 1u);
-                    }
-                }
+                for (int kk = 0; kk < BK / 16; ++kk) mma_f16_ts(acc_main, a_hi + 8 * kk, b_hi + (uint64_t)(kk * 2), idesc, 1u);
                 if (window_end) {
                     // chunks [first, last] of the window belong to this CTA: the 16-wide slices that hold them
                     const int first_chunk = (sb_abs >> 3) == (sb_first >> 3) ? (sb_first & 7) : 0, last_chunk = sb_abs & 7;
-                    const uint32_t mbase = smem_u32(min_a), bbase = smem_u32(min_b);
+                    const uint32_t mbase = smem_u32(min_a), mbb = smem_u32(min_b);
                     const uint64_t ma_hi = smem_desc(mbase), ma_lo = smem_desc(mbase + kTileBytes);
-                    const uint64_t mb_hi = smem_desc(bbase), mb_lo = smem_desc(bbase + bn * 128);
+                    const uint64_t mb_hi = smem_desc(mbb), mb_lo = smem_desc(mbb + bn * 128);
                     for (int kk = first_chunk >> 1; kk <= last_chunk >> 1; ++kk) {
                         const uint64_t adv = (uint64_t)(kk * 2);
                         mma_f16(acc_min, ma_hi + adv, mb_hi + adv, idesc, min_started ? 1u : 0u);
@@ -469,40 +491,48 @@ __global__ void __launch_bounds__(kThreadsKq, 1) rq_matmul_kq_kernel(const __gri
                     }
                     mma_commit(&min_free);  // the minimum tiles may be rewritten once these have finished
                 }
-                // one commit: the stage's sum is complete, and its slot (and the minimum tiles, if read) are free
-                mma_commit(st == n_stages - 1 ? &done_bar : &stage_done[slot]);
-                if (st == n_stages - 1) mma_commit(&stage_done[slot]);
+                // one commit: the slice's sum is complete, and its operand and activation slots are free
+                if (ks == k_steps - 1) mma_commit(&done_bar);
+                mma_commit(&done[ks % kMaxSlots]);
             }
-            __syncwarp();
         }
+        __syncwarp();
     } else {
-        // ------------------------------------------------------------ copy warp (lane 0): the prepared X tiles
-        if (lane == 0) {
+        // ------------------------------------------------------------ copy warp: lane 0 the prepared X tiles, lane 1 the stored weight bytes
+        if (lane == 1) {
+            // weights are constants of the model: nothing to wait for before the first fetches
+            for (int s = 0; s < n_sb; ++s) {
+                const int rslot = s % kRawSlots;
+                if (s >= kRawSlots && !mbar_wait(&raw_empty[rslot], ((s / kRawSlots) - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 19); break; }
+                mbar_expect_tx(&raw_full[rslot], kRawBytes);
+                tma_load_2d(raw + (size_t)rslot * kRawBytes, &p.tile_map, (sb_first + s) * kUnit, (int)m0, &raw_full[rslot]);
+            }
+        } else if (lane == 0) {
             // the activation images were written by the kernel before this one
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            const uint32_t slice_bytes = (uint32_t)b_bytes, bytes = slice_bytes * (uint32_t)per;
+            const uint32_t bytes = (uint32_t)b_bytes;
             const int k_total = p.cols / BK, windows = (nb + 7) >> 3;
-            const uint8_t* src = p.xs + ((size_t)nt * k_total + kg_first) * slice_bytes;
+            const uint8_t* src = p.xs + ((size_t)nt * k_total + kg_first) * bytes;
             int w_issue = 0;
             const int w_last = ((sb_first + n_sb - 1) >> 3) - (sb_first >> 3);  // windows of eight superblocks this CTA touches, counted from its first
-            for (int st = 0; st < n_stages; ++st) {
-                const int slot = st % stages;
-                if (st >= stages && !mbar_wait(&stage_done[slot], ((st / stages) - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 16); break; }
-                mbar_expect_tx(&full_bar[slot], bytes);
-                bulk_g2s(smem + (size_t)slot * stage_bytes + per * a_bytes, src + (size_t)st * bytes, bytes, &full_bar[slot]);
+            for (int ks = 0; ks < k_steps; ++ks) {
+                const int bslot = ks % b_slots;
+                if (ks >= b_slots && !mbar_wait(&done[(ks - b_slots) % kMaxSlots], ((ks - b_slots) / kMaxSlots) & 1, p.wait_ns)) { atomicExch(p.error_flag, 16); break; }
+                mbar_expect_tx(&b_full[ks % kMaxSlots], bytes);
+                bulk_g2s(smem + (size_t)bslot * b_bytes, src + (size_t)ks * bytes, bytes, &b_full[ks % kMaxSlots]);
                 if (kQ4 && w_issue <= w_last) {
-                    // The group sums of window `w_issue`: the CTA's first window at once; a later window `stages` stages into
-                    // it (by then the slot wait above has seen the previous window's last stage finish, and with it the products
-                    // that read this tile), or at the window's last stage when the window is shorter than that.
+                    // The group sums of window `w_issue`: the CTA's first window at once; a later window a few slices into it (by
+                    // then the previous window's products, which read this tile, have finished: min_free says so), or at the
+                    // window's last slice when the window is shorter than that.
                     const int win = (sb_first >> 3) + w_issue;
                     const int win_first_sb = w_issue == 0 ? sb_first : win << 3;
                     const int win_last_sb = min(sb_first + n_sb - 1, (win << 3) + 7);
-                    const int st_begin = ((win_first_sb - sb_first) * 4) / per, st_end = ((win_last_sb - sb_first) * 4 + 3) / per;
-                    const int st_issue = w_issue == 0 ? 0 : min(st_begin + stages, st_end);
-                    if (st == st_issue) {
+                    const int ks_begin = (win_first_sb - sb_first) * 4, ks_end = (win_last_sb - sb_first) * 4 + 3;
+                    const int ks_issue = w_issue == 0 ? 0 : min(ks_begin + b_slots, ks_end);
+                    if (ks == ks_issue) {
                         if (w_issue > 0 && !mbar_wait(&min_free, (w_issue - 1) & 1, p.wait_ns)) { atomicExch(p.error_flag, 16); break; }
-                        mbar_expect_tx(&min_full, slice_bytes);
-                        bulk_g2s(min_b, p.xg + ((size_t)nt * windows + win) * slice_bytes, slice_bytes, &min_full);
+                        mbar_expect_tx(&min_full, bytes);
+                        bulk_g2s(min_b, p.xg + ((size_t)nt * windows + win) * bytes, bytes, &min_full);
                         ++w_issue;
                     }
                 }
@@ -541,24 +571,26 @@ int launch_kq(const KqParams& p, int grid_m, int grid_n, int grid_k, size_t smem
 
 // How a call is cut: tokens per tile, superblocks per CTA, CTAs along K, pipeline depth, shared memory and scratch.
 struct KqCut {
-    int bn, n_tiles, sb_per_split, splits, stages, slices;
+    int bn, n_tiles, sb_per_split, splits, b_slots, a_slots, accs;
     size_t smem, records_bytes, xs_bytes, xg_bytes, partial_bytes;
 };
 KqCut kq_cut(int type, int sm_count, int64_t rows, int64_t cols, int tokens, bool int8) {
     KqCut c;
     c.bn = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : (tokens <= 64 ? 64 : 128));
     c.n_tiles = (tokens + c.bn - 1) / c.bn;
-    const int nb = (int)(cols >> 8), a_tiles = type == RQ_Q4_K ? 1 : 2;
-    // A stage costs a fixed few hundred cycles of hand-offs (fill, one commit, drain): narrow token tiles, whose products are
-    // short, take two 64-wide slices per stage
-    c.slices = c.bn <= 32 ? 2 : 1;
-    const size_t stage = (size_t)c.slices * ((size_t)a_tiles * kTileBytes + 2 * (size_t)c.bn * 128);
-    const size_t fixed = type == RQ_Q4_K ? 2 * (size_t)kTileBytes + 2 * (size_t)c.bn * 128 : 0;
-    c.stages = (int)((220 * 1024 - fixed) / stage);
-    const int acc_room = (512 - (type == RQ_Q4_K ? c.bn : 0)) / c.bn;  // an accumulator per stage
-    if (c.stages > acc_room) c.stages = acc_room;
-    if (c.stages > kMaxStages) c.stages = kMaxStages;
-    c.smem = (size_t)c.stages * stage + fixed + 1024;
+    const int nb = (int)(cols >> 8);
+    const bool q4 = type == RQ_Q4_K;
+    // tensor memory (512 columns): four operand slots, the minimum term's accumulator (Q4_K), the rest accumulators
+    c.a_slots = 4;
+    c.accs = (512 - c.a_slots * (q4 ? 32 : 64) - (q4 ? c.bn : 0)) / c.bn;
+    if (c.accs > 4) c.accs = 4;
+    // shared memory: the stored-byte tiles, the minimum term's tiles (Q4_K), the rest activation slots
+    const size_t raw = (size_t)kRawSlots * 128 * (q4 ? 144 : 208) + 1024;
+    const size_t fixed = q4 ? 2 * (size_t)kTileBytes + 2 * (size_t)c.bn * 128 : 0;
+    const size_t slot = 2 * (size_t)c.bn * 128;
+    c.b_slots = (int)((220 * 1024 - raw - fixed) / slot);
+    if (c.b_slots > 6) c.b_slots = 6;
+    c.smem = (size_t)c.b_slots * slot + raw + fixed + 1024;
     // CTAs along K: the cut that leaves the busiest SM the least work, counting about one superblock's time per CTA for
     // its prologue and drain, with at least two superblocks per CTA
     const int64_t tiles = ((rows + BM - 1) / BM) * c.n_tiles;
@@ -589,7 +621,7 @@ size_t rq_matmul_kq_scratch_bytes(const rq_ctx* ctx, int type, int64_t rows, int
 // RQ_ERR_UNSUPPORTED (no error text) = not a K-quant weight. act_mode FLOAT or INT8 (step 32 / 256).
 int rq_launch_matmul_kq(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, int act_mode,
                         int step, cudaStream_t s) {
-    if ((w->type != RQ_Q4_K && w->type != RQ_Q6_K) || w->cols % 256) return RQ_ERR_UNSUPPORTED;
+    if ((w->type != RQ_Q4_K && w->type != RQ_Q6_K) || w->cols % 256 || !w->has_tile_map) return RQ_ERR_UNSUPPORTED;
     const bool int8 = act_mode != RQ_ACT_FLOAT;
     const KqCut cut = kq_cut(w->type, ctx->sm_count, w->rows, w->cols, tokens, int8);
     int rc = rq_ensure_act_scratch(ctx, cut.records_bytes + cut.xs_bytes + cut.xg_bytes + cut.partial_bytes, s);
@@ -619,7 +651,8 @@ int rq_launch_matmul_kq(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t
     KqParams p;
     p.main = w->main; p.scale = w->scale; p.rows = w->rows; p.cols = (int)w->cols;
     p.xs = xs; p.xg = xg; p.bn = cut.bn; p.tokens = tokens; p.y = y; p.yn = yn; p.yt = yt;
-    p.sb_per_split = cut.sb_per_split; p.partial = partial; p.stages = cut.stages; p.slices_per_stage = cut.slices;
+    p.sb_per_split = cut.sb_per_split; p.partial = partial; p.b_slots = cut.b_slots; p.a_slots = cut.a_slots; p.accs = cut.accs;
+    p.tile_map = w->tile_map;
     p.error_flag = ctx->error_flag; p.wait_ns = ctx->wait_limit_ns;
     const int grid_m = (int)((w->rows + BM - 1) / BM);
     rc = w->type == RQ_Q4_K ? launch_kq<RQ_Q4_K>(p, grid_m, cut.n_tiles, cut.splits, cut.smem, s) : launch_kq<RQ_Q6_K>(p, grid_m, cut.n_tiles, cut.splits, cut.smem, s);

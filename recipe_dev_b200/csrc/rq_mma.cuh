@@ -35,20 +35,29 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
                  : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the time limit ran out. Reading %globaltimer costs about a microsecond, so the clock is
-// looked at only every 256th unsuccessful try (a try itself suspends the thread for a short, system-chosen time).
+// Bounded wait: false when the time limit ran out (the caller records the error and stops waiting). The clock is looked at
+// only every so many unsuccessful tries, so that a wait that is about to succeed does not pay for reading it.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
-    if (mbar_test_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     uint32_t tries = 0;
-    while (!mbar_test_wait(bar, parity)) {
-        if ((++tries & 1023u) == 0) {
+    while (!mbar_try_wait(bar, parity)) {  // a try suspends the thread for a short, system-chosen time
+        if ((++tries & 255u) == 0) {
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
             else if (now - t0 > limit_ns) return false;
         }
     }
     return true;
+}
+// A whole warp waits, one lane looks: every look at a barrier is an operation on its shared-memory word, and thirty-two lanes
+// looking at once cost thirty-two of them (measured: some 300 cycles for a warp-wide look at a barrier that is already
+// complete). Lane 0 waits, the warp meets it at __syncwarp (which also orders memory between the lanes) and learns the outcome.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, limit_ns) ? 1 : 0;
+    __syncwarp();
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes),
@@ -75,6 +84,29 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_d),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
+}
+// The same product with the A operand in tensor memory (128 lanes = rows, eight 32-bit columns = sixteen fp16 along K)
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// sixteen 32-bit registers of each thread into sixteen columns of the thread's lane (this warp's 32 lanes)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr), "r"(r[0]),
+        "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// one tile of a two-dimensional tensor map (innermost coordinate x: its byte offset must be a multiple of 16) into shared memory
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tensor_map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)), "l"(tensor_map),
+                 "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");

@@ -417,7 +417,7 @@ extern "C" int rq_moe_prepare(rq_ctx* ctx, int type, const void* gate, const voi
     if (!ctx || !gate || !up || !down || !out) return rq_fail(RQ_ERR_INVALID, "rq_moe_prepare: null argument");
     *out = nullptr;
     const int per = rq_block_values(type);
-    if (!per) return rq_fail(RQ_ERR_INVALID, "rq_moe_prepare: GGML type %d is not on this path", type);
+    if (!per || !rq_type_has_fast_path(type)) return rq_fail(per ? RQ_ERR_UNSUPPORTED : RQ_ERR_INVALID, "rq_moe_prepare: GGML type %d is not served for expert banks (Q4_0, Q8_0, Q4_K, Q6_K are)", type);
     if (hidden <= 0 || ffn <= 0 || hidden % 256 || ffn % 256) return rq_fail(RQ_ERR_INVALID, "rq_moe_prepare: hidden=%d and ffn=%d must be positive multiples of 256", hidden, ffn);
     if (experts <= 0 || expert_first < 0 || expert_count <= 0 || expert_first + expert_count > experts)
         return rq_fail(RQ_ERR_INVALID, "rq_moe_prepare: experts [%d, %d) outside the bank's %d", expert_first, expert_first + expert_count, experts);

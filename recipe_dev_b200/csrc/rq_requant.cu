@@ -66,6 +66,11 @@ int rq_launch_requant_q8_0(const rq_weight* src, rq_weight* dst, cudaStream_t s)
         case RQ_Q6_K: rq_requant_q8_0_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
         case RQ_Q8_0: rq_requant_q8_0_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
         case RQ_Q4_0: rq_requant_q8_0_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
+        case RQ_Q4_1: rq_requant_q8_0_kernel<RQ_Q4_1><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
+        case RQ_Q5_0: rq_requant_q8_0_kernel<RQ_Q5_0><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
+        case RQ_Q5_1: rq_requant_q8_0_kernel<RQ_Q5_1><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
+        case RQ_Q5_K: rq_requant_q8_0_kernel<RQ_Q5_K><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
+        case RQ_IQ4_NL: rq_requant_q8_0_kernel<RQ_IQ4_NL><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
         default: return rq_fail(RQ_ERR_INVALID, "requantize: source type %d", src->type);
     }
     RQ_CUDA(cudaGetLastError());

@@ -42,6 +42,7 @@ extern "C" int rq_matvec_int8_static(rq_ctx* ctx, const rq_weight* w, const floa
     if (!ctx || !w || !x || !y) return rq_fail(RQ_ERR_INVALID, "rq_matvec_int8_static: null argument");
     if (w->device != ctx->device) return rq_fail(RQ_ERR_INVALID, "rq_matvec_int8_static: weight lives on device %d, context on %d", w->device, ctx->device);
     if (step != 32 && step != 256) return rq_fail(RQ_ERR_INVALID, "rq_matvec_int8_static: int8 step=%d must be 32 or 256", step);
+    if (!rq_type_has_fast_path(w->type)) return rq_fail(RQ_ERR_UNSUPPORTED, "rq_matvec_int8_static: type %d has no int8 dot; re-encode it with rq_weight_requantize first", w->type);
     if (w->cols > RQ_STATIC_MAX_COLS)
         return rq_fail(RQ_ERR_LIMIT, "rq_matvec_int8_static: %lld inputs per row, but the fixed scratch holds at most %d; use rq_matvec, which allocates",
                        (long long)w->cols, RQ_STATIC_MAX_COLS);

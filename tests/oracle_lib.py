@@ -13,8 +13,34 @@ ORACLE_DIR = ROOT / "oracle"
 LIB_PATH = ORACLE_DIR / "librq_oracle.so"
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL = 3, 6, 7, 13, 20   # decoded and run-decoder dotted only; no encoder, no int8 slice helper
+STORED_ONLY = (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL)
 FLOAT_RUN, FLOAT_EXACT, INT8 = 0, 1, 2
-GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
+            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176), IQ4_NL: (32, 18)}
+
+
+def random_blocks(t: int, count: int, rng: np.random.Generator, scale: float = 0.02) -> np.ndarray:
+    """`count` format-valid blocks of type t with arbitrary codes and sane fp16 headers (finite, of a
+    weight's magnitude): test data for formats that have no encoder here."""
+    values, stride = GEOMETRY[t]
+    b = rng.integers(0, 256, size=(count, stride), dtype=np.uint8)
+    def put_half(col, v):
+        b[:, col:col + 2] = np.asarray(v, np.float16).reshape(-1, 1).view(np.uint8)
+    mag = np.abs(rng.normal(0, scale, count)) + 1e-2  # large enough that a Q8_0 step of it is a normal fp16
+    if t in (Q4_1, Q5_1):
+        put_half(0, mag / (15 if t == Q4_1 else 31)); put_half(2, -mag / 2)
+    elif t in (Q5_0, Q4_0):
+        put_half(0, mag / 16)
+    elif t == Q8_0:
+        put_half(0, mag / 127)
+    elif t == IQ4_NL:
+        put_half(0, mag / 127)
+    elif t in (Q5_K, Q4_K):
+        put_half(0, mag / (63 * (31 if t == Q5_K else 15))); put_half(2, mag / 63 / 2)
+    elif t == Q6_K:
+        put_half(208, mag / (127 * 32))
+    return b.reshape(-1)
 THREADS = max(1, os.cpu_count() or 1)
 
 

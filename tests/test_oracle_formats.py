@@ -1,0 +1,91 @@
+"""The other stored formats (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL): the C oracle and the independent NumPy
+restatement read every layout the same way, hand-built blocks decode to the values their definition
+gives, and the entry points that need an encoder or an int8 slice helper refuse them."""
+import numpy as np
+import pytest
+
+from oracle import np_unpack
+from tests import oracle_lib as ol
+
+TYPES = [ol.Q4_1, ol.Q5_0, ol.Q5_1, ol.Q5_K, ol.IQ4_NL]
+
+
+@pytest.mark.parametrize("t", TYPES)
+def test_two_restatements_agree_bit_for_bit(t):
+    oracle = ol.load()
+    rng = np.random.default_rng(100 + t)
+    values, stride = ol.GEOMETRY[t]
+    blocks = ol.random_blocks(t, 300, rng)
+    a = oracle.dequantize(t, blocks)
+    b = np_unpack.dequantize(t, blocks)
+    assert a.shape == (300 * values,)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # arbitrary bytes too (any fp16 header that is finite)
+    raw = rng.integers(0, 256, size=(200, stride), dtype=np.uint8)
+    for col in ((0, 2) if t in (ol.Q4_1, ol.Q5_1, ol.Q5_K) else (0,)):
+        raw[:, col + 1] &= 0x7B  # clear the top exponent bit: no inf / nan, sign dropped too
+    a = oracle.dequantize(t, raw.reshape(-1))
+    b = np_unpack.dequantize(t, raw.reshape(-1))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def _half_bytes(v):
+    return list(np.asarray([v], np.float16).view(np.uint8))
+
+
+def test_hand_built_blocks():
+    oracle = ol.load()
+    # Q4_1: d = 0.5, m = -1; byte k holds value k (low nibble) and value 16 + k (high nibble)
+    blk = _half_bytes(0.5) + _half_bytes(-1.0) + [(k & 15) | (((15 - k) & 15) << 4) for k in range(16)]
+    out = oracle.dequantize(ol.Q4_1, np.array(blk, np.uint8))
+    assert np.array_equal(out, np.array([0.5 * k - 1 for k in range(16)] + [0.5 * (15 - k) - 1 for k in range(16)], np.float32))
+    # Q5_0: d = 0.25; fifth bits 0x0000FFFF: values 0..15 carry it
+    blk = _half_bytes(0.25) + [0xFF, 0xFF, 0, 0] + [3 | (5 << 4)] * 16
+    out = oracle.dequantize(ol.Q5_0, np.array(blk, np.uint8))
+    assert np.array_equal(out, np.array([0.25 * (3 + 16 - 16)] * 16 + [0.25 * (5 - 16)] * 16, np.float32))
+    # Q5_1: d = 2, m = 1; only value 9 carries the fifth bit (bit 1 of the second byte)
+    blk = _half_bytes(2.0) + _half_bytes(1.0) + [0, 2, 0, 0] + [1] * 16
+    out = oracle.dequantize(ol.Q5_1, np.array(blk, np.uint8))
+    want = np.array([2.0 * 1 + 1] * 16 + [1.0] * 16, np.float32)
+    want[9] = 2.0 * 17 + 1
+    assert np.array_equal(out, want)
+    # IQ4_NL: d = 1: the level table itself, values 0..15 from the low nibbles of bytes 0..15
+    blk = _half_bytes(1.0) + [k | ((15 - k) << 4) for k in range(16)]
+    out = oracle.dequantize(ol.IQ4_NL, np.array(blk, np.uint8))
+    levels = [-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113]
+    assert np.array_equal(out, np.array(levels + levels[::-1], np.float32))
+    # Q5_K: d = 1, dmin = 0, every scale 1 (first four sub-blocks: low six bits), nibbles 2, fifth bit of value 0 in sub-block 3
+    scales = [1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1]
+    qh = [0] * 32
+    qh[0] = 1 << 3
+    blk = _half_bytes(1.0) + _half_bytes(0.0) + scales + qh + [2 | (2 << 4)] * 128
+    out = oracle.dequantize(ol.Q5_K, np.array(blk, np.uint8))
+    want = np.full(256, 2.0, np.float32)
+    want[3 * 32] = 18.0
+    assert np.array_equal(out, want)
+
+
+@pytest.mark.parametrize("t", TYPES)
+def test_run_decoder_product_and_reencode(t):
+    oracle = ol.load()
+    rng = np.random.default_rng(7 + t)
+    values, _ = ol.GEOMETRY[t]
+    rows, cols = 24, 1024
+    blocks = ol.random_blocks(t, rows * cols // values, rng)
+    w = oracle.dequantize(t, blocks).reshape(rows, cols).astype(np.float64)
+    x = rng.normal(size=(2, cols)).astype(np.float32)  # token-major
+    y = oracle.matvec(t, blocks, rows, cols, x, ol.FLOAT_RUN)
+    exact = x.astype(np.float64) @ w.T
+    assert np.max(np.abs(y - exact)) <= 1e-5 * np.max(np.abs(exact))
+    # the other two activation handlings need helpers these formats do not have
+    with pytest.raises(Exception):
+        oracle.matvec(t, blocks, rows, cols, x, ol.INT8)
+    with pytest.raises(Exception):
+        oracle.matvec(t, blocks, rows, cols, x, ol.FLOAT_EXACT)
+    with pytest.raises(Exception):
+        oracle.quantize(t, np.zeros(values, np.float32))
+    # `.int(8)`: decoded, then encoded as Q8_0 by the load kernel's encoder; one fp16 step per 32 values: half a step of rounding plus the step's own fp16 rounding (127 * 2^-11 of a step)
+    q8 = oracle.requantize_q8_0(t, blocks)
+    back = oracle.dequantize(ol.Q8_0, q8).reshape(rows, cols)
+    step = np.abs(w).reshape(rows, cols // 32, 32).max(axis=2) / 127
+    assert np.all(np.abs(back - w).reshape(rows, cols // 32, 32) <= 0.57 * step[:, :, None] + 127 * 2.0 ** -25)  # the last term: a step that is a subnormal fp16
