@@ -63,7 +63,7 @@ class Block {
     bool renormalize = true;
     SharedExpert shared{};
     double scale = 1.0;
-    int act_mode = RQ_ACT_FLOAT, step = 32;
+    int act_mode = RQ_ACT_FLOAT, step = 32, int_bits = 0;
 
     Block fp(uint8_t bits) const {
         if (bits != 32) throw RecipeError("fp bits must be 32 on this path");
@@ -73,10 +73,14 @@ class Block {
     }
     Block int_(uint8_t bits) const {  // `int` is a keyword in C++
         if (bits != 4 && bits != 8 && bits != 16 && bits != 32) throw RecipeError("int bits must be 4, 8, 16, or 32");
-        if (bits != 8) throw RecipeError("int(" + std::to_string(bits) + ") has no NVIDIA capability in recipe (recipe.rs:2658-2681); this path serves int(8)");
+        // int(8): storage Q8_0 (Q4_K kept); int(4): storage Q4_1, int8 activation records against four-bit codes (finish_int_sums,
+        // recipe.rs:22345-22369; recipe itself lists no NVIDIA capability for int4, recipe.rs:2658-2681: this library follows its
+        // CPU path). int(16) and int(32) widen the activations, which this path does not serve.
+        if (bits != 8 && bits != 4) throw RecipeError("int(" + std::to_string(bits) + ") is not served on this path; int(8) and int(4) are");
         if (kind == Moe) throw RecipeError("int sums are only for contractions: expert tables keep their activations (recipe.rs:22340)");
         Block b = *this;
         b.act_mode = RQ_ACT_INT8;
+        b.int_bits = bits;
         return b;
     }
     Block with_step(int s) const {
@@ -145,11 +149,12 @@ class Placed {
                 if (b.kind == Block::Layer || b.kind == Block::Embed) {
                     rq_weight* w = nullptr;
                     require(rq_weight_prepare(ctx_, b.tensor.ggml_type, b.tensor.blocks, b.tensor.rows, b.tensor.cols, 0, b.tensor.rows, &w));
-                    if (b.kind == Block::Layer && b.act_mode == RQ_ACT_INT8 && !rq_int8_keeps(b.tensor.ggml_type)) {
-                        // finish_int_sums (recipe.rs:22345-22369): `.int(8)` keeps Q8_0 and Q4_K; any other bound tensor is
-                        // re-encoded to Q8_0 once, at load, and the int8 dot runs over that
+                    const bool kept = b.int_bits == 4 ? rq_int4_keeps(b.tensor.ggml_type) != 0 : rq_int8_keeps(b.tensor.ggml_type) != 0;
+                    if (b.kind == Block::Layer && b.act_mode == RQ_ACT_INT8 && !kept) {
+                        // finish_int_sums (recipe.rs:22345-22369): `.int(8)` keeps Q8_0 and Q4_K, `.int(4)` keeps Q4_1; any other
+                        // bound tensor is re-encoded to the precision's storage (Q8_0, Q4_1) once, at load, and the int dot runs over that
                         rq_weight* q8 = nullptr;
-                        const int rc = rq_weight_requantize(ctx_, w, RQ_Q8_0, &q8, nullptr);
+                        const int rc = rq_weight_requantize(ctx_, w, b.int_bits == 4 ? RQ_Q4_1 : RQ_Q8_0, &q8, nullptr);
                         if (rc == RQ_OK) cudaDeviceSynchronize();
                         rq_weight_free(ctx_, w);
                         require(rc);

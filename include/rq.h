@@ -45,8 +45,9 @@ enum { RQ_Q4_0 = 2, RQ_Q8_0 = 8, RQ_Q4_K = 12, RQ_Q6_K = 14,
        /* The other stored formats the same bodies serve (recipe.rs:15812-15823): bound, decoded bit-exactly (rq_dequant,
         * rq_gather_rows), dotted with fp32 activations (RQ_ACT_FLOAT: the run decoders, recipe.rs:7826-7917) and re-encoded
         * to Q8_0 by rq_weight_requantize, which is what `.int(8)` does to them at load (recipe.rs:22345-22369). They have
-        * no int8 slice helper in the reference either, so RQ_ACT_INT8 on them returns RQ_ERR_UNSUPPORTED and names the
-        * re-encode; rq_quantize (no encoder) and expert banks do not take them. */
+        * no int8 dot here (Q4_1 excepted: it is the storage of int4 sums and RQ_ACT_INT8 over it is what `.int(4)` runs), so
+        * RQ_ACT_INT8 on the others returns RQ_ERR_UNSUPPORTED and names the re-encode; rq_quantize (no encoder) and expert
+        * banks do not take them. */
        RQ_Q4_1 = 3, RQ_Q5_0 = 6, RQ_Q5_1 = 7, RQ_Q5_K = 13, RQ_IQ4_NL = 20 };
 
 /* Activation handling, what `.fp(32)` / `.int(8)` select (recipe.rs:14027-14054, :22326-22369):
@@ -106,13 +107,19 @@ int rq_weight_prepare_device(rq_ctx* ctx, int ggml_type, const void* dev_blocks,
 /* Writes the weight back as GGUF blocks into host memory (round-trip check of the layout). */
 int rq_weight_export(rq_ctx* ctx, const rq_weight* w, void* host_blocks);
 /* The load-time re-encode of a bound tensor: decodes `src` with its own decoder and encodes it as
- * `target_type` (RQ_Q8_0) with the load kernel's encoder, byte-exact with what the reference's
+ * `target_type` (RQ_Q8_0 or RQ_Q4_1) with the load kernel's encoder, byte-exact with what the reference's
  * recipe_model_load writes (requantize_bound recipe.rs:22373-22431, emit_requantize :8016-8127).
- * This is what `.int(8)` does to a tensor bound in a format it does not keep. `src` stays valid. */
+ * This is what `.int(8)` (target Q8_0) and `.int(4)` (target Q4_1) do to a tensor bound in a format
+ * they do not keep. `src` stays valid. */
 int rq_weight_requantize(rq_ctx* ctx, const rq_weight* src, int target_type, rq_weight** out, void* stream);
 /* 1 when `.int(8)` dots a lone tensor of this type as stored (Q8_0, Q4_K), 0 when the reference
  * re-encodes it to Q8_0 at load first (Q6_K, Q4_0): finish_int_sums, recipe.rs:22345-22369. */
 int rq_int8_keeps(int ggml_type);
+/* The same question for `.int(4)`, whose storage is Q4_1 (recipe.rs:22348): 1 for Q4_1, 0 for everything else -- re-encode
+ * with rq_weight_requantize(ctx, w, RQ_Q4_1, ..) (the load kernel's Q4_1 encoder, recipe.rs:8088-8094) and run RQ_ACT_INT8
+ * over the result: int8 activation records against the four-bit codes, q8_d * (d * dot + m * sum) per 16-value slice
+ * (block32 slice kind 3, build.rs:777-796). */
+int rq_int4_keeps(int ggml_type);
 void rq_weight_free(rq_ctx* ctx, rq_weight* w);
 int64_t rq_weight_rows(const rq_weight* w);
 int64_t rq_weight_cols(const rq_weight* w);

@@ -507,7 +507,34 @@ static void requant_block_q8_0(const float* v, uint8_t* out) {
     }
 }
 
-typedef struct { int type; const uint8_t* blocks; int64_t count; uint8_t* out; } requant_ctx;
+/* emit_requantize, DeviceQuantizer::Q4_1 (recipe.rs:8037-8047, :8088-8094, :8099-8112): the block's minimum and maximum
+ * (first of equals kept), step = (max - min) / 15, inverse guarded against a zero step, code = fptoui(clamp((v - min) *
+ * inverse + 0.5, 0, 15)); step and minimum stored with fptrunc (round to nearest even), codes two to a byte (value i low,
+ * value i + 16 high). */
+static void requant_block_q4_1(const float* v, uint8_t* out) {
+    float mn = v[0], mx = v[0];
+    for (int i = 0; i < 32; ++i) {
+        if (v[i] < mn) mn = v[i];
+        if (v[i] > mx) mx = v[i];
+    }
+    float range = mx - mn;
+    float scale = range / 15.0f;
+    float inverse = scale == 0.0f ? 0.0f : 1.0f / scale;
+    put_half(out, scale);
+    put_half(out + 2, mn);
+    uint8_t code[32];
+    for (int i = 0; i < 32; ++i) {
+        float off = v[i] - mn;
+        float q = off * inverse;
+        float sh = q + 0.5f;
+        float cl = sh < 0.0f ? 0.0f : sh;
+        cl = cl > 15.0f ? 15.0f : cl;
+        code[i] = (uint8_t)(uint32_t)cl; /* fptoui: toward zero */
+    }
+    for (int i = 0; i < 16; ++i) out[4 + i] = (uint8_t)(code[i] | (code[i + 16] << 4));
+}
+
+typedef struct { int type; const uint8_t* blocks; int64_t count; uint8_t* out; int target; } requant_ctx;
 static void requant_span(void* p, int64_t first, int64_t last, int worker, int workers) {
     (void)worker; (void)workers;
     requant_ctx* c = (requant_ctx*)p;
@@ -519,7 +546,8 @@ static void requant_span(void* p, int64_t first, int64_t last, int worker, int w
             int64_t at = blk * 32 + i;
             v[i] = at < c->count ? block_value(c->type, c->blocks + (at / per) * bytes, (int)(at % per)) : 0.0f;
         }
-        requant_block_q8_0(v, c->out + blk * 34);
+        if (c->target == RQO_Q4_1) requant_block_q4_1(v, c->out + blk * 20);
+        else requant_block_q8_0(v, c->out + blk * 34);
     }
 }
 /* finish_int_sums + requantize_bound (recipe.rs:22345-22431): a tensor bound in a format that
@@ -527,7 +555,15 @@ static void requant_span(void* p, int64_t first, int64_t last, int worker, int w
  * source decoder and encoded again as Q8_0 by the load kernel, once, before any matvec. */
 int rqo_requantize_q8_0(int type, const uint8_t* blocks, int64_t count, uint8_t* out, int threads) {
     if (!rqo_block_values(type) || count < 0) return -1;
-    requant_ctx c = {type, blocks, count, out};
+    requant_ctx c = {type, blocks, count, out, RQO_Q8_0};
+    run_spans((count + 31) / 32, threads, requant_span, &c);
+    return 0;
+}
+/* The same for `.int(4)`: its storage is Q4_1 (recipe.rs:22348), kept only when the tensor is stored as Q4_1 already;
+ * everything else is decoded and encoded as Q4_1 by the load kernel. out: ceil(count / 32) * 20 bytes. */
+int rqo_requantize_q4_1(int type, const uint8_t* blocks, int64_t count, uint8_t* out, int threads) {
+    if (!rqo_block_values(type) || count < 0) return -1;
+    requant_ctx c = {type, blocks, count, out, RQO_Q4_1};
     run_spans((count + 31) / 32, threads, requant_span, &c);
     return 0;
 }
@@ -574,18 +610,18 @@ static inline const int8_t* rec_codes(const uint8_t* rec) { return (const int8_t
 
 /* ------------------------------------------------------------- int8 dots, step 32 (a11-a13) */
 
-/* build.rs:777-796: r = q8_d * (d * f32(dot) + m * f32(sum a)), m = 0 for Q8_0 / Q4_0;
+/* build.rs:777-796: r = q8_d * (d * f32(dot) + m * f32(sum a)), m = 0 for Q8_0 / Q4_0, the block's minimum for Q4_1;
  * Q4_0 folds its offset of eight into the integer: dot -= 8 * sum a. */
 static float b32_slice(int type, const uint8_t* block, const uint8_t* rec, int slice) {
     const int8_t* a = rec_codes(rec) + 16 * slice;
     int32_t dot = 0, sum = 0;
     for (int i = 0; i < 16; ++i) {
-        int code = type == RQO_Q8_0 ? (int8_t)block[2 + 16 * slice + i] : ((block[2 + i] >> (4 * slice)) & 15);
+        int code = type == RQO_Q8_0 ? (int8_t)block[2 + 16 * slice + i] : ((block[(type == RQO_Q4_1 ? 4 : 2) + i] >> (4 * slice)) & 15);
         dot += code * a[i];
         sum += a[i];
     }
     if (type == RQO_Q4_0) dot -= 8 * sum;
-    float d = half_at(block), m = 0.0f;
+    float d = half_at(block), m = type == RQO_Q4_1 ? half_at(block + 2) : 0.0f; /* kind 3: the block minimum times the activation sum */
     float value = d * (float)dot + m * (float)sum;
     return rec_d(rec) * value;
 }
@@ -832,7 +868,7 @@ int rqo_matvec(int type, const uint8_t* blocks, int64_t rows, int64_t cols,
     if (act_mode < 0 || act_mode > 2) return -1;
     if (act_mode == RQO_ACT_INT8 && step != 32 && step != 256) return -1;
     /* the other stored formats are dotted by the run decoders only; `.int(8)` re-encodes them first */
-    if (act_mode != RQO_ACT_FLOAT_RUN && !type_has_slices(type)) return -1;
+    if (act_mode != RQO_ACT_FLOAT_RUN && !type_has_slices(type) && !(act_mode == RQO_ACT_INT8 && type == RQO_Q4_1)) return -1;
     matvec_ctx c = {type, blocks, rows, cols, x, x_stride, tokens, y, y_stride, act_mode, step, NULL};
     uint8_t* records = NULL;
     if (act_mode == RQO_ACT_INT8) {

@@ -58,6 +58,10 @@ int rqo_quantize(int type, const float* values, int64_t count, uint8_t* blocks, 
  * (a lone Q6_K or Q4_0 tensor): decode with the source decoder, encode as Q8_0 with the load
  * kernel's encoder (recipe.rs:22345-22431, :8016-8127). out: ceil(count / 32) * 34 bytes. */
 int rqo_requantize_q8_0(int type, const uint8_t* blocks, int64_t count, uint8_t* out, int threads);
+/* `.int(4)`: storage Q4_1 (recipe.rs:22348); a tensor not stored as Q4_1 is decoded and encoded as Q4_1 by the load
+ * kernel (recipe.rs:8088-8094). out: ceil(count / 32) * 20 bytes. rqo_matvec with RQO_ACT_INT8 over Q4_1 blocks is the
+ * int dot such a layer then runs (block32 slice kind 3, build.rs:777-796). */
+int rqo_requantize_q4_1(int type, const uint8_t* blocks, int64_t count, uint8_t* out, int threads);
 
 /* int8 activation records (36 bytes each: fp32 d, 32 codes) for one column of `terms`
  * inputs read at x[k * x_stride]; `step` is 32 or 256. ll:1381-1517, CPU wave width 1. */

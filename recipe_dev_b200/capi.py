@@ -49,6 +49,7 @@ def _declare(lib) -> None:
         "rq_weight_export": (i32, [p, p, p]),
         "rq_weight_requantize": (i32, [p, p, i32, C.POINTER(p), p]),
         "rq_int8_keeps": (i32, [i32]),
+        "rq_int4_keeps": (i32, [i32]),
         "rq_weight_free": (None, [p, p]),
         "rq_weight_rows": (i64, [p]),
         "rq_weight_cols": (i64, [p]),
@@ -297,6 +298,10 @@ class Context:
         out = C.c_void_p()
         _check(self.lib.rq_weight_requantize(self.handle, w.handle, target_type, C.byref(out), _stream(stream)))
         return Weight(self, out.value)
+
+    def int4_weight(self, w: Weight, stream=None) -> Weight:
+        """The weight `.int(4)` dots: `w` itself when it is stored as Q4_1, else its load-time Q4_1 re-encode."""
+        return w if self.lib.rq_int4_keeps(w.type) else self.requantize(w, Q4_1, stream)
 
     def int8_weight(self, w: Weight, stream=None) -> Weight:
         """The weight recipe's `.int(8)` dots: `w` itself when the format is kept, else its Q8_0 re-encode."""

@@ -324,19 +324,21 @@ extern "C" int rq_weight_prepare(rq_ctx* ctx, int type, const void* host_blocks,
 extern "C" int rq_weight_requantize(rq_ctx* ctx, const rq_weight* src, int target_type, rq_weight** out, void* stream) {
     if (!ctx || !src || !out) return rq_fail(RQ_ERR_INVALID, "rq_weight_requantize: null argument");
     *out = nullptr;
-    if (target_type != RQ_Q8_0) return rq_fail(RQ_ERR_UNSUPPORTED, "rq_weight_requantize: target type %d; the load kernel's encoder is served for Q8_0(8) only", target_type);
+    if (target_type != RQ_Q8_0 && target_type != RQ_Q4_1)
+        return rq_fail(RQ_ERR_UNSUPPORTED, "rq_weight_requantize: target type %d; the load kernel's encoders served are Q8_0(8), the storage of int8 sums, and Q4_1(3), that of int4 sums", target_type);
     if (src->device != ctx->device) return rq_fail(RQ_ERR_INVALID, "rq_weight_requantize: weight lives on device %d, context on %d", src->device, ctx->device);
     DeviceGuard guard(ctx->device);
     rq_weight* w = nullptr;
     int rc = alloc_weight(ctx, target_type, src->rows, src->cols, &w);
     if (rc) return rc;
-    rc = rq_launch_requant_q8_0(src, w, (cudaStream_t)stream);
+    rc = target_type == RQ_Q8_0 ? rq_launch_requant_q8_0(src, w, (cudaStream_t)stream) : rq_launch_requant_q4_1(src, w, (cudaStream_t)stream);
     if (rc) { rq_weight_free(ctx, w); return rc; }
     *out = w;
     return RQ_OK;
 }
 
 extern "C" int rq_int8_keeps(int ggml_type) { return ggml_type == RQ_Q8_0 || ggml_type == RQ_Q4_K; }
+extern "C" int rq_int4_keeps(int ggml_type) { return ggml_type == RQ_Q4_1; }
 
 extern "C" int rq_weight_export(rq_ctx* ctx, const rq_weight* w, void* host_blocks) {
     if (!ctx || !w || !host_blocks) return rq_fail(RQ_ERR_INVALID, "rq_weight_export: null argument");

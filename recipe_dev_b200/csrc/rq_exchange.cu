@@ -173,8 +173,8 @@ __device__ __forceinline__ unsigned long long ex_now() { unsigned long long t; a
 // the flags; every CTA then waits for the peers' flags and copies out (or adds, in rank order) its part of the slots.
 // Call e (counted in device memory) uses half e & 1 of the slots and the flag value e + 1.
 __global__ void __launch_bounds__(256) rq_exchange_kernel(const ExchangeParams p) {
+    // the launch after this one may start its own prologue (a matvec's first weight copies) while this kernel exchanges
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // the slice was written by the kernel before; so was the call count
     const int tid = threadIdx.x;
     uint32_t* flags = (uint32_t*)(p.peer[p.rank] + 2 * p.half_bytes);
     unsigned int* arrivals = (unsigned int*)(flags + RQ_EXCHANGE_MAX_RANKS);
@@ -203,18 +203,23 @@ __global__ void __launch_bounds__(256) rq_exchange_kernel(const ExchangeParams p
     __shared__ bool s_last;
     if (tid == 0) {
         __threadfence_system();
-        s_last = atomicAdd(arrivals, 1u) == gridDim.x - 1u;
-        if (s_last) {
+        s_last = gridDim.x == 1u || atomicAdd(arrivals, 1u) == gridDim.x - 1u;
+        if (s_last && gridDim.x > 1u) {
             *arrivals = 0;            // nobody adds again before the next call
             __threadfence_system();   // the other CTAs' fenced stores, seen through their arrivals, go before the flags
         }
+        if (s_last) {
+            // 2. every CTA's stores are out and fenced: tell each peer that this rank's slot is complete. The fence above
+            // already orders the stores before these, so the flag stores themselves are relaxed (a release store would
+            // pay for one more system-scope fence each).
+            for (int r = 0; r < p.nranks; ++r) {
+                if (r == p.rank) continue;
+                uint32_t* there = (uint32_t*)(p.peer[r] + 2 * p.half_bytes) + p.rank;
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(there), "r"(epoch + 1u) : "memory");
+            }
+        }
     }
     __syncthreads();
-    if (s_last && tid < p.nranks && tid != p.rank) {
-        // 2. every CTA's stores are out: tell peer `tid` that this rank's slot is complete
-        uint32_t* there = (uint32_t*)(p.peer[tid] + 2 * p.half_bytes) + p.rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(there), "r"(epoch + 1u) : "memory");
-    }
     // 3. wait for every peer's flag of this call (bounded)
     if (tid < p.nranks && tid != p.rank) {
         unsigned long long t0 = 0;
@@ -232,7 +237,17 @@ __global__ void __launch_bounds__(256) rq_exchange_kernel(const ExchangeParams p
     __syncthreads();
     // 4. out of the slots: one after another, or their sum in rank order
     const uint8_t* mine = p.peer[p.rank] + half_off;
-    if (p.sum) {
+    if (p.sum && vec) {
+        const int64_t n4 = p.count >> 2;
+        for (int64_t i = at0; i < n4; i += stride) {
+            float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < p.nranks; ++r) {  // rank order: the same bits on every rank
+                const float4 v = __ldcg((const float4*)(mine + (int64_t)r * p.slot_bytes) + i);
+                total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+            }
+            ((float4*)p.out)[i] = total;
+        }
+    } else if (p.sum) {
         for (int64_t i = at0; i < p.count; i += stride) {
             float total = 0.f;
             for (int r = 0; r < p.nranks; ++r) total += __ldcg((const float*)(mine + (int64_t)r * p.slot_bytes) + i);
@@ -342,19 +357,22 @@ static int exchange_launch(rq_exchange* ex, const char* who, const float* local,
     p.rank = ex->rank; p.nranks = ex->nranks; p.slot_bytes = ex->slot_bytes; p.half_bytes = (int64_t)ex->nranks * ex->slot_bytes;
     p.src = local; p.count = count; p.out = out; p.sum = sum;
     p.error_flag = ex->ctx->error_flag; p.wait_ns = ex->ctx->wait_limit_ns;
-    // a CTA per 16 KB of slice, at most 32: every CTA must be resident while it waits for the peers' flags
-    int64_t ctas = (count * 4 + 16383) / 16384;
+    // A CTA per 4 KB of slice (one 16-byte line per thread: the push is a chain of a load and a store per line, so its time
+    // is the number of lines a thread moves one after another), at most 128: every CTA must be resident while it waits for
+    // the peers' flags, and 128 CTAs of 256 threads and no shared memory fit the device beside anything else that runs.
+    int64_t ctas = (count * 4 + 4095) / 4096;
     if (ctas < 1) ctas = 1;
-    if (ctas > 32) ctas = 32;
+    if (ctas > 128) ctas = 128;
+    if (ctas > ex->ctx->sm_count) ctas = ex->ctx->sm_count;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(256);
     cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    // Launched the plain way, after the kernel before it has finished: with programmatic serialization this kernel's
+    // early trigger let the launch after it (the next step's matvec, itself programmatic) start while the matvec that
+    // feeds this exchange was still running, and the step measured 17 us slower (LM head share of 131072 rows, two GPUs).
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
     RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_exchange_kernel, p));
     return RQ_OK;
 }

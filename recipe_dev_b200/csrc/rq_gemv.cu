@@ -450,6 +450,12 @@ int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, 
     int rc;
     if (!rq_type_has_fast_path(w->type)) {
         // the other stored formats: run decoders over fp32 activations; int sums never see them (recipe.rs:22345-22369)
+        if (mode != RQ_ACT_FLOAT && w->type == RQ_Q4_1) {
+            // `.int(4)`: Q4_1 is the storage of int4 sums (recipe.rs:22348) and has an int8 dot of its own
+            rc = int8_records(ctx, "matvec", x, sk, st, w->cols, tokens, step, act_mode, s);
+            if (rc) return rc;
+            return rq_launch_gemv_q41_int8(ctx, w, ctx->act_scratch, tokens, y, yn, yt, s);
+        }
         if (mode != RQ_ACT_FLOAT)
             return rq_fail(RQ_ERR_UNSUPPORTED, "matvec: int8 activations over a type-%d weight; `.int(8)` re-encodes such a tensor to Q8_0 at load: call rq_weight_requantize(.., RQ_Q8_0, ..) and use the result", w->type);
         return rq_launch_gemv_generic(ctx, w, x, sk, st, tokens, y, yn, yt, s);

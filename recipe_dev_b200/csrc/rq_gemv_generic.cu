@@ -4,7 +4,8 @@
 // row add up, ll:3451-3492). HBM-bound by design: a warp owns a row and walks it in units of 32 values,
 // lane l taking units l, l + 32, ..; the lanes' sums meet in a fixed xor tree, so every run gives the same
 // bits. `.int(8)` never reaches these formats: the reference re-encodes them to Q8_0 at load
-// (rq_weight_requantize), and that weight takes the streaming kernel.
+// (rq_weight_requantize), and that weight takes the streaming kernel. `.int(4)` stores Q4_1 and dots it with
+// int8 activation records: rq_gemv_q41_int8_kernel below.
 #include "rq_decode.cuh"
 
 namespace {
@@ -25,6 +26,50 @@ __global__ void __launch_bounds__(kWarps * 32) rq_gemv_generic_kernel(const uint
 #pragma unroll 8
             for (int j = 0; j < 32; ++j) unit = fmaf(rq_decode_value<TYPE>(main_plane, nullptr, first + j, cols), __ldg(xt + ((u << 5) + j) * sk), unit);
             sum += unit;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (lane == 0) y[row * yn + (int64_t)token * yt] = sum;
+    }
+}
+
+// `.int(4)`: int8 activation records against Q4_1 blocks (block32 slice kind 3, build.rs:777-796). Per 16-value slice
+// r = q8_d * (d * f32(dot) + m * f32(sum of the slice's activation codes)); slice 0 takes the low nibbles, slice 1 the high
+// ones. A warp owns a row, lane l the blocks l, l + 32, ..; dots by dp4a over the nibbles in place; fixed xor tree.
+__global__ void __launch_bounds__(kWarps * 32) rq_gemv_q41_int8_kernel(const uint8_t* __restrict__ blocks, int64_t rows, int64_t cols, const uint8_t* __restrict__ records,
+                                                                         size_t token_bytes, float* __restrict__ y, int64_t yn, int64_t yt) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, token = blockIdx.y;
+    const uint8_t* tok = records + (size_t)token * token_bytes;
+    const bool unit = rq_act_unit_layout(cols);
+    const int64_t nb = cols >> 5;
+    for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
+        float sum = 0.f;
+        for (int64_t b = lane; b < nb; b += 32) {
+            const uint8_t* blk = blocks + (row * nb + b) * 20;  // 20-byte stride from a 256-byte aligned base: words are aligned
+            const uint32_t hdr = *(const uint32_t*)blk;
+            const float d = rq_h2f((uint16_t)(hdr & 0xffff)), m = rq_h2f((uint16_t)(hdr >> 16));
+            const int8_t* codes; float q8_d; const int16_t* sums;
+            if (unit) {
+                const uint8_t* rec = tok + (size_t)(b >> 3) * RQ_ACT_RECORD_INT8;
+                codes = (const int8_t*)rec + 32 * (b & 7);
+                q8_d = ((const float*)(rec + 256))[b & 7];
+                sums = (const int16_t*)(rec + 288) + 2 * (b & 7);
+            } else {
+                codes = (const int8_t*)tok + b * 32;
+                q8_d = ((const float*)(tok + cols))[b];
+                sums = (const int16_t*)(tok + cols + nb * 4) + 2 * b;
+            }
+            int dot_lo = 0, dot_hi = 0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const uint32_t q = *(const uint32_t*)(blk + 4 + 4 * w);
+                dot_lo = __dp4a((int)(q & 0x0F0F0F0Fu), *(const int*)(codes + 4 * w), dot_lo);
+                dot_hi = __dp4a((int)((q >> 4) & 0x0F0F0F0Fu), *(const int*)(codes + 16 + 4 * w), dot_hi);
+            }
+            const float r0 = __fmul_rn(q8_d, __fadd_rn(__fmul_rn(d, (float)dot_lo), __fmul_rn(m, (float)sums[0])));
+            const float r1 = __fmul_rn(q8_d, __fadd_rn(__fmul_rn(d, (float)dot_hi), __fmul_rn(m, (float)sums[1])));
+            sum += r0;
+            sum += r1;
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
@@ -54,4 +99,14 @@ int rq_launch_gemv_generic(rq_ctx* ctx, const rq_weight* w, const float* x, int6
         case RQ_IQ4_NL: return launch_generic<RQ_IQ4_NL>(w, x, sk, st, tokens, y, yn, yt, ctx->sm_count, s);
         default: return rq_fail(RQ_ERR_INVALID, "matvec: type %d", w->type);
     }
+}
+
+int rq_launch_gemv_q41_int8(rq_ctx* ctx, const rq_weight* w, const uint8_t* records, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s) {
+    if (tokens > 65535) return rq_fail(RQ_ERR_LIMIT, "matvec: %d tokens over a Q4_1 weight, at most 65535 per call", tokens);
+    const int64_t ctas = (w->rows + kWarps - 1) / kWarps;
+    const int64_t cap = (int64_t)ctx->sm_count * 8;
+    dim3 grid((unsigned)(ctas < cap ? ctas : cap), (unsigned)tokens);
+    rq_gemv_q41_int8_kernel<<<grid, kWarps * 32, 0, s>>>(w->main, w->rows, w->cols, records, rq_act_token_bytes(w->cols), y, yn, yt);
+    RQ_CUDA(cudaGetLastError());
+    return RQ_OK;
 }

@@ -100,6 +100,8 @@ int rq_launch_gather(const rq_weight* w, const int32_t* ids, int tokens, float* 
 // fills w->tile_map for Q4_K / Q6_K weights (no-op for the others)
 int rq_make_tile_map(rq_weight* w);
 int rq_launch_requant_q8_0(const rq_weight* src, rq_weight* dst, cudaStream_t s);
+int rq_launch_requant_q4_1(const rq_weight* src, rq_weight* dst, cudaStream_t s);
+int rq_launch_gemv_q41_int8(rq_ctx* ctx, const rq_weight* w, const uint8_t* records, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s);
 int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, int tokens, int step,
                         uint8_t* scratch, uint8_t* records36, cudaStream_t s);
 int rq_launch_gemv(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens,

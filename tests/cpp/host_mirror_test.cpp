@@ -72,6 +72,20 @@ int main() {
         if (!(e3 <= 5e-5)) { std::printf("lone Q6_K under int(8): relative error %g against the Q8_0 re-encode\n", e3); return 1; }
         if (lone.resident_bytes()[0] != b8.size()) { std::printf("re-encoded weight holds %zu bytes, expected %zu\n", lone.resident_bytes()[0], b8.size()); return 1; }
     }
+    // .int(4): storage Q4_1 by the load kernel's encoder, int8 records against its codes (recipe.rs:22348); place() re-encodes
+    {
+        std::vector<uint8_t> b4((size_t)mid * hidden / 32 * 20);
+        rqo_requantize_q4_1(RQO_Q4_K, b1.data(), (int64_t)mid * hidden, b4.data(), 4);
+        std::vector<float> xin4(hidden), ref4(mid);
+        rqo_normal(75, 0, 0, hidden, 1.0, xin4.data());
+        rqo_matvec(RQO_Q4_1, b4.data(), mid, hidden, xin4.data(), 1, 1, ref4.data(), 1, RQO_ACT_INT8, 32, 4);
+        auto four = Model().layer({RQ_Q4_K, mid, hidden, b1.data()}).int_(4).place(0);
+        std::vector<double> y4 = four.infer(std::vector<double>(xin4.begin(), xin4.end()));
+        const double e4 = rel_err(y4, ref4);
+        if (!(e4 <= 5e-4)) { std::printf("Q4_K under int(4): relative error %g against the Q4_1 re-encode\n", e4); return 1; }
+        if (four.resident_bytes()[0] != b4.size()) { std::printf("Q4_1 weight holds %zu bytes, expected %zu\n", four.resident_bytes()[0], b4.size()); return 1; }
+        try { Model().layer({RQ_Q4_K, mid, hidden, b1.data()}).int_(16); std::printf("int(16) accepted\n"); return 1; } catch (const RecipeError&) {}
+    }
     // ids -> embedding -> two layers: prefill, step and greedy decode; a step gives the bits its position gets in a prefill
     {
         const int vocab = 96;

@@ -64,6 +64,7 @@ class Oracle:
         lib.rqo_dequantize.argtypes = [i32, p, i64, p, i32]
         lib.rqo_quantize.argtypes = [i32, p, i64, p, i32]
         lib.rqo_requantize_q8_0.argtypes = [i32, p, i64, p, i32]
+        lib.rqo_requantize_q4_1.argtypes = [i32, p, i64, p, i32]
         lib.rqo_quantize_activations.argtypes = [p, i64, i64, i32, p]
         lib.rqo_matvec.argtypes = [i32, p, i64, i64, p, i64, i32, p, i64, i32, i32, i32]
         for name in ("rqo_exp", "rqo_tanh", "rqo_sigmoid", "rqo_silu"):
@@ -106,6 +107,19 @@ class Oracle:
         out = np.empty(count // 32 * 34, dtype=np.uint8)
         assert self.lib.rqo_requantize_q8_0(t, b.ctypes.data, count, out.ctypes.data, THREADS) == 0
         return out
+
+    def requantize_q4_1(self, t: int, blocks: np.ndarray) -> np.ndarray:
+        """The load-time re-encode of `.int(4)`: any stored format -> Q4_1 blocks."""
+        b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        values, stride = GEOMETRY[t]
+        count = b.size // stride * values
+        out = np.empty((count + 31) // 32 * 20, dtype=np.uint8)
+        assert self.lib.rqo_requantize_q4_1(t, b.ctypes.data, count, out.ctypes.data, THREADS) == 0
+        return out
+
+    def int4_blocks(self, t: int, blocks: np.ndarray):
+        """(type, blocks) that recipe's `.int(4)` dots: kept for Q4_1, re-encoded to Q4_1 otherwise."""
+        return (t, blocks) if t == Q4_1 else (Q4_1, self.requantize_q4_1(t, blocks))
 
     def int8_blocks(self, t: int, blocks: np.ndarray):
         """(type, blocks) that recipe's `.int(8)` dots for a lone tensor: kept for Q8_0 / Q4_K, re-encoded to Q8_0 otherwise."""

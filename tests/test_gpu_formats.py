@@ -84,8 +84,9 @@ def test_int8_is_the_q8_0_reencode(rq_ctx, oracle, t):
         assert t8 == ol.Q8_0
         assert rel_err(y, oracle.matvec(t8, b8, rows, cols, x, ol.INT8, step)) <= (5e-5 if step == 32 else 2e-4)
     # the stored blocks themselves have no int8 dot: the call says what to do instead
-    with pytest.raises(rq.RqError, match="rq_weight_requantize"):
-        rq_ctx.matvec(w, torch_cuda(x), act_mode=rq.ACT_INT8)
+    if t != ol.Q4_1:  # Q4_1 is `.int(4)`'s storage and has an int8 dot (test_int4_is_the_q4_1_reencode)
+        with pytest.raises(rq.RqError, match="rq_weight_requantize"):
+            rq_ctx.matvec(w, torch_cuda(x), act_mode=rq.ACT_INT8)
     with pytest.raises(rq.RqError):
         rq_ctx.matvec_int8_static(w, torch_cuda(x))
     with pytest.raises(rq.RqError):
@@ -116,4 +117,41 @@ def test_bound_from_a_gguf_file(rq_ctx, oracle, tmp_path):
         w = g.bind(rq_ctx, name, row_first=8, row_count=24)
         want = oracle.dequantize(t, blocks[name]).reshape(rows, cols)[8:32]
         assert np.array_equal(rq_ctx.dequant(w).cpu().numpy().view(np.uint32), want.view(np.uint32))
+    rq_ctx.check()
+
+
+@pytest.mark.parametrize("t", [ol.Q4_K, ol.Q6_K, ol.Q8_0, ol.Q4_0, ol.Q4_1, ol.Q5_K, ol.IQ4_NL])
+@pytest.mark.parametrize("cols", [2048, 96 * 32 + 32])
+def test_int4_is_the_q4_1_reencode(rq_ctx, oracle, t, cols):
+    """`.int(4)` (recipe.rs:22348): storage Q4_1 by the load kernel's encoder, byte for byte; int8 records against its codes."""
+    import recipe_dev_b200 as rq
+
+    values, _ = ol.GEOMETRY[t]
+    if cols % values:
+        pytest.skip("width is not a whole number of blocks of this format")
+    rows = 48
+    if t in (ol.Q4_K, ol.Q6_K, ol.Q8_0, ol.Q4_0):
+        blocks = oracle.quantize(t, oracle.normal(45, t, rows * cols, 0.02))
+        w = rq_ctx.weight_from_host(t, blocks, rows, cols)
+    else:
+        blocks, w = _weight(rq_ctx, t, rows, cols, 900 + t)
+    assert rq_ctx.lib.rq_int4_keeps(t) == (1 if t == ol.Q4_1 else 0)
+    w4 = rq_ctx.int4_weight(w)
+    assert w4.type == rq.Q4_1
+    t4, b4 = oracle.int4_blocks(t, blocks)
+    got = rq_ctx.export(w4)
+    bad = np.nonzero(got != b4)[0]
+    assert bad.size == 0, f"{bad.size} bytes differ, first in block {bad[0] // 20}"
+    if t != ol.Q4_1:
+        # an explicit re-encode of a Q4_1 tensor is the encoder applied to its decoded values (not the identity in general)
+        again = rq_ctx.export(rq_ctx.requantize(w4, rq.Q4_1))
+        assert np.array_equal(again, oracle.requantize_q4_1(ol.Q4_1, b4))
+    for tokens in (1, 3):
+        x = oracle.normal(46, t, tokens * cols, 1.0).reshape(tokens, cols)
+        for step in (32, 256):
+            y = rq_ctx.matvec(w4, torch_cuda(x), act_mode=rq.ACT_INT8, step=step).cpu().numpy()
+            ref = oracle.matvec(ol.Q4_1, b4, rows, cols, x, ol.INT8, step)
+            # every slice value is the oracle's bits; the slices (whose minimum terms are large and cancel) are added in another order
+            assert rel_err(y, ref) <= 5e-4
+            assert np.array_equal(rq_ctx.matmul(w4, torch_cuda(x), act_mode=rq.ACT_INT8, step=step).cpu().numpy(), y)
     rq_ctx.check()

@@ -78,8 +78,9 @@ def test_run_decoder_product_and_reencode(t):
     exact = x.astype(np.float64) @ w.T
     assert np.max(np.abs(y - exact)) <= 1e-5 * np.max(np.abs(exact))
     # the other two activation handlings need helpers these formats do not have
-    with pytest.raises(Exception):
-        oracle.matvec(t, blocks, rows, cols, x, ol.INT8)
+    if t != ol.Q4_1:  # Q4_1 is `.int(4)`'s storage and has an int8 slice helper (block32 slice kind 3)
+        with pytest.raises(Exception):
+            oracle.matvec(t, blocks, rows, cols, x, ol.INT8)
     with pytest.raises(Exception):
         oracle.matvec(t, blocks, rows, cols, x, ol.FLOAT_EXACT)
     with pytest.raises(Exception):
@@ -89,3 +90,45 @@ def test_run_decoder_product_and_reencode(t):
     back = oracle.dequantize(ol.Q8_0, q8).reshape(rows, cols)
     step = np.abs(w).reshape(rows, cols // 32, 32).max(axis=2) / 127
     assert np.all(np.abs(back - w).reshape(rows, cols // 32, 32) <= 0.57 * step[:, :, None] + 127 * 2.0 ** -25)  # the last term: a step that is a subnormal fp16
+
+
+def test_int4_storage_is_q4_1():
+    """`.int(4)` (recipe.rs:22348): the load kernel's Q4_1 encoder on hand-checked blocks, its error bound on random
+    tensors, and the int dot over Q4_1 blocks against the exact product of the decoded weights and the decoded records."""
+    oracle = ol.load()
+    # values 0, 1, .., 15 twice: minimum 0, maximum 15, step exactly 1, codes = the values
+    v = np.array(list(range(16)) * 2, np.float32)
+    q8 = oracle.quantize(ol.Q8_0, v / 8)            # an exactly representable source: codes 0..15 * 8.47 -> decode gives k * d
+    src = oracle.dequantize(ol.Q8_0, q8)
+    q41 = oracle.requantize_q4_1(ol.Q8_0, q8)
+    assert q41.size == 20
+    back = oracle.dequantize(ol.Q4_1, q41)
+    step = (src.max() - src.min()) / 15
+    assert np.all(np.abs(back - src) <= 0.51 * step + 2e-3 * np.abs(src).max())  # half a step, plus fp16 rounding of step and minimum
+    codes = np.concatenate([q41[4:] & 15, q41[4:] >> 4])
+    assert codes.min() == 0 and codes.max() == 15 and np.all(np.diff(codes[:16]) >= 0)
+    # a constant block: zero step, every code 0, the minimum carries the value
+    const = oracle.requantize_q4_1(ol.Q8_0, oracle.quantize(ol.Q8_0, np.full(32, 0.5, np.float32)))
+    assert np.all(const[4:] == 0) and const[0] == 0 and const[1] == 0
+    assert np.allclose(oracle.dequantize(ol.Q4_1, const), 0.5, rtol=1e-3)
+    # random tensors in every source format
+    rng = np.random.default_rng(5)
+    for t in (ol.Q4_K, ol.Q6_K, ol.Q8_0, ol.Q4_0, ol.Q5_K, ol.IQ4_NL):
+        rows, cols = 16, 1024
+        blocks = oracle.quantize(t, rng.normal(0, 0.02, rows * cols).astype(np.float32)) if t in (ol.Q4_K, ol.Q6_K, ol.Q8_0, ol.Q4_0) else ol.random_blocks(t, rows * cols // ol.GEOMETRY[t][0], rng)
+        w = oracle.dequantize(t, blocks).astype(np.float64)
+        t4, b4 = oracle.int4_blocks(t, blocks)
+        assert t4 == ol.Q4_1 and b4.size == rows * cols // 32 * 20
+        w4 = oracle.dequantize(ol.Q4_1, b4).astype(np.float64)
+        g = w.reshape(-1, 32)
+        step = (g.max(axis=1) - g.min(axis=1)) / 15
+        bound = 0.51 * step + 2.0 ** -10 * (np.abs(g).max(axis=1) + 15 * step) + 2.0 ** -23
+        assert np.all(np.abs(w4.reshape(-1, 32) - g) <= bound[:, None])
+        # the int dot: q8_d * (d * dot + m * sum), slice by slice
+        x = rng.normal(size=cols).astype(np.float32)
+        y = oracle.matvec(ol.Q4_1, b4, rows, cols, x, ol.INT8, 32)
+        recs = oracle.activation_records(x, 32)
+        xq = (recs[:, 4:].view(np.int8).astype(np.float64) * recs[:, :4].copy().view(np.float32).astype(np.float64)).reshape(-1)
+        exact = w4.reshape(rows, cols) @ xq
+        assert np.max(np.abs(y - exact)) <= 2e-5 * np.max(np.abs(exact))
+    assert oracle.int4_blocks(ol.Q4_1, np.zeros(20, np.uint8))[0] == ol.Q4_1
