@@ -727,10 +727,13 @@ def run_sharded_configs(ctx, rq, torch, dist, rank, world, device, steps):
         ex = rq.Exchange(ctx, rank, world, hidden * tokens * 4)
         ex.connect(share(ex.ipc_handle()))
 
+        weights = torch.empty_like(scores)
+
         def compute():
-            routing = ctx.moe_route(scores, top)
-            ctx.moe_forward(bank, xm, routing, top, include_shared=(rank == 0), y=part)  # the whole routing plane: a rank reads its experts' rows
-            return routing
+            # router scores -> routing weights -> this rank's experts, one call (routing and planning share a launch); the whole
+            # routing plane is computed on every rank (the router is replicated) and a rank reads its experts' rows of it
+            ctx.moe_route_forward(bank, scores, xm, top, include_shared=(rank == 0), weights=weights, y=part)
+            return weights
 
         def moe_step():
             compute()

@@ -181,11 +181,17 @@ int rq_add(rq_ctx* ctx, const float* a, const float* b, int64_t n, float* y, voi
 int rq_softcap(rq_ctx* ctx, const float* x, int64_t n, double cap, float* y, void* stream);
 
 /* The batched product (prefill, multi-sequence decode): the same contraction as rq_matvec for many
- * tokens. With RQ_ACT_FLOAT the weights are dequantised a tile at a time into shared memory and
- * multiplied on the tensor cores (tcgen05.mma, fp16 hi + lo operand pairs, fp32 accumulation in
- * tensor memory); with RQ_ACT_INT8 the exact integer dots of the matvec kernels run, four tokens a
- * pass. Replaces contraction_forward_body's position loop and contraction_forward_gemm_body
- * (amd-nv-cpu.ll:1231-2241, :3509-3649). Same arguments as rq_matvec. */
+ * tokens, on the tensor cores (tcgen05.mma, fp32 accumulation in tensor memory) where a kernel serves
+ * the case. Q4_K / Q6_K weights: exact-integer weight operands, activations as fp16 hi + lo pairs,
+ * for RQ_ACT_FLOAT and for RQ_ACT_INT8 windows of twelve and more positions (the int8 answer is the
+ * product over the records' code * step). Q8_0 / Q4_0 with RQ_ACT_FLOAT: weights dequantised a tile at
+ * a time, both operands as hi + lo pairs. Everything else (shorter int8 windows, int8 over the 32-value
+ * formats, the decode-only formats) runs the matvec kernels. Replaces contraction_forward_body's
+ * position loop and contraction_forward_gemm_body (amd-nv-cpu.ll:1231-2241, :3509-3649). Same
+ * arguments as rq_matvec.
+ * Range on the tensor-core routes: operands pass through fp16, so an activation of magnitude above
+ * 65504 overflows (the result row is inf / NaN) and one below 6e-8 counts as zero; on the Q8_0 / Q4_0
+ * route a dequantised weight of magnitude 256 or more overflows as well. rq_matvec has no such limit. */
 int rq_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens,
               float* y, int64_t y_n_stride, int64_t y_t_stride, int act_mode, int step, void* stream);
 
@@ -269,6 +275,14 @@ int64_t rq_moe_bytes(const rq_moe* moe);
 int rq_moe_forward(rq_ctx* ctx, rq_moe* moe, const float* x, int64_t x_k_stride, int64_t x_t_stride, const float* routing,
                    int64_t routing_e_stride, int64_t routing_t_stride, int top_k, int tokens, int include_shared, float* y,
                    int64_t y_n_stride, int64_t y_t_stride, void* stream);
+/* rq_moe_route followed by rq_moe_forward over the same tokens, as one call: the block's router -> TopK -> experts chain
+ * (lower_gguf_moe, recipe.rs:23415-23459) with one launch less, the CTA that routes a token also writing its plan. `weights`
+ * receives the dense routing plane exactly as rq_moe_route writes it (the bank's whole expert count gives its height); the
+ * remaining arguments are those of the two calls. */
+int rq_moe_route_forward(rq_ctx* ctx, rq_moe* moe, const float* scores, int64_t score_e_stride, int64_t score_t_stride, int top_k, int scoring,
+                         int renormalize, const float* selection_bias, float* weights, int64_t weight_e_stride, int64_t weight_t_stride, const float* x,
+                         int64_t x_k_stride, int64_t x_t_stride, int tokens, int include_shared, float* y, int64_t y_n_stride, int64_t y_t_stride,
+                         void* stream);
 
 /* ---- recorded sequences: one boundary crossing per step ------------------------------------------ */
 

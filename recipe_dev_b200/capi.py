@@ -83,6 +83,7 @@ def _declare(lib) -> None:
         "rq_moe_attach_shared": (i32, [p, p, i32, i32, p, p, p, f32p]),
         "rq_moe_bytes": (i64, [p]),
         "rq_moe_forward": (i32, [p, p, f32p, i64, i64, f32p, i64, i64, i32, i32, i32, f32p, i64, i64, p]),
+        "rq_moe_route_forward": (i32, [p, p, f32p, i64, i64, i32, i32, i32, f32p, f32p, i64, i64, f32p, i64, i64, i32, i32, f32p, i64, i64, p]),
         "rq_device_alloc": (i32, [p, i64, C.POINTER(p)]),
         "rq_device_free": (None, [p, p]),
         "rq_sequence_begin": (i32, [p, C.POINTER(p)]),
@@ -502,6 +503,21 @@ class Context:
         _check(self.lib.rq_moe_forward(self.handle, bank.handle, _ptr(x), x.stride(0), x.stride(1), _ptr(routing), routing.stride(0), routing.stride(1),
                                        top_k, tokens, int(include_shared), _ptr(y), y.stride(0), y.stride(1), _stream(stream)))
         return y
+
+    def moe_route_forward(self, bank: "MoeBank", scores, x, top_k: int, scoring: int = SCORE_SOFTMAX, renormalize: bool = True, bias=None, include_shared: bool = True,
+                          weights=None, y=None, stream=None):
+        """moe_route + moe_forward as one call (three launches instead of four). scores: [experts, tokens]; returns (y, weights)."""
+        import torch
+
+        hidden, tokens = x.shape
+        if y is None:
+            y = torch.empty((hidden, tokens), dtype=torch.float32, device=x.device)
+        if weights is None:
+            weights = torch.empty_like(scores)
+        _check(self.lib.rq_moe_route_forward(self.handle, bank.handle, _ptr(scores), scores.stride(0), scores.stride(1), top_k, scoring, int(renormalize),
+                                             _ptr(bias), _ptr(weights), weights.stride(0), weights.stride(1), _ptr(x), x.stride(0),
+                                             x.stride(1), tokens, int(include_shared), _ptr(y), y.stride(0), y.stride(1), _stream(stream)))
+        return y, weights
 
     def activation_records(self, x, step: int, stream=None):
         """The 36-byte int8 records of x ([cols] or [tokens, cols]) as a uint8 CUDA tensor."""

@@ -1605,13 +1605,15 @@ static void row_layout(int ipr, int* group, int* chunks) {
 }
 
 template <int TYPE, int MODE, int NW>
-int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s) {
+int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s, bool one_per_sm = false) {
     // Two CTAs share an SM (eight consumer warps and about 100 KB each): their barriers and waits
     // interleave, and when a CTA of one launch exits, a CTA of the next launch (programmatic
     // dependent launch) takes its place and prefetches weights while the other is still working.
-    constexpr int kCtasPerSm = NW == 5 ? 3 : 2;  // five consumer warps: three CTAs of six warps per SM
+    // five consumer warps: three CTAs of six warps per SM. one_per_sm: a single CTA with the whole SM's shared memory, for
+    // launches whose staged activations leave two CTAs no room for a ring (fp32 records of 14336 inputs are 62 KB).
+    const int kCtasPerSm = one_per_sm ? 1 : (NW == 5 ? 3 : 2);
     // dynamic; with the static tables (about 10 KB) and the 1 KB the system keeps per CTA, two (three) CTAs fit an SM's 228 KB
-    constexpr size_t kSmemBudget = NW == 5 ? 64 * 1024 : 102 * 1024;
+    const size_t kSmemBudget = one_per_sm ? 200 * 1024 : (NW == 5 ? 64 * 1024 : 102 * 1024);
     constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
     // NW = consumer warps: seven, so that with the producer warp a CTA is eight warps and two CTAs per SM leave each
     // thread 128 registers; eight (one CTA per SM then) only for rows too long for seven warps' worth of items.
@@ -1630,7 +1632,7 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     p.act_regs = (MODE == RQ_ACT_INT8 && t == 1 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr) ? 1 : 0;
     if (p.fuse_step && !p.act_regs) return RQ_ERR_UNSUPPORTED;  // the caller quantises with the standalone kernel instead
     if (p.act_regs) p.act_vectors = p.fuse_step ? 1 : 0;        // fused: one token's records are made in shared memory; else nothing is staged
-    if (p.act_bytes * p.act_vectors > 64 * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
+    if (p.act_bytes * p.act_vectors > (size_t)(one_per_sm ? 128 : 64) * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
     const int64_t row_bytes = (int64_t)p.units * p.unit_bytes;
     int ctas = sm_count * kCtasPerSm;
     if (p.plan_count > 1) { ctas /= p.plan_count; if (ctas < 1) ctas = 1; }  // the batch's grid rows share the GPU
@@ -1716,7 +1718,9 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
         if (chunks == 5 && p.tokens == 1 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN)
             return dispatch_stream_nw<TYPE, MODE, 5>(p, sm_count, vectors_per_launch, s);
     }
-    return dispatch_stream_nw<TYPE, MODE, 7>(p, sm_count, vectors_per_launch, s);
+    int rc = dispatch_stream_nw<TYPE, MODE, 7>(p, sm_count, vectors_per_launch, s);
+    if (rc == RQ_ERR_UNSUPPORTED) rc = dispatch_stream_nw<TYPE, MODE, 7>(p, sm_count, vectors_per_launch, s, true);
+    return rc;
 }
 
 }  // namespace

@@ -101,36 +101,42 @@ template <> struct RawKq<RQ_Q4_K> {
         q0 = *(const uint4*)(blk + 16 + 32 * pr);
         q1 = *(const uint4*)(blk + 32 + 32 * pr);
     }
-    // sc * q of sub-block 2 pr + half (low nibbles hold sub-block 2 pr, high nibbles 2 pr + 1)
+    // sc * (q - 8) of sub-block 2 pr + half (low nibbles hold sub-block 2 pr, high nibbles 2 pr + 1). The codes are centred
+    // (the eight goes into the minimum term, which becomes dmin * m - 8 * d * sc: an order of magnitude smaller than dmin * m
+    // for weights that are spread about zero), so the two sums that are subtracted at the end are small and what the tensor
+    // core's truncating accumulation loses of them is small too.
     __device__ __forceinline__ void decode(int kg, int half, uint4* hi, uint4*) const {
         int sc, mn;
         rq_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * (kg & 3) + half, sc, mn);
         const __half2 sc2 = __half2half2(__int2half_rn(sc));
-        const __half2 off2 = __half2half2(__float2half_rn(-1024.0f * (float)sc));  // at most 64512: exact
+        const __half2 k1032 = __half2half2(__float2half_rn(1032.0f));
         const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         const int shift = 4 * half;
         uint32_t o[16];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            // 0x6400 | n is the fp16 number 1024 + n; (1024 + q) * sc - 1024 * sc is exact inside the fused operation
+            // 0x6400 | n is the fp16 number 1024 + n; (1024 + q) - 1032 = q - 8 and (q - 8) * sc (at most 504) are both exact
             const uint32_t a = ((w[j] >> shift) & 0x000F000Fu) | 0x64006400u;        // inputs 4j, 4j + 2
             const uint32_t b = ((w[j] >> (shift + 8)) & 0x000F000Fu) | 0x64006400u;  // inputs 4j + 1, 4j + 3
-            o[2 * j] = as_u32(__hfma2(as_half2(a), sc2, off2));
-            o[2 * j + 1] = as_u32(__hfma2(as_half2(b), sc2, off2));
+            o[2 * j] = as_u32(__hmul2(__hsub2(as_half2(a), k1032), sc2));
+            o[2 * j + 1] = as_u32(__hmul2(__hsub2(as_half2(b), k1032), sc2));
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) hi[c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
     }
-    // dmin * m_g of the superblock's eight sub-blocks, times 2^8, as fp16 hi and lo
+    // dmin * m_g - 8 * d * sc_g of the superblock's eight sub-blocks (what is left of the minimum once the codes are centred),
+    // times 2^8, as fp16 hi and lo
     __device__ __forceinline__ void minimum_terms(uint4& hi, uint4& lo) const {
-        const float dmin = rq_h2f((uint16_t)(hdr.x >> 16));
+        const float dmin = rq_h2f((uint16_t)(hdr.x >> 16)), d8 = __fmul_rn(8.0f, rq_h2f((uint16_t)(hdr.x & 0xffff)));
         uint32_t hw[4], lw[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             int s0, m0, s1, m1;
             rq_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j, s0, m0);
             rq_q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j + 1, s1, m1);
-            const float a = __fmul_rn(__fmul_rn(dmin, (float)m0), kMinScale), b = __fmul_rn(__fmul_rn(dmin, (float)m1), kMinScale);
+            // both products are exact in fp32 (an fp16 times an integer below 64); their difference is rounded once
+            const float a = __fmul_rn(__fsub_rn(__fmul_rn(dmin, (float)m0), __fmul_rn(d8, (float)s0)), kMinScale);
+            const float b = __fmul_rn(__fsub_rn(__fmul_rn(dmin, (float)m1), __fmul_rn(d8, (float)s1)), kMinScale);
             const __half2 h2 = __floats2half2_rn(a, b);
             const float2 back = __half22float2(h2);
             const __half2 l2 = __floats2half2_rn(a - back.x, b - back.y);

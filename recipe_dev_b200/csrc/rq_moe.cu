@@ -133,9 +133,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch, int tid) {
     return m;
 }
 
-__global__ void __launch_bounds__(kRouteThreads) rq_route_kernel(const float* __restrict__ scores, int64_t se, int64_t st, int experts, int top,
-                                                                int sigmoid, int renorm, const float* __restrict__ bias,
-                                                                float* __restrict__ weights, int64_t we, int64_t wt) {
+__device__ __forceinline__ void route_token(const float* __restrict__ scores, int64_t se, int64_t st, int experts, int top, int sigmoid, int renorm,
+                                            const float* __restrict__ bias, float* __restrict__ weights, int64_t we, int64_t wt) {
     extern __shared__ float sm[];      // [experts] raw scores | [experts] values | [experts] keys | [experts] marks
     float* raw = sm;
     float* val = sm + experts;
@@ -253,6 +252,12 @@ __global__ void __launch_bounds__(kRouteThreads) rq_route_kernel(const float* __
     for (int e = tid; e < experts; e += kRouteThreads) weights[e * we + t * wt] = mark[e] ? __fdiv_rn(val[e], denom) : 0.0f;
 }
 
+__global__ void __launch_bounds__(kRouteThreads) rq_route_kernel(const float* __restrict__ scores, int64_t se, int64_t st, int experts, int top,
+                                                                int sigmoid, int renorm, const float* __restrict__ bias,
+                                                                float* __restrict__ weights, int64_t we, int64_t wt) {
+    route_token(scores, se, st, experts, top, sigmoid, renorm, bias, weights, we, wt);
+}
+
 // ---- planner: one CTA per token ------------------------------------------------------------
 struct BankView {
     int type, experts, expert_first, expert_count, hidden, ffn;
@@ -265,9 +270,9 @@ struct BankView {
     const float* sh_vector;
 };
 
-__global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const float* __restrict__ routing, int64_t re, int64_t rt,
-                                                         const float* __restrict__ x, int64_t sk, int64_t st, int top, int include_shared,
-                                                         RqPlan* __restrict__ plans, float* __restrict__ h, float* __restrict__ y, int64_t yn, int64_t yt) {
+__device__ __forceinline__ void plan_token(const BankView& b, const float* __restrict__ routing, int64_t re, int64_t rt, const float* __restrict__ x, int64_t sk,
+                                           int64_t st, int top, int include_shared, RqPlan* __restrict__ plans, float* __restrict__ h, float* __restrict__ y,
+                                           int64_t yn, int64_t yt) {
     const int t = blockIdx.x, tid = threadIdx.x;
     __shared__ float red[256];
     __shared__ float s_gate;
@@ -351,6 +356,25 @@ __global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const floa
     __syncthreads();
     if (pb->total_rows == 0)
         for (int r = tid; r < b.hidden; r += 256) y[r * yn + (int64_t)t * yt] = 0.0f;
+}
+
+__global__ void __launch_bounds__(256) rq_moe_plan_kernel(BankView b, const float* __restrict__ routing, int64_t re, int64_t rt,
+                                                         const float* __restrict__ x, int64_t sk, int64_t st, int top, int include_shared,
+                                                         RqPlan* __restrict__ plans, float* __restrict__ h, float* __restrict__ y, int64_t yn, int64_t yt) {
+    plan_token(b, routing, re, rt, x, sk, st, top, include_shared, plans, h, y, yn, yt);
+}
+
+// Routing and planning of a token in one launch: the CTA that computed the token's routing weights (and wrote them to the
+// dense plane, which stays the block's visible result) reads them back after a barrier and writes the token's two segment
+// tables. One launch and one dependency less on the path of a decode step.
+static_assert(kRouteThreads == 256, "the fused launch runs both bodies with the same CTA");
+__global__ void __launch_bounds__(256) rq_moe_route_plan_kernel(BankView b, const float* __restrict__ scores, int64_t se, int64_t sst, int experts, int top, int sigmoid,
+                                                               int renorm, const float* __restrict__ bias, float* __restrict__ weights, int64_t we, int64_t wt,
+                                                               const float* __restrict__ x, int64_t sk, int64_t st, int include_shared, RqPlan* __restrict__ plans,
+                                                               float* __restrict__ h, float* __restrict__ y, int64_t yn, int64_t yt) {
+    route_token(scores, se, sst, experts, top, sigmoid, renorm, bias, weights, we, wt);
+    __syncthreads();  // the CTA's own stores to the plane are visible to its threads after the barrier
+    plan_token(b, weights, we, wt, x, sk, st, top, include_shared, plans, h, y, yn, yt);
 }
 
 static BankView view_of(const rq_moe* m) {
@@ -548,24 +572,71 @@ extern "C" int rq_moe_route(rq_ctx* ctx, const float* scores, int64_t score_e_st
     return RQ_OK;
 }
 
+static int check_forward(const char* who, const rq_ctx* ctx, const rq_moe* m, const void* x, const void* routing, const void* y, int top_k, int tokens,
+                         int64_t x_k_stride, int64_t y_n_stride) {
+    if (!ctx || !m || !x || !routing || !y) return rq_fail(RQ_ERR_INVALID, "%s: null argument", who);
+    if (m->device != ctx->device) return rq_fail(RQ_ERR_INVALID, "%s: bank lives on device %d, context on %d", who, m->device, ctx->device);
+    if (tokens <= 0 || tokens > kMaxTokens) return rq_fail(RQ_ERR_LIMIT, "%s: tokens=%d, between 1 and %d per call", who, tokens, kMaxTokens);
+    const int shared_slots = m->has_shared ? m->sh_count : 1;
+    if (top_k <= 0 || top_k + shared_slots > RQ_MAX_SUB)
+        return rq_fail(RQ_ERR_LIMIT, "%s: top_k=%d with a shared expert of %d x the expert width: at most %d slots together", who, top_k, shared_slots, RQ_MAX_SUB);
+    if (x_k_stride <= 0 || y_n_stride <= 0) return rq_fail(RQ_ERR_INVALID, "%s: strides must be positive", who);
+    return RQ_OK;
+}
+
+static int launch_banks(rq_ctx* ctx, rq_moe* m, const float* x, int64_t x_k_stride, int64_t x_t_stride, int top_k, int tokens, int64_t y_n_stride, cudaStream_t s);
+
+// rq_moe_route and rq_moe_forward as one call: the routing weights land in `weights` as rq_moe_route writes them, and the
+// token's plan is made by the same launch (three launches per call instead of four).
+extern "C" int rq_moe_route_forward(rq_ctx* ctx, rq_moe* m, const float* scores, int64_t score_e_stride, int64_t score_t_stride, int top_k, int scoring,
+                                    int renormalize, const float* selection_bias, float* weights, int64_t weight_e_stride, int64_t weight_t_stride,
+                                    const float* x, int64_t x_k_stride, int64_t x_t_stride, int tokens, int include_shared, float* y, int64_t y_n_stride,
+                                    int64_t y_t_stride, void* stream) {
+    if (!scores) return rq_fail(RQ_ERR_INVALID, "rq_moe_route_forward: null argument");
+    int rc = check_forward("rq_moe_route_forward", ctx, m, x, weights, y, top_k, tokens, x_k_stride, y_n_stride);
+    if (rc) return rc;
+    const int experts = m->experts;
+    if (top_k > experts) return rq_fail(RQ_ERR_INVALID, "rq_moe_route_forward: top_k=%d of %d experts", top_k, experts);
+    if (experts > 8192) return rq_fail(RQ_ERR_LIMIT, "rq_moe_route_forward: %d experts, at most 8192", experts);
+    if (scoring != RQ_SCORE_SOFTMAX && scoring != RQ_SCORE_SIGMOID) return rq_fail(RQ_ERR_INVALID, "rq_moe_route_forward: scoring=%d", scoring);
+    DeviceGuard guard(ctx->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    rc = rq_order_work_areas(ctx, s);
+    if (rc) return rc;
+    if ((size_t)experts * 16 > 40 * 1024) {
+        static bool configured[64] = {};
+        int dev = ctx->device;
+        if (dev < 0 || dev >= 64 || !configured[dev]) {
+            RQ_CUDA(cudaFuncSetAttribute(rq_moe_route_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8192 * 16));
+            if (dev >= 0 && dev < 64) configured[dev] = true;
+        }
+    }
+    rq_moe_route_plan_kernel<<<tokens, 256, (size_t)experts * 16, s>>>(view_of(m), scores, score_e_stride, score_t_stride, experts, top_k, scoring, renormalize,
+                                                                       selection_bias, weights, weight_e_stride, weight_t_stride, x, x_k_stride, x_t_stride,
+                                                                       include_shared, m->plans, m->h, y, y_n_stride, y_t_stride);
+    RQ_CUDA(cudaGetLastError());
+    return launch_banks(ctx, m, x, x_k_stride, x_t_stride, top_k, tokens, y_n_stride, s);
+}
+
 extern "C" int rq_moe_forward(rq_ctx* ctx, rq_moe* m, const float* x, int64_t x_k_stride, int64_t x_t_stride, const float* routing,
                               int64_t routing_e_stride, int64_t routing_t_stride, int top_k, int tokens, int include_shared, float* y,
                               int64_t y_n_stride, int64_t y_t_stride, void* stream) {
-    if (!ctx || !m || !x || !routing || !y) return rq_fail(RQ_ERR_INVALID, "rq_moe_forward: null argument");
-    if (m->device != ctx->device) return rq_fail(RQ_ERR_INVALID, "rq_moe_forward: bank lives on device %d, context on %d", m->device, ctx->device);
-    if (tokens <= 0 || tokens > kMaxTokens) return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: tokens=%d, between 1 and %d per call", tokens, kMaxTokens);
-    const int shared_slots = m->has_shared ? m->sh_count : 1;
-    if (top_k <= 0 || top_k + shared_slots > RQ_MAX_SUB)
-        return rq_fail(RQ_ERR_LIMIT, "rq_moe_forward: top_k=%d with a shared expert of %d x the expert width: at most %d slots together", top_k, shared_slots, RQ_MAX_SUB);
-    if (x_k_stride <= 0 || y_n_stride <= 0) return rq_fail(RQ_ERR_INVALID, "rq_moe_forward: strides must be positive");
+    int rc = check_forward("rq_moe_forward", ctx, m, x, routing, y, top_k, tokens, x_k_stride, y_n_stride);
+    if (rc) return rc;
     DeviceGuard guard(ctx->device);
     cudaStream_t s = (cudaStream_t)stream;
-    int rc = rq_order_work_areas(ctx, s);  // the bank's plans and hidden activations are shared by every call on it
+    rc = rq_order_work_areas(ctx, s);  // the bank's plans and hidden activations are shared by every call on it
     if (rc) return rc;
-    const int slots = top_k + shared_slots;
     rq_moe_plan_kernel<<<tokens, 256, 0, s>>>(view_of(m), routing, routing_e_stride, routing_t_stride, x, x_k_stride, x_t_stride, top_k, include_shared,
                                               m->plans, m->h, y, y_n_stride, y_t_stride);
     RQ_CUDA(cudaGetLastError());
+    return launch_banks(ctx, m, x, x_k_stride, x_t_stride, top_k, tokens, y_n_stride, s);
+}
+
+static int launch_banks(rq_ctx* ctx, rq_moe* m, const float* x, int64_t x_k_stride, int64_t x_t_stride, int top_k, int tokens, int64_t y_n_stride, cudaStream_t s) {
+    const int shared_slots = m->has_shared ? m->sh_count : 1;
+    const int slots = top_k + shared_slots;
+    int rc;
     // All tokens in two launches: grid row t of each reads token t's plan and activations.
     // expert gate and up rows against the token's x, h = silu(g) * u per slot
     rc = rq_launch_stream_plan(ctx, m->type, m->hidden, m->plans, tokens, 2, slots, 2, RQ_EPI_GLU, (int64_t)slots * m->ffn, x, x_t_stride, x_k_stride, 0,

@@ -67,6 +67,14 @@ def test_moe_forward_parity(rq_ctx, oracle, t, experts, top, hidden, ffn, tokens
     want_r = oracle.moe_forward(t, gate, up, down, experts, top, hidden, ffn, x, routing, shared=None)
     got_r = rq_ctx.moe_forward(bank, cuda(x), routing_d, top, include_shared=False).cpu().numpy()
     assert rel_err(got_r, want_r) <= TOL
+    # routing and the bank as one call: the same weights plane and the same output bits as the two calls
+    for scoring, renorm in ((0, True), (1, False)):
+        routing_2 = rq_ctx.moe_route(cuda(scores), top, scoring, renorm)
+        two = rq_ctx.moe_forward(bank, cuda(x), routing_2, top).cpu().numpy()
+        one, weights = rq_ctx.moe_route_forward(bank, cuda(scores), cuda(x), top, scoring, renorm)
+        assert np.array_equal(weights.cpu().numpy().view(np.uint32), routing_2.cpu().numpy().view(np.uint32))
+        assert np.array_equal(one.cpu().numpy().view(np.uint32), two.view(np.uint32))
+    rq_ctx.check()
 
 
 def test_moe_expert_parallel_split_adds_up(rq_ctx, oracle):

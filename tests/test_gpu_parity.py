@@ -185,7 +185,7 @@ def test_argument_validation(rq_ctx, oracle):
     lib = rq_ctx.lib
     blocks = oracle.quantize(ol.Q4_K, oracle.normal(10, 0, 4 * 256, 0.02))
     out = ctypes.c_void_p()
-    assert lib.rq_weight_prepare(rq_ctx.handle, 13, blocks.ctypes.data, 4, 256, 0, 4, ctypes.byref(out)) == -1
+    assert lib.rq_weight_prepare(rq_ctx.handle, 15, blocks.ctypes.data, 4, 256, 0, 4, ctypes.byref(out)) == -1  # Q8_K: not a format of this path
     assert lib.rq_weight_prepare(rq_ctx.handle, ol.Q4_K, blocks.ctypes.data, 4, 250, 0, 4, ctypes.byref(out)) == -1
     assert b"multiple" in lib.rq_last_error()
     assert lib.rq_weight_prepare(rq_ctx.handle, ol.Q4_K, blocks.ctypes.data, 4, 256, 2, 3, ctypes.byref(out)) == -1
@@ -292,6 +292,9 @@ EDGE_SHAPES = [
     (ol.Q4_K, 1, 256), (ol.Q4_K, 3, 512), (ol.Q4_K, 29, 1024), (ol.Q6_K, 57, 2048), (ol.Q4_K, 15, 4096), (ol.Q4_K, 113, 4096),
     (ol.Q6_K, 5, 14336), (ol.Q4_K, 2, 7168), (ol.Q6_K, 41, 5120), (ol.Q4_K, 9, 1280), (ol.Q6_K, 8, 2560), (ol.Q4_K, 3, 32768),
     (ol.Q4_K, 6, 8192), (ol.Q8_0, 23, 4096), (ol.Q4_0, 31, 2560), (ol.Q8_0, 2, 14336), (ol.Q4_K, 300, 768), (ol.Q6_K, 1, 3072),
+    # wide rows with enough of them for several ring stages per CTA: the fp32 records of 14336 inputs (62 KB) leave two CTAs per
+    # SM no room for a ring, so these launches run one CTA per SM
+    (ol.Q6_K, 700, 14336), (ol.Q4_K, 450, 14336),
 ]
 
 
