@@ -42,13 +42,14 @@ enum rq_status {
 
 /* GGML tensor types on this path (recipe.rs:9925-9962). */
 enum { RQ_Q4_0 = 2, RQ_Q8_0 = 8, RQ_Q4_K = 12, RQ_Q6_K = 14,
-       /* The other stored formats the same bodies serve (recipe.rs:15812-15823): bound, decoded bit-exactly (rq_dequant,
+       /* The other stored formats the same bodies serve (recipe.rs:15812-15824; the IQ1 / IQ2 / IQ3 grid formats are not among them): bound, decoded bit-exactly (rq_dequant,
         * rq_gather_rows), dotted with fp32 activations (RQ_ACT_FLOAT: the run decoders, recipe.rs:7826-7917) and re-encoded
         * to Q8_0 by rq_weight_requantize, which is what `.int(8)` does to them at load (recipe.rs:22345-22369). They have
         * no int8 dot here (Q4_1 excepted: it is the storage of int4 sums and RQ_ACT_INT8 over it is what `.int(4)` runs), so
         * RQ_ACT_INT8 on the others returns RQ_ERR_UNSUPPORTED and names the re-encode; rq_quantize (no encoder) and expert
         * banks do not take them. */
-       RQ_Q4_1 = 3, RQ_Q5_0 = 6, RQ_Q5_1 = 7, RQ_Q5_K = 13, RQ_IQ4_NL = 20 };
+       RQ_Q4_1 = 3, RQ_Q5_0 = 6, RQ_Q5_1 = 7, RQ_Q5_K = 13, RQ_IQ4_NL = 20,
+       RQ_Q8_1 = 9, RQ_Q2_K = 10, RQ_Q3_K = 11, RQ_Q8_K = 15, RQ_IQ4_XS = 23 };
 
 /* Activation handling, what `.fp(32)` / `.int(8)` select (recipe.rs:14027-14054, :22326-22369):
  * FLOAT keeps the activations as they are (run decoders, recipe.rs:7826-7917);

@@ -18,8 +18,8 @@
 /* recipe.rs:15811-15822: block / stride of the four formats on the path. */
 int rqo_block_values(int type) {
     switch (type) {
-        case RQO_Q4_0: case RQO_Q8_0: case RQO_Q4_1: case RQO_Q5_0: case RQO_Q5_1: case RQO_IQ4_NL: return 32;
-        case RQO_Q4_K: case RQO_Q6_K: case RQO_Q5_K: return 256;
+        case RQO_Q4_0: case RQO_Q8_0: case RQO_Q4_1: case RQO_Q5_0: case RQO_Q5_1: case RQO_IQ4_NL: case RQO_Q8_1: return 32;
+        case RQO_Q4_K: case RQO_Q6_K: case RQO_Q5_K: case RQO_Q2_K: case RQO_Q3_K: case RQO_Q8_K: case RQO_IQ4_XS: return 256;
         default: return 0;
     }
 }
@@ -34,6 +34,11 @@ int rqo_block_bytes(int type) {
         case RQO_Q5_1: return 24;
         case RQO_Q5_K: return 176;
         case RQO_IQ4_NL: return 18;
+        case RQO_Q8_1: return 36;
+        case RQO_Q2_K: return 84;
+        case RQO_Q3_K: return 110;
+        case RQO_Q8_K: return 292;
+        case RQO_IQ4_XS: return 136;
         default: return 0;
     }
 }
@@ -198,6 +203,51 @@ static inline float iq4nl_value(const uint8_t* b, int i) {
     return scaled * (float)IQ4_LEVELS[code];
 }
 
+/* recipe.rs:3782-3833, man 8 variant 1 (Q8_1): header d, s; the code times d (the stored sum s is not part of a value). */
+static inline float q81_value(const uint8_t* b, int i) { return (float)(int8_t)b[4 + i] * half_at(b); }
+/* recipe.rs:3835-3866: sixteen (scale | minimum << 4) bytes, 64 bytes of two-bit codes, d @80, dmin @82. Group `order` of
+ * sixteen values reads metadata byte `order`; its codes sit in byte 16 + 32 (order / 8) + 16 (order % 2) + i % 16 at bit
+ * 2 ((order % 8) / 2). */
+static inline float q2k_value(const uint8_t* b, int i) {
+    int order = i / 16, section = order / 8, shift = 2 * ((order % 8) / 2), half_index = order % 2;
+    uint8_t metadata = b[section * 8 + shift + half_index];
+    int code = (b[16 + section * 32 + half_index * 16 + i % 16] >> shift) & 3;
+    float scaled = half_at(b + 80) * (float)(metadata & 15);
+    float product = scaled * (float)code;
+    float minimum = half_at(b + 82) * (float)(metadata >> 4);
+    return product - minimum;
+}
+/* recipe.rs:3868-3907: high-bit mask 0..31, two-bit codes 32..95, twelve scale bytes 96..107 (four low bits per group in
+ * bytes 96..103, two high bits in bytes 104..107), d @108. A clear mask bit subtracts four from the code. */
+static inline float q3k_value(const uint8_t* b, int i) {
+    int block = i / 16;
+    int low = (b[96 + (block < 8 ? block : block - 8)] >> (block < 8 ? 0 : 4)) & 15;
+    int high = (b[104 + block % 4] >> ((block / 4) * 2)) & 3;
+    int scale_code = (low | (high << 4)) - 32;
+    int code = (b[32 + (i / 128) * 32 + i % 32] >> (((i % 128) / 32) * 2)) & 3;
+    int sign = (b[i % 32] >> (i / 32)) & 1;
+    code -= sign ? 0 : 4;
+    float scaled = half_at(b + 108) * (float)scale_code;
+    return scaled * (float)code;
+}
+/* recipe.rs:3909-3917: an fp32 step, 256 int8 codes from byte 4 (the sixteen partial sums after them are not part of a value). */
+static inline float q8k_value(const uint8_t* b, int i) {
+    float d;
+    memcpy(&d, b, 4);
+    return d * (float)(int8_t)b[4 + i];
+}
+/* recipe.rs:3919-3958 with a six-bit exponent per 32 values (xs = true): two high bits from the u16 @2, four low bits
+ * from bytes 4..7, less 32; (d * exponent) * IQ4[nibble], nibbles from byte 8. */
+static inline float iq4xs_value(const uint8_t* b, int i) {
+    int block = i / 32;
+    int high = ((b[2] | (b[3] << 8)) >> (2 * block)) & 3;
+    int low = (b[4 + block / 2] >> ((block % 2) * 4)) & 15;
+    int exponent = (low | (high << 4)) - 32;
+    int code = (b[8 + block * 16 + i % 16] >> (i % 32 < 16 ? 0 : 4)) & 15;
+    float scaled = half_at(b) * (float)exponent;
+    return scaled * (float)IQ4_LEVELS[code];
+}
+
 static inline float block_value(int type, const uint8_t* b, int i) {
     switch (type) {
         case RQO_Q4_0: return q40_value(b, i);
@@ -208,6 +258,11 @@ static inline float block_value(int type, const uint8_t* b, int i) {
         case RQO_Q5_1: return q51_value(b, i);
         case RQO_Q5_K: return q5k_value(b, i);
         case RQO_IQ4_NL: return iq4nl_value(b, i);
+        case RQO_Q8_1: return q81_value(b, i);
+        case RQO_Q2_K: return q2k_value(b, i);
+        case RQO_Q3_K: return q3k_value(b, i);
+        case RQO_Q8_K: return q8k_value(b, i);
+        case RQO_IQ4_XS: return iq4xs_value(b, i);
         default: return q6k_value(b, i);
     }
 }

@@ -36,6 +36,11 @@ extern "C" {
 #define RQO_Q5_1 7
 #define RQO_Q5_K 13
 #define RQO_IQ4_NL 20
+#define RQO_Q8_1 9
+#define RQO_Q2_K 10
+#define RQO_Q3_K 11
+#define RQO_Q8_K 15
+#define RQO_IQ4_XS 23
 
 /* activation handling, as a layer gets it from its precision (recipe.rs:22326-22369) */
 #define RQO_ACT_FLOAT_RUN 0   /* packed bodies + run decoders: recipe.rs:7826-7917, ll:3136-3508 */
@@ -43,7 +48,7 @@ extern "C" {
 #define RQO_ACT_INT8 2        /* int8 records: ll:1381-1517 and the slice/block dots */
 
 int rqo_block_values(int type);  /* 32 or 256, 0 if unknown */
-int rqo_block_bytes(int type);   /* 18, 34, 144, 210; 20, 22, 24, 176, 18 */
+int rqo_block_bytes(int type);   /* 18, 34, 144, 210; 20, 22, 24, 176, 18; 36, 84, 110, 292, 136 */
 
 uint16_t rqo_fp16(float value);      /* recipe.rs:15098-15112 */
 float rqo_unfp16(uint16_t value);    /* recipe.rs:15114-15126 */

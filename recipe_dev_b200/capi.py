@@ -13,6 +13,7 @@ import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
 Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL = 3, 6, 7, 13, 20  # bound, decoded, dotted with fp32 activations, re-encoded under int8
+Q8_1, Q2_K, Q3_K, Q8_K, IQ4_XS = 9, 10, 11, 15, 23  # the same
 ACT_FLOAT, ACT_INT8 = 0, 1
 SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
 

@@ -22,8 +22,8 @@ extern "C" const char* rq_last_error(void) { return g_error; }
 
 extern "C" int rq_block_values(int t) {
     switch (t) {
-        case RQ_Q4_0: case RQ_Q8_0: case RQ_Q4_1: case RQ_Q5_0: case RQ_Q5_1: case RQ_IQ4_NL: return 32;
-        case RQ_Q4_K: case RQ_Q6_K: case RQ_Q5_K: return 256;
+        case RQ_Q4_0: case RQ_Q8_0: case RQ_Q4_1: case RQ_Q5_0: case RQ_Q5_1: case RQ_IQ4_NL: case RQ_Q8_1: return 32;
+        case RQ_Q4_K: case RQ_Q6_K: case RQ_Q5_K: case RQ_Q2_K: case RQ_Q3_K: case RQ_Q8_K: case RQ_IQ4_XS: return 256;
         default: return 0;
     }
 }
@@ -38,6 +38,11 @@ extern "C" int rq_block_bytes(int t) {
         case RQ_Q5_1: return 24;
         case RQ_Q5_K: return 176;
         case RQ_IQ4_NL: return 18;
+        case RQ_Q8_1: return 36;
+        case RQ_Q2_K: return 84;
+        case RQ_Q3_K: return 110;
+        case RQ_Q8_K: return 292;
+        case RQ_IQ4_XS: return 136;
         default: return 0;
     }
 }
@@ -220,7 +225,7 @@ extern "C" int rq_wait_selftest(rq_ctx* ctx, void* stream) {
 
 static int check_shape(const char* who, int type, int64_t rows, int64_t cols) {
     int per = rq_block_values(type);
-    if (!per) return rq_fail(RQ_ERR_INVALID, "%s: GGML type %d is not one of Q4_0(2) Q4_1(3) Q5_0(6) Q5_1(7) Q8_0(8) Q4_K(12) Q5_K(13) Q6_K(14) IQ4_NL(20)", who, type);
+    if (!per) return rq_fail(RQ_ERR_INVALID, "%s: GGML type %d is not one of Q4_0(2) Q4_1(3) Q5_0(6) Q5_1(7) Q8_0(8) Q8_1(9) Q2_K(10) Q3_K(11) Q4_K(12) Q5_K(13) Q6_K(14) Q8_K(15) IQ4_NL(20) IQ4_XS(23)", who, type);
     if (rows <= 0 || cols <= 0) return rq_fail(RQ_ERR_INVALID, "%s: rows=%lld cols=%lld must be positive", who, (long long)rows, (long long)cols);
     if (cols % per) return rq_fail(RQ_ERR_INVALID, "%s: cols=%lld is not a multiple of the %d-value block", who, (long long)cols, per);
     if (cols > (int64_t)1 << 24 || rows > (int64_t)1 << 31) return rq_fail(RQ_ERR_LIMIT, "%s: shape %lld x %lld beyond the supported range", who, (long long)rows, (long long)cols);

@@ -92,11 +92,9 @@ int launch_generic(const rq_weight* w, const float* x, int64_t sk, int64_t st, i
 int rq_launch_gemv_generic(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk, int64_t st, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s) {
     if (tokens > 65535) return rq_fail(RQ_ERR_LIMIT, "matvec: %d tokens over a %d-type weight, at most 65535 per call", tokens, w->type);
     switch (w->type) {
-        case RQ_Q4_1: return launch_generic<RQ_Q4_1>(w, x, sk, st, tokens, y, yn, yt, ctx->sm_count, s);
-        case RQ_Q5_0: return launch_generic<RQ_Q5_0>(w, x, sk, st, tokens, y, yn, yt, ctx->sm_count, s);
-        case RQ_Q5_1: return launch_generic<RQ_Q5_1>(w, x, sk, st, tokens, y, yn, yt, ctx->sm_count, s);
-        case RQ_Q5_K: return launch_generic<RQ_Q5_K>(w, x, sk, st, tokens, y, yn, yt, ctx->sm_count, s);
-        case RQ_IQ4_NL: return launch_generic<RQ_IQ4_NL>(w, x, sk, st, tokens, y, yn, yt, ctx->sm_count, s);
+#define RQ_CASE(T) case T: return launch_generic<T>(w, x, sk, st, tokens, y, yn, yt, ctx->sm_count, s);
+        RQ_DECODE_ONLY_TYPES(RQ_CASE)
+#undef RQ_CASE
         default: return rq_fail(RQ_ERR_INVALID, "matvec: type %d", w->type);
     }
 }

@@ -167,9 +167,12 @@ __device__ __forceinline__ float rq_h2f(uint16_t h) { return __half2float(__usho
 // its unit index. In shared memory a thread's unit starts at a multiple of 128 bytes, so eight threads on adjacent
 // units reading the same logical chunk would otherwise all hit one 16-byte bank group; permuted, they hit eight.
 // The map is its own inverse. Rows that are not whole units (the tiled kernel's) are stored as they come.
+// every format that is served by per-value decode alone, for switch statements over kernels templated on the type
+#define RQ_DECODE_ONLY_TYPES(X) X(RQ_Q4_1) X(RQ_Q5_0) X(RQ_Q5_1) X(RQ_Q5_K) X(RQ_IQ4_NL) X(RQ_Q8_1) X(RQ_Q2_K) X(RQ_Q3_K) X(RQ_Q8_K) X(RQ_IQ4_XS)
 // Q4_K and the formats served by per-value decode alone stay in HBM as their GGUF blocks (one plane, no scale plane)
 __host__ __device__ __forceinline__ bool rq_type_keeps_blocks(int type) {
-    return type == RQ_Q4_K || type == RQ_Q4_1 || type == RQ_Q5_0 || type == RQ_Q5_1 || type == RQ_Q5_K || type == RQ_IQ4_NL;
+    return type == RQ_Q4_K || type == RQ_Q4_1 || type == RQ_Q5_0 || type == RQ_Q5_1 || type == RQ_Q5_K || type == RQ_IQ4_NL || type == RQ_Q8_1 || type == RQ_Q2_K ||
+           type == RQ_Q3_K || type == RQ_Q8_K || type == RQ_IQ4_XS;
 }
 // the formats with streaming / tensor-core kernels and int8 slice dots of their own; the rest go through rq_gemv_generic.cu
 __host__ __device__ __forceinline__ bool rq_type_has_fast_path(int type) { return type == RQ_Q4_0 || type == RQ_Q8_0 || type == RQ_Q4_K || type == RQ_Q6_K; }

@@ -80,11 +80,9 @@ int rq_launch_dequant(const rq_weight* w, float* out, cudaStream_t s) {
         case RQ_Q6_K: rq_dequant_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
         case RQ_Q8_0: rq_dequant_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
         case RQ_Q4_0: rq_dequant_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
-        case RQ_Q4_1: rq_dequant_kernel<RQ_Q4_1><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
-        case RQ_Q5_0: rq_dequant_kernel<RQ_Q5_0><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
-        case RQ_Q5_1: rq_dequant_kernel<RQ_Q5_1><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
-        case RQ_Q5_K: rq_dequant_kernel<RQ_Q5_K><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
-        case RQ_IQ4_NL: rq_dequant_kernel<RQ_IQ4_NL><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+#define RQ_CASE(T) case T: rq_dequant_kernel<T><<<grid, threads, 0, s>>>(w->main, w->scale, out, count, w->cols); break;
+        RQ_DECODE_ONLY_TYPES(RQ_CASE)
+#undef RQ_CASE
         default: return rq_fail(RQ_ERR_INVALID, "dequant: type %d", w->type);
     }
     RQ_CUDA(cudaGetLastError());
@@ -118,11 +116,9 @@ int rq_launch_gather(const rq_weight* w, const int32_t* ids, int tokens, float* 
         case RQ_Q6_K: rq_gather_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
         case RQ_Q8_0: rq_gather_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
         case RQ_Q4_0: rq_gather_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
-        case RQ_Q4_1: rq_gather_kernel<RQ_Q4_1><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
-        case RQ_Q5_0: rq_gather_kernel<RQ_Q5_0><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
-        case RQ_Q5_1: rq_gather_kernel<RQ_Q5_1><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
-        case RQ_Q5_K: rq_gather_kernel<RQ_Q5_K><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
-        case RQ_IQ4_NL: rq_gather_kernel<RQ_IQ4_NL><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+#define RQ_CASE(T) case T: rq_gather_kernel<T><<<grid, threads, 0, s>>>(w->main, w->scale, w->rows, w->cols, ids, tokens, y, yn, yt); break;
+        RQ_DECODE_ONLY_TYPES(RQ_CASE)
+#undef RQ_CASE
         default: return rq_fail(RQ_ERR_INVALID, "gather: type %d", w->type);
     }
     RQ_CUDA(cudaGetLastError());

@@ -101,7 +101,7 @@ int rq_launch_requant_q4_1(const rq_weight* src, rq_weight* dst, cudaStream_t s)
     const int grid = (int)(want < 148 * 32 ? (want < 1 ? 1 : want) : 148 * 32);
     switch (src->type) {
 #define RQ_CASE(T) case T: rq_requant_q4_1_kernel<T><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main); break;
-        RQ_CASE(RQ_Q4_K) RQ_CASE(RQ_Q6_K) RQ_CASE(RQ_Q8_0) RQ_CASE(RQ_Q4_0) RQ_CASE(RQ_Q4_1) RQ_CASE(RQ_Q5_0) RQ_CASE(RQ_Q5_1) RQ_CASE(RQ_Q5_K) RQ_CASE(RQ_IQ4_NL)
+        RQ_CASE(RQ_Q4_K) RQ_CASE(RQ_Q6_K) RQ_CASE(RQ_Q8_0) RQ_CASE(RQ_Q4_0) RQ_DECODE_ONLY_TYPES(RQ_CASE)
 #undef RQ_CASE
         default: return rq_fail(RQ_ERR_INVALID, "requantize: source type %d", src->type);
     }
@@ -119,11 +119,9 @@ int rq_launch_requant_q8_0(const rq_weight* src, rq_weight* dst, cudaStream_t s)
         case RQ_Q6_K: rq_requant_q8_0_kernel<RQ_Q6_K><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
         case RQ_Q8_0: rq_requant_q8_0_kernel<RQ_Q8_0><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
         case RQ_Q4_0: rq_requant_q8_0_kernel<RQ_Q4_0><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
-        case RQ_Q4_1: rq_requant_q8_0_kernel<RQ_Q4_1><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
-        case RQ_Q5_0: rq_requant_q8_0_kernel<RQ_Q5_0><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
-        case RQ_Q5_1: rq_requant_q8_0_kernel<RQ_Q5_1><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
-        case RQ_Q5_K: rq_requant_q8_0_kernel<RQ_Q5_K><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
-        case RQ_IQ4_NL: rq_requant_q8_0_kernel<RQ_IQ4_NL><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
+#define RQ_CASE(T) case T: rq_requant_q8_0_kernel<T><<<grid, threads, 0, s>>>(src->main, src->scale, src->rows, src->cols, dst->main, dst->scale); break;
+        RQ_DECODE_ONLY_TYPES(RQ_CASE)
+#undef RQ_CASE
         default: return rq_fail(RQ_ERR_INVALID, "requantize: source type %d", src->type);
     }
     RQ_CUDA(cudaGetLastError());

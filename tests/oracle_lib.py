@@ -14,10 +14,26 @@ LIB_PATH = ORACLE_DIR / "librq_oracle.so"
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
 Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL = 3, 6, 7, 13, 20   # decoded and run-decoder dotted only; no encoder, no int8 slice helper
-STORED_ONLY = (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL)
+Q8_1, Q2_K, Q3_K, Q8_K, IQ4_XS = 9, 10, 11, 15, 23
+STORED_ONLY = (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL, Q8_1, Q2_K, Q3_K, Q8_K, IQ4_XS)
 FLOAT_RUN, FLOAT_EXACT, INT8 = 0, 1, 2
 GEOMETRY = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
-            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176), IQ4_NL: (32, 18)}
+            Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176), IQ4_NL: (32, 18),
+            Q8_1: (32, 36), Q2_K: (256, 84), Q3_K: (256, 110), Q8_K: (256, 292), IQ4_XS: (256, 136)}
+
+
+# where a block's floating-point header fields sit: (byte offset, bytes)
+HEADERS = {Q4_0: [(0, 2)], Q8_0: [(0, 2)], Q4_K: [(0, 2), (2, 2)], Q6_K: [(208, 2)], Q4_1: [(0, 2), (2, 2)], Q5_0: [(0, 2)], Q5_1: [(0, 2), (2, 2)],
+           Q5_K: [(0, 2), (2, 2)], IQ4_NL: [(0, 2)], Q8_1: [(0, 2), (2, 2)], Q2_K: [(80, 2), (82, 2)], Q3_K: [(108, 2)], Q8_K: [(0, 4)], IQ4_XS: [(0, 2)]}
+
+
+def arbitrary_blocks(t: int, count: int, rng: np.random.Generator) -> np.ndarray:
+    """`count` blocks of arbitrary bytes whose header fields are finite and below 2 in magnitude (the top exponent bit cleared)."""
+    _, stride = GEOMETRY[t]
+    raw = rng.integers(0, 256, size=(count, stride), dtype=np.uint8)
+    for at, width in HEADERS[t]:
+        raw[:, at + width - 1] &= 0x3F
+    return raw.reshape(-1)
 
 
 def random_blocks(t: int, count: int, rng: np.random.Generator, scale: float = 0.02) -> np.ndarray:
@@ -40,6 +56,16 @@ def random_blocks(t: int, count: int, rng: np.random.Generator, scale: float = 0
         put_half(0, mag / (63 * (31 if t == Q5_K else 15))); put_half(2, mag / 63 / 2)
     elif t == Q6_K:
         put_half(208, mag / (127 * 32))
+    elif t == Q8_1:
+        put_half(0, mag / 127); put_half(2, mag)
+    elif t == Q2_K:
+        put_half(80, mag / (15 * 3)); put_half(82, mag / 15 / 2)
+    elif t == Q3_K:
+        put_half(108, mag / (32 * 4))
+    elif t == Q8_K:
+        b[:, 0:4] = (mag / 127).astype(np.float32).reshape(-1, 1).view(np.uint8)
+    elif t == IQ4_XS:
+        put_half(0, mag / (32 * 127))
     return b.reshape(-1)
 THREADS = max(1, os.cpu_count() or 1)
 

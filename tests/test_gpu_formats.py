@@ -1,4 +1,4 @@
-"""The other stored formats (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL; recipe.rs:15812-15823) on the device: decode bit for
+"""The other stored formats (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL, Q8_1, Q2_K, Q3_K, Q8_K, IQ4_XS; recipe.rs:15812-15824) on the device: decode bit for
 bit with the oracle, export gives back the bytes, embedding gather, the run-decoder product within 1e-3, the Q8_0
 re-encode byte for byte (what `.int(8)` does to them at load, recipe.rs:22345-22369), int8 over the re-encoded
 weight against the oracle doing the same, and the refusals. GPU only (-m gpu)."""
@@ -10,17 +10,14 @@ from tests.test_gpu_parity import TOL, rel_err, torch_cuda
 
 pytestmark = pytest.mark.gpu
 
-TYPES = [ol.Q4_1, ol.Q5_0, ol.Q5_1, ol.Q5_K, ol.IQ4_NL]
+TYPES = [ol.Q4_1, ol.Q5_0, ol.Q5_1, ol.Q5_K, ol.IQ4_NL, ol.Q8_1, ol.Q2_K, ol.Q3_K, ol.Q8_K, ol.IQ4_XS]
 
 
 def _weight(rq_ctx, t, rows, cols, seed, arbitrary=False):
     values, stride = ol.GEOMETRY[t]
     rng = np.random.default_rng(seed)
     if arbitrary:
-        raw = rng.integers(0, 256, size=(rows * cols // values, stride), dtype=np.uint8)
-        for col in ((0, 2) if t in (ol.Q4_1, ol.Q5_1, ol.Q5_K) else (0,)):
-            raw[:, col + 1] &= 0x3F  # finite headers below 2 in magnitude
-        blocks = raw.reshape(-1)
+        blocks = ol.arbitrary_blocks(t, rows * cols // values, rng)
     else:
         blocks = ol.random_blocks(t, rows * cols // values, rng)
     return blocks, rq_ctx.weight_from_host(t, blocks, rows, cols)
@@ -120,7 +117,7 @@ def test_bound_from_a_gguf_file(rq_ctx, oracle, tmp_path):
     rq_ctx.check()
 
 
-@pytest.mark.parametrize("t", [ol.Q4_K, ol.Q6_K, ol.Q8_0, ol.Q4_0, ol.Q4_1, ol.Q5_K, ol.IQ4_NL])
+@pytest.mark.parametrize("t", [ol.Q4_K, ol.Q6_K, ol.Q8_0, ol.Q4_0, ol.Q4_1, ol.Q5_K, ol.IQ4_NL, ol.Q3_K, ol.Q8_K])
 @pytest.mark.parametrize("cols", [2048, 96 * 32 + 32])
 def test_int4_is_the_q4_1_reencode(rq_ctx, oracle, t, cols):
     """`.int(4)` (recipe.rs:22348): storage Q4_1 by the load kernel's encoder, byte for byte; int8 records against its codes."""

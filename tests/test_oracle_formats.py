@@ -1,4 +1,4 @@
-"""The other stored formats (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL): the C oracle and the independent NumPy
+"""The other stored formats (Q4_1, Q5_0, Q5_1, Q5_K, IQ4_NL, Q8_1, Q2_K, Q3_K, Q8_K, IQ4_XS): the C oracle and the independent NumPy
 restatement read every layout the same way, hand-built blocks decode to the values their definition
 gives, and the entry points that need an encoder or an int8 slice helper refuse them."""
 import numpy as np
@@ -7,7 +7,7 @@ import pytest
 from oracle import np_unpack
 from tests import oracle_lib as ol
 
-TYPES = [ol.Q4_1, ol.Q5_0, ol.Q5_1, ol.Q5_K, ol.IQ4_NL]
+TYPES = [ol.Q4_1, ol.Q5_0, ol.Q5_1, ol.Q5_K, ol.IQ4_NL, ol.Q8_1, ol.Q2_K, ol.Q3_K, ol.Q8_K, ol.IQ4_XS]
 
 
 @pytest.mark.parametrize("t", TYPES)
@@ -21,11 +21,9 @@ def test_two_restatements_agree_bit_for_bit(t):
     assert a.shape == (300 * values,)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
     # arbitrary bytes too (any fp16 header that is finite)
-    raw = rng.integers(0, 256, size=(200, stride), dtype=np.uint8)
-    for col in ((0, 2) if t in (ol.Q4_1, ol.Q5_1, ol.Q5_K) else (0,)):
-        raw[:, col + 1] &= 0x7B  # clear the top exponent bit: no inf / nan, sign dropped too
-    a = oracle.dequantize(t, raw.reshape(-1))
-    b = np_unpack.dequantize(t, raw.reshape(-1))
+    raw = ol.arbitrary_blocks(t, 200, rng)  # any code and scale pattern, finite headers
+    a = oracle.dequantize(t, raw)
+    b = np_unpack.dequantize(t, raw)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
@@ -63,6 +61,33 @@ def test_hand_built_blocks():
     want = np.full(256, 2.0, np.float32)
     want[3 * 32] = 18.0
     assert np.array_equal(out, want)
+
+
+def test_hand_built_blocks_of_the_k_and_iq_formats():
+    oracle = ol.load()
+    # Q2_K: d = 1, dmin = 0.5; group g has scale g and minimum 15 - g; every code 2 -> value 2 g - 0.5 (15 - g)
+    blk = [g | ((15 - g) << 4) for g in range(16)] + [0xAA] * 64 + _half_bytes(1.0) + _half_bytes(0.5)
+    out = oracle.dequantize(ol.Q2_K, np.array(blk, np.uint8)).reshape(16, 16)
+    assert np.array_equal(out, np.repeat(np.array([2.0 * g - 0.5 * (15 - g) for g in range(16)], np.float32)[:, None], 16, axis=1))
+    # Q3_K: d = 1, every scale code 33 (low four bits 1, high two bits 2 -> 33 - 32 = 1), codes 3, mask set only for values of part 0
+    blk = [1] * 32 + [0xFF] * 64 + [0x11] * 8 + [0xAA] * 4 + _half_bytes(1.0)
+    out = oracle.dequantize(ol.Q3_K, np.array(blk, np.uint8))
+    want = np.full(256, -1.0, np.float32)   # 3 - 4
+    want[:32] = 3.0
+    assert np.array_equal(out, want)
+    # Q8_K: an fp32 step of 0.25 and codes -128 .. 127
+    blk = list(np.array([0.25], np.float32).view(np.uint8)) + list(np.arange(-128, 128, dtype=np.int8).view(np.uint8)) + [0] * 32
+    out = oracle.dequantize(ol.Q8_K, np.array(blk, np.uint8))
+    assert np.array_equal(out, 0.25 * np.arange(-128, 128, dtype=np.float32))
+    # Q8_1: d = 0.5, the stored sum is not part of a value
+    blk = _half_bytes(0.5) + _half_bytes(123.0) + list(np.arange(-16, 16, dtype=np.int8).view(np.uint8))
+    out = oracle.dequantize(ol.Q8_1, np.array(blk, np.uint8))
+    assert np.array_equal(out, 0.5 * np.arange(-16, 16, dtype=np.float32))
+    # IQ4_XS: d = 1; block b of 32 values has exponent code 32 + b (low bits b, high bits 2) -> exponent b; nibble 8 -> level 1
+    hi = sum(2 << (2 * b) for b in range(8))
+    blk = _half_bytes(1.0) + [hi & 0xFF, hi >> 8] + [(2 * k) | ((2 * k + 1) << 4) for k in range(4)] + [0x88] * 128
+    out = oracle.dequantize(ol.IQ4_XS, np.array(blk, np.uint8)).reshape(8, 32)
+    assert np.array_equal(out, np.repeat(np.arange(8, dtype=np.float32)[:, None], 32, axis=1))
 
 
 @pytest.mark.parametrize("t", TYPES)
