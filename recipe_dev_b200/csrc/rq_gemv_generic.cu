@@ -1,11 +1,11 @@
-// Matrix-vector product over the stored formats that have no streaming kernel of their own (Q4_1, Q5_0,
-// Q5_1, Q5_K, IQ4_NL): fp32 activations against per-value decoded weights, the reference's run decoders
-// (recipe.rs:7826-7917: one fused-multiply-add chain per unit of 32 values in index order; the units of a
-// row add up, ll:3451-3492). HBM-bound by design: a warp owns a row and walks it in units of 32 values,
-// lane l taking units l, l + 32, ..; the lanes' sums meet in a fixed xor tree, so every run gives the same
-// bits. `.int(8)` never reaches these formats: the reference re-encodes them to Q8_0 at load
-// (rq_weight_requantize), and that weight takes the streaming kernel. `.int(4)` stores Q4_1 and dots it with
-// int8 activation records: rq_gemv_q41_int8_kernel below.
+// Matrix-vector product over the stored formats that have no streaming kernel of their own (Q4_1, Q5_0, Q5_1, Q5_K,
+// IQ4_NL, Q8_1, Q2_K, Q3_K, Q8_K, IQ4_XS): fp32 activations against per-value decoded weights, the reference's run
+// decoders (recipe.rs:7826-7917: one fused-multiply-add chain per unit of 32 values in index order; the units of a row
+// add up, ll:3451-3492; here the additions are regrouped, within the 1e-3 band). A warp owns a row and walks it in units
+// of 32 values, lane l taking value l of every unit, so that a unit's activations are one coalesced line and its weight
+// bytes one block; the lanes' sums meet in a fixed xor tree, so every run gives the same bits. `.int(8)` never reaches
+// these formats: the reference re-encodes them to Q8_0 at load (rq_weight_requantize), and that weight takes the
+// streaming kernel. `.int(4)` stores Q4_1 and dots it with int8 activation records: rq_gemv_q41_int8_kernel below.
 #include "rq_decode.cuh"
 
 namespace {
@@ -19,14 +19,11 @@ __global__ void __launch_bounds__(kWarps * 32) rq_gemv_generic_kernel(const uint
     const float* xt = x + (int64_t)token * st;
     const int64_t units = cols >> 5;
     for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
+        // lane l takes value l of every unit: the warp's activation loads are one line, its weight bytes one block
         float sum = 0.f;
-        for (int64_t u = lane; u < units; u += 32) {
-            float unit = 0.f;
-            const int64_t first = row * cols + (u << 5);
-#pragma unroll 8
-            for (int j = 0; j < 32; ++j) unit = fmaf(rq_decode_value<TYPE>(main_plane, nullptr, first + j, cols), __ldg(xt + ((u << 5) + j) * sk), unit);
-            sum += unit;
-        }
+        const int64_t first = row * cols + lane;
+#pragma unroll 4
+        for (int64_t u = 0; u < units; ++u) sum = fmaf(rq_decode_value<TYPE>(main_plane, nullptr, first + (u << 5), cols), __ldg(xt + ((u << 5) + lane) * sk), sum);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
         if (lane == 0) y[row * yn + (int64_t)token * yt] = sum;
