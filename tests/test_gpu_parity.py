@@ -185,7 +185,7 @@ def test_argument_validation(rq_ctx, oracle):
     lib = rq_ctx.lib
     blocks = oracle.quantize(ol.Q4_K, oracle.normal(10, 0, 4 * 256, 0.02))
     out = ctypes.c_void_p()
-    assert lib.rq_weight_prepare(rq_ctx.handle, 15, blocks.ctypes.data, 4, 256, 0, 4, ctypes.byref(out)) == -1  # Q8_K: not a format of this path
+    assert lib.rq_weight_prepare(rq_ctx.handle, 16, blocks.ctypes.data, 4, 256, 0, 4, ctypes.byref(out)) == -1  # IQ2_XXS: a grid format, not served
     assert lib.rq_weight_prepare(rq_ctx.handle, ol.Q4_K, blocks.ctypes.data, 4, 250, 0, 4, ctypes.byref(out)) == -1
     assert b"multiple" in lib.rq_last_error()
     assert lib.rq_weight_prepare(rq_ctx.handle, ol.Q4_K, blocks.ctypes.data, 4, 256, 2, 3, ctypes.byref(out)) == -1
