@@ -34,7 +34,7 @@ if str(ROOT) not in sys.path:
 import numpy as np  # noqa: E402
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
-GEOM = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+GEOM = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), 3: (32, 20)}  # 3 = Q4_1, the storage of int4 sums
 # name, type, rows, cols, shares the activation column of the previous projection
 LAYER = [
     ("q", Q4_K, 4096, 4096, False),
@@ -842,6 +842,14 @@ def run_other_configs(ctx, rq, torch, oracle, ol, device):
         matvec_line(Q8_0, rows, cols, rq.ACT_INT8, 4, f"{name}_int8_recipe_q8_0_reencode_batch1", weights=reenc)
         for w in reenc:
             w.free()
+    # `.int(4)`: storage Q4_1 made at load from the Q4_K tensor, int8 records against its four-bit codes (a plain warp-per-row kernel)
+    stored = quantised(Q4_K, 14336, 4096, 4)
+    four = [ctx.int4_weight(w) for w in stored]
+    for w in stored:
+        w.free()
+    matvec_line(rq.Q4_1, 14336, 4096, rq.ACT_INT8, 4, "q4k_14336x4096_int4_recipe_q4_1_reencode_batch1", weights=four)
+    for w in four:
+        w.free()
     # cfg 5: the batched product on the tensor cores, fp32 and int8 activations, each call's launches captured in a graph
     for name, t, rows, cols in (("q4k_14336x4096", Q4_K, 14336, 4096), ("q6k_4096x14336", Q6_K, 4096, 14336)):
         ws = quantised(t, rows, cols, 4)
