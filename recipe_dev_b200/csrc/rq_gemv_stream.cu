@@ -969,7 +969,7 @@ __device__ __forceinline__ float rq_silu_portable(float x) { return __fmul_rn(x,
 
 // R = rows a thread takes per stage in the warp scheme (its weight registers): 2 only where the launch uses two
 template <int TYPE, int MODE, int T, int NW, int R>
-__global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1)) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+__global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? (T == 2 ? 2 : 3) : (NW <= 7 ? 2 : 1)) rq_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int kConsumers = NW * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[2 * kMaxStages];  // [slot][piece]
@@ -992,7 +992,8 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
     __shared__ int4 stage_info[kMaxStages];
     // warp scheme with rows split over the warps: per stage in flight, each warp's sum of each row, and how many warps have
     // delivered. A warp is never more than the ring's depth ahead of the slowest, so kMaxStages + 1 buffers never collide.
-    __shared__ float cross_sum[kMaxStages + 1][8][NW];
+    constexpr int TR = T == 2 ? 2 : 1;  // tokens a thread keeps in registers (the warp schemes)
+    __shared__ float cross_sum[kMaxStages + 1][TR][8][NW];
     __shared__ int cross_count[kMaxStages + 1];
 
     // Programmatic dependent launch: the next kernel in the stream may start its own prologue now.
@@ -1187,7 +1188,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             my_h = item >= p.units && act_owner ? 1 : 0;
             my_u = act_owner ? item - my_h * p.units : 0;
         }
-        ActHalf areg;
+        ActHalf areg[TR];
         if (MODE == RQ_ACT_INT8 && p.act_regs) {
             // single token: this thread's 128 codes, steps and sums, kept in registers for the whole
             // kernel. They come from the records an earlier launch left in the scratch, or (fused
@@ -1195,14 +1196,18 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             if (p.fuse_step) {
                 quantise_to_smem<kThreads>(p.x, p.sk, p.cols, p.fuse_step, act_smem, tid);
                 __syncthreads();  // with the producer warp: records complete, barriers initialised
-                if (act_owner) areg.load(act_smem + (size_t)my_u * kRecord, my_h);
+                if (act_owner) areg[0].load(act_smem + (size_t)my_u * kRecord, my_h);
                 if (blockIdx.x == 0 && p.act_out) {
                     const uint4* src = (const uint4*)act_smem;
                     uint4* dst = (uint4*)p.act_out;
                     for (int i = tid; i < p.units * (kRecord / 16); i += kConsumers) dst[i] = src[i];
                 }
             } else if (act_owner) {
-                areg.load(p.act + ((size_t)tok0 * p.units + my_u) * kRecord, my_h);
+#pragma unroll
+                for (int j = 0; j < TR; ++j) {
+                    const int tok = tok0 + j < p.tokens ? tok0 + j : tok0;  // a pair past the last token dots the first again and stores nothing
+                    areg[j].load(p.act + ((size_t)tok * p.units + my_u) * kRecord, my_h);
+                }
             }
         } else if (MODE == RQ_ACT_FLOAT) {
             // stage the activations while the first weight stages are in flight
@@ -1373,7 +1378,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
             }
         };
         constexpr int kSweep = kConsumers / 8;  // row tasks per sweep of the consumer threads
-        if (T == 1 && p.warp_rows) {
+        if (T <= 2 && p.warp_rows) {
             // ---- the warp scheme: no partial sums in shared memory, no CTA-wide barrier. A row's items are
             // `group` adjacent lanes; a thread takes up to two rows of a stage (one per pass), holds their
             // weights in registers, releases the stage, and the lanes of a row join their sums by an xor tree.
@@ -1408,34 +1413,44 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[slot]);
                 if (++slot == p.stages) { slot = 0; phase ^= 1; }
-                float v[R];
+                // v[j][k]: token tok0 + j (the tokens a thread holds in registers) against row k of the stage; every token's
+                // dot and sums are the single-token ones, so a position gets the bits its own call gives
+                float v[TR][R];
                 if (MODE == RQ_ACT_INT8) {
 #pragma unroll
-                    for (int k = 0; k < R; ++k) v[k] = have[k] ? dot_regs(wr[k], areg, my_h) : 0.f;
+                    for (int j = 0; j < TR; ++j)
+#pragma unroll
+                        for (int k = 0; k < R; ++k) v[j][k] = have[k] ? dot_regs(wr[k], areg[j], my_h) : 0.f;
                 } else {
-                    dot_regs_float<R>(wr, have, act_smem + (size_t)my_u * kRecord, my_h, v);
+                    dot_regs_float<R>(wr, have, act_smem + (size_t)my_u * kRecord, my_h, v[0]);
                 }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) {
                     if (off < group) {  // uniform over the launch
 #pragma unroll
-                        for (int k = 0; k < R; ++k) v[k] += __shfl_xor_sync(0xffffffffu, v[k], off);
+                        for (int j = 0; j < TR; ++j)
+#pragma unroll
+                            for (int k = 0; k < R; ++k) v[j][k] += __shfl_xor_sync(0xffffffffu, v[j][k], off);
                     }
                 }
                 if (!split) {
                     if (writer) {
                         float* yb = table[info.y].y;
 #pragma unroll
-                        for (int k = 0; k < R; ++k)
-                            if (have[k]) yb[(int64_t)(info.z + row_in_pass + k * rows_per_pass) * p.yn + (int64_t)tok0 * p.yt] = v[k];
+                        for (int j = 0; j < TR; ++j)
+#pragma unroll
+                            for (int k = 0; k < R; ++k)
+                                if (have[k] && tok0 + j < p.tokens) yb[(int64_t)(info.z + row_in_pass + k * rows_per_pass) * p.yn + (int64_t)(tok0 + j) * p.yt] = v[j][k];
                     }
                 } else {
                     // this warp's share of each row goes to shared memory; the warp that finds the others all
                     // there adds the shares in warp order (whichever warp that is, the order is the same)
                     if (writer) {
 #pragma unroll
-                        for (int k = 0; k < R; ++k)
-                            cross_sum[cross_buf][row_in_pass + k * rows_per_pass][warp] = v[k];
+                        for (int j = 0; j < TR; ++j)
+#pragma unroll
+                            for (int k = 0; k < R; ++k)
+                                cross_sum[cross_buf][j][row_in_pass + k * rows_per_pass][warp] = v[j][k];
                     }
                     __threadfence_block();
                     __syncwarp();
@@ -1445,11 +1460,13 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                     if (arrived == NW - 1) {
                         __threadfence_block();
                         const int rows_here = info.x;
-                        if (lane < rows_here && lane < 8) {
+                        // lanes 0..7 take the rows for the first token, lanes 8..15 for the second
+                        const int row = lane & 7, j = lane >> 3;
+                        if (row < rows_here && j < TR && tok0 + j < p.tokens) {
                             float out = 0.f;
 #pragma unroll
-                            for (int w = 0; w < NW; ++w) out += *(volatile float*)&cross_sum[cross_buf][lane][w];
-                            table[info.y].y[(int64_t)(info.z + lane) * p.yn + (int64_t)tok0 * p.yt] = out;
+                            for (int w = 0; w < NW; ++w) out += *(volatile float*)&cross_sum[cross_buf][j][row][w];
+                            table[info.y].y[(int64_t)(info.z + row) * p.yn + (int64_t)(tok0 + j) * p.yt] = out;
                         }
                         __syncwarp();
                         if (lane == 0) cross_count[cross_buf] = 0;
@@ -1504,7 +1521,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
                 buf ^= 1;
 #pragma unroll
                 for (int k = 0; k < PAIR; ++k)
-                    if (have[k]) part[k * stage_items + tid] = dot_regs(wr[k], areg, my_h);
+                    if (have[k]) part[k * stage_items + tid] = dot_regs(wr[k], areg[0], my_h);
                 consumer_sync<kConsumers>();
                 // the rows of both stages, dealt to the warps in turn
                 reduce_rows(part, table[st_seg[0]], st_nr[0], st_lr0[0], tid >> 3, kSweep);
@@ -1544,8 +1561,8 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? 3 : (NW <= 7 ? 2 : 1))
 #pragma unroll
                         for (int t = 0; t < T; ++t) {
                             const uint8_t* ar = a0 + t * p.act_bytes;
-                            if (MODE == RQ_ACT_INT8) areg.load(ar, my_h);
-                            part[t * stage_items + tid] = item_dot<TYPE, MODE>(w, sc, ar, areg, my_h, my_u);
+                            if (MODE == RQ_ACT_INT8) areg[0].load(ar, my_h);
+                            part[t * stage_items + tid] = item_dot<TYPE, MODE>(w, sc, ar, areg[0], my_h, my_u);
                         }
                     }
                 }
@@ -1605,15 +1622,17 @@ static void row_layout(int ipr, int* group, int* chunks) {
 }
 
 template <int TYPE, int MODE, int NW>
-int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s, bool one_per_sm = false) {
+int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cudaStream_t s, bool one_per_sm = false, bool token_pairs = false) {
     // Two CTAs share an SM (eight consumer warps and about 100 KB each): their barriers and waits
     // interleave, and when a CTA of one launch exits, a CTA of the next launch (programmatic
     // dependent launch) takes its place and prefetches weights while the other is still working.
     // five consumer warps: three CTAs of six warps per SM. one_per_sm: a single CTA with the whole SM's shared memory, for
     // launches whose staged activations leave two CTAs no room for a ring (fp32 records of 14336 inputs are 62 KB).
-    const int kCtasPerSm = one_per_sm ? 1 : (NW == 5 ? 3 : 2);
+    // token_pairs (int8 windows over rows of five consumer warps): two tokens' records in every thread's registers, 170
+    // registers a thread, so two CTAs per SM instead of three
+    const int kCtasPerSm = one_per_sm ? 1 : (NW == 5 && !token_pairs ? 3 : 2);
     // dynamic; with the static tables (about 10 KB) and the 1 KB the system keeps per CTA, two (three) CTAs fit an SM's 228 KB
-    const size_t kSmemBudget = one_per_sm ? 200 * 1024 : (NW == 5 ? 64 * 1024 : 102 * 1024);
+    const size_t kSmemBudget = one_per_sm ? 200 * 1024 : (NW == 5 && !token_pairs ? 64 * 1024 : 102 * 1024);
     constexpr int kRecord = MODE == RQ_ACT_INT8 ? RQ_ACT_RECORD_INT8 : RQ_ACT_RECORD_FLOAT;
     // NW = consumer warps: seven, so that with the producer warp a CTA is eight warps and two CTAs per SM leave each
     // thread 128 registers; eight (one CTA per SM then) only for rows too long for seven warps' worth of items.
@@ -1623,13 +1642,13 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
     if (vectors_per_launch > 0) {
         p.act_vectors = vectors_per_launch;  // expert banks: one token, a vector per slot
     } else {
-        t = (p.tokens >= 2 && 4 * p.act_bytes <= 40 * 1024) ? 4 : 1;
+        t = token_pairs ? 2 : ((p.tokens >= 2 && 4 * p.act_bytes <= 40 * 1024) ? 4 : 1);
         p.act_vectors = t;
         // four int8 tokens are staged interleaved, kRecord4 bytes per unit: a quarter of that per vector
         if (MODE == RQ_ACT_INT8 && t == 4) p.act_bytes = ((size_t)p.units * (kRecord4 / 4) + 127) & ~(size_t)127;
     }
     // single-token INT8 launches whose sub-rows all read vector 0 keep the activations in registers
-    p.act_regs = (MODE == RQ_ACT_INT8 && t == 1 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr) ? 1 : 0;
+    p.act_regs = (MODE == RQ_ACT_INT8 && (t == 1 || token_pairs) && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr) ? 1 : 0;
     if (p.fuse_step && !p.act_regs) return RQ_ERR_UNSUPPORTED;  // the caller quantises with the standalone kernel instead
     if (p.act_regs) p.act_vectors = p.fuse_step ? 1 : 0;        // fused: one token's records are made in shared memory; else nothing is staged
     if (p.act_bytes * p.act_vectors > (size_t)(one_per_sm ? 128 : 64) * 1024) return RQ_ERR_UNSUPPORTED;  // the caller falls back to the tiled kernel
@@ -1670,6 +1689,10 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
         p.rows_per_thread = (int64_t)2 * p.warp_rows * row_bytes <= 34 * 1024 && rows_per_cta > p.warp_rows && 2 * p.warp_rows <= 8 ? 2 : 1;
         stage_rows = p.warp_rows * p.rows_per_thread;
     }
+    if (token_pairs) {
+        if (!p.warp_rows) return RQ_ERR_UNSUPPORTED;  // pairs run a warp scheme or not at all
+        if (p.rows_per_thread == 2) { p.rows_per_thread = 1; stage_rows /= 2; }  // two tokens' records leave no registers for a second row
+    }
     p.stage_rows = stage_rows;
     p.pieces = 1; p.piece_rows = stage_rows;
     if (p.warp_rows && p.rows_per_thread == 2) { p.pieces = 2; p.piece_rows = stage_rows / 2; }
@@ -1702,6 +1725,9 @@ int dispatch_stream_nw(StreamParams& p, int sm_count, int vectors_per_launch, cu
         for (int i = p.n_segments; i <= RQ_INLINE_SEGMENTS; ++i) p.seg_stage_begin[i] = at;
         p.total_stages = at;
     }
+    if constexpr (NW == 5 && MODE == RQ_ACT_INT8) {
+        if (token_pairs) return launch_stream<TYPE, MODE, 2, NW, 1>(p, grid_x, smem, s);
+    }
     if (t == 4) return launch_stream<TYPE, MODE, 4, NW, 1>(p, grid_x, smem, s);
     if (p.rows_per_thread == 2) return launch_stream<TYPE, MODE, 1, NW, 2>(p, grid_x, smem, s);
     return launch_stream<TYPE, MODE, 1, NW, 1>(p, grid_x, smem, s);
@@ -1715,8 +1741,15 @@ int dispatch_stream(StreamParams& p, int sm_count, int vectors_per_launch, cudaS
         // rows of 5 x 2^k items (2560 inputs): single-token launches run five consumer warps, three CTAs per SM
         int group = 0, chunks = 1;
         row_layout(ipr, &group, &chunks);
-        if (chunks == 5 && p.tokens == 1 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN)
-            return dispatch_stream_nw<TYPE, MODE, 5>(p, sm_count, vectors_per_launch, s);
+        if (chunks == 5 && vectors_per_launch == 0 && p.table == nullptr && p.plan == nullptr && p.subs == 1 && p.epilogue == RQ_EPI_PLAIN) {
+            if (p.tokens == 1) return dispatch_stream_nw<TYPE, MODE, 5>(p, sm_count, vectors_per_launch, s);
+            // a window of positions: token pairs in registers (the weights are read once per pair, at the single-token rate)
+            // where the staged four-token pass is bound by its shared-memory loads
+            if (!p.fuse_step) {
+                const int rc = dispatch_stream_nw<TYPE, MODE, 5>(p, sm_count, vectors_per_launch, s, false, true);
+                if (rc != RQ_ERR_UNSUPPORTED) return rc;
+            }
+        }
     }
     int rc = dispatch_stream_nw<TYPE, MODE, 7>(p, sm_count, vectors_per_launch, s);
     if (rc == RQ_ERR_UNSUPPORTED) rc = dispatch_stream_nw<TYPE, MODE, 7>(p, sm_count, vectors_per_launch, s, true);
