@@ -335,3 +335,33 @@ def test_matvec_multi_ragged_segments(rq_ctx, oracle):
             one = rq_ctx.matvec(w, torch_cuda(x), act_mode=mode, step=32)
             assert torch.equal(one, y)
     rq_ctx.check()
+
+
+@pytest.mark.parametrize("t,cols", [(ol.Q6_K, 2560), (ol.Q8_0, 2560), (ol.Q4_K, 1280), (ol.Q4_0, 5120)])
+@pytest.mark.parametrize("tokens", [2, 3, 5])
+def test_int8_windows_over_rows_of_five_warps(rq_ctx, oracle, t, cols, tokens):
+    """Rows of 5 x 2^k items take token pairs in registers: every position of a window (even and odd lengths, one matrix and
+    several in one launch) gets the bits its own single-token call gives, and the oracle's int8 answer."""
+    import torch
+
+    rows = [300, 17, 64]
+    bl = [oracle.quantize(t, oracle.normal(43, 10 * t + i, r * cols, 0.02)) for i, r in enumerate(rows)]
+    ws = [rq_ctx.weight_from_host(t, b, r, cols) for b, r in zip(bl, rows)]
+    x = oracle.normal(43, 99 + tokens, tokens * cols, 1.0).reshape(tokens, cols)
+    xd = torch_cuda(x)
+    for step in (32, 256):
+        singles = [[rq_ctx.matvec(w, xd[p], act_mode=1, step=step) for p in range(tokens)] for w in ws]
+        for w, b, r, ones in zip(ws, bl, rows, singles):
+            y = rq_ctx.matvec(w, xd, act_mode=1, step=step)
+            for p in range(tokens):
+                assert torch.equal(y[p], ones[p]), (step, p)
+            ref = oracle.matvec(t, b, r, cols, x, ol.INT8, step)
+            assert rel_err(y.cpu().numpy(), ref) <= 2e-4  # exact integer dots; the fp32 sums over 2560 .. 5120 inputs are added in another order
+        plane = torch.zeros(tokens, sum(rows), dtype=torch.float32, device="cuda")
+        offs = np.cumsum([0] + rows)
+        ys = [plane[:, int(offs[i]):int(offs[i + 1])] for i in range(len(rows))]
+        rq_ctx.matvec_multi(ws, xd, ys, act_mode=1, step=step)
+        for y, ones in zip(ys, singles):
+            for p in range(tokens):
+                assert torch.equal(y[p], ones[p]), ("multi", step, p)
+    rq_ctx.check()
