@@ -220,16 +220,32 @@ __global__ void __launch_bounds__(128) rq_split_x_kernel(const float* __restrict
     }
 }
 
-// y[row][token] = the splits' sums added in split order (the same bits on every run)
+// y[row][token] = the splits' sums added in split order (the same bits on every run). Grid row = token; a thread takes four
+// adjacent rows at a time where the planes allow 16-byte accesses (the partial sums are [split][token][row]).
 __global__ void __launch_bounds__(256) rq_sum_splits_kernel(const float* __restrict__ partial, int splits, int64_t rows, int tokens, float* __restrict__ y, int64_t yn, int64_t yt) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t total = rows * tokens;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t token = i / rows, row = i - token * rows;
-        float sum = 0.f;
-        for (int z = 0; z < splits; ++z) sum += partial[(size_t)z * total + i];
-        y[row * yn + token * yt] = sum;
+    const bool vec = yn == 1 && (rows & 3) == 0 && (yt & 3) == 0 && (((uintptr_t)partial | (uintptr_t)y) & 15) == 0;
+    for (int token = blockIdx.y; token < tokens; token += gridDim.y) {
+        const float* src = partial + (int64_t)token * rows;
+        if (vec) {
+            float4* dst = (float4*)(y + (int64_t)token * yt);
+            for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < (rows >> 2); q += (int64_t)gridDim.x * blockDim.x) {
+                float4 sum = __ldcs((const float4*)src + q);
+                for (int z = 1; z < splits; ++z) {
+                    const float4 v = __ldcs((const float4*)(src + (size_t)z * total) + q);
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                dst[q] = sum;
+            }
+        } else {
+            for (int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += (int64_t)gridDim.x * blockDim.x) {
+                float sum = src[row];
+                for (int z = 1; z < splits; ++z) sum += src[(size_t)z * total + row];
+                y[row * yn + (int64_t)token * yt] = sum;
+            }
+        }
     }
 }
 
@@ -491,8 +507,8 @@ int rq_launch_matmul(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t sk
 
 int rq_launch_sum_splits(const float* partial, int splits, int64_t rows, int tokens, float* y, int64_t yn, int64_t yt, cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
-    const int64_t total = rows * tokens;
-    cfg.gridDim = dim3((unsigned)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184));
+    const int64_t per_token = (rows / 4 + 255) / 256;  // CTAs that cover a token's rows four at a time
+    cfg.gridDim = dim3((unsigned)(per_token < 1 ? 1 : (per_token > 64 ? 64 : per_token)), (unsigned)(tokens < 65535 ? tokens : 65535));
     cfg.blockDim = dim3(256);
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
