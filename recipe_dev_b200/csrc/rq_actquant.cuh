@@ -27,12 +27,15 @@ __device__ __forceinline__ void rq_quantise_group(const float* __restrict__ xt, 
             if (fabsf(v[j]) > fabsf(best)) { best = v[j]; best_at = j * 32 + lane; }
         }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-        const int oa = __shfl_xor_sync(0xffffffffu, best_at, off);
-        const bool take = fabsf(ob) > fabsf(best) || (fabsf(ob) == fabsf(best) && oa < best_at);
-        if (take) { best = ob; best_at = oa; }
+    {
+        // The first input of largest magnitude over the warp, by integer reductions (one instruction each): magnitudes of finite
+        // floats order as their bits do; among the lanes that hold the largest, the lowest input index wins; its lane (the index's
+        // low five bits) hands out the signed value. A lane's own `best` is never a NaN (a NaN loses every comparison above).
+        const unsigned key = __float_as_uint(fabsf(best));
+        const unsigned top = __reduce_max_sync(0xffffffffu, key);
+        const unsigned first = __reduce_min_sync(0xffffffffu, key == top ? (unsigned)best_at : 0xffffffffu);
+        best = __shfl_sync(0xffffffffu, best, (int)(first & 31u));
+        best_at = (int)first;
     }
     const bool nonzero = fabsf(best) > 0.f;
     const float inverse = nonzero ? __fdiv_rn(-127.0f, best) : 0.f;
@@ -56,11 +59,8 @@ __device__ __forceinline__ void rq_quantise_group(const float* __restrict__ xt, 
                 sp = (int16_t*)(tok + cols + recs * 4) + rec * 2;
             }
             codes[lane] = (int8_t)code;
-            int s = code;
-            s += __shfl_xor_sync(0xffffffffu, s, 8);
-            s += __shfl_xor_sync(0xffffffffu, s, 4);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            // the two slices' sums: one integer reduction over each half of the warp
+            const int s = __reduce_add_sync(lane < 16 ? 0x0000ffffu : 0xffff0000u, code);
             if ((lane & 15) == 0) sp[lane >> 4] = (int16_t)s;
             if (lane == 0) *dp = d;
             if (unit_layout) {

@@ -41,9 +41,9 @@
 // are collected for eight superblocks at a time in one more pair of swizzled tiles in shared memory
 // and multiplied into an accumulator that lives for the whole K.
 //
-// INT8 activations take the same kernel: the int8 records are made by the standalone quantiser
-// (bit-exact with the reference's) and the prepared image holds code * step, which is what the
-// integer dot multiplies out to; only the order of the fp32 additions differs.
+// INT8 activations take the same kernel: rq_kq_prep_int8_kernel quantises them with the reference's
+// arithmetic while it writes the image, which then holds code * step -- what the integer dot
+// multiplies out to; only the order of the fp32 additions differs.
 //
 // Every wait is bounded; a wait that runs out records a code in the context's error word, the
 // thread stops waiting and the CTA still frees its tensor memory before it exits.
@@ -200,12 +200,11 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t&
 }
 
 // ------------------------------------------------------------------------------------------
-// X -> the tensor core's operand images. grid (64-wide slices, token tiles), one thread per token
-// row of the tile; rows past the last token are zero. With `records` the inputs are the int8
-// activation records' code * step (unit records, one after another per token).
+// X -> the tensor core's operand images (fp32 activations). grid (64-wide slices, token tiles), one
+// thread per token row of the tile; rows past the last token are zero.
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) rq_kq_prep_kernel(const float* __restrict__ x, int64_t sk, int64_t st, const uint8_t* __restrict__ records, int cols,
-                                                          int tokens, int bn, uint8_t* __restrict__ xs, uint8_t* __restrict__ xg) {
+__global__ void __launch_bounds__(128) rq_kq_prep_kernel(const float* __restrict__ x, int64_t sk, int64_t st, int cols, int tokens, int bn,
+                                                          uint8_t* __restrict__ xs, uint8_t* __restrict__ xg) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int kg = blockIdx.x, nt = blockIdx.y, r = threadIdx.x;
@@ -214,20 +213,13 @@ __global__ void __launch_bounds__(128) rq_kq_prep_kernel(const float* __restrict
     uint8_t* hi = xs + ((size_t)nt * gridDim.x + kg) * 2 * (size_t)bn * 128;
     uint8_t* lo = hi + (size_t)bn * 128;
     float sums[2] = {0.f, 0.f};
-    const bool vec = !records && sk == 1 && (st & 3) == 0 && ((uintptr_t)x & 15) == 0;
+    const bool vec = sk == 1 && (st & 3) == 0 && ((uintptr_t)x & 15) == 0;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         float v[8];
         if (token >= tokens) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.f;
-        } else if (records) {
-            const uint8_t* rec = records + ((size_t)token * (cols >> 8) + (kg >> 2)) * RQ_ACT_RECORD_INT8;
-            const uint2 codes = *(const uint2*)(rec + 64 * (kg & 3) + 8 * c);
-            const float d = ((const float*)(rec + 256))[2 * (kg & 3) + (c >> 2)];
-            const uint32_t cw[2] = {codes.x, codes.y};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __fmul_rn((float)(int8_t)(cw[j >> 2] >> (8 * (j & 3))), d);
         } else {
             const float* src = x + (int64_t)token * st + (int64_t)(kg * BK + 8 * c) * sk;
             if (vec) {
@@ -253,6 +245,93 @@ __global__ void __launch_bounds__(128) rq_kq_prep_kernel(const float* __restrict
         // the sums of this slice's two 32-input groups: elements 2 pr, 2 pr + 1 of the superblock's chunk
         const int sb = kg >> 2, pr = kg & 3;
         const int windows = ((cols >> 8) + 7) >> 3;
+        uint8_t* ghi = xg + ((size_t)nt * windows + (sb >> 3)) * 2 * (size_t)bn * 128;
+        uint8_t* glo = ghi + (size_t)bn * 128;
+        uint32_t h, l;
+        split2(sums[0], sums[1], h, l);
+        *(uint32_t*)(ghi + swizzled(r, sb & 7) + 4 * pr) = h;
+        *(uint32_t*)(glo + swizzled(r, sb & 7) + 4 * pr) = l;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// INT8 activations: the reference's quantiser and the operand images in one pass, with no int8
+// records in between. grid (superblocks, token tiles), block (bn, 4): thread (r, pr) holds the 64
+// inputs of token row r in slice pr of the superblock. The extreme of a group is the FIRST input of
+// strictly largest magnitude, signed: a serial scan in input order finds it (a 32-input group lies
+// within one thread; a 256-input group is settled over the four threads of a row, slice by slice,
+// through shared memory); inverse = -127 / extreme and d = 1 / inverse are IEEE divides,
+// code = clamp(rint(x * inverse)), and the image holds code * d -- the standalone quantiser's
+// arithmetic, bit for bit, so the sums equal the ones its records would give.
+// ------------------------------------------------------------------------------------------
+template <int STEP>
+__global__ void __launch_bounds__(512) rq_kq_prep_int8_kernel(const float* __restrict__ x, int64_t sk, int64_t st, int tokens, int bn,
+                                                              uint8_t* __restrict__ xs, uint8_t* __restrict__ xg) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float row_best[4][128];
+    const int r = threadIdx.x, pr = threadIdx.y, sb = blockIdx.x, nt = blockIdx.y;
+    const int kg = sb * 4 + pr;
+    const int token = nt * bn + r;
+    uint8_t* hi = xs + ((size_t)nt * gridDim.x * 4 + kg) * 2 * (size_t)bn * 128;
+    uint8_t* lo = hi + (size_t)bn * 128;
+    float v[64];
+    if (token < tokens) {
+        const float* src = x + (int64_t)token * st + (int64_t)kg * BK * sk;
+        if (sk == 1 && (st & 3) == 0 && ((uintptr_t)x & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) *(float4*)(v + 4 * j) = __ldg((const float4*)src + j);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = __ldg(src + j * sk);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) v[j] = 0.f;
+    }
+    float best[2] = {0.f, 0.f};  // a NaN is never larger, so it never becomes the extreme
+#pragma unroll
+    for (int j = 0; j < 64; ++j)
+        if (fabsf(v[j]) > fabsf(best[j >> 5])) best[j >> 5] = v[j];
+    if (STEP == 256) {
+        row_best[pr][r] = fabsf(best[1]) > fabsf(best[0]) ? best[1] : best[0];
+        __syncthreads();
+        float e = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float c = row_best[q][r];
+            if (fabsf(c) > fabsf(e)) e = c;
+        }
+        best[0] = best[1] = e;
+    }
+    float inverse[2], d[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const bool nonzero = fabsf(best[g]) > 0.f;
+        inverse[g] = nonzero ? __fdiv_rn(-127.0f, best[g]) : 0.f;
+        d[g] = nonzero ? __fdiv_rn(1.0f, inverse[g]) : 0.f;
+    }
+    float sums[2] = {0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        float q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int code = __float2int_rn(__fmul_rn(v[8 * c + j], inverse[c >> 2]));
+            code = code < -128 ? -128 : (code > 127 ? 127 : code);
+            q[j] = __fmul_rn((float)code, d[c >> 2]);
+            sums[c >> 2] += q[j];
+        }
+        uint32_t hw[4], lw[4];
+        split2(q[0], q[2], hw[0], lw[0]);
+        split2(q[1], q[3], hw[1], lw[1]);
+        split2(q[4], q[6], hw[2], lw[2]);
+        split2(q[5], q[7], hw[3], lw[3]);
+        *(uint4*)(hi + swizzled(r, c)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        *(uint4*)(lo + swizzled(r, c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+    }
+    if (xg) {
+        const int windows = ((int)gridDim.x + 7) >> 3;
         uint8_t* ghi = xg + ((size_t)nt * windows + (sb >> 3)) * 2 * (size_t)bn * 128;
         uint8_t* glo = ghi + (size_t)bn * 128;
         uint32_t h, l;
@@ -578,9 +657,9 @@ int launch_kq(const KqParams& p, int grid_m, int grid_n, int grid_k, size_t smem
 // How a call is cut: tokens per tile, superblocks per CTA, CTAs along K, pipeline depth, shared memory and scratch.
 struct KqCut {
     int bn, n_tiles, sb_per_split, splits, b_slots, a_slots, accs;
-    size_t smem, records_bytes, xs_bytes, xg_bytes, partial_bytes;
+    size_t smem, xs_bytes, xg_bytes, partial_bytes;
 };
-KqCut kq_cut(int type, int sm_count, int64_t rows, int64_t cols, int tokens, bool int8) {
+KqCut kq_cut(int type, int sm_count, int64_t rows, int64_t cols, int tokens) {
     KqCut c;
     c.bn = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : (tokens <= 64 ? 64 : 128));
     c.n_tiles = (tokens + c.bn - 1) / c.bn;
@@ -610,7 +689,6 @@ KqCut kq_cut(int type, int sm_count, int64_t rows, int64_t cols, int tokens, boo
     }
     c.sb_per_split = (nb + best - 1) / best;
     c.splits = (nb + c.sb_per_split - 1) / c.sb_per_split;
-    c.records_bytes = int8 ? (((size_t)tokens * nb * RQ_ACT_RECORD_INT8 + 1023) & ~(size_t)1023) : 0;
     c.xs_bytes = (size_t)c.n_tiles * (size_t)(cols / BK) * 2 * c.bn * 128;
     c.xg_bytes = type == RQ_Q4_K ? (size_t)c.n_tiles * (size_t)((nb + 7) / 8) * 2 * c.bn * 128 : 0;
     c.partial_bytes = c.splits > 1 ? (size_t)c.splits * tokens * rows * 4 : 0;
@@ -620,8 +698,8 @@ KqCut kq_cut(int type, int sm_count, int64_t rows, int64_t cols, int tokens, boo
 }  // namespace
 
 size_t rq_matmul_kq_scratch_bytes(const rq_ctx* ctx, int type, int64_t rows, int64_t cols, int tokens) {
-    const KqCut c = kq_cut(type, ctx->sm_count, rows, cols, tokens, true);
-    return c.records_bytes + c.xs_bytes + c.xg_bytes + c.partial_bytes;
+    const KqCut c = kq_cut(type, ctx->sm_count, rows, cols, tokens);
+    return c.xs_bytes + c.xg_bytes + c.partial_bytes;
 }
 
 // RQ_ERR_UNSUPPORTED (no error text) = not a K-quant weight. act_mode FLOAT or INT8 (step 32 / 256).
@@ -629,30 +707,32 @@ int rq_launch_matmul_kq(rq_ctx* ctx, const rq_weight* w, const float* x, int64_t
                         int step, cudaStream_t s) {
     if ((w->type != RQ_Q4_K && w->type != RQ_Q6_K) || w->cols % 256 || !w->has_tile_map) return RQ_ERR_UNSUPPORTED;
     const bool int8 = act_mode != RQ_ACT_FLOAT;
-    const KqCut cut = kq_cut(w->type, ctx->sm_count, w->rows, w->cols, tokens, int8);
-    int rc = rq_ensure_act_scratch(ctx, cut.records_bytes + cut.xs_bytes + cut.xg_bytes + cut.partial_bytes, s);
+    const KqCut cut = kq_cut(w->type, ctx->sm_count, w->rows, w->cols, tokens);
+    int rc = rq_ensure_act_scratch(ctx, cut.xs_bytes + cut.xg_bytes + cut.partial_bytes, s);
     if (rc) return rc;
     ctx->act_cols = 0;  // whatever int8 records the scratch held for INT8_CACHED calls are gone
-    uint8_t* records = ctx->act_scratch;
-    uint8_t* xs = records + cut.records_bytes;
+    uint8_t* xs = ctx->act_scratch;
     uint8_t* xg = cut.xg_bytes ? xs + cut.xs_bytes : nullptr;
     float* partial = cut.splits > 1 ? (float*)(xs + cut.xs_bytes + cut.xg_bytes) : nullptr;
-    if (int8) {
-        rc = rq_launch_act_quant(x, sk, st, w->cols, tokens, step, records, nullptr, s);
-        if (rc) return rc;
-    }
     if (xg) RQ_CUDA(cudaMemsetAsync(xg, 0, cut.xg_bytes, s));  // groups past the last superblock of a window count as zeros
     {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(w->cols / BK), (unsigned)cut.n_tiles);
-        cfg.blockDim = dim3(128);
         cfg.stream = s;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = int8 ? 1 : 0;  // after a memset node the kernel is launched the plain way
-        RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_kq_prep_kernel, x, sk, st, (const uint8_t*)(int8 ? records : nullptr), (int)w->cols, tokens, cut.bn, xs, xg));
+        cfg.numAttrs = int8 && !xg ? 1 : 0;  // after a memset node the kernel is launched the plain way
+        if (int8) {
+            cfg.gridDim = dim3((unsigned)(w->cols >> 8), (unsigned)cut.n_tiles);
+            cfg.blockDim = dim3((unsigned)cut.bn, 4);
+            if (step == 256) RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_kq_prep_int8_kernel<256>, x, sk, st, tokens, cut.bn, xs, xg));
+            else RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_kq_prep_int8_kernel<32>, x, sk, st, tokens, cut.bn, xs, xg));
+        } else {
+            cfg.gridDim = dim3((unsigned)(w->cols / BK), (unsigned)cut.n_tiles);
+            cfg.blockDim = dim3(128);
+            RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_kq_prep_kernel, x, sk, st, (int)w->cols, tokens, cut.bn, xs, xg));
+        }
     }
     KqParams p;
     p.main = w->main; p.scale = w->scale; p.rows = w->rows; p.cols = (int)w->cols;

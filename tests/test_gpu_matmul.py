@@ -95,6 +95,37 @@ def test_kquant_matmul_parity(rq_ctx, oracle, t, rows, cols, tokens, mode):
     assert rel_err(y[:, pick], ref) <= TOL
 
 
+@pytest.mark.parametrize("t,rows,cols,tokens", [(ol.Q4_K, 130, 2304, 20), (ol.Q6_K, 200, 2560, 130), (ol.Q4_K, 256, 4096, 512), (ol.Q6_K, 256, 14336, 64)])
+@pytest.mark.parametrize("step", [32, 256])
+def test_kquant_matmul_int8_equals_float_over_the_records(rq_ctx, oracle, t, rows, cols, tokens, step):
+    """The batched INT8 call quantises while it prepares its operands; the result must equal, bit for bit, the batched
+    FLOAT call over code * d of the standalone quantiser's records (themselves bit-exact with the oracle's), ties, zero
+    groups and strided inputs included."""
+    import torch
+
+    x = oracle.normal(65, t + tokens + step, tokens * cols, 1.0).reshape(tokens, cols)
+    x[0, :256] = 0.0                      # a group of zeros: inverse and d are zero
+    x[1, 5], x[1, 9] = -3.5, 3.5          # equal magnitudes: the first one is the extreme
+    x[2, 40], x[2, 300 % cols] = 7.0, -7.0
+    x[3 % tokens, 64:96] = np.float32(1e-30)
+    w = rq_ctx.weight_from_host(t, oracle.quantize(t, oracle.normal(65, t + rows, rows * cols, 0.02)), rows, cols)
+    xd = cuda(x)
+    rec = rq_ctx.activation_records(xd, step).cpu().numpy()
+    d = rec[:, :, :4].copy().view(np.float32)
+    back = (rec[:, :, 4:].view(np.int8).astype(np.float32) * d).reshape(tokens, cols)
+    for i in range(min(tokens, 4)):
+        assert np.array_equal(rec[i], oracle.activation_records(x[i], step))
+    y8 = rq_ctx.matmul(w, xd, act_mode=1, step=step)
+    yf = rq_ctx.matmul(w, cuda(back))
+    rq_ctx.check()
+    assert torch.equal(y8, yf)
+    # a padded, strided view of the same inputs takes the scalar loads
+    wide = torch.zeros((tokens, cols + 3), dtype=torch.float32, device="cuda")
+    wide[:, 1:cols + 1] = xd
+    assert torch.equal(rq_ctx.matmul(w, wide[:, 1:cols + 1], act_mode=1, step=step), y8)
+    rq_ctx.check()
+
+
 def test_kquant_matmul_extreme_blocks(rq_ctx, oracle):
     """Arbitrary block bytes: every six-bit scale and minimum, every int8 scale, codes at both ends of their range."""
     rng = np.random.default_rng(5)
