@@ -39,34 +39,60 @@ __global__ void __launch_bounds__(kWarps * 32) rq_gemv_q41_int8_kernel(const uin
     const uint8_t* tok = records + (size_t)token * token_bytes;
     const bool unit = rq_act_unit_layout(cols);
     const int64_t nb = cols >> 5;
+    // Programmatic dependent launch: the records come from the quantiser launched before this kernel; the weights are
+    // constants of the model, so the first round's weight loads go out before the wait for that kernel.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    bool records_ready = false;
     for (int64_t row = (int64_t)blockIdx.x * kWarps + warp; row < rows; row += (int64_t)gridDim.x * kWarps) {
         float sum = 0.f;
-        for (int64_t b = lane; b < nb; b += 32) {
-            const uint8_t* blk = blocks + (row * nb + b) * 20;  // 20-byte stride from a 256-byte aligned base: words are aligned
-            const uint32_t hdr = *(const uint32_t*)blk;
-            const float d = rq_h2f((uint16_t)(hdr & 0xffff)), m = rq_h2f((uint16_t)(hdr >> 16));
-            const int8_t* codes; float q8_d; const int16_t* sums;
-            if (unit) {
-                const uint8_t* rec = tok + (size_t)(b >> 3) * RQ_ACT_RECORD_INT8;
-                codes = (const int8_t*)rec + 32 * (b & 7);
-                q8_d = ((const float*)(rec + 256))[b & 7];
-                sums = (const int16_t*)(rec + 288) + 2 * (b & 7);
-            } else {
-                codes = (const int8_t*)tok + b * 32;
-                q8_d = ((const float*)(tok + cols))[b];
-                sums = (const int16_t*)(tok + cols + nb * 4) + 2 * b;
-            }
-            int dot_lo = 0, dot_hi = 0;
+        // four blocks per lane and round, their twenty weight words loaded before the first is used: the row is read once,
+        // from HBM, and a round trip per block would leave the warp waiting on latency
+        for (int64_t b0 = 0; b0 < nb; b0 += 128) {
+            uint32_t wq[4][5];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const uint32_t q = *(const uint32_t*)(blk + 4 + 4 * w);
-                dot_lo = __dp4a((int)(q & 0x0F0F0F0Fu), *(const int*)(codes + 4 * w), dot_lo);
-                dot_hi = __dp4a((int)((q >> 4) & 0x0F0F0F0Fu), *(const int*)(codes + 16 + 4 * w), dot_hi);
+            for (int i = 0; i < 4; ++i) {
+                const int64_t b = b0 + 32 * i + lane;
+                const uint32_t* blk = (const uint32_t*)(blocks + (row * nb + (b < nb ? b : nb - 1)) * 20);  // 20-byte stride from a 256-byte aligned base: words are aligned
+#pragma unroll
+                for (int w = 0; w < 5; ++w) wq[i][w] = __ldcs(blk + w);
             }
-            const float r0 = __fmul_rn(q8_d, __fadd_rn(__fmul_rn(d, (float)dot_lo), __fmul_rn(m, (float)sums[0])));
-            const float r1 = __fmul_rn(q8_d, __fadd_rn(__fmul_rn(d, (float)dot_hi), __fmul_rn(m, (float)sums[1])));
-            sum += r0;
-            sum += r1;
+            if (!records_ready) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                records_ready = true;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int64_t b = b0 + 32 * i + lane;
+                if (b >= nb) break;
+                const float d = rq_h2f((uint16_t)(wq[i][0] & 0xffff)), m = rq_h2f((uint16_t)(wq[i][0] >> 16));
+                int cl[4], ch[4];
+                float q8_d; uint32_t sums;
+                if (unit) {
+                    const uint8_t* rec = tok + (size_t)(b >> 3) * RQ_ACT_RECORD_INT8;  // records are 16-byte aligned
+                    const uint4 lo = __ldg((const uint4*)(rec + 32 * (b & 7))), hi = __ldg((const uint4*)(rec + 32 * (b & 7)) + 1);
+                    cl[0] = (int)lo.x; cl[1] = (int)lo.y; cl[2] = (int)lo.z; cl[3] = (int)lo.w;
+                    ch[0] = (int)hi.x; ch[1] = (int)hi.y; ch[2] = (int)hi.z; ch[3] = (int)hi.w;
+                    q8_d = ((const float*)(rec + 256))[b & 7];
+                    sums = ((const uint32_t*)(rec + 288))[b & 7];
+                } else {
+                    const int* codes = (const int*)(tok + b * 32);  // a token's planes start on a multiple of 8 bytes
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) { cl[w] = __ldg(codes + w); ch[w] = __ldg(codes + 4 + w); }
+                    q8_d = ((const float*)(tok + cols))[b];
+                    sums = ((const uint32_t*)(tok + cols + nb * 4))[b];
+                }
+                int dot_lo = 0, dot_hi = 0;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t q = wq[i][1 + w];
+                    dot_lo = __dp4a((int)(q & 0x0F0F0F0Fu), cl[w], dot_lo);
+                    dot_hi = __dp4a((int)((q >> 4) & 0x0F0F0F0Fu), ch[w], dot_hi);
+                }
+                const float r0 = __fmul_rn(q8_d, __fadd_rn(__fmul_rn(d, (float)dot_lo), __fmul_rn(m, (float)(int16_t)(sums & 0xffff))));
+                const float r1 = __fmul_rn(q8_d, __fadd_rn(__fmul_rn(d, (float)dot_hi), __fmul_rn(m, (float)(int16_t)(sums >> 16))));
+                sum += r0;
+                sum += r1;
+            }
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
@@ -101,7 +127,15 @@ int rq_launch_gemv_q41_int8(rq_ctx* ctx, const rq_weight* w, const uint8_t* reco
     const int64_t ctas = (w->rows + kWarps - 1) / kWarps;
     const int64_t cap = (int64_t)ctx->sm_count * 8;
     dim3 grid((unsigned)(ctas < cap ? ctas : cap), (unsigned)tokens);
-    rq_gemv_q41_int8_kernel<<<grid, kWarps * 32, 0, s>>>(w->main, w->rows, w->cols, records, rq_act_token_bytes(w->cols), y, yn, yt);
-    RQ_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kWarps * 32);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_gemv_q41_int8_kernel, (const uint8_t*)w->main, w->rows, w->cols, records, rq_act_token_bytes(w->cols), y, yn, yt));
     return RQ_OK;
 }
