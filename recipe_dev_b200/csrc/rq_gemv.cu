@@ -292,15 +292,18 @@ __global__ void __launch_bounds__(kThreads) rq_act_quant_kernel(const float* __r
     // Programmatic dependent launch: the matvec behind this kernel may start streaming its weights
     // now; x may come from the kernel before this one, so wait for that one before reading it.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int span = step >> 5;
-    const int64_t recs = cols >> 5, groups = (recs + span - 1) / span;
+    const int span_shift = step == 256 ? 3 : 0;  // 32-value records per group: 8 or 1
+    const int64_t recs = cols >> 5, groups = (recs + (1 << span_shift) - 1) >> span_shift;
     const int64_t g = (int64_t)blockIdx.x * (kThreads / 32) + warp;
     const int t = blockIdx.y;
     if (g >= groups || t >= tokens) return;
-    rq_quantise_group(x + (int64_t)t * st, sk, cols, step, g, lane, scratch + (size_t)t * rq_act_token_bytes(cols), rq_act_unit_layout(cols),
-                      records36 ? records36 + (size_t)t * recs * 36 : nullptr);
+    const float* xt = x + (int64_t)t * st;
+    uint8_t* tok = scratch + (size_t)t * rq_act_token_bytes(cols);
+    const bool unit_layout = rq_act_unit_layout(cols);
+    uint8_t* r36 = records36 ? records36 + (size_t)t * recs * 36 : nullptr;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // after the index arithmetic: the wait is where the chain of launches passes through
+    rq_quantise_group(xt, sk, cols, step, g, lane, tok, unit_layout, r36);
 }
 
 template <int TYPE, int MODE, int LPR, int R, int T>

@@ -1168,8 +1168,6 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? (T == 2 ? 2 : 3) : (NW
             for (int i = tid; i < words; i += kConsumers) dst[i] = src[i];
         };
         if (direct) stage_table();
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (!direct) stage_table();
         // A thread's item is the same (half, sub-row, row slot, unit) in every stage: thread t takes
         // item t of the stage's grid [half][sub-row][row][unit]. Halves are outermost so that a warp
         // works on one half of adjacent units: no divergence, no bank conflicts.
@@ -1188,6 +1186,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, NW == 5 ? (T == 2 ? 2 : 3) : (NW
             my_h = item >= p.units && act_owner ? 1 : 0;
             my_u = act_owner ? item - my_h * p.units : 0;
         }
+        // (all of the above is arithmetic on the launch's parameters: done before the wait, it costs the chain nothing)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (!direct) stage_table();
         ActHalf areg[TR];
         if (MODE == RQ_ACT_INT8 && p.act_regs) {
             // single token: this thread's 128 codes, steps and sums, kept in registers for the whole
