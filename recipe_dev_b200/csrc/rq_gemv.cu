@@ -306,6 +306,38 @@ __global__ void __launch_bounds__(kThreads) rq_act_quant_kernel(const float* __r
     rq_quantise_group(xt, sk, cols, step, g, lane, tok, unit_layout, r36);
 }
 
+// The same for the common call -- groups of 32 contiguous inputs into unit records, no copy in the reference's record
+// format -- as a short straight line of code: the kernel sits in the chain of a decode layer's launches (between gate/up and
+// down), runs once per layer on an instruction cache that other kernels have filled, and what it costs there is the length of
+// its instruction stream and its one trip to L2, not its arithmetic. Same operations in the same order as rq_quantise_group.
+__global__ void __launch_bounds__(kThreads) rq_act_quant32_kernel(const float* __restrict__ x, int64_t st, int units, uint8_t* __restrict__ scratch) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int lane = threadIdx.x & 31;
+    const int rec = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);  // 32-value record = group
+    if (rec >= units * 8) return;
+    const float* src = x + (int64_t)blockIdx.y * st + rec * 32 + lane;
+    uint8_t* unit = scratch + ((size_t)blockIdx.y * units + (rec >> 3)) * RQ_ACT_RECORD_INT8;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const float v = __ldg(src);
+    const unsigned key = __float_as_uint(fabsf(v)) <= 0x7f800000u ? __float_as_uint(fabsf(v)) : 0u;  // a NaN is never the extreme
+    const unsigned top = __reduce_max_sync(0xffffffffu, key);
+    const unsigned first = __reduce_min_sync(0xffffffffu, key == top && top != 0u ? (unsigned)lane : 0xffffffffu);
+    const float best = first == 0xffffffffu ? 0.f : __shfl_sync(0xffffffffu, v, (int)(first & 31u));
+    const bool nonzero = fabsf(best) > 0.f;
+    const float inverse = nonzero ? __fdiv_rn(-127.0f, best) : 0.f;
+    const float d = nonzero ? __fdiv_rn(1.0f, inverse) : 0.f;
+    int code = __float2int_rn(__fmul_rn(v, inverse));
+    code = code < -128 ? -128 : (code > 127 ? 127 : code);
+    ((int8_t*)unit)[32 * (rec & 7) + lane] = (int8_t)code;
+    const int s = __reduce_add_sync(lane < 16 ? 0x0000ffffu : 0xffff0000u, code);
+    const int gs = s + __shfl_xor_sync(0xffffffffu, s, 16);
+    if ((lane & 15) == 0) ((int16_t*)(unit + 288))[2 * (rec & 7) + (lane >> 4)] = (int16_t)s;
+    if (lane == 0) {
+        ((float*)(unit + 256))[rec & 7] = d;
+        ((int16_t*)(unit + 320))[rec & 7] = (int16_t)gs;
+    }
+}
+
 template <int TYPE, int MODE, int LPR, int R, int T>
 int launch_one(const GemvParams& p, size_t smem_bytes, cudaStream_t s) {
     auto kernel = rq_gemv_kernel<TYPE, MODE, LPR, R, T>;
@@ -363,6 +395,10 @@ int rq_launch_act_quant(const float* x, int64_t sk, int64_t st, int64_t cols, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (step == 32 && sk == 1 && records36 == nullptr && rq_act_unit_layout(cols) && cols <= ((int64_t)1 << 30)) {
+        RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_act_quant32_kernel, x, st, (int)(cols >> 8), scratch));
+        return RQ_OK;
+    }
     RQ_CUDA(cudaLaunchKernelEx(&cfg, rq_act_quant_kernel, x, sk, st, cols, tokens, step, scratch, records36));
     return RQ_OK;
 }
