@@ -141,7 +141,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ scores, in
     float* key = sm + 2 * experts;
     int* mark = (int*)(sm + 3 * experts);
     __shared__ float s_max, s_total, s_wmax[kRouteThreads / 32], s_wkey[kRouteThreads / 32];
-    __shared__ int s_best, s_widx[kRouteThreads / 32];
+    __shared__ int s_widx[kRouteThreads / 32];
     const int t = blockIdx.x, tid = threadIdx.x;
     const bool sig = sigmoid != 0, every = renorm == 0, divide = renorm != 0 || !sig;
     const float kLowest = __int_as_float(0xff800000);  // -inf
@@ -185,7 +185,24 @@ __device__ __forceinline__ void route_token(const float* __restrict__ scores, in
     }
     const bool ordered_pick = __syncthreads_or(key_nan) != 0 || ordered;
     // pick `top` times the unmarked expert of strictly greatest key; ties go to the lowest index
-    for (int pick = 0; pick < top; ++pick) {
+    const bool by_rank = !ordered_pick && experts <= 512;
+    if (by_rank) {
+        // Without NaNs that is the `top` first experts in the order "greater key first, equal keys by index": an expert's
+        // place is the number of experts ahead of it, which every thread counts for its own expert with no barrier in between
+        // (eight rounds of a block-wide argmax are sixteen barriers; this kernel is one CTA of latency per token).
+        for (int e = tid; e < experts; e += kRouteThreads) {
+            const float k = key[e];
+            int ahead = 0;
+#pragma unroll 8
+            for (int o = 0; o < experts; ++o) {
+                const float ko = key[o];
+                ahead += (ko > k || (ko == k && o < e)) ? 1 : 0;
+            }
+            mark[e] = ahead < top ? 1 : 0;
+        }
+        __syncthreads();
+    }
+    for (int pick = 0; pick < top && !by_rank; ++pick) {
         if (ordered_pick) {
             if (tid == 0) {
                 int best = -1;
@@ -244,7 +261,8 @@ __device__ __forceinline__ void route_token(const float* __restrict__ scores, in
     if (tid == 0) {
         float total = 0.0f;
 #pragma unroll 8
-        for (int e = 0; e < experts; ++e) total = __fadd_rn(total, (mark[e] || every) ? val[e] : 0.0f);
+        for (int e = 0; e < experts; ++e)
+            if (mark[e] || every) total = __fadd_rn(total, val[e]);  // (the reference adds 0.0 for the others, which leaves every total as it is)
         s_total = total;
     }
     __syncthreads();

@@ -32,6 +32,32 @@ def test_routing_bit_exact(rq_ctx, oracle, experts, top, tokens, scoring, renorm
     assert np.all((got != 0).sum(axis=0) == top)
 
 
+@pytest.mark.parametrize("experts,top", [(256, 8), (512, 6), (96, 8), (1024, 8)])
+def test_routing_with_many_equal_scores(rq_ctx, oracle, experts, top):
+    """Scores drawn from a handful of values, zeros of both signs and infinities: the kept experts are the first of each
+    run of equal keys, whichever way the kernel orders them (counting for up to 512 experts, repeated maxima beyond)."""
+    rng = np.random.default_rng(experts)
+    levels = np.float32([-2.0, -0.0, 0.0, 0.5, 0.5, 1.25, 3.0])
+    scores = levels[rng.integers(0, levels.size, size=(experts, 6))]
+    scores[:, 4] = 1.0                               # all equal: the first `top` experts
+    scores[:, 5] = -np.inf
+    scores[experts // 2:experts // 2 + 3, 5] = np.inf
+    bias = levels[rng.integers(0, levels.size, size=experts)]
+    for scoring in (0, 1):
+        for renorm in (True, False):
+            want = oracle.topk(scores[:, :5], top, scoring, renorm)
+            got = rq_ctx.moe_route(cuda(scores[:, :5]), top, scoring, renorm).cpu().numpy()
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (scoring, renorm)
+        want = oracle.topk(scores[:, :5], top, scoring, True, bias)
+        got = rq_ctx.moe_route(cuda(scores[:, :5]), top, scoring, True, bias=cuda(bias)).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), ("bias", scoring)
+    # infinities among the scores (sigmoid scoring keeps them finite)
+    want = oracle.topk(scores[:, 5:6], top, 1, True)
+    got = rq_ctx.moe_route(cuda(scores[:, 5:6]), top, 1, True).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    rq_ctx.check()
+
+
 def test_routing_with_selection_bias(rq_ctx, oracle):
     scores = oracle.normal(32, 0, 64 * 4, 1.0).reshape(64, 4)
     bias = oracle.normal(32, 1, 64, 0.5)
