@@ -152,30 +152,34 @@ __device__ __forceinline__ void route_token(const float* __restrict__ scores, in
         nan_here |= (v != v) || (bias && bias[e] != bias[e]);
     }
     const bool ordered = __syncthreads_or(nan_here) != 0;  // a NaN somewhere: every step in index order by one thread
-    // the maximum over every expert
-    if (ordered) {
+    // the scores over every expert, which only a selection bias reads (its key is the score plus the bias): without one the
+    // selection key is the raw score, and this pass -- a maximum, an exponential per expert, a total in expert order -- is skipped
+    if (bias) {
+        // the maximum over every expert
+        if (ordered) {
+            if (tid == 0) {
+                float mx = raw[0];
+                for (int e = 1; e < experts; ++e) if (raw[e] > mx) mx = raw[e];
+                s_max = mx;
+            }
+            __syncthreads();
+        } else {
+            float mx = kLowest;
+            for (int e = tid; e < experts; e += kRouteThreads) mx = fmaxf(mx, raw[e]);
+            mx = block_max(mx, s_wmax, tid);
+            if (tid == 0) s_max = mx;
+            __syncthreads();
+        }
+        for (int e = tid; e < experts; e += kRouteThreads) val[e] = topk_score(raw[e], s_max, sig);
+        __syncthreads();
         if (tid == 0) {
-            float mx = raw[0];
-            for (int e = 1; e < experts; ++e) if (raw[e] > mx) mx = raw[e];
-            s_max = mx;
+            float total = 0.0f;
+#pragma unroll 8
+            for (int e = 0; e < experts; ++e) total = __fadd_rn(total, val[e]);
+            s_total = total;
         }
         __syncthreads();
-    } else {
-        float mx = kLowest;
-        for (int e = tid; e < experts; e += kRouteThreads) mx = fmaxf(mx, raw[e]);
-        mx = block_max(mx, s_wmax, tid);
-        if (tid == 0) s_max = mx;
-        __syncthreads();
     }
-    for (int e = tid; e < experts; e += kRouteThreads) val[e] = topk_score(raw[e], s_max, sig);
-    __syncthreads();
-    if (tid == 0) {
-        float total = 0.0f;
-#pragma unroll 8
-        for (int e = 0; e < experts; ++e) total = __fadd_rn(total, val[e]);
-        s_total = total;
-    }
-    __syncthreads();
     // selection key: the raw score, or the probability over every expert plus the expert's bias
     int key_nan = 0;
     for (int e = tid; e < experts; e += kRouteThreads) {
@@ -304,8 +308,15 @@ __device__ __forceinline__ void plan_token(const BankView& b, const float* __res
         for (int k = tid; k < b.hidden; k += 256) acc = __fadd_rn(acc, __fmul_rn(b.sh_vector[k], x[k * sk + t * st]));
         red[tid] = acc;
         __syncthreads();
-        for (int off = 128; off > 0; off >>= 1) { if (tid < off) red[tid] = __fadd_rn(red[tid], red[tid + off]); __syncthreads(); }
-        if (tid == 0) s_gate = sigmoid_portable(red[0]);
+        // the fixed tree red[i] += red[i + off], off = 128 .. 1: across warps through shared memory, inside warp 0 by shuffles
+        // (the same pairs in the same order, five barriers fewer)
+        for (int off = 128; off >= 32; off >>= 1) { if (tid < off) red[tid] = __fadd_rn(red[tid], red[tid + off]); __syncthreads(); }
+        if (tid < 32) {
+            float v = red[tid];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, off));
+            if (tid == 0) s_gate = sigmoid_portable(v);
+        }
         __syncthreads();
     }
     RqPlan* pa = plans + 2 * t;
